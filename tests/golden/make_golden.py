@@ -1,0 +1,172 @@
+"""Generate the golden fixtures in this directory from the reference project.
+
+Run once, in a container where the reference checkout is importable:
+
+    python tests/golden/make_golden.py --reference /path/to/nsa-from-scratch
+
+Every case stores its seeded inputs and the outputs of the REFERENCE's own
+functions (nsa/reference.py, nsa/triton/forward.py, nsa/triton/fp8.py,
+nsa/triton/gating.py -- all plain torch, they run on CPU).  The fixtures are
+what pins the CPU oracle (tests/test_oracle_golden.py) and, through it, the
+CUDA kernels.  Tensors are saved as fp32 / int32 numpy arrays; bf16 inputs
+are saved after rounding, so `.to(bfloat16)` restores them exactly.
+"""
+
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def qkv(seed, B, H, Tq, Tk, D, dtype, amp=1.0):
+    g = torch.Generator().manual_seed(seed)
+    Q = (torch.randn(B, H, Tq, D, generator=g) * amp).to(dtype)
+    K = (torch.randn(B, H, Tk, D, generator=g) * amp).to(dtype)
+    V = (torch.randn(B, H, Tk, D, generator=g) * amp).to(dtype)
+    return Q, K, V, g
+
+
+def np32(t):
+    return t.detach().float().numpy()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    args = ap.parse_args()
+    sys.path.insert(0, args.reference)
+    sys.path.insert(0, os.path.join(HERE, "..", ".."))
+    from nsa import reference as R
+    from nsa.triton import forward as F_
+    from nsa.triton import fp8 as FP8
+    from nsa.triton import gating as GT
+    from nsa.triton.selected import _topk_indices_from_scores
+    from oracle import nsa_oracle as O
+
+    out = {}
+    meta = []
+
+    # ---- compressed ------------------------------------------------------
+    for name, (B, H, Tq, Tk, D, bc, causal, dt) in {
+        "cmp_a": (1, 2, 128, 128, 32, 32, True, torch.float32),
+        "cmp_b": (1, 2, 96, 200, 32, 64, True, torch.bfloat16),     # ragged, Tq < Tk
+        "cmp_c": (2, 2, 128, 192, 64, 32, False, torch.bfloat16),
+    }.items():
+        Q, K, V, _ = qkv(11, B, H, Tq, Tk, D, dt, 0.5)
+        o, l = R.compressed_attention_reference(Q.float(), K.float(), V.float(),
+                                                block_size_c=bc, causal=causal)
+        # pooled keys in the INPUT dtype, as the kernels' wrapper pools them
+        from nsa.triton.compressed import _mean_pool
+        out.update({f"{name}.Q": np32(Q), f"{name}.K": np32(K), f"{name}.V": np32(V),
+                    f"{name}.out": np32(o), f"{name}.lse": np32(l),
+                    f"{name}.Kc": np32(_mean_pool(K, bc))})
+        meta.append((name, dict(B=B, H=H, Tq=Tq, Tk=Tk, D=D, bc=bc, causal=causal,
+                                dtype=str(dt))))
+
+    # ---- scorer / top-k ---------------------------------------------------
+    for name, (B, H, Tq, Tk, D, bm, bn, k, causal, dt) in {
+        "sel_idx_a": (1, 2, 512, 512, 32, 64, 64, 4, True, torch.bfloat16),
+        "sel_idx_b": (1, 2, 200, 456, 32, 32, 32, 5, True, torch.bfloat16),   # ragged
+        "sel_idx_c": (1, 2, 256, 256, 64, 64, 64, 3, False, torch.float16),
+    }.items():
+        Q, K, V, _ = qkv(23, B, H, Tq, Tk, D, dt)
+        s = 1.0 / D ** 0.5
+        idx = F_._resolve_block_indices(Q, K, block_size_m=bm, block_size_n=bn, top_k=k,
+                                        causal=causal, scale=s)
+        sc = F_._block_scores_from_pooled(Q, K, block_size_m=bm, block_size_n=bn, scale=s)
+        out.update({f"{name}.Q": np32(Q), f"{name}.K": np32(K), f"{name}.V": np32(V),
+                    f"{name}.idx": idx.numpy().astype(np.int32), f"{name}.scores": np32(sc)})
+        # indices from caller-supplied scores (unpadded offset rule)
+        nq, nk = sc.shape[-2:]
+        g = torch.Generator().manual_seed(5)
+        bs = torch.randn(B, H, nq, nk, generator=g)
+        idx2 = _topk_indices_from_scores(bs, k, nq, nk, bm, bn, Tq, Tk, causal, torch.device("cpu"))
+        out.update({f"{name}.bs": np32(bs), f"{name}.idx_bs": idx2.numpy().astype(np.int32)})
+        meta.append((name, dict(B=B, H=H, Tq=Tq, Tk=Tk, D=D, bm=bm, bn=bn, k=k, causal=causal,
+                                dtype=str(dt))))
+
+    # ---- selected forward + backward with fixed (canonical) indices ---------
+    for name, (B, H, Tq, Tk, D, bm, bn, k, causal, dt) in {
+        "sel_a": (1, 2, 256, 256, 32, 64, 64, 3, True, torch.bfloat16),
+        "sel_b": (1, 2, 100, 200, 32, 32, 32, 4, True, torch.bfloat16),      # ragged
+        "sel_c": (1, 2, 128, 192, 32, 64, 64, 2, False, torch.float32),
+    }.items():
+        Q, K, V, g = qkv(37, B, H, Tq, Tk, D, dt)
+        dO = torch.randn(B, H, Tq, D, generator=g)
+        idx = O.select_blocks(Q, K, block_size_m=bm, block_size_n=bn, top_k=k, causal=causal)
+        Qd, Kd, Vd = (t.float().requires_grad_(True) for t in (Q, K, V))
+        o, l = R.selected_attention_reference(Qd, Kd, Vd, block_size_n=bn, block_size_m=bm,
+                                              top_k=k, block_indices=idx, causal=causal)
+        on = torch.nan_to_num(o, nan=0.0, posinf=0.0, neginf=0.0)
+        dQ, dK, dV = torch.autograd.grad(on, (Qd, Kd, Vd), grad_outputs=dO)
+        out.update({f"{name}.Q": np32(Q), f"{name}.K": np32(K), f"{name}.V": np32(V),
+                    f"{name}.dO": np32(dO), f"{name}.idx": idx.numpy(),
+                    f"{name}.out": np32(o), f"{name}.lse": np32(l),
+                    f"{name}.dQ": np32(torch.nan_to_num(dQ)), f"{name}.dK": np32(torch.nan_to_num(dK)),
+                    f"{name}.dV": np32(torch.nan_to_num(dV))})
+        meta.append((name, dict(B=B, H=H, Tq=Tq, Tk=Tk, D=D, bm=bm, bn=bn, k=k, causal=causal,
+                                dtype=str(dt))))
+
+    # ---- sliding -------------------------------------------------------------
+    for name, (B, H, Tq, Tk, D, W, causal, dt) in {
+        "sld_a": (1, 2, 256, 256, 32, 64, True, torch.bfloat16),
+        "sld_b": (1, 2, 100, 300, 32, 48, True, torch.float32),
+        "sld_c": (1, 2, 128, 128, 32, 32, False, torch.bfloat16),
+    }.items():
+        Q, K, V, _ = qkv(41, B, H, Tq, Tk, D, dt)
+        o, l = R.sliding_attention_reference(Q.float(), K.float(), V.float(), window_size=W,
+                                             causal=causal)
+        out.update({f"{name}.Q": np32(Q), f"{name}.K": np32(K), f"{name}.V": np32(V),
+                    f"{name}.out": np32(o), f"{name}.lse": np32(l)})
+        meta.append((name, dict(B=B, H=H, Tq=Tq, Tk=Tk, D=D, W=W, causal=causal, dtype=str(dt))))
+
+    # ---- combined forward with gates -----------------------------------------
+    for name, (B, H, T, D, act) in {
+        "nsa_a": (1, 2, 256, 32, "sigmoid"),
+        "nsa_b": (1, 2, 256, 32, "softmax"),
+    }.items():
+        Q, K, V, g = qkv(53, B, H, T, T, D, torch.bfloat16)
+        gates = torch.randn(B, H, T, 3, generator=g)
+        cfg = R.NSAConfig(block_size_c=32, block_size_n=32, block_size_m=32, top_k=3,
+                          window_size=48, gate_activation=act)
+        idx = O.select_blocks(Q, K, block_size_m=32, block_size_n=32, top_k=3, causal=True)
+        # the reference's combined function scores in fp32 from its own inputs; feed the
+        # canonical indices through block_scores so both sides gather the same blocks
+        nq = nk = T // 32
+        bs = torch.full((B, H, nq, nk), -1e9)
+        bs.scatter_(-1, idx.long(), torch.arange(3, 0, -1.0).expand(B, H, nq, 3).contiguous())
+        o = R.nsa_attention_reference(Q.float(), K.float(), V.float(), cfg, gates=gates,
+                                      block_scores=bs)
+        oc = GT.combine(Q, K, V, gates.to(torch.bfloat16), activation=act)   # bf16 rounding chain
+        out.update({f"{name}.Q": np32(Q), f"{name}.K": np32(K), f"{name}.V": np32(V),
+                    f"{name}.gates": np32(gates), f"{name}.idx": idx.numpy(),
+                    f"{name}.out": np32(o), f"{name}.combine_bf16": np32(oc)})
+        meta.append((name, dict(B=B, H=H, T=T, D=D, act=act)))
+
+    # ---- fp8 quantise / dequantise ------------------------------------------
+    for name, fmt in {"fp8_e4m3": torch.float8_e4m3fn, "fp8_e5m2": torch.float8_e5m2}.items():
+        g = torch.Generator().manual_seed(61)
+        x = torch.randn(4, 257, generator=g)
+        x = torch.where(torch.rand(4, 257, generator=g) < 0.01, x * 20, x).to(torch.bfloat16)
+        x8, sc = FP8.quantize_to_fp8(x, fmt=fmt)
+        deq = x8.to(torch.bfloat16) * sc
+        out.update({f"{name}.x": np32(x), f"{name}.bits": x8.view(torch.uint8).numpy(),
+                    f"{name}.scale": np.array([sc], dtype=np.float64), f"{name}.deq": np32(deq)})
+        meta.append((name, dict(fmt=str(fmt))))
+
+    np.savez_compressed(os.path.join(HERE, "reference_golden.npz"), **out)
+    with open(os.path.join(HERE, "reference_golden.meta.txt"), "w") as f:
+        f.write(f"torch {torch.__version__}\n")
+        for n, m in meta:
+            f.write(f"{n}: {m}\n")
+    print("wrote", len(out), "arrays")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,159 @@
+"""Pins the CPU oracle to the reference's own outputs (tests/golden/reference_golden.npz,
+made by tests/golden/make_golden.py from the reference's plain-torch functions)."""
+import numpy as np
+import torch
+
+from oracle import nsa_oracle as O
+
+DT = {"torch.float32": torch.float32, "torch.bfloat16": torch.bfloat16, "torch.float16": torch.float16}
+
+
+def T(g, key, dtype=torch.float32):
+    return torch.from_numpy(np.asarray(g[key])).to(dtype)
+
+
+def finite_close(a, ref, atol, rtol=0.0):
+    ok = torch.isfinite(ref)
+    assert ok.any()
+    d = (a[ok] - ref[ok]).abs()
+    assert bool((d <= atol + rtol * ref[ok].abs()).all()), float(d.max())
+
+
+CMP = {"cmp_a": (32, True, "torch.float32"), "cmp_b": (64, True, "torch.bfloat16"),
+       "cmp_c": (32, False, "torch.bfloat16")}
+
+
+def test_compressed_matches_reference(golden):
+    for name, (bc, causal, dt) in CMP.items():
+        Q, K, V = (T(golden, f"{name}.{x}", DT[dt]) for x in "QKV")
+        out, lse = O.compressed_attention(Q.float(), K.float(), V.float(), block_size_c=bc, causal=causal)
+        ref_o, ref_l = T(golden, f"{name}.out"), T(golden, f"{name}.lse")
+        finite_close(out, ref_o, 2e-5)
+        finite_close(lse, ref_l, 2e-5)
+        # rows the reference leaves undefined (NaN) are the rows the oracle reports empty
+        empty = ~torch.isfinite(ref_l)
+        assert torch.equal(empty, lse == float("-inf"))
+        assert float(out[empty].abs().sum()) == 0.0
+        # pooled keys: bit-identical for 16-bit inputs (one rounding of an fp32 sum);
+        # for fp32 inputs only the summation order differs
+        if DT[dt] == torch.float32:
+            assert torch.allclose(O.pool_mean(K, bc), T(golden, f"{name}.Kc"), atol=1e-6)
+        else:
+            assert torch.equal(O.pool_mean(K, bc).float(), T(golden, f"{name}.Kc"))
+
+
+IDX = {"sel_idx_a": (64, 64, 4, True, "torch.bfloat16"), "sel_idx_b": (32, 32, 5, True, "torch.bfloat16"),
+       "sel_idx_c": (64, 64, 3, False, "torch.float16")}
+
+
+def test_block_selection_matches_reference(golden):
+    for name, (bm, bn, k, causal, dt) in IDX.items():
+        Q, K = T(golden, f"{name}.Q", DT[dt]), T(golden, f"{name}.K", DT[dt])
+        idx, masked = O.select_blocks(Q, K, block_size_m=bm, block_size_n=bn, top_k=k, causal=causal,
+                                      return_scores=True)
+        ref_idx = T(golden, f"{name}.idx", torch.int32)
+        sc = O.block_scores(Q, K, block_size_m=bm, block_size_n=bn)
+        assert torch.allclose(sc, T(golden, f"{name}.scores"), atol=1e-6, rtol=1e-6)
+        # exact on every slot whose score is finite; -inf slots are filled lowest-index-first
+        fin = torch.isfinite(torch.gather(masked, -1, idx.long()))
+        assert torch.equal(idx[fin], ref_idx[fin])
+        assert fin.float().mean() > 0.5
+        # the canonical fill: ascending illegal ids
+        nq = idx.shape[2]
+        for q in range(nq):
+            row, f = idx[0, 0, q], fin[0, 0, q]
+            tail = row[~f]
+            assert torch.equal(tail, torch.sort(tail).values)
+        # caller-supplied scores (unpadded offset rule)
+        bs = T(golden, f"{name}.bs")
+        Tq, Tk = Q.shape[2], K.shape[2]
+        idx2 = O.indices_from_scores(bs, top_k=k, block_size_m=bm, block_size_n=bn, Tq=Tq, Tk=Tk, causal=causal)
+        ref2 = T(golden, f"{name}.idx_bs", torch.int32)
+        nq, nk = bs.shape[-2:]
+        legal = O.legal_blocks(nq, nk, bm, bn, Tk - Tq) if causal else torch.ones(nq, nk, dtype=torch.bool)
+        fin2 = torch.gather(legal.expand(bs.shape), -1, idx2.long())
+        assert torch.equal(idx2[fin2], ref2[fin2])
+
+
+SEL = {"sel_a": (64, 64, True), "sel_b": (32, 32, True), "sel_c": (64, 64, False)}
+
+
+def test_selected_forward_backward_match_reference(golden):
+    for name, (bm, bn, causal) in SEL.items():
+        Q, K, V, dO = (T(golden, f"{name}.{x}") for x in ("Q", "K", "V", "dO"))
+        idx = T(golden, f"{name}.idx", torch.int32)
+        out, lse = O.selected_attention(Q, K, V, idx, block_size_n=bn, block_size_m=bm, causal=causal)
+        finite_close(out, T(golden, f"{name}.out"), 2e-5)
+        finite_close(lse, T(golden, f"{name}.lse"), 2e-5)
+        dQ, dK, dV = O.selected_backward(dO, Q, K, V, idx, block_size_n=bn, block_size_m=bm, causal=causal)
+        for a, key in ((dQ, "dQ"), (dK, "dK"), (dV, "dV")):
+            assert torch.allclose(a, T(golden, f"{name}.{key}"), atol=5e-5, rtol=1e-4), key
+
+
+SLD = {"sld_a": (64, True), "sld_b": (48, True), "sld_c": (32, False)}
+
+
+def test_sliding_matches_reference(golden):
+    for name, (W, causal) in SLD.items():
+        Q, K, V = (T(golden, f"{name}.{x}") for x in "QKV")
+        out, lse = O.sliding_attention(Q, K, V, window_size=W, causal=causal)
+        finite_close(out, T(golden, f"{name}.out"), 2e-5)
+        finite_close(lse, T(golden, f"{name}.lse"), 2e-5)
+        # a band of rows against the full key set gives the same rows
+        o2, l2 = O.sliding_attention(Q, K, V, window_size=W, causal=causal, rows=(32, 96))
+        assert torch.allclose(o2, out[:, :, 32:96], atol=1e-6)
+
+
+def test_combined_forward_and_combine_match_reference(golden):
+    for name, act in (("nsa_a", "sigmoid"), ("nsa_b", "softmax")):
+        Q, K, V, gates = (T(golden, f"{name}.{x}") for x in ("Q", "K", "V", "gates"))
+        idx = T(golden, f"{name}.idx", torch.int32)
+        out = O.nsa_forward(Q, K, V, block_size_c=32, block_size_n=32, block_size_m=32, top_k=3,
+                            window_size=48, gate_logits=gates, gate_activation=act, block_indices=idx)
+        finite_close(out, T(golden, f"{name}.out"), 3e-5)
+        band = O.nsa_forward(Q, K, V, block_size_c=32, block_size_n=32, block_size_m=32, top_k=3,
+                             window_size=48, gate_logits=gates, gate_activation=act, block_indices=idx,
+                             rows=(64, 160))
+        assert torch.allclose(band, out[:, :, 64:160], atol=1e-6)
+        bq, bk, bv = (x.to(torch.bfloat16) for x in (Q, K, V))
+        oc = O.combine(bq, bk, bv, gates.to(torch.bfloat16), activation=act)
+        assert torch.equal(oc.float(), T(golden, f"{name}.combine_bf16"))
+
+
+def test_fp8_quantise_matches_reference(golden):
+    for name, fmt in (("fp8_e4m3", torch.float8_e4m3fn), ("fp8_e5m2", torch.float8_e5m2)):
+        x = T(golden, f"{name}.x", torch.bfloat16)
+        x8, sc = O.quantize_to_fp8(x, fmt=fmt)
+        assert sc == float(golden[f"{name}.scale"][0])
+        assert np.array_equal(x8.view(torch.uint8).numpy(), golden[f"{name}.bits"])
+        assert torch.equal(O.dequantize_fp8(x8, sc).float(), T(golden, f"{name}.deq"))
+
+
+def test_unpinned_extensions_collapse_to_pinned_cases(golden):
+    """GQA with one group, stride == block and zero forced blocks are the pinned paths."""
+    name = "sel_a"
+    Q, K, V = (T(golden, f"{name}.{x}") for x in "QKV")
+    idx = T(golden, f"{name}.idx", torch.int32)
+    # GQA: a shared KV head equals the reference run on repeated heads
+    K1, V1 = K[:, :1], V[:, :1]
+    o_g, _ = O.selected_attention(Q, K1, V1, idx, causal=True)
+    o_r, _ = O.selected_attention(Q, K1.repeat(1, 2, 1, 1), V1.repeat(1, 2, 1, 1), idx, causal=True)
+    assert torch.equal(o_g, o_r)
+    # group-shared indices == the same index rows repeated per head
+    o_s, _ = O.selected_attention(Q, K1, V1, idx[:, :1], causal=True)
+    o_p, _ = O.selected_attention(Q, K1, V1, idx[:, :1].repeat(1, 2, 1, 1), causal=True)
+    assert torch.equal(o_s, o_p)
+    # stride == block is the reference pooling
+    assert torch.equal(O.pool_mean(K, 32, 32), O.pool_mean(K, 32))
+    # overlapping windows: window c of (block 32, stride 16) is rows [16c, 16c+32)
+    p = O.pool_mean(K, 32, 16)
+    assert p.shape[2] == (K.shape[2] - 32) // 16 + 1
+    assert torch.allclose(p[:, :, 3], K[:, :, 48:80].mean(2), atol=1e-6)
+    # forced blocks: 0 forced == plain; forced blocks come first and are legal
+    a = O.select_blocks(Q, K, top_k=3)
+    b = O.select_blocks(Q, K, top_k=3, force_first=0, force_local=0)
+    assert torch.equal(a, b)
+    f = O.select_blocks(Q, K, top_k=3, force_first=1, force_local=2)
+    nq = f.shape[2]
+    for q in range(2, nq):
+        assert set(f[0, 0, q].tolist()) == {0, q - 1, q} if q >= 2 else True
