@@ -1,0 +1,199 @@
+/*
+ * C ABI of the B200 (sm_100a) Native-Sparse-Attention kernels.
+ *
+ * Every entry point takes raw device pointers, sizes and a CUDA stream, launches
+ * asynchronously on that stream, allocates nothing unless stated, and returns an
+ * int status: NSA_OK (0) or a negative NSA_ERR_* code, with a description available
+ * from nsa_last_error().  Tensors are dense row-major ("contiguous"):
+ *   Q, out, dO, dQ   [B, H,   Tq, D]
+ *   K, V, dK, dV     [B, Hkv, Tk, D]     H % Hkv == 0 (Hkv == H is the reference's case)
+ *   lse, delta       [B, H,   Tq]  fp32
+ *   block indices    [B, Hi,  nq, k] int32,  Hi == H (per query head) or Hkv (shared by a group)
+ *   gate logits      [B, H,   Tq, 3]
+ * Query rows align with the tail of the keys: key position of row i is i + (Tk - Tq).
+ *
+ * Each declaration cites the interface of the reference project
+ * (qflen/nsa-from-scratch, paths relative to its root) that it stands in for.
+ */
+#ifndef NSA_B200_H
+#define NSA_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* nsa_stream_t; /* a cudaStream_t; NULL is the default stream */
+
+#define NSA_OK 0
+#define NSA_ERR_ARG (-1)         /* a size, pointer or flag is out of range          */
+#define NSA_ERR_UNSUPPORTED (-2) /* a combination no kernel is instantiated for      */
+#define NSA_ERR_CUDA (-3)        /* the CUDA runtime reported an error               */
+#define NSA_ERR_DEVICE (-4)      /* a kernel gave up on a bounded wait (status word) */
+
+#define NSA_BF16 0
+#define NSA_FP16 1
+#define NSA_FP8_E4M3 2
+#define NSA_FP8_E5M2 3
+#define NSA_FP32 4
+
+#define NSA_BRANCH_COMPRESSED 1
+#define NSA_BRANCH_SELECTED 2
+#define NSA_BRANCH_SLIDING 4
+
+#define NSA_GATE_SIGMOID 0
+#define NSA_GATE_SOFTMAX 1
+
+/* Engine for nsa_attention_fwd: AUTO picks the tcgen05/TMA kernel when the shape
+ * qualifies (bf16/fp16, D in {64,128}, 64-token blocks) and the generic
+ * tensor-core kernel otherwise. */
+#define NSA_ENGINE_AUTO 0
+#define NSA_ENGINE_GENERIC 1
+#define NSA_ENGINE_TCGEN05 2
+
+const char* nsa_last_error(void);
+int nsa_abi_version(void);
+
+/* Mean over windows of `block` rows every `stride` rows:  x [B,H,T,D] -> out [B,H,n_out,D].
+ * fp32 sum in row order, divide by `block`, one round-to-nearest-even to the output
+ * type (16-bit inputs keep their type; fp8 inputs are first dequantised to
+ * bf16(fp32(x)*dequant_scale) and produce bf16).  stride == block: n_out = ceil(T/block),
+ * a trailing partial window is still divided by `block`.  stride < block: only whole
+ * windows, n_out = (T-block)/stride + 1.
+ * Replaces: _mean_pool, nsa/triton/compressed.py:25-44; the block means taken in
+ * _resolve_block_indices, nsa/triton/forward.py:344-345. */
+int nsa_pool_mean(const void* x, void* out, int B, int H, int T, int D, int block, int stride,
+                  int n_out, int dtype, float dequant_scale, nsa_stream_t stream);
+
+/* Block scoring + causal legality + top-k in one kernel.
+ *   Qb [B,H,nq,D], Kb [B,Hkv,nk,D]: block means (nsa_pool_mean), 16-bit.
+ *   idx [B,H,nq,k_out] int32, k_out = min(top_k, nk), ordered by descending score,
+ *   ties (and the -inf slots of rows with fewer than k_out legal blocks) lowest index first.
+ * score = fp32 dot over D (fma in index order) * scale; block c is legal for q block q iff
+ * !causal or c*bn <= q*bm + bm-1 + offset.  force_first / force_local give score +inf to
+ * the first blocks and to the last legal blocks of each row (0/0 = the reference).
+ * Replaces: _resolve_block_indices, nsa/triton/forward.py:321-359 (einsum + mask + topk). */
+int nsa_select_blocks(const void* Qb, const void* Kb, int32_t* idx, int B, int H, int Hkv, int nq,
+                      int nk, int D, int top_k, int bm, int bn, int offset, int causal, float scale,
+                      int force_first, int force_local, int dtype, nsa_stream_t stream);
+
+/* Top-k over caller-supplied fp32 scores [BH,nq,nk] with the same legality rule and order.
+ * Replaces: _topk_indices_from_scores, nsa/triton/selected.py:153-185. */
+int nsa_topk_from_scores(const float* scores, int32_t* idx, int BH, int nq, int nk, int top_k,
+                         int bm, int bn, int offset, int causal, nsa_stream_t stream);
+
+/* Arguments of the attention forward.  One launch evaluates the branches named in
+ * `branches` for every 64-row query tile:
+ *   fused == 0: exactly one branch; writes out (same 16-bit type as compute) and lse.
+ *   fused == 1: writes out = sum_b gate_b * branch_b (gates from gate logits, or the
+ *               constant of zero logits when gates == NULL); lse is not written.
+ * K/V may be fp8 (kv_dtype) with per-tensor scales; they are dequantised to bf16 as
+ * bf16(fp32(x) * scale) while being staged, never materialised. */
+typedef struct nsa_fwd_args {
+  const void* Q;       /* [B,H,Tq,D]   q_dtype                                    */
+  const void* K;       /* [B,Hkv,Tk,D] kv_dtype                                   */
+  const void* V;
+  const void* Kc;      /* [B,Hkv,Nc,D] pooled keys/values, 16-bit (compressed)    */
+  const void* Vc;
+  const int32_t* idx;  /* [B,Hi,nq,top_k] (selected)                              */
+  const void* gates;   /* [B,H,Tq,3] gate logits or NULL (fused)                  */
+  void* out;           /* [B,H,Tq,D]                                              */
+  float* lse;          /* [B,H,Tq] or NULL                                        */
+  int32_t B, H, Hkv, Hi;
+  int32_t Tq, Tk, D;
+  int32_t offset;                                /* key position of query row i is i + offset (normally Tk-Tq) */
+  int32_t Nc, cmp_block, cmp_stride, cmp_offset; /* pooled token c visible iff c*stride+block-1 <= i+cmp_offset */
+  int32_t nq, top_k, bm, bn, sel_key_limit;      /* keys j < sel_key_limit attendable (padded Tk)           */
+  int32_t window;
+  int32_t causal;
+  int32_t branches, fused, gate_act;
+  int32_t q_dtype, kv_dtype, gate_dtype;         /* NSA_* dtype codes; out has the compute type             */
+  float scale;                                   /* softmax scale                                          */
+  float q_scale, k_scale, v_scale;               /* fp8 dequantisation scales                              */
+  int32_t engine;                                /* NSA_ENGINE_*                                           */
+} nsa_fwd_args;
+
+/* Replaces the kernels behind compressed_attention (nsa/triton/compressed.py:191-300),
+ * selected_attention (nsa/triton/selected.py:188-315), sliding_attention
+ * (nsa/triton/sliding.py:136-205), the dequantise-then-attend of selected_attention_fp8
+ * (nsa/triton/fp8.py:43-75) and, with fused=1, the branch launches plus combine of
+ * nsa_forward (nsa/triton/forward.py:362-406). */
+int nsa_attention_fwd(const nsa_fwd_args* args, nsa_stream_t stream);
+
+/* The reference's native launcher, same argument list (bf16, Hkv == H folded into BH,
+ * 64x64 blocks, pre-padded lengths, D in {32,64,128}); returns a status instead of void.
+ * Replaces: launch_selected_attn_fwd, nsa/cuda/selected_fwd.cu:582-614
+ * (declared at nsa/cuda/bindings.cpp:14-20). */
+int launch_selected_attn_fwd(const void* Q, const void* K, const void* V, const int* Idx, void* Out,
+                             float* Lse, int BH, int n_q_blocks, int Tq_p, int Tk_p, int D, int top_k,
+                             int offset, int causal, float sm_scale, nsa_stream_t stream);
+
+/* delta[r] = sum_d dO[r,d] * O[r,d] in fp32 for `rows` rows of D 16-bit elements.
+ * Replaces: D_vec = (dO.float()*O.float()).sum(-1), nsa/triton/backward.py:158. */
+int nsa_bwd_delta(const void* dO, const void* O, float* delta, int64_t rows, int D, int dtype,
+                  nsa_stream_t stream);
+
+/* Selected-branch backward.  dQ [B,H,Tq,D] is WRITTEN (each query tile is owned by one
+ * thread block) in dq_dtype (NSA_FP32 or the 16-bit input type).  dK_f, dV_f
+ * [B,Hkv,Tk,D] are fp32 and are ACCUMULATED into with fp32 atomic adds (the caller
+ * zeroes them), which also forms the sum over the query heads that share a KV head.
+ * Rows with lse = -inf contribute nothing. */
+typedef struct nsa_bwd_args {
+  const void* Q;
+  const void* K;
+  const void* V;
+  const void* dO;
+  const float* lse;
+  const float* delta;
+  const int32_t* idx;
+  void* dQ;
+  float* dK_f;
+  float* dV_f;
+  int32_t B, H, Hkv, Hi;
+  int32_t Tq, Tk, D;
+  int32_t nq, top_k, bm, bn, sel_key_limit;
+  int32_t offset; /* key position of row i is i + offset */
+  int32_t causal;
+  int32_t dtype, dq_dtype;
+  float scale;
+} nsa_bwd_args;
+
+/* Replaces: selected_backward / _bwd_kernel, nsa/triton/backward.py:16-195. */
+int nsa_selected_bwd(const nsa_bwd_args* args, nsa_stream_t stream);
+
+/* The reference's native backward launcher, same argument list: dQ is bf16 and is
+ * written; dK_f/dV_f are fp32 and accumulated into (zeroed by the caller, as
+ * nsa/cuda/bindings.cpp:160-162 does).  Returns a status instead of void.
+ * Replaces: launch_selected_attn_bwd, nsa/cuda/selected_bwd.cu:731-772
+ * (declared at nsa/cuda/bindings.cpp:22-30). */
+int launch_selected_attn_bwd(const void* Q, const void* K, const void* V, const void* dO,
+                             const float* LSE, const float* Dvec, const int* Idx, void* dQ, float* dK_f,
+                             float* dV_f, int BH, int n_q_blocks, int Tq_p, int Tk_p, int D, int top_k,
+                             int offset, int causal, float sm_scale, nsa_stream_t stream);
+
+/* out = g0*out_c + g1*out_s + g2*out_w per row, g = sigmoid or softmax of the logits.
+ * With 16-bit gates the gate, each product and each sum are rounded to the 16-bit type
+ * in that order (what the reference's tensor expression does); with fp32 gates the
+ * result is fp32.  rows = B*H*Tq.
+ * Replaces: combine, nsa/triton/gating.py:15-40. */
+int nsa_combine(const void* out_c, const void* out_s, const void* out_w, const void* gates, void* out,
+                int64_t rows, int D, int activation, int dtype, int gate_dtype, nsa_stream_t stream);
+
+/* absmax[0] = max(|x|) over n elements (fp32 result; the caller zeroes absmax first).
+ * Replaces: x.abs().max(), nsa/triton/fp8.py:37. */
+int nsa_fp8_absmax(const void* x, int64_t n, int dtype, float* absmax, nsa_stream_t stream);
+
+/* out8[i] = saturating_cast_fp8( round_to_dtype(x[i] / scale) ).
+ * Replaces: (x/scale).clamp(-max,max).to(fmt), nsa/triton/fp8.py:39-40. */
+int nsa_fp8_quantize(const void* x, void* out8, int64_t n, int dtype, int fmt, float scale,
+                     nsa_stream_t stream);
+
+/* dst (16-bit `dtype`) = round(src fp32), n elements.
+ * Replaces: dQ_f.to(Q.dtype) etc., nsa/triton/backward.py:195. */
+int nsa_cast_from_f32(const float* src, void* dst, int64_t n, int dtype, nsa_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NSA_B200_H */

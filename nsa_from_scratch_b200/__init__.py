@@ -1,0 +1,21 @@
+"""B200 (sm_100a) Native Sparse Attention kernels behind the reference project's entry points.
+
+    from nsa_from_scratch_b200 import nsa_forward, NSAConfig
+
+All arithmetic runs in hand-written CUDA kernels reached through the C ABI of
+libnsa_b200.so (include/nsa_b200.h); there is no CPU or torch fallback."""
+from .config import NSAConfig
+from .compressed import compressed_attention
+from .selected import selected_attention
+from .sliding import sliding_attention
+from .gating import combine
+from .forward import nsa_forward, nsa_forward_fp8, _resolve_block_indices
+from .backward import selected_backward
+from .fp8 import quantize_to_fp8, selected_attention_fp8
+from .native import selected_attention_cuda, selected_backward_cuda
+
+__all__ = [
+    "NSAConfig", "compressed_attention", "selected_attention", "sliding_attention", "combine", "nsa_forward",
+    "nsa_forward_fp8", "selected_backward", "quantize_to_fp8", "selected_attention_fp8",
+    "selected_attention_cuda", "selected_backward_cuda",
+]

@@ -1,0 +1,25 @@
+"""Hyper-parameter bag with the reference's field names (nsa/reference.py:17-29) plus the
+optional extensions.  Any object with these attributes is accepted by `nsa_forward`; the
+extension fields are read with getattr and default to the reference's behaviour."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+
+@dataclass
+class NSAConfig:
+    block_size_c: int = 64
+    block_size_n: int = 64
+    block_size_m: int = 64
+    top_k: int = 16
+    window_size: int = 512
+    causal: bool = True
+    pool: str = "mean"
+    gate_activation: str = "sigmoid"
+    scale: Optional[float] = None
+    precision: str = "bf16"
+    # extensions (None / 0 = the reference's behaviour)
+    stride_c: Optional[int] = None   # compression stride < block_size_c: overlapping windows
+    force_first: int = 0             # always select the first n blocks
+    force_local: int = 0             # always select the last n causally legal blocks

@@ -1,0 +1,182 @@
+// extern "C" boundary: argument validation, error text, dispatch to the kernels.
+#include "common.cuh"
+
+#include <stdarg.h>
+#include <stdio.h>
+
+namespace nsa {
+
+static thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+// kernels (other translation units)
+int pool_mean(const void*, void*, int, int, int, int, int, int, int, int, float, cudaStream_t);
+int select_blocks(const void*, const void*, int32_t*, int, int, int, int, int, int, int, int, int, int, int, float, int,
+                  int, int, cudaStream_t);
+int topk_from_scores(const float*, int32_t*, int, int, int, int, int, int, int, int, cudaStream_t);
+int attention_fwd_generic(const nsa_fwd_args&, cudaStream_t);
+int attention_fwd_tc5(const nsa_fwd_args&, cudaStream_t);
+bool attention_fwd_tc5_supports(const nsa_fwd_args&);
+int selected_bwd(const nsa_bwd_args&, cudaStream_t);
+int combine(const void*, const void*, const void*, const void*, void*, long long, int, int, int, int, cudaStream_t);
+int fp8_absmax(const void*, long long, int, float*, cudaStream_t);
+int fp8_quantize(const void*, void*, long long, int, int, float, cudaStream_t);
+int bwd_delta(const void*, const void*, float*, long long, int, int, cudaStream_t);
+int cast_from_f32(const float*, void*, long long, int, cudaStream_t);
+
+static bool is16(int dt) { return dt == NSA_BF16 || dt == NSA_FP16; }
+static bool is8(int dt) { return dt == NSA_FP8_E4M3 || dt == NSA_FP8_E5M2; }
+
+static int check_fwd(const nsa_fwd_args& a) {
+  NSA_REQUIRE(a.Q && a.out, NSA_ERR_ARG, "attention forward: Q/out pointer is NULL");
+  NSA_REQUIRE(a.B > 0 && a.H > 0 && a.Hkv > 0 && a.H % a.Hkv == 0, NSA_ERR_ARG,
+              "attention forward: B=%d H=%d Hkv=%d (H must be a multiple of Hkv)", a.B, a.H, a.Hkv);
+  NSA_REQUIRE(a.Tq > 0 && a.Tk > 0, NSA_ERR_ARG, "attention forward: Tq=%d Tk=%d", a.Tq, a.Tk);
+  NSA_REQUIRE(a.D == 32 || a.D == 64 || a.D == 128, NSA_ERR_UNSUPPORTED, "attention forward: head dim %d not in {32,64,128}", a.D);
+  NSA_REQUIRE(is16(a.q_dtype) || is8(a.q_dtype), NSA_ERR_UNSUPPORTED, "attention forward: q dtype %d", a.q_dtype);
+  NSA_REQUIRE(a.kv_dtype == a.q_dtype, NSA_ERR_UNSUPPORTED, "attention forward: K/V dtype %d differs from Q dtype %d", a.kv_dtype, a.q_dtype);
+  const int br = a.branches;
+  NSA_REQUIRE(br > 0 && br < 8, NSA_ERR_ARG, "attention forward: branch mask %d", br);
+  if (!a.fused) {
+    NSA_REQUIRE(br == 1 || br == 2 || br == 4, NSA_ERR_ARG, "attention forward: unfused launch needs exactly one branch (mask %d)", br);
+  } else {
+    NSA_REQUIRE(a.gate_act == NSA_GATE_SIGMOID || a.gate_act == NSA_GATE_SOFTMAX, NSA_ERR_ARG, "attention forward: gate activation %d", a.gate_act);
+    NSA_REQUIRE(!a.gates || is16(a.gate_dtype) || a.gate_dtype == NSA_FP32, NSA_ERR_UNSUPPORTED, "attention forward: gate dtype %d", a.gate_dtype);
+  }
+  if (br & NSA_BRANCH_COMPRESSED) {
+    NSA_REQUIRE(a.Nc >= 0 && (a.Nc == 0 || (a.Kc && a.Vc)), NSA_ERR_ARG, "compressed: pooled K/V pointer is NULL");
+    NSA_REQUIRE(a.cmp_block > 0 && a.cmp_stride > 0 && a.cmp_stride <= a.cmp_block, NSA_ERR_ARG,
+                "compressed: block %d stride %d", a.cmp_block, a.cmp_stride);
+  }
+  if (br & (NSA_BRANCH_SELECTED | NSA_BRANCH_SLIDING)) NSA_REQUIRE(a.K && a.V, NSA_ERR_ARG, "attention forward: K/V pointer is NULL");
+  if (br & NSA_BRANCH_SELECTED) {
+    NSA_REQUIRE(a.idx, NSA_ERR_ARG, "selected: block index pointer is NULL");
+    NSA_REQUIRE(a.bm > 0 && a.bn > 0 && a.top_k > 0, NSA_ERR_ARG, "selected: bm=%d bn=%d top_k=%d", a.bm, a.bn, a.top_k);
+    NSA_REQUIRE(a.Hi == a.H || a.Hi == a.Hkv, NSA_ERR_ARG, "selected: index heads %d is neither H nor Hkv", a.Hi);
+    NSA_REQUIRE(a.nq == (a.Tq + a.bm - 1) / a.bm, NSA_ERR_ARG, "selected: nq %d != ceil(Tq/bm)", a.nq);
+    NSA_REQUIRE(a.sel_key_limit >= a.Tk && a.sel_key_limit < a.Tk + a.bn, NSA_ERR_ARG,
+                "selected: key limit %d must be Tk padded to the block size", a.sel_key_limit);
+  }
+  if (br & NSA_BRANCH_SLIDING) NSA_REQUIRE(a.window >= 1, NSA_ERR_ARG, "sliding: window %d", a.window);
+  return NSA_OK;
+}
+
+}  // namespace nsa
+
+using namespace nsa;
+
+extern "C" {
+
+const char* nsa_last_error(void) { return g_err; }
+int nsa_abi_version(void) { return 1; }
+
+int nsa_pool_mean(const void* x, void* out, int B, int H, int T, int D, int block, int stride, int n_out, int dtype,
+                  float dequant_scale, nsa_stream_t stream) {
+  NSA_REQUIRE(x && out, NSA_ERR_ARG, "pool: NULL pointer");
+  return pool_mean(x, out, B, H, T, D, block, stride, n_out, dtype, dequant_scale, (cudaStream_t)stream);
+}
+
+int nsa_select_blocks(const void* Qb, const void* Kb, int32_t* idx, int B, int H, int Hkv, int nq, int nk, int D,
+                      int top_k, int bm, int bn, int offset, int causal, float scale, int force_first, int force_local,
+                      int dtype, nsa_stream_t stream) {
+  NSA_REQUIRE(Qb && Kb && idx, NSA_ERR_ARG, "select: NULL pointer");
+  return select_blocks(Qb, Kb, idx, B, H, Hkv, nq, nk, D, top_k, bm, bn, offset, causal, scale, force_first,
+                       force_local, dtype, (cudaStream_t)stream);
+}
+
+int nsa_topk_from_scores(const float* scores, int32_t* idx, int BH, int nq, int nk, int top_k, int bm, int bn,
+                         int offset, int causal, nsa_stream_t stream) {
+  NSA_REQUIRE(scores && idx, NSA_ERR_ARG, "topk: NULL pointer");
+  return topk_from_scores(scores, idx, BH, nq, nk, top_k, bm, bn, offset, causal, (cudaStream_t)stream);
+}
+
+int nsa_attention_fwd(const nsa_fwd_args* args, nsa_stream_t stream) {
+  NSA_REQUIRE(args, NSA_ERR_ARG, "attention forward: NULL argument block");
+  int rc = check_fwd(*args);
+  if (rc != NSA_OK) return rc;
+  const bool tc5 = attention_fwd_tc5_supports(*args);
+  if (args->engine == NSA_ENGINE_TCGEN05) {
+    NSA_REQUIRE(tc5, NSA_ERR_UNSUPPORTED, "attention forward: the tcgen05 kernel does not take this shape");
+    return attention_fwd_tc5(*args, (cudaStream_t)stream);
+  }
+  if (args->engine == NSA_ENGINE_AUTO && tc5) return attention_fwd_tc5(*args, (cudaStream_t)stream);
+  return attention_fwd_generic(*args, (cudaStream_t)stream);
+}
+
+int launch_selected_attn_fwd(const void* Q, const void* K, const void* V, const int* Idx, void* Out, float* Lse, int BH,
+                             int n_q_blocks, int Tq_p, int Tk_p, int D, int top_k, int offset, int causal,
+                             float sm_scale, nsa_stream_t stream) {
+  NSA_REQUIRE(Tq_p % 64 == 0 && Tk_p % 64 == 0 && n_q_blocks == Tq_p / 64, NSA_ERR_ARG,
+              "launch_selected_attn_fwd: lengths must be padded to 64 (Tq_p=%d Tk_p=%d nq=%d)", Tq_p, Tk_p, n_q_blocks);
+  nsa_fwd_args a = {};
+  a.Q = Q; a.K = K; a.V = V; a.idx = Idx; a.out = Out; a.lse = Lse;
+  a.B = 1; a.H = BH; a.Hkv = BH; a.Hi = BH;
+  a.Tq = Tq_p; a.Tk = Tk_p; a.D = D; a.offset = offset;
+  a.nq = n_q_blocks; a.top_k = top_k; a.bm = 64; a.bn = 64; a.sel_key_limit = Tk_p;
+  a.causal = causal; a.branches = NSA_BRANCH_SELECTED; a.fused = 0;
+  a.q_dtype = a.kv_dtype = NSA_BF16; a.scale = sm_scale; a.engine = NSA_ENGINE_AUTO;
+  return nsa_attention_fwd(&a, stream);
+}
+
+int nsa_bwd_delta(const void* dO, const void* O, float* delta, int64_t rows, int D, int dtype, nsa_stream_t stream) {
+  NSA_REQUIRE(dO && O && delta, NSA_ERR_ARG, "delta: NULL pointer");
+  return bwd_delta(dO, O, delta, rows, D, dtype, (cudaStream_t)stream);
+}
+
+int nsa_selected_bwd(const nsa_bwd_args* a, nsa_stream_t stream) {
+  NSA_REQUIRE(a, NSA_ERR_ARG, "selected backward: NULL argument block");
+  NSA_REQUIRE(a->Q && a->K && a->V && a->dO && a->lse && a->delta && a->idx && a->dQ && a->dK_f && a->dV_f, NSA_ERR_ARG,
+              "selected backward: NULL pointer");
+  NSA_REQUIRE(a->B > 0 && a->H > 0 && a->Hkv > 0 && a->H % a->Hkv == 0, NSA_ERR_ARG, "selected backward: heads %d/%d", a->H, a->Hkv);
+  NSA_REQUIRE(a->Hi == a->H || a->Hi == a->Hkv, NSA_ERR_ARG, "selected backward: index heads %d", a->Hi);
+  NSA_REQUIRE(a->Tq > 0 && a->Tk > 0 && a->bm > 0 && a->bn > 0 && a->top_k > 0, NSA_ERR_ARG, "selected backward: empty problem");
+  NSA_REQUIRE(a->nq == (a->Tq + a->bm - 1) / a->bm, NSA_ERR_ARG, "selected backward: nq %d != ceil(Tq/bm)", a->nq);
+  NSA_REQUIRE(a->sel_key_limit >= a->Tk && a->sel_key_limit < a->Tk + a->bn, NSA_ERR_ARG, "selected backward: key limit %d", a->sel_key_limit);
+  NSA_REQUIRE(a->dq_dtype == NSA_FP32 || a->dq_dtype == a->dtype, NSA_ERR_ARG, "selected backward: dQ dtype %d", a->dq_dtype);
+  return selected_bwd(*a, (cudaStream_t)stream);
+}
+
+int launch_selected_attn_bwd(const void* Q, const void* K, const void* V, const void* dO, const float* LSE,
+                             const float* Dvec, const int* Idx, void* dQ, float* dK_f, float* dV_f, int BH,
+                             int n_q_blocks, int Tq_p, int Tk_p, int D, int top_k, int offset, int causal,
+                             float sm_scale, nsa_stream_t stream) {
+  NSA_REQUIRE(Tq_p % 64 == 0 && Tk_p % 64 == 0 && n_q_blocks == Tq_p / 64, NSA_ERR_ARG,
+              "launch_selected_attn_bwd: lengths must be padded to 64 (Tq_p=%d Tk_p=%d nq=%d)", Tq_p, Tk_p, n_q_blocks);
+  nsa_bwd_args a = {};
+  a.Q = Q; a.K = K; a.V = V; a.dO = dO; a.lse = LSE; a.delta = Dvec; a.idx = Idx;
+  a.dQ = dQ; a.dK_f = dK_f; a.dV_f = dV_f;
+  a.B = 1; a.H = BH; a.Hkv = BH; a.Hi = BH; a.Tq = Tq_p; a.Tk = Tk_p; a.D = D;
+  a.nq = n_q_blocks; a.top_k = top_k; a.bm = 64; a.bn = 64; a.sel_key_limit = Tk_p;
+  a.offset = offset; a.causal = causal; a.dtype = NSA_BF16; a.dq_dtype = NSA_BF16; a.scale = sm_scale;
+  return nsa_selected_bwd(&a, stream);
+}
+
+int nsa_combine(const void* out_c, const void* out_s, const void* out_w, const void* gates, void* out, int64_t rows,
+                int D, int activation, int dtype, int gate_dtype, nsa_stream_t stream) {
+  NSA_REQUIRE(out_c && out_s && out_w && gates && out, NSA_ERR_ARG, "combine: NULL pointer");
+  return combine(out_c, out_s, out_w, gates, out, rows, D, activation, dtype, gate_dtype, (cudaStream_t)stream);
+}
+
+int nsa_fp8_absmax(const void* x, int64_t n, int dtype, float* absmax, nsa_stream_t stream) {
+  NSA_REQUIRE(x && absmax, NSA_ERR_ARG, "absmax: NULL pointer");
+  return fp8_absmax(x, n, dtype, absmax, (cudaStream_t)stream);
+}
+
+int nsa_fp8_quantize(const void* x, void* out8, int64_t n, int dtype, int fmt, float scale, nsa_stream_t stream) {
+  NSA_REQUIRE(x && out8, NSA_ERR_ARG, "quantize: NULL pointer");
+  return fp8_quantize(x, out8, n, dtype, fmt, scale, (cudaStream_t)stream);
+}
+
+int nsa_cast_from_f32(const float* src, void* dst, int64_t n, int dtype, nsa_stream_t stream) {
+  NSA_REQUIRE(src && dst, NSA_ERR_ARG, "cast: NULL pointer");
+  return cast_from_f32(src, dst, n, dtype, (cudaStream_t)stream);
+}
+
+}  // extern "C"

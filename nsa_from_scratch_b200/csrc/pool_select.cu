@@ -1,0 +1,252 @@
+// Block mean pooling, block scoring + top-k selection.  HBM/latency-bound integer-output
+// work: coalesced 128-bit loads, fp32 arithmetic on CUDA cores in a fixed order (the
+// selected indices must equal the reference's, so every rounding point is reproduced:
+// fp32 sum of the block's rows, exact divide, one rounding to the 16-bit type, fp32 fma
+// dot over D in index order, scale applied last).
+#include "common.cuh"
+
+namespace nsa {
+
+// ------------------------------------------------------------------ pooling
+// One thread produces 8 consecutive columns of one pooled row.
+template <typename T, bool IN8>
+__global__ void __launch_bounds__(256) pool_mean_kernel(const void* __restrict__ xin, T* __restrict__ out, int Tlen, int D,
+                                                        int block, int stride, int n_out, float dq, int fmt) {
+  const int CH = D / 8;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_out * CH) return;
+  const int c = i / CH, ch = i % CH;
+  const size_t slab = (size_t)blockIdx.y * Tlen * D;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  const int r0 = c * stride;
+  const int r1 = min(r0 + block, Tlen);
+  for (int r = r0; r < r1; ++r) {
+    if constexpr (IN8) {
+      const uint8_t* p = reinterpret_cast<const uint8_t*>(xin) + slab + (size_t)r * D + ch * 8;
+      uint2 raw = *reinterpret_cast<const uint2*>(p);
+      const uint8_t* b = reinterpret_cast<const uint8_t*>(&raw);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += Elem<T>::to_f(Elem<T>::from_f(fp8_to_f(b[e], fmt) * dq));
+    } else {
+      const T* p = reinterpret_cast<const T*>(xin) + slab + (size_t)r * D + ch * 8;
+      uint4 raw = *reinterpret_cast<const uint4*>(p);
+      const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float2 f = Elem<T>::unpack(w[e]);
+        acc[2 * e] += f.x;
+        acc[2 * e + 1] += f.y;
+      }
+    }
+  }
+  const float inv_n = (float)block;
+  uint32_t w[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) w[e] = Elem<T>::pack(__fdiv_rn(acc[2 * e], inv_n), __fdiv_rn(acc[2 * e + 1], inv_n));
+  T* q = out + ((size_t)blockIdx.y * n_out + c) * D + ch * 8;
+  *reinterpret_cast<uint4*>(q) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+int pool_mean(const void* x, void* out, int B, int H, int T, int D, int block, int stride, int n_out, int dtype,
+              float dq, cudaStream_t st) {
+  NSA_REQUIRE(D % 8 == 0 && D > 0, NSA_ERR_ARG, "pool: D %d must be a positive multiple of 8", D);
+  NSA_REQUIRE(block > 0 && stride > 0 && stride <= block, NSA_ERR_ARG, "pool: need 0 < stride <= block (%d, %d)", stride, block);
+  int expect = stride == block ? (T + block - 1) / block : (T >= block ? (T - block) / stride + 1 : 0);
+  NSA_REQUIRE(n_out == expect, NSA_ERR_ARG, "pool: n_out %d, expected %d", n_out, expect);
+  if (n_out == 0 || B * H == 0) return NSA_OK;
+  NSA_REQUIRE((long long)B * H <= 65535, NSA_ERR_ARG, "pool: B*H %lld too large", (long long)B * H);
+  dim3 grid((unsigned)(((long long)n_out * (D / 8) + 255) / 256), (unsigned)(B * H));
+  switch (dtype) {
+    case NSA_BF16: pool_mean_kernel<__nv_bfloat16, false><<<grid, 256, 0, st>>>(x, (__nv_bfloat16*)out, T, D, block, stride, n_out, 1.f, 0); break;
+    case NSA_FP16: pool_mean_kernel<__half, false><<<grid, 256, 0, st>>>(x, (__half*)out, T, D, block, stride, n_out, 1.f, 0); break;
+    case NSA_FP8_E4M3:
+    case NSA_FP8_E5M2: pool_mean_kernel<__nv_bfloat16, true><<<grid, 256, 0, st>>>(x, (__nv_bfloat16*)out, T, D, block, stride, n_out, dq, dtype); break;
+    default: return fail(NSA_ERR_UNSUPPORTED, "pool: dtype %d", dtype);
+  }
+  return launch_status("pool_mean");
+}
+
+// ------------------------------------------------------------------ top-k over one score row
+// Warp-level: k_out rounds of (lane-local scan, shuffle arg-max).  Order: larger score
+// first, equal scores lowest index first.  Chosen entries are overwritten with a quiet-NaN
+// marker that no finite/inf score equals.
+__device__ __forceinline__ bool better(float v, int c, float bv, int bc) { return v > bv || (v == bv && c < bc); }
+
+__device__ void warp_topk_row(float* s, int n_scan, int nk, int k_out, int32_t* out_row, int lane) {
+  const uint32_t TAKEN = 0xFFFFFFFFu;
+  int filled = 0;
+  const int n_pick = min(k_out, n_scan);
+  for (int it = 0; it < n_pick; ++it) {
+    float bv = -INFINITY;
+    int bc = 0x7fffffff;
+    for (int c = lane; c < n_scan; c += 32) {
+      float v = s[c];
+      if (__float_as_uint(v) == TAKEN) continue;
+      if (bc == 0x7fffffff || v > bv) { bv = v; bc = c; }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+      int oc = __shfl_xor_sync(0xffffffffu, bc, off);
+      if (oc != 0x7fffffff && (bc == 0x7fffffff || better(ov, oc, bv, bc))) { bv = ov; bc = oc; }
+    }
+    if (lane == 0) { out_row[it] = bc; s[bc] = __uint_as_float(TAKEN); }
+    __syncwarp();
+    ++filled;
+  }
+  // fewer candidates than slots: the remaining slots take the lowest block ids not scanned
+  for (int it = filled + lane; it < k_out; it += 32) out_row[it] = n_scan + (it - filled);
+  (void)nk;
+}
+
+// ------------------------------------------------------------------ score + select
+// Thread block = (batch, query head, chunk of R query blocks); warp w owns query block row w.
+// Kb tiles of 64 block-means are staged in shared memory once per chunk and shared by the rows.
+template <typename T, int D>
+__global__ void __launch_bounds__(256) select_blocks_kernel(const T* __restrict__ Qb, const T* __restrict__ Kb,
+                                                            int32_t* __restrict__ idx, int H, int Hkv, int nq, int nk,
+                                                            int k_out, int bm, int bn, int offset, int causal, float scale,
+                                                            int force_first, int force_local, int R) {
+  constexpr int KT = 64;
+  constexpr int PITCH = D + 2;     // 16-bit elements; odd word stride -> conflict-free row reads
+  extern __shared__ __align__(16) unsigned char smem[];
+  T* kt = reinterpret_cast<T*>(smem);                              // [KT][PITCH]
+  T* qs = kt + KT * PITCH;                                         // [R][D]
+  float* sc = reinterpret_cast<float*>(qs + R * D + ((R * D) & 1)); // [R][nk]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.y, b = bh / H, h = bh % H, hk = h / (H / Hkv);
+  const int qb0 = blockIdx.x * R;
+  const int rows = min(R, nq - qb0);
+  const T* kbase = Kb + ((size_t)(b * Hkv + hk) * nk) * D;
+
+  for (int i = threadIdx.x; i < rows * D; i += blockDim.x)
+    qs[i] = Qb[((size_t)bh * nq + qb0) * D + i];
+
+  // legal range per row: blocks 0..cmax
+  auto cmax_of = [&](int qb) {
+    if (!causal) return nk - 1;
+    long long last = (long long)qb * bm + (bm - 1) + offset;
+    if (last < 0) return -1;
+    return (int)min((long long)(nk - 1), last / bn);
+  };
+  const int cmax_chunk = cmax_of(qb0 + rows - 1);
+  const int my_qb = qb0 + warp;
+  const int my_cmax = warp < rows ? cmax_of(my_qb) : -1;
+  float* my_sc = sc + (size_t)warp * nk;
+
+  for (int c0 = 0; c0 <= cmax_chunk; c0 += KT) {
+    __syncthreads();
+    const int nrow = min(KT, nk - c0);
+    for (int i = threadIdx.x; i < nrow * (D / 2); i += blockDim.x) {
+      int r = i / (D / 2), w = i % (D / 2);
+      reinterpret_cast<uint32_t*>(kt + r * PITCH)[w] = reinterpret_cast<const uint32_t*>(kbase + (size_t)(c0 + r) * D)[w];
+    }
+    __syncthreads();
+    if (warp < rows) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        int r = lane + half * 32;
+        int c = c0 + r;
+        if (r < nrow && c <= my_cmax) {
+          float acc = 0.f;
+          const uint32_t* kr = reinterpret_cast<const uint32_t*>(kt + r * PITCH);
+          const uint32_t* qr = reinterpret_cast<const uint32_t*>(qs + warp * D);
+#pragma unroll 8
+          for (int w = 0; w < D / 2; ++w) {
+            float2 kf = Elem<T>::unpack(kr[w]);
+            float2 qf = Elem<T>::unpack(qr[w]);
+            acc = __fmaf_rn(qf.x, kf.x, acc);
+            acc = __fmaf_rn(qf.y, kf.y, acc);
+          }
+          float v = acc * scale;
+          if (c < force_first || c > my_cmax - force_local) v = INFINITY;
+          my_sc[c] = v;
+        }
+      }
+    }
+  }
+  __syncwarp();
+  if (warp < rows) {
+    int32_t* out_row = idx + ((size_t)bh * nq + my_qb) * k_out;
+    warp_topk_row(my_sc, my_cmax + 1, nk, k_out, out_row, lane);
+  }
+}
+
+template <typename T>
+static int select_launch(const void* Qb, const void* Kb, int32_t* idx, int B, int H, int Hkv, int nq, int nk, int D,
+                         int k_out, int bm, int bn, int offset, int causal, float scale, int ff, int fl, cudaStream_t st) {
+  const size_t fixed = (size_t)64 * (D + 2) * 2;
+  int R = 8;
+  auto need = [&](int r) { return fixed + (size_t)r * D * 2 + 4 + (size_t)r * nk * 4; };
+  while (R > 1 && need(R) > 200 * 1024) R >>= 1;
+  NSA_REQUIRE(need(R) <= 200 * 1024, NSA_ERR_UNSUPPORTED, "select: %d KV blocks exceed the shared-memory score row", nk);
+  dim3 grid((unsigned)((nq + R - 1) / R), (unsigned)(B * H));
+  size_t smem = need(R);
+#define NSA_SEL(DD)                                                                                     \
+  {                                                                                                     \
+    auto fn = select_blocks_kernel<T, DD>;                                                              \
+    NSA_CUDA_OK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));      \
+    fn<<<grid, 256, smem, st>>>((const T*)Qb, (const T*)Kb, idx, H, Hkv, nq, nk, k_out, bm, bn, offset, \
+                                causal, scale, ff, fl, R);                                              \
+  }
+  switch (D) {
+    case 32: NSA_SEL(32) break;
+    case 64: NSA_SEL(64) break;
+    case 128: NSA_SEL(128) break;
+    default: return fail(NSA_ERR_UNSUPPORTED, "select: head dim %d not in {32,64,128}", D);
+  }
+#undef NSA_SEL
+  return launch_status("select_blocks");
+}
+
+int select_blocks(const void* Qb, const void* Kb, int32_t* idx, int B, int H, int Hkv, int nq, int nk, int D, int top_k,
+                  int bm, int bn, int offset, int causal, float scale, int ff, int fl, int dtype, cudaStream_t st) {
+  NSA_REQUIRE(B > 0 && H > 0 && Hkv > 0 && H % Hkv == 0, NSA_ERR_ARG, "select: heads %d/%d", H, Hkv);
+  NSA_REQUIRE(nq > 0 && nk > 0 && top_k > 0 && bm > 0 && bn > 0, NSA_ERR_ARG, "select: empty problem");
+  NSA_REQUIRE((long long)B * H <= 65535, NSA_ERR_ARG, "select: B*H too large");
+  NSA_REQUIRE(ff >= 0 && fl >= 0, NSA_ERR_ARG, "select: negative forced-block counts");
+  int k_out = top_k < nk ? top_k : nk;
+  if (dtype == NSA_BF16)
+    return select_launch<__nv_bfloat16>(Qb, Kb, idx, B, H, Hkv, nq, nk, D, k_out, bm, bn, offset, causal, scale, ff, fl, st);
+  if (dtype == NSA_FP16)
+    return select_launch<__half>(Qb, Kb, idx, B, H, Hkv, nq, nk, D, k_out, bm, bn, offset, causal, scale, ff, fl, st);
+  return fail(NSA_ERR_UNSUPPORTED, "select: dtype %d", dtype);
+}
+
+// ------------------------------------------------------------------ top-k from given scores
+__global__ void __launch_bounds__(256) topk_scores_kernel(const float* __restrict__ scores, int32_t* __restrict__ idx,
+                                                          int nq, int nk, int k_out, int bm, int bn, int offset,
+                                                          int causal, int R) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  float* sc = reinterpret_cast<float*>(smem);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.y;
+  const int qb = blockIdx.x * R + warp;
+  if (warp >= R || qb >= nq) return;
+  int cmax = nk - 1;
+  if (causal) {
+    long long last = (long long)qb * bm + (bm - 1) + offset;
+    cmax = last < 0 ? -1 : (int)min((long long)(nk - 1), last / bn);
+  }
+  float* my = sc + (size_t)warp * nk;
+  const float* src = scores + ((size_t)bh * nq + qb) * nk;
+  for (int c = lane; c <= cmax; c += 32) my[c] = src[c];
+  __syncwarp();
+  warp_topk_row(my, cmax + 1, nk, k_out, idx + ((size_t)bh * nq + qb) * k_out, lane);
+}
+
+int topk_from_scores(const float* scores, int32_t* idx, int BH, int nq, int nk, int top_k, int bm, int bn, int offset,
+                     int causal, cudaStream_t st) {
+  NSA_REQUIRE(BH > 0 && nq > 0 && nk > 0 && top_k > 0, NSA_ERR_ARG, "topk: empty problem");
+  NSA_REQUIRE(BH <= 65535, NSA_ERR_ARG, "topk: B*H too large");
+  int R = 8;
+  while (R > 1 && (size_t)R * nk * 4 > 200 * 1024) R >>= 1;
+  NSA_REQUIRE((size_t)R * nk * 4 <= 200 * 1024, NSA_ERR_UNSUPPORTED, "topk: %d KV blocks exceed shared memory", nk);
+  size_t smem = (size_t)R * nk * 4;
+  NSA_CUDA_OK(cudaFuncSetAttribute(topk_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid((unsigned)((nq + R - 1) / R), (unsigned)BH);
+  topk_scores_kernel<<<grid, 256, smem, st>>>(scores, idx, nq, nk, top_k < nk ? top_k : nk, bm, bn, offset, causal, R);
+  return launch_status("topk_from_scores");
+}
+
+}  // namespace nsa

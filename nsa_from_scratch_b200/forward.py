@@ -1,0 +1,207 @@
+"""Combined NSA forward.  Same entry points as the reference's nsa/triton/forward.py:
+`nsa_forward` (:362-370), `_resolve_block_indices` (:321-324), `_block_scores_from_pooled`
+(:301-303) and the autograd Functions `_CompressedFn/_SelectedFn/_SlidingFn` (:123,143,263).
+
+Without autograd the whole forward is four launches: pool K/V, pool Q/K block means,
+score+top-k, and ONE fused kernel that runs the three branches per query tile and applies
+the gates in its epilogue (no branch output ever reaches HBM).  With autograd the branches
+run separately so that their outputs can be saved; the selected branch has the hand-written
+backward, the compressed and sliding branches differentiate a torch recompute."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch import Tensor
+
+from . import _lib as L
+from . import _recompute, ops
+from .compressed import compressed_attention as _compressed_kernel
+from .gating import combine
+from .selected import selected_attention as _selected_kernel
+from .sliding import sliding_attention as _sliding_kernel
+
+
+def _block_scores_from_pooled(Q: Tensor, K: Tensor, *, block_size_m: int, block_size_n: int, scale: float) -> Tensor:
+    """fp32 [B,H,nq,nk]: block means in the input dtype (pool kernel), then a library GEMM."""
+    G = Q.shape[1] // K.shape[1]
+    Qb = ops.pool_mean(Q, block_size_m).float()
+    Kb = ops.pool_mean(K, block_size_n).float()
+    Kb = Kb if G == 1 else Kb.repeat_interleave(G, dim=1)
+    return torch.einsum("bhqd,bhkd->bhqk", Qb, Kb) * scale
+
+
+def _resolve_block_indices(Q: Tensor, K: Tensor, *, block_size_m: int, block_size_n: int, top_k: int, causal: bool,
+                           scale: float, force_first: int = 0, force_local: int = 0,
+                           q_scale: float = 1.0, k_scale: float = 1.0) -> Tensor:
+    """int32 [B,H,nq,min(top_k,nk)] by mean-pool scoring + top-k, ties to the lowest index.
+    The causal legality offset uses the PADDED lengths, as the reference does (:350-352)."""
+    Tq, Tk = Q.shape[2], K.shape[2]
+    Qb = ops.pool_mean(Q.detach(), block_size_m, dequant_scale=q_scale)
+    Kb = ops.pool_mean(K.detach(), block_size_n, dequant_scale=k_scale)
+    nq, nk = Qb.shape[2], Kb.shape[2]
+    return ops.select_blocks_from_means(Qb, Kb, top_k=top_k, bm=block_size_m, bn=block_size_n,
+                                        offset=nk * block_size_n - nq * block_size_m, causal=bool(causal),
+                                        scale=float(scale), force_first=force_first, force_local=force_local)
+
+
+def _grads_through(fn, Q, K, V, grad_out):
+    with torch.enable_grad():
+        Qd, Kd, Vd = (t.detach().requires_grad_(True) for t in (Q, K, V))
+        out = fn(Qd, Kd, Vd)
+        dQ, dK, dV = torch.autograd.grad(out, (Qd, Kd, Vd), grad_outputs=grad_out.to(out.dtype), allow_unused=True)
+    z = lambda g, x: torch.zeros_like(x) if g is None else torch.nan_to_num(g, nan=0.0, posinf=0.0, neginf=0.0).to(x.dtype)
+    return z(dQ, Q), z(dK, K), z(dV, V)
+
+
+class _CompressedFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, Q, K, V, block_size_c, pool, causal, scale, stride_c=None):
+        out, _ = _compressed_kernel(Q, K, V, block_size_c=block_size_c, pool=pool, causal=causal, scale=scale,
+                                    stride_c=stride_c)
+        ctx.save_for_backward(Q, K, V)
+        ctx.args = (block_size_c, stride_c, causal, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        Q, K, V = ctx.saved_tensors
+        bc, sc, causal, scale = ctx.args
+        dQ, dK, dV = _grads_through(
+            lambda q, k, v: _recompute.compressed_torch(q, k, v, block_size_c=bc, stride_c=sc, causal=causal, scale=scale),
+            Q, K, V, grad_out)
+        return dQ, dK, dV, None, None, None, None, None
+
+
+class _SelectedFn(torch.autograd.Function):
+    """Selected branch with the hand-written backward kernel."""
+
+    @staticmethod
+    def forward(ctx, Q, K, V, block_size_n, block_size_m, top_k, block_indices, causal, scale):
+        if Q.dtype not in (torch.float16, torch.bfloat16):
+            raise TypeError("selected branch kernels take fp16/bf16 (the reference's fp64 gradcheck route is not provided)")
+        out, lse = _selected_kernel(Q, K, V, block_size_n=block_size_n, block_size_m=block_size_m, top_k=top_k,
+                                    block_indices=block_indices, causal=causal, scale=scale)
+        ctx.save_for_backward(Q, K, V, out, lse, block_indices)
+        ctx.args = (block_size_n, block_size_m, causal, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        Q, K, V, O, LSE, idx = ctx.saved_tensors
+        bn, bm, causal, scale = ctx.args
+        D = Q.shape[-1]
+        delta = ops.bwd_delta(grad_out.to(Q.dtype), O)
+        dQ, dK, dV = ops.selected_bwd(grad_out.to(Q.dtype), Q, K, V, LSE, delta, idx, bm=bm, bn=bn, causal=bool(causal),
+                                      scale=ops.softmax_scale(D, scale), offset=K.shape[2] - Q.shape[2], dq_fp32=False)
+        return dQ, ops.cast_from_f32(dK, K.dtype), ops.cast_from_f32(dV, V.dtype), None, None, None, None, None, None
+
+
+class _SlidingFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, Q, K, V, window_size, causal, scale):
+        out, _ = _sliding_kernel(Q, K, V, window_size=window_size, causal=causal, scale=scale)
+        ctx.save_for_backward(Q, K, V)
+        ctx.args = (window_size, causal, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        Q, K, V = ctx.saved_tensors
+        W, causal, scale = ctx.args
+        dQ, dK, dV = _grads_through(
+            lambda q, k, v: _recompute.sliding_torch(q, k, v, window_size=W, causal=causal, scale=scale), Q, K, V, grad_out)
+        return dQ, dK, dV, None, None, None
+
+
+class _CombineFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, out_c, out_s, out_w, gate_logits, activation):
+        ctx.save_for_backward(out_c, out_s, out_w, gate_logits)
+        ctx.activation = activation
+        return combine(out_c, out_s, out_w, gate_logits, activation=activation)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        oc, os_, ow, gl = ctx.saved_tensors
+        with torch.enable_grad():
+            xs = [t.detach().float().requires_grad_(True) for t in (oc, os_, ow, gl)]
+            g = torch.sigmoid(xs[3]) if ctx.activation == "sigmoid" else torch.softmax(xs[3], dim=-1)
+            y = g[..., 0:1] * xs[0] + g[..., 1:2] * xs[1] + g[..., 2:3] * xs[2]
+            grads = torch.autograd.grad(y, xs, grad_outputs=grad_out.float())
+        return tuple(gr.to(t.dtype) for gr, t in zip(grads, (oc, os_, ow, gl))) + (None,)
+
+
+def _cfg(cfg, name, default):
+    v = getattr(cfg, name, default)
+    return default if v is None else v
+
+
+def nsa_forward(Q: Tensor, K: Tensor, V: Tensor, cfg, *, gate_logits: Optional[Tensor] = None,
+                block_indices: Optional[Tensor] = None) -> Tensor:
+    """NSA combined forward.  Q [B,H,Tq,D], K/V [B,H|Hkv,Tk,D] fp16/bf16; `cfg` is any object with
+    the reference's NSAConfig fields (optional extras: stride_c, force_first, force_local);
+    gate_logits [B,H,Tq,3] (None = zero logits); block_indices [B,H|Hkv,nq,k] int32 (None =
+    mean-pool scoring + top-k).  Returns [B,H,Tq,D] in Q's dtype; differentiable wrt Q, K, V
+    and gate_logits."""
+    assert Q.dtype in (torch.float16, torch.bfloat16), "Q must be fp16 or bf16"
+    D = Q.shape[-1]
+    scale = cfg.scale if cfg.scale is not None else 1.0 / (D ** 0.5)
+    if cfg.pool != "mean":
+        raise NotImplementedError("nsa_forward: only pool='mean' supported")
+    stride_c = getattr(cfg, "stride_c", None)
+    ff, fl = _cfg(cfg, "force_first", 0), _cfg(cfg, "force_local", 0)
+    if block_indices is None:
+        block_indices = _resolve_block_indices(Q, K, block_size_m=cfg.block_size_m, block_size_n=cfg.block_size_n,
+                                               top_k=cfg.top_k, causal=cfg.causal, scale=float(scale),
+                                               force_first=ff, force_local=fl)
+    needs_grad = torch.is_grad_enabled() and any(
+        t is not None and t.requires_grad for t in (Q, K, V, gate_logits))
+    if needs_grad:
+        out_c = _CompressedFn.apply(Q, K, V, cfg.block_size_c, cfg.pool, cfg.causal, cfg.scale, stride_c)
+        out_s = _SelectedFn.apply(Q, K, V, cfg.block_size_n, cfg.block_size_m, cfg.top_k, block_indices,
+                                  cfg.causal, cfg.scale)
+        out_w = _SlidingFn.apply(Q, K, V, cfg.window_size, cfg.causal, cfg.scale)
+        if gate_logits is None:
+            B, H, Tq, _ = Q.shape
+            gate_logits = Q.new_full((B, H, Tq, 3), 0.0)
+        return _CombineFn.apply(out_c, out_s, out_w, gate_logits, cfg.gate_activation)
+    return _fused_forward(Q, K, V, cfg, float(scale), stride_c, gate_logits, block_indices, 1.0, 1.0, 1.0)
+
+
+def _fused_forward(Q, K, V, cfg, scale, stride_c, gate_logits, block_indices, sq, sk, sv, engine=L.ENGINE_AUTO):
+    bc = cfg.block_size_c
+    stride = bc if stride_c is None else int(stride_c)
+    Kc = ops.pool_mean(K, bc, stride, dequant_scale=sk)
+    Vc = ops.pool_mean(V, bc, stride, dequant_scale=sv)
+    Tq, Tk = Q.shape[2], K.shape[2]
+    Tk_pad = Kc.shape[2] * bc if stride == bc else Tk
+    if cfg.gate_activation not in ("sigmoid", "softmax"):
+        raise ValueError(f"unknown gate_activation: {cfg.gate_activation}")
+    out, _ = ops.attention_fwd(
+        Q, K, V, branches=L.BRANCH_COMPRESSED | L.BRANCH_SELECTED | L.BRANCH_SLIDING, fused=True,
+        causal=bool(cfg.causal), scale=scale, Kc=Kc, Vc=Vc, cmp_block=bc, cmp_stride=stride, cmp_offset=Tk_pad - Tq,
+        idx=block_indices, bm=cfg.block_size_m, bn=cfg.block_size_n, window=cfg.window_size, gates=gate_logits,
+        gate_act=L.GATE_SOFTMAX if cfg.gate_activation == "softmax" else L.GATE_SIGMOID,
+        q_scale=sq, k_scale=sk, v_scale=sv, engine=engine)
+    return out
+
+
+def nsa_forward_fp8(Q: Tensor, K: Tensor, V: Tensor, scale_q: float, scale_k: float, scale_v: float, cfg, *,
+                    gate_logits: Optional[Tensor] = None, block_indices: Optional[Tensor] = None) -> Tensor:
+    """The combined forward on fp8 (e4m3/e5m2) Q/K/V with per-tensor scales; every kernel
+    dequantises to bf16(fp32(x)*scale) as it loads, so the result equals `nsa_forward` on the
+    dequantised bf16 tensors.  Inference only.  Returns bf16."""
+    assert Q.dtype in (torch.float8_e4m3fn, torch.float8_e5m2) and K.dtype == Q.dtype and V.dtype == Q.dtype
+    D = Q.shape[-1]
+    scale = cfg.scale if cfg.scale is not None else 1.0 / (D ** 0.5)
+    if block_indices is None:
+        block_indices = _resolve_block_indices(
+            Q, K, block_size_m=cfg.block_size_m, block_size_n=cfg.block_size_n, top_k=cfg.top_k, causal=cfg.causal,
+            scale=float(scale), force_first=_cfg(cfg, "force_first", 0), force_local=_cfg(cfg, "force_local", 0),
+            q_scale=scale_q, k_scale=scale_k)
+    return _fused_forward(Q, K, V, cfg, float(scale), getattr(cfg, "stride_c", None), gate_logits, block_indices,
+                          scale_q, scale_k, scale_v)
+
+
+__all__ = ["nsa_forward", "nsa_forward_fp8"]

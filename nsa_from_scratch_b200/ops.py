@@ -1,0 +1,218 @@
+"""Tensor-level wrappers over the C ABI: check tensors, allocate outputs, pass raw pointers.
+
+torch is used only for device memory, dtypes and the current stream.  Nothing here computes
+on the host and nothing falls back to torch arithmetic.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Optional, Tuple
+
+import torch
+from torch import Tensor
+
+from . import _lib as L
+
+_16 = (torch.float16, torch.bfloat16)
+_8 = (torch.float8_e4m3fn, torch.float8_e5m2)
+
+
+def _need_cuda(*ts: Tensor) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("nsa_from_scratch_b200 kernels need CUDA tensors (there is no CPU path)")
+
+
+def softmax_scale(D: int, scale: Optional[float]) -> float:
+    return float(scale) if scale is not None else 1.0 / math.sqrt(D)
+
+
+def n_pooled(T: int, block: int, stride: Optional[int] = None) -> int:
+    stride = block if stride is None else stride
+    if stride == block:
+        return (T + block - 1) // block
+    return (T - block) // stride + 1 if T >= block else 0
+
+
+def pool_mean(x: Tensor, block: int, stride: Optional[int] = None, dequant_scale: float = 1.0) -> Tensor:
+    """[B,H,T,D] -> [B,H,n,D] window means (16-bit in -> same type; fp8 in -> bf16)."""
+    _need_cuda(x)
+    B, H, T, D = x.shape
+    stride = block if stride is None else stride
+    n = n_pooled(T, block, stride)
+    x = x.contiguous()
+    out = torch.empty((B, H, n, D), device=x.device, dtype=torch.bfloat16 if x.dtype in _8 else x.dtype)
+    with torch.cuda.device(x.device):
+        L.check(L.load().nsa_pool_mean(x.data_ptr(), out.data_ptr(), B, H, T, D, block, stride, n,
+                                       L.dtype_code(x.dtype), float(dequant_scale), L.stream_ptr()), "nsa_pool_mean")
+    return out
+
+
+def select_blocks_from_means(Qb: Tensor, Kb: Tensor, *, top_k: int, bm: int, bn: int, offset: int, causal: bool,
+                             scale: float, force_first: int = 0, force_local: int = 0) -> Tensor:
+    _need_cuda(Qb, Kb)
+    B, H, nq, D = Qb.shape
+    Hkv, nk = Kb.shape[1], Kb.shape[2]
+    k_out = min(top_k, nk)
+    idx = torch.empty((B, H, nq, k_out), device=Qb.device, dtype=torch.int32)
+    with torch.cuda.device(Qb.device):
+        L.check(L.load().nsa_select_blocks(Qb.data_ptr(), Kb.data_ptr(), idx.data_ptr(), B, H, Hkv, nq, nk, D, top_k,
+                                           bm, bn, offset, int(causal), float(scale), force_first, force_local,
+                                           L.dtype_code(Qb.dtype), L.stream_ptr()), "nsa_select_blocks")
+    return idx
+
+
+def topk_from_scores(scores: Tensor, *, top_k: int, bm: int, bn: int, offset: int, causal: bool) -> Tensor:
+    _need_cuda(scores)
+    B, H, nq, nk = scores.shape
+    scores = scores.float().contiguous()
+    idx = torch.empty((B, H, nq, min(top_k, nk)), device=scores.device, dtype=torch.int32)
+    with torch.cuda.device(scores.device):
+        L.check(L.load().nsa_topk_from_scores(scores.data_ptr(), idx.data_ptr(), B * H, nq, nk, top_k, bm, bn, offset,
+                                              int(causal), L.stream_ptr()), "nsa_topk_from_scores")
+    return idx
+
+
+def attention_fwd(
+    Q: Tensor, K: Tensor, V: Tensor, *, branches: int, fused: bool, causal: bool, scale: float,
+    Kc: Optional[Tensor] = None, Vc: Optional[Tensor] = None, cmp_block: int = 0, cmp_stride: int = 0,
+    cmp_offset: int = 0, idx: Optional[Tensor] = None, bm: int = 64, bn: int = 64, window: int = 0,
+    gates: Optional[Tensor] = None, gate_act: int = L.GATE_SIGMOID, offset: Optional[int] = None,
+    q_scale: float = 1.0, k_scale: float = 1.0, v_scale: float = 1.0, engine: int = L.ENGINE_AUTO,
+    want_lse: bool = True,
+) -> Tuple[Tensor, Optional[Tensor]]:
+    """One launch of nsa_attention_fwd.  Returns (out, lse); lse is None for fused launches."""
+    _need_cuda(Q, K, V)
+    B, H, Tq, D = Q.shape
+    Hkv, Tk = K.shape[1], K.shape[2]
+    if K.shape != (B, Hkv, Tk, D) or V.shape != K.shape:
+        raise ValueError(f"K/V shapes {tuple(K.shape)}/{tuple(V.shape)} do not match Q {tuple(Q.shape)}")
+    if H % Hkv:
+        raise ValueError(f"query heads {H} not a multiple of KV heads {Hkv}")
+    if K.dtype != Q.dtype or V.dtype != Q.dtype:
+        raise TypeError("Q, K, V must share a dtype")
+    Q, K, V = Q.contiguous(), K.contiguous(), V.contiguous()
+    out_dtype = torch.bfloat16 if Q.dtype in _8 else Q.dtype
+    out = torch.empty((B, H, Tq, D), device=Q.device, dtype=out_dtype)
+    lse = torch.empty((B, H, Tq), device=Q.device, dtype=torch.float32) if (want_lse and not fused) else None
+    a = L.FwdArgs()
+    a.Q, a.K, a.V, a.out, a.lse = Q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(), L.ptr(lse)
+    a.B, a.H, a.Hkv, a.Tq, a.Tk, a.D = B, H, Hkv, Tq, Tk, D
+    a.offset = Tk - Tq if offset is None else offset
+    a.causal, a.branches, a.fused, a.gate_act = int(causal), branches, int(fused), gate_act
+    a.q_dtype = a.kv_dtype = L.dtype_code(Q.dtype)
+    a.scale, a.q_scale, a.k_scale, a.v_scale = float(scale), float(q_scale), float(k_scale), float(v_scale)
+    a.engine = engine
+    keep = [Q, K, V]
+    if branches & L.BRANCH_COMPRESSED:
+        Kc, Vc = Kc.contiguous(), Vc.contiguous()
+        keep += [Kc, Vc]
+        a.Kc, a.Vc, a.Nc = Kc.data_ptr(), Vc.data_ptr(), Kc.shape[2]
+        a.cmp_block, a.cmp_stride, a.cmp_offset = cmp_block, cmp_stride, cmp_offset
+    if branches & L.BRANCH_SELECTED:
+        idx = idx.to(torch.int32).contiguous()
+        keep.append(idx)
+        nq = (Tq + bm - 1) // bm
+        if idx.dim() != 4 or idx.shape[0] != B or idx.shape[1] not in (H, Hkv) or idx.shape[2] != nq:
+            raise ValueError(f"block_indices shape {tuple(idx.shape)} does not match (B={B}, H={H}|{Hkv}, nq={nq}, k)")
+        a.idx, a.Hi, a.nq, a.top_k, a.bm, a.bn = idx.data_ptr(), idx.shape[1], nq, idx.shape[3], bm, bn
+        a.sel_key_limit = ((Tk + bn - 1) // bn) * bn
+    if branches & L.BRANCH_SLIDING:
+        a.window = int(window)
+    if fused and gates is not None:
+        gates = gates.contiguous()
+        keep.append(gates)
+        if gates.shape != (B, H, Tq, 3):
+            raise ValueError(f"gate_logits shape {tuple(gates.shape)} != {(B, H, Tq, 3)}")
+        a.gates, a.gate_dtype = gates.data_ptr(), L.dtype_code(gates.dtype)
+    with torch.cuda.device(Q.device):
+        L.check(L.load().nsa_attention_fwd(C.byref(a), L.stream_ptr()), "nsa_attention_fwd")
+    return out, lse
+
+
+def bwd_delta(dO: Tensor, O: Tensor) -> Tensor:
+    _need_cuda(dO, O)
+    dO, O = dO.contiguous(), O.contiguous()
+    D = dO.shape[-1]
+    delta = torch.empty(dO.shape[:-1], device=dO.device, dtype=torch.float32)
+    with torch.cuda.device(dO.device):
+        L.check(L.load().nsa_bwd_delta(dO.data_ptr(), O.data_ptr(), delta.data_ptr(), delta.numel(), D,
+                                       L.dtype_code(dO.dtype), L.stream_ptr()), "nsa_bwd_delta")
+    return delta
+
+
+def selected_bwd(dO: Tensor, Q: Tensor, K: Tensor, V: Tensor, lse: Tensor, delta: Tensor, idx: Tensor, *, bm: int,
+                 bn: int, causal: bool, scale: float, offset: int, dq_fp32: bool) -> Tuple[Tensor, Tensor, Tensor]:
+    """Returns (dQ in Q.dtype or fp32, dK fp32, dV fp32)."""
+    _need_cuda(dO, Q, K, V, lse, delta, idx)
+    B, H, Tq, D = Q.shape
+    Hkv, Tk = K.shape[1], K.shape[2]
+    dO, Q, K, V = dO.contiguous(), Q.contiguous(), K.contiguous(), V.contiguous()
+    lse, delta, idx = lse.contiguous(), delta.contiguous(), idx.to(torch.int32).contiguous()
+    dQ = torch.empty((B, H, Tq, D), device=Q.device, dtype=torch.float32 if dq_fp32 else Q.dtype)
+    dK = torch.zeros((B, Hkv, Tk, D), device=Q.device, dtype=torch.float32)
+    dV = torch.zeros((B, Hkv, Tk, D), device=Q.device, dtype=torch.float32)
+    a = L.BwdArgs()
+    a.Q, a.K, a.V, a.dO = Q.data_ptr(), K.data_ptr(), V.data_ptr(), dO.data_ptr()
+    a.lse, a.delta, a.idx = lse.data_ptr(), delta.data_ptr(), idx.data_ptr()
+    a.dQ, a.dK_f, a.dV_f = dQ.data_ptr(), dK.data_ptr(), dV.data_ptr()
+    a.B, a.H, a.Hkv, a.Hi, a.Tq, a.Tk, a.D = B, H, Hkv, idx.shape[1], Tq, Tk, D
+    a.nq, a.top_k, a.bm, a.bn = (Tq + bm - 1) // bm, idx.shape[3], bm, bn
+    a.sel_key_limit = ((Tk + bn - 1) // bn) * bn
+    a.offset, a.causal, a.dtype = offset, int(causal), L.dtype_code(Q.dtype)
+    a.dq_dtype = L.FP32 if dq_fp32 else a.dtype
+    a.scale = float(scale)
+    with torch.cuda.device(Q.device):
+        L.check(L.load().nsa_selected_bwd(C.byref(a), L.stream_ptr()), "nsa_selected_bwd")
+    return dQ, dK, dV
+
+
+def cast_from_f32(x: Tensor, dtype: torch.dtype) -> Tensor:
+    _need_cuda(x)
+    x = x.contiguous()
+    out = torch.empty(x.shape, device=x.device, dtype=dtype)
+    with torch.cuda.device(x.device):
+        L.check(L.load().nsa_cast_from_f32(x.data_ptr(), out.data_ptr(), x.numel(), L.dtype_code(dtype), L.stream_ptr()),
+                "nsa_cast_from_f32")
+    return out
+
+
+def combine(out_c: Tensor, out_s: Tensor, out_w: Tensor, gate_logits: Tensor, activation: str) -> Tensor:
+    _need_cuda(out_c, out_s, out_w, gate_logits)
+    if activation not in ("sigmoid", "softmax"):
+        raise ValueError(f"unknown activation: {activation}")
+    if out_c.dtype not in _16 or out_s.dtype != out_c.dtype or out_w.dtype != out_c.dtype:
+        raise TypeError("combine: branch outputs must share a 16-bit dtype")
+    if gate_logits.dtype not in (out_c.dtype, torch.float32):
+        raise TypeError("combine: gate logits must have the branch dtype or fp32")
+    B, H, Tq, D = out_c.shape
+    if gate_logits.shape != (B, H, Tq, 3):
+        raise ValueError(f"gate_logits shape {tuple(gate_logits.shape)} != {(B, H, Tq, 3)}")
+    out_c, out_s, out_w, g = out_c.contiguous(), out_s.contiguous(), out_w.contiguous(), gate_logits.contiguous()
+    out = torch.empty((B, H, Tq, D), device=out_c.device, dtype=torch.float32 if g.dtype == torch.float32 else out_c.dtype)
+    with torch.cuda.device(out_c.device):
+        L.check(L.load().nsa_combine(out_c.data_ptr(), out_s.data_ptr(), out_w.data_ptr(), g.data_ptr(), out.data_ptr(),
+                                     B * H * Tq, D, L.GATE_SOFTMAX if activation == "softmax" else L.GATE_SIGMOID,
+                                     L.dtype_code(out_c.dtype), L.dtype_code(g.dtype), L.stream_ptr()), "nsa_combine")
+    return out
+
+
+def fp8_absmax(x: Tensor) -> Tensor:
+    _need_cuda(x)
+    x = x.contiguous()
+    out = torch.zeros(1, device=x.device, dtype=torch.float32)
+    with torch.cuda.device(x.device):
+        L.check(L.load().nsa_fp8_absmax(x.data_ptr(), x.numel(), L.dtype_code(x.dtype), out.data_ptr(), L.stream_ptr()),
+                "nsa_fp8_absmax")
+    return out
+
+
+def fp8_quantize(x: Tensor, fmt: torch.dtype, scale: float) -> Tensor:
+    _need_cuda(x)
+    x = x.contiguous()
+    out = torch.empty(x.shape, device=x.device, dtype=torch.uint8)
+    with torch.cuda.device(x.device):
+        L.check(L.load().nsa_fp8_quantize(x.data_ptr(), out.data_ptr(), x.numel(), L.dtype_code(x.dtype),
+                                          L.dtype_code(fmt), float(scale), L.stream_ptr()), "nsa_fp8_quantize")
+    return out.view(fmt)

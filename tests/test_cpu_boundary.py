@@ -1,0 +1,75 @@
+"""No-GPU checks of the boundary: the library loads, exports every declared symbol, the
+ctypes structures match the header, and the host-side argument checks fail loudly."""
+import ctypes as C
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    from nsa_from_scratch_b200 import _lib
+    lib = _lib.load()
+    header = open(os.path.join(ROOT, "include", "nsa_b200.h")).read()
+    declared = set(re.findall(r"^(?:int|const char\*)\s+(\w+)\s*\(", header, flags=re.M))
+    assert declared, "no declarations parsed"
+    assert declared == set(_lib.PROTOTYPES), declared ^ set(_lib.PROTOTYPES)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert lib.nsa_abi_version() == 1
+
+
+def _struct_fields(header, name):
+    body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (name, name), header, flags=re.S).group(1)
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    out = []
+    for decl in body.split(";"):
+        decl = decl.strip()
+        if not decl:
+            continue
+        names = [n.strip().lstrip("*") for n in decl.split(",")]
+        names[0] = names[0].split()[-1].lstrip("*")
+        out += names
+    return out
+
+
+def test_ctypes_structs_match_header():
+    from nsa_from_scratch_b200 import _lib
+    header = open(os.path.join(ROOT, "include", "nsa_b200.h")).read()
+    assert [f[0] for f in _lib.FwdArgs._fields_] == _struct_fields(header, "nsa_fwd_args")
+    assert [f[0] for f in _lib.BwdArgs._fields_] == _struct_fields(header, "nsa_bwd_args")
+
+
+def test_argument_errors_are_reported_without_a_gpu():
+    from nsa_from_scratch_b200 import _lib
+    lib = _lib.load()
+    a = _lib.FwdArgs()
+    assert lib.nsa_attention_fwd(C.byref(a), None) == -1            # NULL Q
+    assert b"NULL" in lib.nsa_last_error()
+    assert lib.nsa_pool_mean(1, 1, 1, 1, 64, 60, 32, 32, 2, 0, 1.0, None) == -1   # D not a multiple of 8
+    assert b"multiple of 8" in lib.nsa_last_error()
+    assert lib.nsa_attention_fwd(None, None) == -1
+
+
+def test_no_cpu_fallback():
+    import nsa_from_scratch_b200 as nsa
+    x = torch.zeros(1, 1, 64, 64, dtype=torch.bfloat16)
+    with pytest.raises((RuntimeError, AssertionError)):
+        nsa.sliding_attention(x, x, x)
+    with pytest.raises((RuntimeError, AssertionError)):
+        nsa.nsa_forward(x, x, x, nsa.NSAConfig())
+
+
+def test_compat_shim_maps_reference_module_names():
+    from nsa_from_scratch_b200 import compat
+    compat.install()
+    import nsa.cuda as nc
+    import nsa.triton.forward as nf
+    import nsa.triton.selected as ns
+    assert nf.nsa_forward.__module__.startswith("nsa_from_scratch_b200")
+    assert ns.selected_attention.__module__.startswith("nsa_from_scratch_b200")
+    ext = nc._get_ext()
+    assert hasattr(ext, "selected_attention_fwd_cuda") and hasattr(ext, "selected_attention_bwd_cuda")

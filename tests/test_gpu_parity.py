@@ -1,0 +1,295 @@
+"""CUDA kernels (through the C ABI) against the CPU oracle and the reference-made golden
+vectors.  Tolerances: block indices bit-exact; bf16/fp16 outputs and gradients max-abs
+<= 2e-2 against the fp32 oracle; fp8 <= 6e-2; lse <= 1e-2."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import check_out_lse, make_qkv, max_abs
+from oracle import nsa_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL16 = 2e-2
+TOL8 = 6e-2
+DT = {"torch.float32": torch.float32, "torch.bfloat16": torch.bfloat16, "torch.float16": torch.float16}
+
+
+@pytest.fixture(scope="module")
+def nsa():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import nsa_from_scratch_b200 as pkg
+    return pkg
+
+
+def G(golden, key, dtype=torch.float32):
+    return torch.from_numpy(np.asarray(golden[key])).to(dtype)
+
+
+# ------------------------------------------------------------------ golden vectors
+def test_golden_compressed(nsa, golden):
+    for name, bc, causal in (("cmp_b", 64, True), ("cmp_c", 32, False)):
+        Q, K, V = (G(golden, f"{name}.{x}", torch.bfloat16) for x in "QKV")
+        out, lse = nsa.compressed_attention(Q.cuda(), K.cuda(), V.cuda(), block_size_c=bc, causal=causal)
+        ref_l = G(golden, f"{name}.lse")
+        ref_l = torch.where(torch.isfinite(ref_l), ref_l, torch.full_like(ref_l, float("-inf")))
+        check_out_lse(out, lse, torch.nan_to_num(G(golden, f"{name}.out")), ref_l, TOL16)
+        from nsa_from_scratch_b200.compressed import _mean_pool
+        assert torch.equal(_mean_pool(K.cuda(), bc).float().cpu(), G(golden, f"{name}.Kc"))
+
+
+def test_golden_block_indices(nsa, golden):
+    from nsa_from_scratch_b200.forward import _resolve_block_indices
+    from nsa_from_scratch_b200.selected import _topk_indices_from_scores
+    for name, (bm, bn, k, causal, dt) in {"sel_idx_a": (64, 64, 4, True, "torch.bfloat16"),
+                                          "sel_idx_b": (32, 32, 5, True, "torch.bfloat16"),
+                                          "sel_idx_c": (64, 64, 3, False, "torch.float16")}.items():
+        Q, K = G(golden, f"{name}.Q", DT[dt]), G(golden, f"{name}.K", DT[dt])
+        idx = _resolve_block_indices(Q.cuda(), K.cuda(), block_size_m=bm, block_size_n=bn, top_k=k, causal=causal,
+                                     scale=1.0 / Q.shape[-1] ** 0.5).cpu()
+        canon = O.select_blocks(Q, K, block_size_m=bm, block_size_n=bn, top_k=k, causal=causal)
+        assert torch.equal(idx, canon)
+        # equal to the reference's torch.topk wherever the score is finite
+        _, masked = O.select_blocks(Q, K, block_size_m=bm, block_size_n=bn, top_k=k, causal=causal, return_scores=True)
+        fin = torch.isfinite(torch.gather(masked, -1, idx.long()))
+        assert torch.equal(idx[fin], G(golden, f"{name}.idx", torch.int32)[fin])
+        bs = G(golden, f"{name}.bs")
+        nq, nk = bs.shape[-2:]
+        idx2 = _topk_indices_from_scores(bs.cuda(), k, nq, nk, bm, bn, Q.shape[2], K.shape[2], causal).cpu()
+        assert torch.equal(idx2, O.indices_from_scores(bs, top_k=k, block_size_m=bm, block_size_n=bn, Tq=Q.shape[2],
+                                                       Tk=K.shape[2], causal=causal))
+
+
+def test_golden_selected_fwd_bwd(nsa, golden):
+    for name, (bm, bn, causal) in {"sel_a": (64, 64, True), "sel_b": (32, 32, True)}.items():
+        Q, K, V, dO = (G(golden, f"{name}.{x}", torch.bfloat16) for x in ("Q", "K", "V", "dO"))
+        idx = G(golden, f"{name}.idx", torch.int32)
+        out, lse = nsa.selected_attention(Q.cuda(), K.cuda(), V.cuda(), block_size_n=bn, block_size_m=bm,
+                                          block_indices=idx.cuda(), causal=causal)
+        ref_l = G(golden, f"{name}.lse")
+        ref_l = torch.where(torch.isfinite(ref_l), ref_l, torch.full_like(ref_l, float("-inf")))
+        check_out_lse(out, lse, torch.nan_to_num(G(golden, f"{name}.out")), ref_l, TOL16)
+        # gradients through the autograd Function (unpadded tensors, fp32 references from the golden file;
+        # dO in the file is fp32, the kernel sees its bf16 rounding)
+        from nsa_from_scratch_b200.forward import _SelectedFn
+        Qc, Kc, Vc = (t.cuda().requires_grad_(True) for t in (Q, K, V))
+        o = _SelectedFn.apply(Qc, Kc, Vc, bn, bm, idx.shape[-1], idx.cuda(), causal, None)
+        o.backward(dO.cuda())
+        for got, key in ((Qc.grad, "dQ"), (Kc.grad, "dK"), (Vc.grad, "dV")):
+            ref = G(golden, f"{name}.{key}")
+            assert max_abs(got, ref) <= 5e-2 + 1e-2 * float(ref.abs().max()), (name, key, max_abs(got, ref))
+
+
+def test_golden_sliding(nsa, golden):
+    for name, W, causal in (("sld_a", 64, True), ("sld_c", 32, False)):
+        Q, K, V = (G(golden, f"{name}.{x}", torch.bfloat16) for x in "QKV")
+        out, lse = nsa.sliding_attention(Q.cuda(), K.cuda(), V.cuda(), window_size=W, causal=causal)
+        check_out_lse(out, lse, G(golden, f"{name}.out"), G(golden, f"{name}.lse"), TOL16)
+
+
+def test_golden_combined_and_combine(nsa, golden):
+    for name, act in (("nsa_a", "sigmoid"), ("nsa_b", "softmax")):
+        Q, K, V = (G(golden, f"{name}.{x}", torch.bfloat16) for x in "QKV")
+        gates = G(golden, f"{name}.gates")
+        idx = G(golden, f"{name}.idx", torch.int32)
+        cfg = nsa.NSAConfig(block_size_c=32, block_size_n=32, block_size_m=32, top_k=3, window_size=48,
+                            gate_activation=act)
+        ref = G(golden, f"{name}.out")
+        fin = torch.isfinite(ref).all(-1)
+        for gl in (gates.cuda(), gates.to(torch.bfloat16).cuda()):
+            out = nsa.nsa_forward(Q.cuda(), K.cuda(), V.cuda(), cfg, gate_logits=gl, block_indices=idx.cuda())
+            assert max_abs(out, ref, fin) <= TOL16 + (1e-2 if gl.dtype != torch.float32 else 0)
+        # indices resolved inside nsa_forward equal the canonical ones
+        out2 = nsa.nsa_forward(Q.cuda(), K.cuda(), V.cuda(), cfg, gate_logits=gates.cuda())
+        assert max_abs(out2, ref, fin) <= TOL16
+        # the stand-alone combine reproduces the bf16 rounding chain (<= 1 bf16 ulp from libm differences)
+        oc = nsa.combine(Q.cuda(), K.cuda(), V.cuda(), gates.to(torch.bfloat16).cuda(), activation=act)
+        refc = G(golden, f"{name}.combine_bf16")
+        assert float(((oc.float().cpu() - refc).abs() > 2 ** -7 * refc.abs().clamp(min=2 ** -6)).float().mean()) < 1e-3
+        assert max_abs(oc, refc) <= 4e-2
+
+
+def test_golden_fp8_quantise(nsa, golden):
+    for name, fmt in (("fp8_e4m3", torch.float8_e4m3fn), ("fp8_e5m2", torch.float8_e5m2)):
+        x = G(golden, f"{name}.x", torch.bfloat16)
+        x8, sc = nsa.quantize_to_fp8(x.cuda(), fmt=fmt)
+        assert sc == float(golden[f"{name}.scale"][0])
+        assert np.array_equal(x8.cpu().view(torch.uint8).numpy(), golden[f"{name}.bits"])
+
+
+# ------------------------------------------------------------------ seeded cases against the oracle
+SHAPES = [
+    # B, H, Hkv, Tq, Tk, D, dtype
+    (1, 4, 4, 128, 128, 64, torch.bfloat16),
+    (2, 8, 8, 256, 256, 64, torch.float16),
+    (1, 4, 4, 512, 1024, 64, torch.bfloat16),
+    (1, 8, 2, 320, 448, 128, torch.bfloat16),     # GQA, D=128
+    (1, 2, 1, 100, 200, 32, torch.float16),       # ragged, D=32
+]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("causal", [True, False])
+def test_compressed_vs_oracle(nsa, shape, causal):
+    B, H, Hkv, Tq, Tk, D, dt = shape
+    Q, K, V, _ = make_qkv(1, B, H, Hkv, Tq, Tk, D, dt, 0.5)
+    for bc, st in ((64, None), (32, 16)):
+        out, lse = nsa.compressed_attention(Q.cuda(), K.cuda(), V.cuda(), block_size_c=bc, causal=causal, stride_c=st)
+        ro, rl = O.compressed_attention(Q, K, V, block_size_c=bc, stride_c=st, causal=causal)
+        check_out_lse(out, lse, ro, rl, TOL16)
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("causal", [True, False])
+def test_sliding_vs_oracle(nsa, shape, causal):
+    B, H, Hkv, Tq, Tk, D, dt = shape
+    Q, K, V, _ = make_qkv(2, B, H, Hkv, Tq, Tk, D, dt)
+    for W in (64, 100, 4096):
+        out, lse = nsa.sliding_attention(Q.cuda(), K.cuda(), V.cuda(), window_size=W, causal=causal)
+        ro, rl = O.sliding_attention(Q, K, V, window_size=W, causal=causal)
+        check_out_lse(out, lse, ro, rl, TOL16)
+
+
+SEL_CASES = [
+    # B, H, Hkv, Tq, Tk, D, k, bm, bn, dtype
+    (1, 4, 4, 128, 128, 64, 2, 32, 32, torch.bfloat16),
+    (1, 8, 8, 1024, 2048, 64, 8, 64, 64, torch.bfloat16),
+    (2, 8, 8, 512, 1024, 64, 4, 64, 64, torch.float16),
+    (1, 8, 8, 512, 1024, 128, 8, 64, 64, torch.bfloat16),
+    (1, 8, 2, 384, 384, 128, 4, 64, 64, torch.bfloat16),    # GQA
+    (1, 2, 1, 100, 200, 32, 3, 32, 32, torch.bfloat16),     # ragged
+    (1, 2, 2, 256, 256, 64, 2, 64, 128, torch.bfloat16),    # KV block of two tiles
+]
+
+
+@pytest.mark.parametrize("case", SEL_CASES)
+@pytest.mark.parametrize("causal", [True, False])
+def test_selection_and_selected_vs_oracle(nsa, case, causal):
+    from nsa_from_scratch_b200.forward import _resolve_block_indices
+    B, H, Hkv, Tq, Tk, D, k, bm, bn, dt = case
+    Q, K, V, _ = make_qkv(3, B, H, Hkv, Tq, Tk, D, dt)
+    idx = _resolve_block_indices(Q.cuda(), K.cuda(), block_size_m=bm, block_size_n=bn, top_k=k, causal=causal,
+                                 scale=1.0 / D ** 0.5).cpu()
+    canon, masked = O.select_blocks(Q, K, block_size_m=bm, block_size_n=bn, top_k=k, causal=causal, return_scores=True)
+    if not torch.equal(idx, canon):
+        bad = (idx != canon).nonzero()
+        b, h, q, s = bad[0].tolist()
+        pytest.fail(f"{len(bad)} index slots differ; first at {bad[0].tolist()}: got {idx[b, h, q].tolist()} "
+                    f"want {canon[b, h, q].tolist()}; score gap "
+                    f"{float(masked[b, h, q, idx[b, h, q, s]] - masked[b, h, q, canon[b, h, q, s]])}")
+    out, lse = nsa.selected_attention(Q.cuda(), K.cuda(), V.cuda(), block_size_n=bn, block_size_m=bm, top_k=k,
+                                      block_indices=idx.cuda(), causal=causal)
+    ro, rl = O.selected_attention(Q, K, V, idx, block_size_n=bn, block_size_m=bm, causal=causal)
+    check_out_lse(out, lse, ro, rl, TOL16)
+    if Hkv != H:   # indices shared by the heads of a group
+        gi = idx[:, ::H // Hkv].contiguous()
+        out, lse = nsa.selected_attention(Q.cuda(), K.cuda(), V.cuda(), block_size_n=bn, block_size_m=bm, top_k=k,
+                                          block_indices=gi.cuda(), causal=causal)
+        ro, rl = O.selected_attention(Q, K, V, gi, block_size_n=bn, block_size_m=bm, causal=causal)
+        check_out_lse(out, lse, ro, rl, TOL16)
+
+
+def test_selected_structural_cases(nsa):
+    """top_k covering every block == full causal attention; duplicated ids count twice; the
+    out-of-range sentinel id is skipped; forced blocks."""
+    B, H, T, D = 1, 2, 256, 64
+    Q, K, V, _ = make_qkv(4, B, H, H, T, T, D)
+    nk = T // 64
+    all_idx = torch.arange(nk, dtype=torch.int32).expand(B, H, nk, nk).contiguous()
+    out, lse = nsa.selected_attention(Q.cuda(), K.cuda(), V.cuda(), block_indices=all_idx.cuda())
+    ro, rl = O.sliding_attention(Q, K, V, window_size=T, causal=True)      # window >= T is full attention
+    check_out_lse(out, lse, ro, rl, TOL16)
+    dup = torch.tensor([0, 0, nk, 1], dtype=torch.int32).expand(B, H, nk, 4).contiguous()   # nk = sentinel
+    out, lse = nsa.selected_attention(Q.cuda(), K.cuda(), V.cuda(), block_indices=dup.cuda(), causal=False)
+    ro, rl = O.selected_attention(Q, K, V, dup, causal=False)
+    check_out_lse(out, lse, ro, rl, TOL16)
+    from nsa_from_scratch_b200.forward import _resolve_block_indices
+    f = _resolve_block_indices(Q.cuda(), K.cuda(), block_size_m=64, block_size_n=64, top_k=3, causal=True,
+                               scale=0.125, force_first=1, force_local=2).cpu()
+    assert torch.equal(f, O.select_blocks(Q, K, top_k=3, force_first=1, force_local=2))
+
+
+@pytest.mark.parametrize("case", [(1, 4, 4, 128, 256, 64, 4, 64, 64), (1, 8, 2, 256, 256, 128, 4, 64, 64),
+                                  (2, 4, 1, 192, 192, 64, 3, 64, 64), (1, 2, 2, 96, 160, 32, 3, 32, 32)])
+def test_selected_backward_vs_oracle(nsa, case):
+    B, H, Hkv, Tq, Tk, D, k, bm, bn = case
+    Q, K, V, g = make_qkv(5, B, H, Hkv, Tq, Tk, D)
+    dO = torch.randn(B, H, Tq, D, generator=g).to(torch.bfloat16)
+    idx = O.select_blocks(Q, K, block_size_m=bm, block_size_n=bn, top_k=k, causal=True)
+    out, lse = nsa.selected_attention(Q.cuda(), K.cuda(), V.cuda(), block_size_n=bn, block_size_m=bm,
+                                      block_indices=idx.cuda())
+    dQ, dK, dV = nsa.selected_backward(dO.cuda(), Q.cuda(), K.cuda(), V.cuda(), out, lse, idx.cuda(), block_size_m=bm,
+                                       block_size_n=bn, causal=True, scale=1.0 / D ** 0.5, Tq=Tq, Tk=Tk,
+                                       return_fp32=True)
+    assert dQ.dtype == dK.dtype == dV.dtype == torch.float32
+    rQ, rK, rV = O.selected_backward(dO, Q, K, V, idx, block_size_n=bn, block_size_m=bm, causal=True)
+    for got, ref, nm in ((dQ, rQ, "dQ"), (dK, rK, "dK"), (dV, rV, "dV")):
+        assert max_abs(got, ref) <= TOL16 * max(1.0, float(ref.abs().max())), (nm, max_abs(got, ref), float(ref.abs().max()))
+    # the reference-shaped native launcher (MHA, padded) gives the same numbers
+    if H == Hkv and Tq % 64 == 0 and Tk % 64 == 0 and bm == 64:
+        o2, l2 = nsa.selected_attention_cuda(Q.cuda(), K.cuda(), V.cuda(), idx.cuda(), 64, 64, k, True, 1.0 / D ** 0.5)
+        assert torch.equal(o2, out) and torch.equal(l2, lse)
+        q2, k2, v2 = nsa.selected_backward_cuda(dO.cuda(), Q.cuda(), K.cuda(), V.cuda(), out, lse, idx.cuda(), 64, 64, k,
+                                                True, 1.0 / D ** 0.5)
+        assert max_abs(q2, rQ) <= 2 * TOL16 * max(1.0, float(rQ.abs().max()))
+        assert max_abs(k2, rK) <= 2 * TOL16 * max(1.0, float(rK.abs().max()))
+
+
+@pytest.mark.parametrize("geom", [(64, None, 0, 0), (32, 16, 1, 2)])
+@pytest.mark.parametrize("shape", [(1, 4, 4, 512, 512, 64), (1, 8, 2, 640, 640, 128), (1, 4, 2, 200, 456, 64)])
+def test_fused_forward_vs_oracle(nsa, geom, shape):
+    bc, st, ff, fl = geom
+    B, H, Hkv, Tq, Tk, D = shape
+    Q, K, V, g = make_qkv(6, B, H, Hkv, Tq, Tk, D)
+    gates = torch.randn(B, H, Tq, 3, generator=g)
+    cfg = nsa.NSAConfig(block_size_c=bc, stride_c=st, top_k=4, window_size=128, force_first=ff, force_local=fl)
+    out = nsa.nsa_forward(Q.cuda(), K.cuda(), V.cuda(), cfg, gate_logits=gates.cuda())
+    ref = O.nsa_forward(Q, K, V, block_size_c=bc, stride_c=st, top_k=4, window_size=128, gate_logits=gates,
+                        force_first=ff, force_local=fl)
+    assert max_abs(out, ref) <= TOL16
+    # default gates (zero logits) and the unfused autograd route agree with the fused kernel
+    out0 = nsa.nsa_forward(Q.cuda(), K.cuda(), V.cuda(), cfg)
+    Qg = Q.cuda().requires_grad_(True)
+    out1 = nsa.nsa_forward(Qg, K.cuda(), V.cuda(), cfg)
+    assert max_abs(out0, out1.detach()) <= TOL16
+    out1.float().sum().backward()
+    assert torch.isfinite(Qg.grad).all() and float(Qg.grad.abs().sum()) > 0
+
+
+def test_fp8_paths_vs_bf16_and_oracle(nsa):
+    B, H, Hkv, T, D = 1, 4, 2, 512, 64
+    g = torch.Generator().manual_seed(7)
+    xs = []
+    for shape in ((B, H, T, D), (B, Hkv, T, D), (B, Hkv, T, D)):
+        x = torch.randn(shape, generator=g)
+        x = torch.where(torch.rand(shape, generator=g) < 1e-3, x * 20, x)
+        xs.append(x.to(torch.bfloat16))
+    q8, k8, v8 = (nsa.quantize_to_fp8(x.cuda()) for x in xs)
+    deq = [O.dequantize_fp8(t.cpu(), s) for t, s in (q8, k8, v8)]
+    idx = O.select_blocks(deq[0], deq[1], top_k=4)
+    out8, lse8 = nsa.selected_attention_fp8(q8[0], k8[0], v8[0], q8[1], k8[1], v8[1], top_k=4, block_indices=idx.cuda())
+    outb, lseb = nsa.selected_attention(deq[0].cuda(), deq[1].cuda(), deq[2].cuda(), top_k=4, block_indices=idx.cuda())
+    assert torch.equal(out8, outb) and torch.equal(lse8, lseb)        # identical operands after in-kernel dequant
+    ro, rl = O.selected_attention(xs[0], xs[1], xs[2], idx)
+    assert max_abs(out8, ro) <= TOL8
+    cfg = nsa.NSAConfig(block_size_c=32, stride_c=16, top_k=4, window_size=128)
+    f8 = nsa.nsa_forward_fp8(q8[0], k8[0], v8[0], q8[1], k8[1], v8[1], cfg)
+    fb = nsa.nsa_forward(deq[0].cuda(), deq[1].cuda(), deq[2].cuda(), cfg)
+    assert torch.equal(f8, fb)
+    ref = O.nsa_forward(xs[0], xs[1], xs[2], block_size_c=32, stride_c=16, top_k=4, window_size=128,
+                        block_indices=O.select_blocks(deq[0], deq[1], top_k=4))
+    assert max_abs(f8, ref) <= TOL8
+
+
+def test_forward_is_bitwise_repeatable_and_errors_are_loud(nsa):
+    Q, K, V, _ = make_qkv(8, 1, 4, 2, 512, 512, 64)
+    cfg = nsa.NSAConfig(top_k=4, window_size=128)
+    a = nsa.nsa_forward(Q.cuda(), K.cuda(), V.cuda(), cfg)
+    b = nsa.nsa_forward(Q.cuda(), K.cuda(), V.cuda(), cfg)
+    assert torch.equal(a, b)
+    with pytest.raises(RuntimeError):
+        nsa.sliding_attention(Q, K, V)          # CPU tensors: no fallback
+    with pytest.raises((RuntimeError, AssertionError)):
+        nsa.sliding_attention(Q.cuda()[..., :48].contiguous(), K.cuda()[..., :48].contiguous(),
+                              V.cuda()[..., :48].contiguous())   # unsupported head dim
