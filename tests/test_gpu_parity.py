@@ -271,13 +271,14 @@ def test_fp8_paths_vs_bf16_and_oracle(nsa):
     out8, lse8 = nsa.selected_attention_fp8(q8[0], k8[0], v8[0], q8[1], k8[1], v8[1], top_k=4, block_indices=idx.cuda())
     outb, lseb = nsa.selected_attention(deq[0].cuda(), deq[1].cuda(), deq[2].cuda(), top_k=4, block_indices=idx.cuda())
     assert torch.equal(out8, outb) and torch.equal(lse8, lseb)        # identical operands after in-kernel dequant
-    ro, rl = O.selected_attention(xs[0], xs[1], xs[2], idx)
+    # fp32 oracle on the dequantised values (what the fp8 tensors actually hold)
+    ro, rl = O.selected_attention(deq[0], deq[1], deq[2], idx)
     assert max_abs(out8, ro) <= TOL8
     cfg = nsa.NSAConfig(block_size_c=32, stride_c=16, top_k=4, window_size=128)
     f8 = nsa.nsa_forward_fp8(q8[0], k8[0], v8[0], q8[1], k8[1], v8[1], cfg)
     fb = nsa.nsa_forward(deq[0].cuda(), deq[1].cuda(), deq[2].cuda(), cfg)
     assert torch.equal(f8, fb)
-    ref = O.nsa_forward(xs[0], xs[1], xs[2], block_size_c=32, stride_c=16, top_k=4, window_size=128,
+    ref = O.nsa_forward(deq[0], deq[1], deq[2], block_size_c=32, stride_c=16, top_k=4, window_size=128,
                         block_indices=O.select_blocks(deq[0], deq[1], top_k=4))
     assert max_abs(f8, ref) <= TOL8
 
