@@ -1,0 +1,359 @@
+"""NSA forward throughput benchmark.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--seq-len T] ...
+
+One "step" is one NSA forward (pool K/V, pool block means, score + top-k, fused three-branch
+attention with the gated combine) over one synthetic batch.  Default workload: bf16, B=1 per GPU,
+T=65536 causal, Hq=64, Hkv=4, D=128, compression block 32 / stride 16, selection block 64 with
+top-16 (block 0 and the 2 local blocks forced), window 512, sigmoid gates from a random
+Linear(D,3) applied to Q.  With N GPUs every rank runs the same workload on its own batch
+element (batch x KV-head partitioning, no collective): weak scaling, value = N*T / max-rank time.
+
+Prints ONE JSON line (rank 0).  `--impl reference` times the CPU oracle port (the reference's
+plain-torch algorithm) on a bounded sample of the same workload on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "nsa_fwd_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--seq-len", type=int, default=65536)
+    ap.add_argument("--heads", type=int, default=64)
+    ap.add_argument("--kv-heads", type=int, default=4)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--cmp-block", type=int, default=32)
+    ap.add_argument("--cmp-stride", type=int, default=16)
+    ap.add_argument("--top-k", type=int, default=16)
+    ap.add_argument("--window", type=int, default=512)
+    ap.add_argument("--engine", default="auto", choices=["auto", "generic", "tcgen05"])
+    ap.add_argument("--select", default="group", choices=["group", "head"],
+                    help="block lists shared by the query heads of a KV head (group) or one per query head (head)")
+    ap.add_argument("--cpu-tiles", type=int, default=40, help="64-row query tiles in the CPU-baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--seed", type=int, default=0)
+    return ap.parse_args()
+
+
+def workload_name(a):
+    return (f"nsa_fwd bf16 B=1/gpu T={a.seq_len} Hq={a.heads} Hkv={a.kv_heads} D={a.head_dim} "
+            f"cmp={a.cmp_block}/{a.cmp_stride} sel=64x{a.top_k}(forced 1+2, per {a.select}) win={a.window} sigmoid-gates")
+
+
+def make_inputs(a, seed):
+    """Q, K, V ~ N(0,1) bf16 and gate logits = Linear(D,3)(Q) from a CPU generator (order Q, K, V, W)."""
+    g = torch.Generator().manual_seed(seed)
+    B, H, Hkv, T, D = 1, a.heads, a.kv_heads, a.seq_len, a.head_dim
+    Q = torch.randn(B, H, T, D, generator=g).to(torch.bfloat16)
+    K = torch.randn(B, Hkv, T, D, generator=g).to(torch.bfloat16)
+    V = torch.randn(B, Hkv, T, D, generator=g).to(torch.bfloat16)
+    bound = 1.0 / D ** 0.5                                           # torch.nn.Linear default init range
+    Wg = (torch.rand(3, D, generator=g) * 2 - 1) * bound
+    gates = torch.einsum("bhtd,cd->bhtc", Q.float(), Wg).to(torch.bfloat16)
+    return Q, K, V, gates
+
+
+# ------------------------------------------------------------------ CPU baseline (oracle port)
+def cpu_sample(a, n_tiles, repeats=1):
+    """Times the CPU oracle on `n_tiles` 64-row query tiles (all heads) spread evenly over the
+    sequence; each tile sees its full causal prefix of keys.  Returns (tokens/s, seconds, description)."""
+    from oracle import nsa_oracle as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    Q, K, V, gates = make_inputs(a, a.seed)
+    T = a.seq_len
+    nq = T // 64
+    tiles = sorted({min(nq - 1, int((i + 0.5) * nq / n_tiles)) for i in range(n_tiles)})
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        for qb in tiles:
+            q0, q1 = qb * 64, (qb + 1) * 64
+            O.nsa_forward(Q[:, :, q0:q1], K[:, :, :q1], V[:, :, :q1], block_size_c=a.cmp_block,
+                          stride_c=a.cmp_stride, top_k=a.top_k, window_size=a.window,
+                          gate_logits=gates[:, :, q0:q1].float(), force_first=1, force_local=2,
+                          group_shared=a.select == "group")
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    toks = len(tiles) * 64
+    return toks / best, best, f"{len(tiles)} query tiles of 64 rows x {a.heads} heads at blocks {tiles}, full causal key prefix each"
+
+
+def run_reference(a):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    n_tiles = max(2, a.cpu_tiles)
+    times = []
+    for _ in range(a.warmup if a.warmup < 2 else 1):
+        cpu_sample(a, 2)
+    val = None
+    for _ in range(max(1, min(a.steps, 3))):
+        v, dt, desc = cpu_sample(a, n_tiles)
+        times.append(dt)
+        val = v if val is None else max(val, v)
+    cores = torch.get_num_threads()
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": a.gpus, "steps": len(times),
+        "warmup": 1, "ms_per_step": 1e3 * min(times), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(a), "note": "CPU oracle port of the reference's plain-torch path"},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------ clocks
+class ClockSampler:
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(index)], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip().split(", "))
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            pass
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.strip().lower() == "active":
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------ ours
+def algorithmic_flops(a, idx):
+    """4*D*(unmasked q,k pairs) per branch, summed over heads; selected pairs from the index tensor."""
+    T, D, H = a.seq_len, a.head_dim, a.heads
+    l, d, W = a.cmp_block, a.cmp_stride, a.window
+    t = torch.arange(T, dtype=torch.int64)
+    n_c = (T - l) // d + 1 if d != l else -(-T // l)
+    vis = torch.clamp((t - (l - 1)) // d + 1, min=0, max=n_c)
+    vis = torch.where(t - (l - 1) >= 0, vis, torch.zeros_like(vis))
+    cmp_pairs = int(vis.sum()) * H
+    sld_pairs = int(torch.clamp(t + 1, max=W).sum()) * H
+    nq = idx.shape[2]
+    qb = torch.arange(nq, device=idx.device).view(1, 1, nq, 1)
+    full = (idx < qb) & (idx >= 0)
+    diag = idx == qb
+    sel_pairs = int(full.sum()) * 64 * 64 + int(diag.sum()) * (64 * 65 // 2)
+    if idx.shape[1] != H:
+        sel_pairs *= H // idx.shape[1]
+    f = lambda p: 4.0 * D * p
+    return {"compressed": f(cmp_pairs), "selected": f(sel_pairs), "sliding": f(sld_pairs),
+            "total": f(cmp_pairs + sel_pairs + sld_pairs)}
+
+
+def run_ours(a):
+    import nsa_from_scratch_b200 as nsa
+    from nsa_from_scratch_b200 import _lib as L, forward as F, ops
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path for --impl ours)"
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    cfg = nsa.NSAConfig(block_size_c=a.cmp_block, stride_c=a.cmp_stride, block_size_n=64, block_size_m=64,
+                        top_k=a.top_k, window_size=a.window, force_first=1, force_local=2,
+                        select_per_group=a.select == "group")
+    engine = {"auto": L.ENGINE_AUTO, "generic": L.ENGINE_GENERIC, "tcgen05": L.ENGINE_TCGEN05}[a.engine]
+    Qh, Kh, Vh, Gh = make_inputs(a, a.seed + rank)
+    Qh, Kh, Vh, Gh = (t.pin_memory() for t in (Qh, Kh, Vh, Gh))
+    Q, K, V, G = (t.cuda(non_blocking=True) for t in (Qh, Kh, Vh, Gh))
+    torch.cuda.synchronize()
+    T, D = a.seq_len, a.head_dim
+    scale = D ** -0.5
+
+    shared = a.select == "group"
+
+    def step():
+        idx = F._resolve_block_indices(Q, K, block_size_m=64, block_size_n=64, top_k=a.top_k, causal=True, scale=scale,
+                                       force_first=1, force_local=2, shared_per_group=shared)
+        return F._fused_forward(Q, K, V, cfg, scale, a.cmp_stride, G, idx, 1.0, 1.0, 1.0, engine=engine)
+    LAUNCHES_PER_STEP = 6   # pool Q means, pool K means, select, pool K, pool V, fused attention
+
+    for _ in range(a.warmup):
+        out = step()
+    barrier()
+
+    # ---- timed region: K steps, CUDA events, max over ranks -----------------------------
+    sampler = ClockSampler(local) if rank == 0 else None
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    barrier()
+    ev[0].record()
+    for _ in range(a.steps):
+        out = step()
+    ev[1].record()
+    barrier()
+    ms_total = ev[0].elapsed_time(ev[1])
+    clocks = sampler.stop() if sampler else None
+    if dist is not None:
+        t_ = torch.tensor([ms_total], device="cuda")
+        dist.all_reduce(t_, op=dist.ReduceOp.MAX)
+        ms_total = float(t_.item())
+    ms_step = ms_total / a.steps
+    value = world * T / (ms_step * 1e-3)
+
+    # ---- per-kernel timing of the dominant (fused attention) kernel ---------------------------------
+    idx = F._resolve_block_indices(Q, K, block_size_m=64, block_size_n=64, top_k=a.top_k, causal=True, scale=scale,
+                                   force_first=1, force_local=2, shared_per_group=shared)
+    flops = algorithmic_flops(a, idx)
+    stage_ms = {"pool_select": [], "fused_attention": []}
+    for _ in range(a.steps):
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record()
+        idx = F._resolve_block_indices(Q, K, block_size_m=64, block_size_n=64, top_k=a.top_k, causal=True, scale=scale,
+                                       force_first=1, force_local=2, shared_per_group=shared)
+        Kc = ops.pool_mean(K, a.cmp_block, a.cmp_stride)
+        Vc = ops.pool_mean(V, a.cmp_block, a.cmp_stride)
+        e[1].record()
+        ops.attention_fwd(Q, K, V, branches=7, fused=True, causal=True, scale=scale, Kc=Kc, Vc=Vc,
+                          cmp_block=a.cmp_block, cmp_stride=a.cmp_stride,
+                          cmp_offset=(Kc.shape[2] * a.cmp_block if a.cmp_stride == a.cmp_block else T) - T,
+                          idx=idx, bm=64, bn=64, window=a.window, gates=G, engine=engine)
+        e[2].record()
+        torch.cuda.synchronize()
+        stage_ms["pool_select"].append(e[0].elapsed_time(e[1]))
+        stage_ms["fused_attention"].append(e[1].elapsed_time(e[2]))
+    fused_ms = statistics.mean(stage_ms["fused_attention"])
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak = peaks.get("bf16_tflops_sustained")
+    peak_src = "measured (sustained cuBLAS bf16, MEASURED_PEAKS.json)"
+    if peak is None:
+        peak, peak_src = 1590.0, "fallback"
+    achieved = flops["total"] / (fused_ms * 1e-3) / 1e12
+    traffic = None
+    try:
+        traffic = json.load(open(os.path.join(ROOT, "profiles", "fused_attention_traffic.json"))).get("dram_bytes_per_launch")
+    except Exception:
+        pass
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "traffic": traffic, "peak_source": peak_src, "kernel": "fused three-branch attention",
+                "kernel_ms": fused_ms, "algorithmic_tflop": {k: v / 1e12 for k, v in flops.items()},
+                "frac_of_burst_peak": achieved / peaks["bf16_tflops"] if "bf16_tflops" in peaks else None,
+                "pool_select_ms": statistics.mean(stage_ms["pool_select"])}
+
+    # ---- end to end: pinned host buffers in, host buffer out, copies inside the timed region ------
+    e2e = None
+    if not a.no_e2e:
+        out_h = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+
+        def e2e_step():
+            q, k, v, g = (t.cuda(non_blocking=True) for t in (Qh, Kh, Vh, Gh))
+            o = nsa.nsa_forward(q, k, v, cfg, gate_logits=g)
+            out_h.copy_(o, non_blocking=True)
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n_e2e = max(2, min(a.steps, 5))
+        e0.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if dist is not None:
+            t_ = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t_, op=dist.ReduceOp.MAX)
+            ms = float(t_.item())
+        h2d = sum(t.numel() * t.element_size() for t in (Qh, Kh, Vh, Gh))
+        e2e = {"value": world * T / (ms / n_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": out_h.numel() * out_h.element_size(), "ms_per_step": ms / n_e2e}
+
+    cpu = None
+    if rank == 0 and world == 1 and not a.no_cpu_baseline:
+        v, dt, desc = cpu_sample(a, a.cpu_tiles)
+        cpu = {"value": v, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": desc,
+               "seconds": dt}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": workload_name(a), "global_batch": world, "seq_len": T,
+                       "parallelism": f"batch x kv-head partition, {world} rank(s), no collective",
+                       "l2": "inputs (Q alone 1 GiB at the default size) exceed the 126 MB L2", "engine": a.engine},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
+            "gpu_launches": LAUNCHES_PER_STEP * a.steps,
+        }
+        ops.device_status()
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    a = parse()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)
+
+
+if __name__ == "__main__":
+    main()

@@ -73,10 +73,14 @@ int nsa_pool_mean(const void* x, void* out, int B, int H, int T, int D, int bloc
  * score = fp32 dot over D (fma in index order) * scale; block c is legal for q block q iff
  * !causal or c*bn <= q*bm + bm-1 + offset.  force_first / force_local give score +inf to
  * the first blocks and to the last legal blocks of each row (0/0 = the reference).
+ * shared_per_group != 0: one index row per KV head, idx [B,Hkv,nq,k_out]; its score is the
+ * sum, in head order, of the per-head scores of the H/Hkv query heads that share the KV head
+ * (0 = the reference: one row per query head).
  * Replaces: _resolve_block_indices, nsa/triton/forward.py:321-359 (einsum + mask + topk). */
 int nsa_select_blocks(const void* Qb, const void* Kb, int32_t* idx, int B, int H, int Hkv, int nq,
                       int nk, int D, int top_k, int bm, int bn, int offset, int causal, float scale,
-                      int force_first, int force_local, int dtype, nsa_stream_t stream);
+                      int force_first, int force_local, int shared_per_group, int dtype,
+                      nsa_stream_t stream);
 
 /* Top-k over caller-supplied fp32 scores [BH,nq,nk] with the same legality rule and order.
  * Replaces: _topk_indices_from_scores, nsa/triton/selected.py:153-185. */
@@ -120,6 +124,11 @@ typedef struct nsa_fwd_args {
  * (nsa/triton/fp8.py:43-75) and, with fused=1, the branch launches plus combine of
  * nsa_forward (nsa/triton/forward.py:362-406). */
 int nsa_attention_fwd(const nsa_fwd_args* args, nsa_stream_t stream);
+
+/* Synchronises `stream`, then reports whether any kernel launched so far gave up on one of
+ * its bounded device-side waits: NSA_OK, or NSA_ERR_DEVICE (and the condition is cleared).
+ * No counterpart in the reference (its kernels have no device-side waits). */
+int nsa_device_status(nsa_stream_t stream);
 
 /* The reference's native launcher, same argument list (bf16, Hkv == H folded into BH,
  * 64x64 blocks, pre-padded lengths, D in {32,64,128}); returns a status instead of void.

@@ -71,9 +71,10 @@ PROTOTYPES = {
     "nsa_last_error": (C.c_char_p, []),
     "nsa_abi_version": (_i, []),
     "nsa_pool_mean": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp]),
-    "nsa_select_blocks": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp]),
+    "nsa_select_blocks": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp]),
     "nsa_topk_from_scores": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "nsa_attention_fwd": (_i, [C.POINTER(FwdArgs), _vp]),
+    "nsa_device_status": (_i, [_vp]),
     "launch_selected_attn_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "nsa_bwd_delta": (_i, [_vp, _vp, _vp, _i64, _i, _i, _vp]),
     "nsa_selected_bwd": (_i, [C.POINTER(BwdArgs), _vp]),

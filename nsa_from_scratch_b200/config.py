@@ -23,3 +23,5 @@ class NSAConfig:
     stride_c: Optional[int] = None   # compression stride < block_size_c: overlapping windows
     force_first: int = 0             # always select the first n blocks
     force_local: int = 0             # always select the last n causally legal blocks
+    select_per_group: bool = False   # one block list per KV head (shared by its query heads), scored by
+                                     # the sum of the heads' scores; False = one list per query head

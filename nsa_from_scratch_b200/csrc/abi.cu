@@ -19,11 +19,12 @@ int fail(int code, const char* fmt, ...) {
 // kernels (other translation units)
 int pool_mean(const void*, void*, int, int, int, int, int, int, int, int, float, cudaStream_t);
 int select_blocks(const void*, const void*, int32_t*, int, int, int, int, int, int, int, int, int, int, int, float, int,
-                  int, int, cudaStream_t);
+                  int, int, int, cudaStream_t);
 int topk_from_scores(const float*, int32_t*, int, int, int, int, int, int, int, int, cudaStream_t);
 int attention_fwd_generic(const nsa_fwd_args&, cudaStream_t);
 int attention_fwd_tc5(const nsa_fwd_args&, cudaStream_t);
 bool attention_fwd_tc5_supports(const nsa_fwd_args&);
+int tc5_take_status(cudaStream_t, int*);
 int selected_bwd(const nsa_bwd_args&, cudaStream_t);
 int combine(const void*, const void*, const void*, const void*, void*, long long, int, int, int, int, cudaStream_t);
 int fp8_absmax(const void*, long long, int, float*, cudaStream_t);
@@ -85,10 +86,10 @@ int nsa_pool_mean(const void* x, void* out, int B, int H, int T, int D, int bloc
 
 int nsa_select_blocks(const void* Qb, const void* Kb, int32_t* idx, int B, int H, int Hkv, int nq, int nk, int D,
                       int top_k, int bm, int bn, int offset, int causal, float scale, int force_first, int force_local,
-                      int dtype, nsa_stream_t stream) {
+                      int shared_per_group, int dtype, nsa_stream_t stream) {
   NSA_REQUIRE(Qb && Kb && idx, NSA_ERR_ARG, "select: NULL pointer");
   return select_blocks(Qb, Kb, idx, B, H, Hkv, nq, nk, D, top_k, bm, bn, offset, causal, scale, force_first,
-                       force_local, dtype, (cudaStream_t)stream);
+                       force_local, shared_per_group, dtype, (cudaStream_t)stream);
 }
 
 int nsa_topk_from_scores(const float* scores, int32_t* idx, int BH, int nq, int nk, int top_k, int bm, int bn,
@@ -108,6 +109,14 @@ int nsa_attention_fwd(const nsa_fwd_args* args, nsa_stream_t stream) {
   }
   if (args->engine == NSA_ENGINE_AUTO && tc5) return attention_fwd_tc5(*args, (cudaStream_t)stream);
   return attention_fwd_generic(*args, (cudaStream_t)stream);
+}
+
+int nsa_device_status(nsa_stream_t stream) {
+  int v = 0;
+  int rc = tc5_take_status((cudaStream_t)stream, &v);
+  if (rc != NSA_OK) return rc;
+  if (v != 0) return fail(NSA_ERR_DEVICE, "a kernel gave up waiting on barrier %d (bounded wait expired)", v - 1);
+  return NSA_OK;
 }
 
 int launch_selected_attn_fwd(const void* Q, const void* K, const void* V, const int* Idx, void* Out, float* Lse, int BH,

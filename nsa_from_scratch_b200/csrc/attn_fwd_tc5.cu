@@ -1,13 +1,542 @@
-// tcgen05 / TMEM / TMA attention forward (performance path).  Placeholder until the kernel lands:
-// reports that no shape is supported so that every call takes the generic kernel.
+// NSA attention forward on the 5th-generation tensor cores (tcgen05 + TMEM + TMA), sm_100a.
+//
+// Work item = (batch, KV head, 4 query heads of its group, one 64-position query block):
+// 256 rows = two 128-row MMA tiles (tile X holds heads 2X and 2X+1 of the quad, 64 positions each).
+// All rows of a work item see the same KV tiles in every branch (the selected blocks are
+// shared by the heads of a GQA group), so a K/V tile staged once by TMA feeds both tiles.
+//
+// Warp roles (12 warps, one block per SM):
+//   warp 0      TMA producer: Q once, then K and V tiles (1 or 2 chunks of 64 keys) into two
+//               2-deep rings of 128-byte-swizzled shared memory; pooled K/V for the compressed
+//               branch, raw K/V for the selected and sliding branches
+//   warp 1      MMA issuer (one thread): S_X = Q_X K^T into TMEM, then O_X (+)= P_X V with P read
+//               from TMEM (it aliases S_X) and V as an MN-major shared-memory operand
+//   warps 4-7   softmax of tile 0, warps 8-11 softmax of tile 1 (one thread per row): read S from
+//               TMEM, mask, running max with lazy rescale of O (only when the max grows by > 2^8),
+//               exp2, row sum, P as 16-bit back into TMEM; at the end of a branch they read O,
+//               apply gate/l and keep the gated sum of the branches in registers
+// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D).
+// Tile X's chain QK -> softmax -> PV is serial; the tensor pipe stays busy because the other
+// tile's MMAs run in the gaps.  Every mbarrier wait is bounded; a wait that gives up raises a
+// block-wide abort flag, sets the device status word and the block still frees its TMEM.
 #include "common.cuh"
+#include "tc5_ptx.cuh"
+
+#include <cudaTypedefs.h>
 
 namespace nsa {
 
-bool attention_fwd_tc5_supports(const nsa_fwd_args&) { return false; }
+using namespace tc5;
 
-int attention_fwd_tc5(const nsa_fwd_args&, cudaStream_t) {
-  return fail(NSA_ERR_UNSUPPORTED, "attention forward: tcgen05 kernel not built");
+constexpr int T5_MAX_SEL = 64;
+constexpr int T5_THREADS = 384;
+
+__device__ int g_tc5_status;   // 0 ok; otherwise (1 + id of the barrier a wait gave up on)
+
+struct Tc5Params {
+  CUtensorMap tmQ, tmK, tmV, tmKc, tmVc;
+  nsa_fwd_args a;
+  float scale_log2;
+  int nk_blocks;
+  int G4;          // query-head quads per KV head
+};
+
+struct Tile {
+  int nch;
+  int j0[2];
+  int jlim[2];
+};
+
+// barrier ids
+enum { B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 3, B_VFULL = 5, B_VEMPTY = 7, B_SFULL = 9, B_PFULL = 11, B_PVDONE = 13, B_COUNT = 15 };
+
+template <int D, int FMT>
+__global__ void __launch_bounds__(T5_THREADS, 1) nsa_fwd_tc5_kernel(const __grid_constant__ Tc5Params p) {
+  using T = typename std::conditional<FMT == 1, __nv_bfloat16, __half>::type;
+  constexpr int DH = D / 64;                    // 64-element (128-byte) halves of a row
+  constexpr int QTILE = DH * 128 * 128;         // bytes of one 128-row Q tile
+  constexpr int KVTILE = DH * 128 * 128;        // bytes of one 128-key K or V tile
+  constexpr int DHSTRIDE = 128 * 128;           // bytes between the halves
+  const nsa_fwd_args& a = p.a;
+
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sQ = smem_u32(smem);
+  const uint32_t sK = sQ + 2 * QTILE;
+  const uint32_t sV = sK + 2 * KVTILE;
+  __shared__ __align__(8) uint64_t bars[B_COUNT];
+  __shared__ int sel_list[T5_MAX_SEL];
+  __shared__ int sel_n;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  // ---- work item -------------------------------------------------------------------
+  const int per_q = a.B * a.Hkv * p.G4;
+  const int qb = a.nq - 1 - (int)(blockIdx.x / per_q);   // long rows first
+  const int rem = (int)(blockIdx.x % per_q);
+  const int b = rem / (a.Hkv * p.G4);
+  const int hk = (rem / p.G4) % a.Hkv;
+  const int g4 = rem % p.G4;
+  const int G = a.H / a.Hkv;
+  const int h_base = hk * G + g4 * 4;
+  const int q0 = qb * 64;
+  const int i_last = min(q0 + 64, a.Tq) - 1;
+  const int kv_slab = b * a.Hkv + hk;
+
+  auto bar = [&](int id) { return smem_u32(&bars[id]); };
+
+  // ---- per-branch key bounds of a query row -------------------------------------------
+  auto bounds = [&](int br, int i, bool ok, int& lo, int& hi) {
+    lo = 0; hi = -1;
+    if (!ok) return;
+    if (br == 0) {
+      if (a.causal) {
+        int num = i + a.cmp_offset - (a.cmp_block - 1);
+        hi = num < 0 ? -1 : num / a.cmp_stride;
+      } else hi = a.Nc - 1;
+      hi = min(hi, a.Nc - 1);
+    } else if (br == 1) {
+      hi = a.causal ? min(i + a.offset, a.sel_key_limit - 1) : a.sel_key_limit - 1;
+    } else {
+      int pos = i + a.offset;
+      if (a.causal) { lo = pos - a.window + 1; hi = pos; }
+      else { lo = pos - a.window; hi = pos + a.window; }
+      lo = max(lo, 0); hi = min(hi, a.Tk - 1);
+    }
+  };
+
+  // ---- setup: barriers, TMEM, list of selected blocks ---------------------------------------
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int i = 0; i < B_COUNT; ++i) mbar_init(bar(i), (i == B_PFULL || i == B_PFULL + 1) ? 128 : 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(&tmem_base_s), 512); tmem_relinquish(); }
+  if (warp == 2) {
+    int n = 0;
+    if (a.branches & NSA_BRANCH_SELECTED) {
+      const int hi_ = (a.Hi == a.H) ? h_base : hk;
+      const int32_t* row = a.idx + (((size_t)b * a.Hi + hi_) * a.nq + qb) * a.top_k;
+      const int last_pos = i_last + a.offset;
+      for (int s0 = 0; s0 < a.top_k; s0 += 32) {
+        int s = s0 + lane;
+        int blk = s < a.top_k ? row[s] : -1;
+        bool ok = blk >= 0 && blk < p.nk_blocks && (!a.causal || (long long)blk * 64 <= last_pos);
+        unsigned m = __ballot_sync(0xffffffffu, ok);
+        if (ok) sel_list[n + __popc(m & ((1u << lane) - 1))] = blk;
+        n += __popc(m);
+      }
+    }
+    if (lane == 0) sel_n = n;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+
+  // chunk counts of the three branches (uniform over the block)
+  int nchunks[3] = {0, 0, 0};
+  int sld_c0 = 0;
+  {
+    int lo_f, hi_f, lo_l, hi_l;
+    if (a.branches & NSA_BRANCH_COMPRESSED) {
+      bounds(0, i_last, true, lo_l, hi_l);
+      nchunks[0] = hi_l < 0 ? 0 : hi_l / 64 + 1;
+    }
+    if (a.branches & NSA_BRANCH_SELECTED) nchunks[1] = sel_n;
+    if (a.branches & NSA_BRANCH_SLIDING) {
+      bounds(2, q0, true, lo_f, hi_f);
+      bounds(2, i_last, true, lo_l, hi_l);
+      if (hi_l >= lo_f) { sld_c0 = lo_f / 64; nchunks[2] = hi_l / 64 - sld_c0 + 1; }
+    }
+  }
+  auto get_tile = [&](int br, int t) {
+    Tile tl;
+    tl.nch = min(2, nchunks[br] - 2 * t);
+    for (int c = 0; c < 2; ++c) {
+      int ci = min(2 * t + c, nchunks[br] - 1);
+      if (br == 0) { tl.j0[c] = ci * 64; tl.jlim[c] = a.Nc; }
+      else if (br == 1) { int blk = sel_list[ci]; tl.j0[c] = blk * 64; tl.jlim[c] = min(blk * 64 + 64, a.sel_key_limit); }
+      else { tl.j0[c] = (sld_c0 + ci) * 64; tl.jlim[c] = a.Tk; }
+    }
+    return tl;
+  };
+  int fail_id = 0;   // barrier id (+1) this thread gave up on
+  int last_k_it = -1, last_v_it = -1;   // producer: last tile whose K / V copies were issued
+
+  if (warp == 0) {
+    // =============================== TMA producer ===============================
+    if (lane == 0) {
+      tma_prefetch_desc(&p.tmQ); tma_prefetch_desc(&p.tmK); tma_prefetch_desc(&p.tmV);
+      if (a.branches & NSA_BRANCH_COMPRESSED) { tma_prefetch_desc(&p.tmKc); tma_prefetch_desc(&p.tmVc); }
+      mbar_expect_tx(bar(B_QFULL), 2 * QTILE);
+      for (int X = 0; X < 2; ++X)
+        for (int hh = 0; hh < 2; ++hh)
+          for (int dh = 0; dh < DH; ++dh)
+            tma_load_3d(sQ + X * QTILE + dh * DHSTRIDE + hh * 8192, &p.tmQ, bar(B_QFULL), dh * 64, q0,
+                        b * a.H + h_base + 2 * X + hh);
+      int it = 0;
+      bool ok = true;
+      for (int br = 0; br < 3 && ok; ++br) {
+        const int nt = (nchunks[br] + 1) >> 1;
+        const CUtensorMap* mk = br == 0 ? &p.tmKc : &p.tmK;
+        const CUtensorMap* mv = br == 0 ? &p.tmVc : &p.tmV;
+        for (int t = 0; t < nt && ok; ++t, ++it) {
+          const Tile tl = get_tile(br, t);
+          const int s = it & 1, ph = (it >> 1) & 1;
+          const uint32_t bytes = (uint32_t)tl.nch * 64 * D * 2;
+          ok = mbar_wait(bar(B_KEMPTY + s), ph ^ 1, &abort_flag);
+          if (!ok) { fail_id = B_KEMPTY + s + 1; break; }
+          mbar_expect_tx(bar(B_KFULL + s), bytes);
+          for (int c = 0; c < tl.nch; ++c)
+            for (int dh = 0; dh < DH; ++dh)
+              tma_load_3d(sK + s * KVTILE + dh * DHSTRIDE + c * 8192, mk, bar(B_KFULL + s), dh * 64, tl.j0[c], kv_slab);
+          last_k_it = it;
+          ok = mbar_wait(bar(B_VEMPTY + s), ph ^ 1, &abort_flag);
+          if (!ok) { fail_id = B_VEMPTY + s + 1; break; }
+          mbar_expect_tx(bar(B_VFULL + s), bytes);
+          for (int c = 0; c < tl.nch; ++c)
+            for (int dh = 0; dh < DH; ++dh)
+              tma_load_3d(sV + s * KVTILE + dh * DHSTRIDE + c * 8192, mv, bar(B_VFULL + s), dh * 64, tl.j0[c], kv_slab);
+          last_v_it = it;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // =============================== MMA issuer ===============================
+    if (lane == 0) {
+      constexpr uint32_t IDESC_PV = idesc_f16(FMT, 128, D, 0, 1);
+      bool ok = mbar_wait(bar(B_QFULL), 0, &abort_flag);
+      if (!ok) fail_id = B_QFULL + 1;
+      // flattened tile sequence over the branches
+      int br_of[3], nt_of[3], nbr = 0, total_tiles = 0;
+      for (int br = 0; br < 3; ++br) {
+        int nt = (nchunks[br] + 1) >> 1;
+        if (nt > 0) { br_of[nbr] = br; nt_of[nbr] = nt; ++nbr; total_tiles += nt; }
+      }
+      auto locate = [&](int it, int& br, int& t) {
+        int k = 0;
+        while (it >= nt_of[k]) { it -= nt_of[k]; ++k; }
+        br = br_of[k]; t = it;
+      };
+      auto issue_qk = [&](int X, int it) {
+        int br, t;
+        locate(it, br, t);
+        const Tile tl = get_tile(br, t);
+        const int s = it & 1, ph = (it >> 1) & 1;
+        if (X == 0) {
+          if (!mbar_wait(bar(B_KFULL + s), ph, &abort_flag)) { fail_id = B_KFULL + s + 1; return false; }
+          tc_fence_after();
+        }
+        const uint32_t idesc = idesc_f16(FMT, 128, 64 * tl.nch, 0, 0);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * DHSTRIDE + (ks & 3) * 32;
+          mma_ss(tmem + X * 128, smem_desc_sw128(sQ + X * QTILE + off, 16, 1024),
+                 smem_desc_sw128(sK + s * KVTILE + off, 16, 1024), idesc, ks > 0);
+        }
+        tc_commit(bar(B_SFULL + X));
+        if (X == 1) tc_commit(bar(B_KEMPTY + s));
+        return true;
+      };
+      if (ok && total_tiles > 0) ok = issue_qk(0, 0) && issue_qk(1, 0);
+      for (int it = 0; it < total_tiles && ok; ++it) {
+        int br, t;
+        locate(it, br, t);
+        const Tile tl = get_tile(br, t);
+        const int s = it & 1, ph = (it >> 1) & 1;
+        ok = mbar_wait(bar(B_VFULL + s), ph, &abort_flag);
+        if (!ok) { fail_id = B_VFULL + s + 1; break; }
+        for (int X = 0; X < 2 && ok; ++X) {
+          ok = mbar_wait(bar(B_PFULL + X), it & 1, &abort_flag);
+          if (!ok) { fail_id = B_PFULL + X + 1; break; }
+          tc_fence_after();
+          for (int kk = 0; kk < 4 * tl.nch; ++kk)
+            mma_ts(tmem + 256 + X * 128, tmem + X * 128 + kk * 8,
+                   smem_desc_sw128(sV + s * KVTILE + kk * 2048, DHSTRIDE, 1024), IDESC_PV, (t > 0 || kk > 0) ? 1u : 0u);
+          tc_commit(bar(B_PVDONE + X));
+          if (X == 1) tc_commit(bar(B_VEMPTY + s));
+          if (it + 1 < total_tiles) ok = issue_qk(X, it + 1);
+        }
+      }
+    }
+  } else if (warp >= 4) {
+    // =============================== softmax / epilogue ===============================
+    const int X = (warp - 4) >> 2;
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;                       // row of the tile == TMEM lane
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tS = tmem + lane_addr + X * 128;
+    const uint32_t tO = tmem + lane_addr + 256 + X * 128;
+    const int head = h_base + 2 * X + (r >> 6);
+    const int qi = q0 + (r & 63);
+    const bool row_ok = qi < a.Tq;
+    const size_t row_index = ((size_t)b * a.H + head) * a.Tq + qi;
+
+    float gate[3] = {0.5f, 0.5f, 0.5f};
+    if (a.fused) {
+      float x[3] = {0.f, 0.f, 0.f};
+      if (a.gates != nullptr && row_ok) {
+#pragma unroll
+        for (int c = 0; c < 3; ++c) {
+          const size_t gi = row_index * 3 + c;
+          x[c] = a.gate_dtype == NSA_FP32 ? reinterpret_cast<const float*>(a.gates)[gi]
+               : a.gate_dtype == NSA_FP16 ? __half2float(reinterpret_cast<const __half*>(a.gates)[gi])
+                                          : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.gates)[gi]);
+        }
+      }
+      if (a.gate_act == NSA_GATE_SOFTMAX) {
+        float mx = fmaxf(x[0], fmaxf(x[1], x[2]));
+        float e0 = __expf(x[0] - mx), e1 = __expf(x[1] - mx), e2 = __expf(x[2] - mx);
+        float inv = 1.f / (e0 + e1 + e2);
+        gate[0] = e0 * inv; gate[1] = e1 * inv; gate[2] = e2 * inv;
+      } else {
+#pragma unroll
+        for (int c = 0; c < 3; ++c) gate[c] = 1.f / (1.f + __expf(-x[c]));
+      }
+    }
+
+    // gated sum of the finished branches, kept as packed 16-bit pairs (D/2 registers); the last
+    // branch is added in fp32 straight into the output row
+    uint32_t total[D / 2];
+#pragma unroll
+    for (int d = 0; d < D / 2; ++d) total[d] = 0u;
+    float lse_out = -INFINITY;
+    int last_br = -1;
+#pragma unroll
+    for (int br = 0; br < 3; ++br) if (nchunks[br] > 0) last_br = br;
+    T* orow = reinterpret_cast<T*>(a.out) + row_index * D;
+
+    int it = 0;
+    bool ok = true;
+#pragma unroll 1
+    for (int br = 0; br < 3 && ok; ++br) {
+      const int nt = (nchunks[br] + 1) >> 1;
+      if (nt == 0) continue;
+      int lo, hi;
+      bounds(br, qi, row_ok, lo, hi);
+      float m_used = -INFINITY, l = 0.f;
+#pragma unroll 1
+      for (int t = 0; t < nt && ok; ++t, ++it) {
+        const Tile tl = get_tile(br, t);
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(B_SFULL + X), it & 1, &abort_flag));
+        if (!ok) { fail_id = B_SFULL + X + 1; break; }
+        tc_fence_after();
+        // valid column range of each chunk for this row
+        int vlo[2], vhi[2];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          vlo[c] = max(lo - tl.j0[c], 0);
+          vhi[c] = min(hi, tl.jlim[c] - 1) - tl.j0[c];
+          if (c >= tl.nch) vhi[c] = -1;
+        }
+        // pass 1: row maximum
+        float mx = -INFINITY;
+        for (int g = 0; g < 2 * tl.nch; ++g) {
+          uint32_t v[32];
+          tmem_ld32(tS + g * 32, v);
+          tc_wait_ld();
+          const int c = g >> 1, base = (g & 1) * 32;
+          if (vlo[c] <= base && vhi[c] >= base + 31) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (base + i >= vlo[c] && base + i <= vhi[c]) mx = fmaxf(mx, __uint_as_float(v[i]));
+          }
+        }
+        mx *= p.scale_log2;                                  // scale > 0 keeps the order
+        // lazy rescale: only when some row of the warp outgrows its reference maximum by 2^8
+        const bool grow = mx > m_used + 8.f;
+        if (__any_sync(0xffffffffu, grow)) {
+          const float m_new = fmaxf(m_used, mx);
+          const float alpha = m_new == -INFINITY ? 1.f : ex2(m_used - m_new);
+          if (t > 0) {
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(B_PVDONE + X), (it - 1) & 1, &abort_flag));
+            if (!ok) { fail_id = B_PVDONE + X + 1; break; }
+            tc_fence_after();
+            for (int g = 0; g < D / 32; ++g) {
+              uint32_t v[32];
+              tmem_ld32(tO + g * 32, v);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+              tmem_st32(tO + g * 32, v);
+            }
+            tc_wait_st();
+          }
+          l *= alpha;
+          m_used = m_new;
+        }
+        const float m_ref = m_used == -INFINITY ? 0.f : m_used;
+        // pass 2: P = exp2(S*scale - m_ref) as 16-bit into the columns S occupied
+        float psum = 0.f;
+        for (int g = 0; g < 2 * tl.nch; ++g) {
+          uint32_t v[32];
+          tmem_ld32(tS + g * 32, v);
+          tc_wait_ld();
+          const int c = g >> 1, base = (g & 1) * 32;
+          const bool full = vlo[c] <= base && vhi[c] >= base + 31;
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float p0 = ex2(__uint_as_float(v[2 * i]) * p.scale_log2 - m_ref);
+            float p1 = ex2(__uint_as_float(v[2 * i + 1]) * p.scale_log2 - m_ref);
+            if (!full) {
+              if (base + 2 * i < vlo[c] || base + 2 * i > vhi[c]) p0 = 0.f;
+              if (base + 2 * i + 1 < vlo[c] || base + 2 * i + 1 > vhi[c]) p1 = 0.f;
+            }
+            psum += p0 + p1;
+            pk[i] = Elem<T>::pack(p0, p1);
+          }
+          tmem_st16(tS + g * 16, pk);
+        }
+        l += psum;
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar(B_PFULL + X));
+      }
+      if (!ok) break;
+      // ---- end of the branch: O is complete once the last PV has landed ---------------------------
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(B_PVDONE + X), (it - 1) & 1, &abort_flag));
+      if (!ok) { fail_id = B_PVDONE + X + 1; break; }
+      tc_fence_after();
+      const bool has = l > 0.f;
+      const float coef = has ? (a.fused ? gate[br] : 1.f) / l : 0.f;
+      if (!a.fused) lse_out = has ? m_used * kLn2 + __logf(l) : -INFINITY;
+#pragma unroll
+      for (int g = 0; g < D / 32; ++g) {
+        uint32_t v[32];
+        tmem_ld32(tO + g * 32, v);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float2 acc = Elem<T>::unpack(total[g * 16 + i]);
+          total[g * 16 + i] = Elem<T>::pack(acc.x + __uint_as_float(v[2 * i]) * coef, acc.y + __uint_as_float(v[2 * i + 1]) * coef);
+        }
+        if (br == last_br && row_ok) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            reinterpret_cast<uint4*>(orow)[g * 4 + c] =
+                make_uint4(total[g * 16 + 4 * c], total[g * 16 + 4 * c + 1], total[g * 16 + 4 * c + 2], total[g * 16 + 4 * c + 3]);
+        }
+      }
+      tc_fence_before();
+    }
+    if (ok && row_ok) {
+      if (last_br < 0) {                      // no branch had a visible key: the row is zero
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(orow)[c] = make_uint4(0u, 0u, 0u, 0u);
+      }
+      if (!a.fused && a.lse != nullptr) a.lse[row_index] = lse_out;
+    }
+  }
+
+  // ---- teardown (every path reaches it) -------------------------------------------------------
+  if (fail_id != 0) atomicCAS(&g_tc5_status, 0, fail_id);
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag && warp == 0 && lane == 0) {
+    // let copies already in flight land (bounded) before the block's shared memory is handed back
+    for (int i = 0; i < 20000 && !mbar_try_wait(bar(B_QFULL), 0); ++i) __nanosleep(100);
+    if (last_k_it >= 0)
+      for (int i = 0; i < 20000 && !mbar_try_wait(bar(B_KFULL + (last_k_it & 1)), (last_k_it >> 1) & 1); ++i) __nanosleep(100);
+    if (last_v_it >= 0)
+      for (int i = 0; i < 20000 && !mbar_try_wait(bar(B_VFULL + (last_v_it & 1)), (last_v_it >> 1) & 1); ++i) __nanosleep(100);
+  }
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
+// ---------------------------------------------------------------- host side
+static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (!fn) {
+    cudaDriverEntryPointQueryResult q;
+    void* ptr = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+  }
+  return fn;
+}
+
+// [slabs][rows][D] 16-bit tensor, boxes of 64 rows x 64 elements, 128-byte swizzle, zero fill outside
+static int make_map(CUtensorMap* m, const void* ptr, long long slabs, long long rows, int D, int dtype) {
+  auto enc = encode_fn();
+  NSA_REQUIRE(enc != nullptr, NSA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  NSA_REQUIRE((reinterpret_cast<uintptr_t>(ptr) & 15) == 0, NSA_ERR_ARG, "tensor base %p is not 16-byte aligned", ptr);
+  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)rows, (cuuint64_t)slabs};
+  cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)rows * D * 2};
+  cuuint32_t box[3] = {64, 64, 1};
+  cuuint32_t es[3] = {1, 1, 1};
+  CUresult r = enc(m, dtype == NSA_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                   const_cast<void*>(ptr), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  NSA_REQUIRE(r == CUDA_SUCCESS, NSA_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  return NSA_OK;
+}
+
+bool attention_fwd_tc5_supports(const nsa_fwd_args& a) {
+  if (!(a.q_dtype == NSA_BF16 || a.q_dtype == NSA_FP16) || a.kv_dtype != a.q_dtype) return false;
+  if (!(a.D == 64 || a.D == 128)) return false;
+  if (!(a.scale > 0.f)) return false;
+  const int G = a.H / a.Hkv;
+  if (G % 4 != 0) return false;
+  if (a.branches & NSA_BRANCH_SELECTED) {
+    if (a.bm != 64 || a.bn != 64 || a.Hi != a.Hkv || a.top_k > T5_MAX_SEL) return false;
+  }
+  if ((a.branches & NSA_BRANCH_COMPRESSED) && a.Nc <= 0) return false;
+  return true;
+}
+
+int attention_fwd_tc5(const nsa_fwd_args& a, cudaStream_t st) {
+  Tc5Params p;
+  p.a = a;
+  if (!(a.branches & NSA_BRANCH_SELECTED)) p.a.nq = (a.Tq + 63) / 64;
+  p.scale_log2 = a.scale * kLog2e;
+  p.nk_blocks = (a.sel_key_limit + 63) / 64;
+  p.G4 = (a.H / a.Hkv) / 4;
+  int rc;
+  if ((rc = make_map(&p.tmQ, a.Q, (long long)a.B * a.H, a.Tq, a.D, a.q_dtype)) != NSA_OK) return rc;
+  if ((rc = make_map(&p.tmK, a.K, (long long)a.B * a.Hkv, a.Tk, a.D, a.q_dtype)) != NSA_OK) return rc;
+  if ((rc = make_map(&p.tmV, a.V, (long long)a.B * a.Hkv, a.Tk, a.D, a.q_dtype)) != NSA_OK) return rc;
+  if (a.branches & NSA_BRANCH_COMPRESSED) {
+    if ((rc = make_map(&p.tmKc, a.Kc, (long long)a.B * a.Hkv, a.Nc, a.D, a.q_dtype)) != NSA_OK) return rc;
+    if ((rc = make_map(&p.tmVc, a.Vc, (long long)a.B * a.Hkv, a.Nc, a.D, a.q_dtype)) != NSA_OK) return rc;
+  } else {
+    p.tmKc = p.tmK;
+    p.tmVc = p.tmV;
+  }
+  const long long blocks = (long long)p.a.nq * a.B * a.Hkv * p.G4;
+  NSA_REQUIRE(blocks > 0 && blocks < 2147483647LL, NSA_ERR_ARG, "attention forward: %lld work items do not fit a grid", blocks);
+  const size_t smem = (size_t)(2 + 2 + 2) * (a.D / 64) * 128 * 128 + 1024;
+#define NSA_TC5_LAUNCH(DD, FF)                                                                              \
+  {                                                                                                         \
+    auto fn = nsa_fwd_tc5_kernel<DD, FF>;                                                                   \
+    NSA_CUDA_OK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));         \
+    fn<<<(unsigned)blocks, T5_THREADS, smem, st>>>(p);                                                     \
+  }
+  const int fmt = a.q_dtype == NSA_BF16 ? 1 : 0;
+  if (a.D == 128 && fmt == 1) NSA_TC5_LAUNCH(128, 1)
+  else if (a.D == 128) NSA_TC5_LAUNCH(128, 0)
+  else if (fmt == 1) NSA_TC5_LAUNCH(64, 1)
+  else NSA_TC5_LAUNCH(64, 0)
+#undef NSA_TC5_LAUNCH
+  return launch_status("attn_fwd_tc5");
+}
+
+// Synchronises `st`, returns and clears the status word the tcgen05 kernels set when a bounded wait gave up.
+int tc5_take_status(cudaStream_t st, int* status) {
+  NSA_CUDA_OK(cudaStreamSynchronize(st));
+  int v = 0, zero = 0;
+  NSA_CUDA_OK(cudaMemcpyFromSymbol(&v, g_tc5_status, sizeof(int)));
+  if (v != 0) NSA_CUDA_OK(cudaMemcpyToSymbol(g_tc5_status, &zero, sizeof(int)));
+  *status = v;
+  return NSA_OK;
 }
 
 }  // namespace nsa

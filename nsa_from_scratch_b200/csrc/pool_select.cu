@@ -100,27 +100,35 @@ __device__ void warp_topk_row(float* s, int n_scan, int nk, int k_out, int32_t* 
 }
 
 // ------------------------------------------------------------------ score + select
-// Thread block = (batch, query head, chunk of R query blocks); warp w owns query block row w.
+// Thread block = (batch, index head, chunk of R query blocks); warp w owns query block row w.
+// An index head is a query head (GS = 1) or, for indices shared by a GQA group, a KV head whose
+// score is the sum over its GS = H/Hkv query heads (per-head dots added in head order).
 // Kb tiles of 64 block-means are staged in shared memory once per chunk and shared by the rows.
 template <typename T, int D>
 __global__ void __launch_bounds__(256) select_blocks_kernel(const T* __restrict__ Qb, const T* __restrict__ Kb,
-                                                            int32_t* __restrict__ idx, int H, int Hkv, int nq, int nk,
+                                                            int32_t* __restrict__ idx, int H, int Hkv, int Hi, int nq, int nk,
                                                             int k_out, int bm, int bn, int offset, int causal, float scale,
                                                             int force_first, int force_local, int R) {
   constexpr int KT = 64;
   constexpr int PITCH = D + 2;     // 16-bit elements; odd word stride -> conflict-free row reads
   extern __shared__ __align__(16) unsigned char smem[];
   T* kt = reinterpret_cast<T*>(smem);                              // [KT][PITCH]
-  T* qs = kt + KT * PITCH;                                         // [R][D]
-  float* sc = reinterpret_cast<float*>(qs + R * D + ((R * D) & 1)); // [R][nk]
+  const int G = H / Hkv;
+  const int GS = Hi == H ? 1 : G;                                  // query heads summed per index head
+  T* qs = kt + KT * PITCH;                                         // [R][GS][D]
+  float* sc = reinterpret_cast<float*>(qs + R * GS * D);           // [R][nk]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int bh = blockIdx.y, b = bh / H, h = bh % H, hk = h / (H / Hkv);
+  const int bh = blockIdx.y, b = bh / Hi, hi = bh % Hi;
+  const int hk = Hi == H ? hi / G : hi;
+  const int h0 = Hi == H ? hi : hi * G;                            // first query head of this index head
   const int qb0 = blockIdx.x * R;
   const int rows = min(R, nq - qb0);
   const T* kbase = Kb + ((size_t)(b * Hkv + hk) * nk) * D;
 
-  for (int i = threadIdx.x; i < rows * D; i += blockDim.x)
-    qs[i] = Qb[((size_t)bh * nq + qb0) * D + i];
+  for (int i = threadIdx.x; i < rows * GS * D; i += blockDim.x) {
+    const int r = i / (GS * D), gs = (i / D) % GS, d = i % D;
+    qs[i] = Qb[(((size_t)b * H + h0 + gs) * nq + qb0 + r) * D + d];
+  }
 
   // legal range per row: blocks 0..cmax
   auto cmax_of = [&](int qb) {
@@ -148,17 +156,21 @@ __global__ void __launch_bounds__(256) select_blocks_kernel(const T* __restrict_
         int r = lane + half * 32;
         int c = c0 + r;
         if (r < nrow && c <= my_cmax) {
-          float acc = 0.f;
           const uint32_t* kr = reinterpret_cast<const uint32_t*>(kt + r * PITCH);
-          const uint32_t* qr = reinterpret_cast<const uint32_t*>(qs + warp * D);
+          float tot = 0.f;
+          for (int gs = 0; gs < GS; ++gs) {
+            const uint32_t* qr = reinterpret_cast<const uint32_t*>(qs + (warp * GS + gs) * D);
+            float acc = 0.f;
 #pragma unroll 8
-          for (int w = 0; w < D / 2; ++w) {
-            float2 kf = Elem<T>::unpack(kr[w]);
-            float2 qf = Elem<T>::unpack(qr[w]);
-            acc = __fmaf_rn(qf.x, kf.x, acc);
-            acc = __fmaf_rn(qf.y, kf.y, acc);
+            for (int w = 0; w < D / 2; ++w) {
+              float2 kf = Elem<T>::unpack(kr[w]);
+              float2 qf = Elem<T>::unpack(qr[w]);
+              acc = __fmaf_rn(qf.x, kf.x, acc);
+              acc = __fmaf_rn(qf.y, kf.y, acc);
+            }
+            tot = gs == 0 ? acc : __fadd_rn(tot, acc);
           }
-          float v = acc * scale;
+          float v = tot * scale;
           if (c < force_first || c > my_cmax - force_local) v = INFINITY;
           my_sc[c] = v;
         }
@@ -173,20 +185,21 @@ __global__ void __launch_bounds__(256) select_blocks_kernel(const T* __restrict_
 }
 
 template <typename T>
-static int select_launch(const void* Qb, const void* Kb, int32_t* idx, int B, int H, int Hkv, int nq, int nk, int D,
+static int select_launch(const void* Qb, const void* Kb, int32_t* idx, int B, int H, int Hkv, int Hi, int nq, int nk, int D,
                          int k_out, int bm, int bn, int offset, int causal, float scale, int ff, int fl, cudaStream_t st) {
   const size_t fixed = (size_t)64 * (D + 2) * 2;
   int R = 8;
-  auto need = [&](int r) { return fixed + (size_t)r * D * 2 + 4 + (size_t)r * nk * 4; };
+  const int GS = Hi == H ? 1 : H / Hkv;
+  auto need = [&](int r) { return fixed + (size_t)r * GS * D * 2 + 4 + (size_t)r * nk * 4; };
   while (R > 1 && need(R) > 200 * 1024) R >>= 1;
   NSA_REQUIRE(need(R) <= 200 * 1024, NSA_ERR_UNSUPPORTED, "select: %d KV blocks exceed the shared-memory score row", nk);
-  dim3 grid((unsigned)((nq + R - 1) / R), (unsigned)(B * H));
+  dim3 grid((unsigned)((nq + R - 1) / R), (unsigned)(B * Hi));
   size_t smem = need(R);
 #define NSA_SEL(DD)                                                                                     \
   {                                                                                                     \
     auto fn = select_blocks_kernel<T, DD>;                                                              \
     NSA_CUDA_OK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));      \
-    fn<<<grid, 256, smem, st>>>((const T*)Qb, (const T*)Kb, idx, H, Hkv, nq, nk, k_out, bm, bn, offset, \
+    fn<<<grid, 256, smem, st>>>((const T*)Qb, (const T*)Kb, idx, H, Hkv, Hi, nq, nk, k_out, bm, bn, offset, \
                                 causal, scale, ff, fl, R);                                              \
   }
   switch (D) {
@@ -200,16 +213,18 @@ static int select_launch(const void* Qb, const void* Kb, int32_t* idx, int B, in
 }
 
 int select_blocks(const void* Qb, const void* Kb, int32_t* idx, int B, int H, int Hkv, int nq, int nk, int D, int top_k,
-                  int bm, int bn, int offset, int causal, float scale, int ff, int fl, int dtype, cudaStream_t st) {
+                  int bm, int bn, int offset, int causal, float scale, int ff, int fl, int shared, int dtype,
+                  cudaStream_t st) {
+  const int Hi = shared ? Hkv : H;
   NSA_REQUIRE(B > 0 && H > 0 && Hkv > 0 && H % Hkv == 0, NSA_ERR_ARG, "select: heads %d/%d", H, Hkv);
   NSA_REQUIRE(nq > 0 && nk > 0 && top_k > 0 && bm > 0 && bn > 0, NSA_ERR_ARG, "select: empty problem");
   NSA_REQUIRE((long long)B * H <= 65535, NSA_ERR_ARG, "select: B*H too large");
   NSA_REQUIRE(ff >= 0 && fl >= 0, NSA_ERR_ARG, "select: negative forced-block counts");
   int k_out = top_k < nk ? top_k : nk;
   if (dtype == NSA_BF16)
-    return select_launch<__nv_bfloat16>(Qb, Kb, idx, B, H, Hkv, nq, nk, D, k_out, bm, bn, offset, causal, scale, ff, fl, st);
+    return select_launch<__nv_bfloat16>(Qb, Kb, idx, B, H, Hkv, Hi, nq, nk, D, k_out, bm, bn, offset, causal, scale, ff, fl, st);
   if (dtype == NSA_FP16)
-    return select_launch<__half>(Qb, Kb, idx, B, H, Hkv, nq, nk, D, k_out, bm, bn, offset, causal, scale, ff, fl, st);
+    return select_launch<__half>(Qb, Kb, idx, B, H, Hkv, Hi, nq, nk, D, k_out, bm, bn, offset, causal, scale, ff, fl, st);
   return fail(NSA_ERR_UNSUPPORTED, "select: dtype %d", dtype);
 }
 

@@ -33,16 +33,18 @@ def _block_scores_from_pooled(Q: Tensor, K: Tensor, *, block_size_m: int, block_
 
 def _resolve_block_indices(Q: Tensor, K: Tensor, *, block_size_m: int, block_size_n: int, top_k: int, causal: bool,
                            scale: float, force_first: int = 0, force_local: int = 0,
-                           q_scale: float = 1.0, k_scale: float = 1.0) -> Tensor:
+                           q_scale: float = 1.0, k_scale: float = 1.0, shared_per_group: bool = False) -> Tensor:
     """int32 [B,H,nq,min(top_k,nk)] by mean-pool scoring + top-k, ties to the lowest index.
-    The causal legality offset uses the PADDED lengths, as the reference does (:350-352)."""
+    The causal legality offset uses the PADDED lengths, as the reference does (:350-352).
+    shared_per_group: one row per KV head, [B,Hkv,nq,k], scored by the sum of its query heads' scores."""
     Tq, Tk = Q.shape[2], K.shape[2]
     Qb = ops.pool_mean(Q.detach(), block_size_m, dequant_scale=q_scale)
     Kb = ops.pool_mean(K.detach(), block_size_n, dequant_scale=k_scale)
     nq, nk = Qb.shape[2], Kb.shape[2]
     return ops.select_blocks_from_means(Qb, Kb, top_k=top_k, bm=block_size_m, bn=block_size_n,
                                         offset=nk * block_size_n - nq * block_size_m, causal=bool(causal),
-                                        scale=float(scale), force_first=force_first, force_local=force_local)
+                                        scale=float(scale), force_first=force_first, force_local=force_local,
+                                        shared_per_group=shared_per_group)
 
 
 def _grads_through(fn, Q, K, V, grad_out):
@@ -154,7 +156,8 @@ def nsa_forward(Q: Tensor, K: Tensor, V: Tensor, cfg, *, gate_logits: Optional[T
     if block_indices is None:
         block_indices = _resolve_block_indices(Q, K, block_size_m=cfg.block_size_m, block_size_n=cfg.block_size_n,
                                                top_k=cfg.top_k, causal=cfg.causal, scale=float(scale),
-                                               force_first=ff, force_local=fl)
+                                               force_first=ff, force_local=fl,
+                                               shared_per_group=bool(_cfg(cfg, "select_per_group", False)))
     needs_grad = torch.is_grad_enabled() and any(
         t is not None and t.requires_grad for t in (Q, K, V, gate_logits))
     if needs_grad:
@@ -169,7 +172,7 @@ def nsa_forward(Q: Tensor, K: Tensor, V: Tensor, cfg, *, gate_logits: Optional[T
     return _fused_forward(Q, K, V, cfg, float(scale), stride_c, gate_logits, block_indices, 1.0, 1.0, 1.0)
 
 
-def _fused_forward(Q, K, V, cfg, scale, stride_c, gate_logits, block_indices, sq, sk, sv, engine=L.ENGINE_AUTO):
+def _fused_forward(Q, K, V, cfg, scale, stride_c, gate_logits, block_indices, sq, sk, sv, engine=None):
     bc = cfg.block_size_c
     stride = bc if stride_c is None else int(stride_c)
     Kc = ops.pool_mean(K, bc, stride, dequant_scale=sk)
@@ -199,7 +202,7 @@ def nsa_forward_fp8(Q: Tensor, K: Tensor, V: Tensor, scale_q: float, scale_k: fl
         block_indices = _resolve_block_indices(
             Q, K, block_size_m=cfg.block_size_m, block_size_n=cfg.block_size_n, top_k=cfg.top_k, causal=cfg.causal,
             scale=float(scale), force_first=_cfg(cfg, "force_first", 0), force_local=_cfg(cfg, "force_local", 0),
-            q_scale=scale_q, k_scale=scale_k)
+            q_scale=scale_q, k_scale=scale_k, shared_per_group=bool(_cfg(cfg, "select_per_group", False)))
     return _fused_forward(Q, K, V, cfg, float(scale), getattr(cfg, "stride_c", None), gate_logits, block_indices,
                           scale_q, scale_k, scale_v)
 

@@ -14,6 +14,21 @@ from torch import Tensor
 
 from . import _lib as L
 
+_ENGINE = L.ENGINE_AUTO
+
+
+def set_engine(name: str) -> None:
+    """Which attention-forward kernel nsa_attention_fwd uses: "auto" (tcgen05 when the shape
+    qualifies, else generic), "generic" or "tcgen05" (error when the shape does not qualify)."""
+    global _ENGINE
+    _ENGINE = {"auto": L.ENGINE_AUTO, "generic": L.ENGINE_GENERIC, "tcgen05": L.ENGINE_TCGEN05}[name]
+
+
+def device_status() -> None:
+    """Synchronise the current stream and raise if a kernel gave up on a bounded device-side wait."""
+    L.check(L.load().nsa_device_status(L.stream_ptr()), "nsa_device_status")
+
+
 _16 = (torch.float16, torch.bfloat16)
 _8 = (torch.float8_e4m3fn, torch.float8_e5m2)
 
@@ -50,16 +65,17 @@ def pool_mean(x: Tensor, block: int, stride: Optional[int] = None, dequant_scale
 
 
 def select_blocks_from_means(Qb: Tensor, Kb: Tensor, *, top_k: int, bm: int, bn: int, offset: int, causal: bool,
-                             scale: float, force_first: int = 0, force_local: int = 0) -> Tensor:
+                             scale: float, force_first: int = 0, force_local: int = 0,
+                             shared_per_group: bool = False) -> Tensor:
     _need_cuda(Qb, Kb)
     B, H, nq, D = Qb.shape
     Hkv, nk = Kb.shape[1], Kb.shape[2]
     k_out = min(top_k, nk)
-    idx = torch.empty((B, H, nq, k_out), device=Qb.device, dtype=torch.int32)
+    idx = torch.empty((B, Hkv if shared_per_group else H, nq, k_out), device=Qb.device, dtype=torch.int32)
     with torch.cuda.device(Qb.device):
         L.check(L.load().nsa_select_blocks(Qb.data_ptr(), Kb.data_ptr(), idx.data_ptr(), B, H, Hkv, nq, nk, D, top_k,
                                            bm, bn, offset, int(causal), float(scale), force_first, force_local,
-                                           L.dtype_code(Qb.dtype), L.stream_ptr()), "nsa_select_blocks")
+                                           int(shared_per_group), L.dtype_code(Qb.dtype), L.stream_ptr()), "nsa_select_blocks")
     return idx
 
 
@@ -79,7 +95,7 @@ def attention_fwd(
     Kc: Optional[Tensor] = None, Vc: Optional[Tensor] = None, cmp_block: int = 0, cmp_stride: int = 0,
     cmp_offset: int = 0, idx: Optional[Tensor] = None, bm: int = 64, bn: int = 64, window: int = 0,
     gates: Optional[Tensor] = None, gate_act: int = L.GATE_SIGMOID, offset: Optional[int] = None,
-    q_scale: float = 1.0, k_scale: float = 1.0, v_scale: float = 1.0, engine: int = L.ENGINE_AUTO,
+    q_scale: float = 1.0, k_scale: float = 1.0, v_scale: float = 1.0, engine: Optional[int] = None,
     want_lse: bool = True,
 ) -> Tuple[Tensor, Optional[Tensor]]:
     """One launch of nsa_attention_fwd.  Returns (out, lse); lse is None for fused launches."""
@@ -103,7 +119,7 @@ def attention_fwd(
     a.causal, a.branches, a.fused, a.gate_act = int(causal), branches, int(fused), gate_act
     a.q_dtype = a.kv_dtype = L.dtype_code(Q.dtype)
     a.scale, a.q_scale, a.k_scale, a.v_scale = float(scale), float(q_scale), float(k_scale), float(v_scale)
-    a.engine = engine
+    a.engine = _ENGINE if engine is None else engine
     keep = [Q, K, V]
     if branches & L.BRANCH_COMPRESSED:
         Kc, Vc = Kc.contiguous(), Vc.contiguous()

@@ -175,15 +175,25 @@ def compressed_attention(
 # --------------------------------------------------------------------------
 
 def block_scores(Q: Tensor, K: Tensor, *, block_size_m: int = 64, block_size_n: int = 64,
-                 scale: Optional[float] = None) -> Tensor:
+                 scale: Optional[float] = None, group_shared: bool = False) -> Tensor:
     """fp32 [B,H,nq,nk] scores: block means of Q and K taken in the input
-    dtype, cast to fp32, dotted, times scale (forward.py:301-318,344-347)."""
+    dtype, cast to fp32, dotted, times scale (forward.py:301-318,344-347).
+    group_shared (parity unpinned): [B,Hkv,nq,nk], the per-head dots of the
+    heads sharing a KV head added in head order, then scaled."""
     B, H, Tq, D = Q.shape
-    G = _group(H, K.shape[1])
+    Hkv = K.shape[1]
+    G = _group(H, Hkv)
     Qb = pool_mean(Q, block_size_m).float()
     Kb = pool_mean(K, block_size_n).float()
     Kb = Kb.repeat_interleave(G, dim=1) if G > 1 else Kb
-    return torch.matmul(Qb, Kb.transpose(-1, -2)) * _softmax_scale(D, scale)
+    dots = torch.matmul(Qb, Kb.transpose(-1, -2))
+    if group_shared:
+        dots = dots.view(B, Hkv, G, dots.shape[-2], dots.shape[-1])
+        acc = dots[:, :, 0].clone()
+        for g in range(1, G):
+            acc = acc + dots[:, :, g]
+        dots = acc
+    return dots * _softmax_scale(D, scale)
 
 
 def legal_blocks(nq: int, nk: int, bm: int, bn: int, offset: int) -> Tensor:
@@ -222,14 +232,15 @@ def topk_canonical(scores: Tensor, top_k: int, *, legal: Optional[Tensor] = None
 
 def select_blocks(Q: Tensor, K: Tensor, *, block_size_m: int = 64, block_size_n: int = 64,
                   top_k: int = 16, causal: bool = True, scale: Optional[float] = None,
-                  force_first: int = 0, force_local: int = 0,
+                  force_first: int = 0, force_local: int = 0, group_shared: bool = False,
                   return_scores: bool = False):
     """Indices the combined forward uses (forward.py:321-359).  The causal
     offset here is taken from the PADDED lengths, Tk_p - Tq_p (forward.py:350-352)."""
     Tq, Tk = Q.shape[2], K.shape[2]
     nq = (Tq + block_size_m - 1) // block_size_m
     nk = (Tk + block_size_n - 1) // block_size_n
-    sc = block_scores(Q, K, block_size_m=block_size_m, block_size_n=block_size_n, scale=scale)
+    sc = block_scores(Q, K, block_size_m=block_size_m, block_size_n=block_size_n, scale=scale,
+                      group_shared=group_shared)
     legal = None
     if causal:
         legal = legal_blocks(nq, nk, block_size_m, block_size_n,
@@ -399,7 +410,8 @@ def nsa_forward(
     block_size_n: int = 64, block_size_m: int = 64, top_k: int = 16, window_size: int = 512,
     causal: bool = True, scale: Optional[float] = None, gate_logits: Optional[Tensor] = None,
     gate_activation: str = "sigmoid", block_indices: Optional[Tensor] = None,
-    force_first: int = 0, force_local: int = 0, rows: Optional[Tuple[int, int]] = None,
+    force_first: int = 0, force_local: int = 0, group_shared: bool = False,
+    rows: Optional[Tuple[int, int]] = None,
 ) -> Tensor:
     """fp32 combined forward (forward.py:362-406 / reference.py:288-347): the
     three branches on the same inputs, gates applied in fp32.  With
@@ -408,7 +420,8 @@ def nsa_forward(
     if block_indices is None:
         block_indices = select_blocks(Q, K, block_size_m=block_size_m, block_size_n=block_size_n,
                                       top_k=top_k, causal=causal, scale=scale,
-                                      force_first=force_first, force_local=force_local)
+                                      force_first=force_first, force_local=force_local,
+                                      group_shared=group_shared)
     q0, q1 = _rows(rows, Tq)
     oc, _ = compressed_attention(Q, K, V, block_size_c=block_size_c, stride_c=stride_c,
                                  causal=causal, scale=scale, rows=(q0, q1))

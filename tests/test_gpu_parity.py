@@ -289,8 +289,83 @@ def test_forward_is_bitwise_repeatable_and_errors_are_loud(nsa):
     a = nsa.nsa_forward(Q.cuda(), K.cuda(), V.cuda(), cfg)
     b = nsa.nsa_forward(Q.cuda(), K.cuda(), V.cuda(), cfg)
     assert torch.equal(a, b)
-    with pytest.raises(RuntimeError):
+    with pytest.raises((RuntimeError, AssertionError)):
         nsa.sliding_attention(Q, K, V)          # CPU tensors: no fallback
     with pytest.raises((RuntimeError, AssertionError)):
         nsa.sliding_attention(Q.cuda()[..., :48].contiguous(), K.cuda()[..., :48].contiguous(),
                               V.cuda()[..., :48].contiguous())   # unsupported head dim
+
+
+# ------------------------------------------------------------------ tcgen05 engine
+TC5_SHAPES = [
+    # B, H, Hkv, Tq, Tk, D, dtype
+    (1, 4, 1, 256, 256, 128, torch.bfloat16),
+    (1, 8, 2, 512, 512, 128, torch.bfloat16),
+    (2, 8, 1, 384, 384, 64, torch.float16),
+    (1, 4, 1, 200, 456, 128, torch.bfloat16),      # ragged, Tq < Tk
+    (1, 16, 4, 1024, 1024, 64, torch.bfloat16),
+]
+
+
+@pytest.mark.parametrize("shape", TC5_SHAPES)
+@pytest.mark.parametrize("causal", [True, False])
+def test_tcgen05_branches_vs_oracle(nsa, shape, causal):
+    """Each branch alone through the tcgen05 kernel: out and lse against the oracle."""
+    from nsa_from_scratch_b200 import _lib as L, ops
+    from nsa_from_scratch_b200.forward import _resolve_block_indices
+    B, H, Hkv, Tq, Tk, D, dt = shape
+    Q, K, V, _ = make_qkv(9, B, H, Hkv, Tq, Tk, D, dt)
+    Qc, Kc_, Vc_ = Q.cuda(), K.cuda(), V.cuda()
+    scale = D ** -0.5
+    try:
+        # sliding
+        for W in (100, 512):
+            out, lse = ops.attention_fwd(Qc, Kc_, Vc_, branches=L.BRANCH_SLIDING, fused=False, causal=causal, scale=scale,
+                                         window=W, engine=L.ENGINE_TCGEN05)
+            ro, rl = O.sliding_attention(Q, K, V, window_size=W, causal=causal)
+            check_out_lse(out, lse, ro, rl, TOL16)
+        # compressed, both geometries
+        for bc, st in ((64, 64), (32, 16)):
+            Kp, Vp = ops.pool_mean(Kc_, bc, st), ops.pool_mean(Vc_, bc, st)
+            Tk_pad = Kp.shape[2] * bc if st == bc else Tk
+            out, lse = ops.attention_fwd(Qc, Kc_, Vc_, branches=L.BRANCH_COMPRESSED, fused=False, causal=causal, scale=scale,
+                                         Kc=Kp, Vc=Vp, cmp_block=bc, cmp_stride=st, cmp_offset=Tk_pad - Tq,
+                                         engine=L.ENGINE_TCGEN05)
+            ro, rl = O.compressed_attention(Q, K, V, block_size_c=bc, stride_c=st, causal=causal)
+            check_out_lse(out, lse, ro, rl, TOL16)
+        # selected with indices shared per KV head (odd and even counts of listed blocks)
+        for k in (3, 4):
+            idx = _resolve_block_indices(Qc, Kc_, block_size_m=64, block_size_n=64, top_k=k, causal=causal, scale=scale,
+                                         shared_per_group=True)
+            canon = O.select_blocks(Q, K, top_k=k, causal=causal, group_shared=True)
+            assert torch.equal(idx.cpu(), canon)
+            out, lse = ops.attention_fwd(Qc, Kc_, Vc_, branches=L.BRANCH_SELECTED, fused=False, causal=causal, scale=scale,
+                                         idx=idx, engine=L.ENGINE_TCGEN05)
+            ro, rl = O.selected_attention(Q, K, V, canon, causal=causal)
+            check_out_lse(out, lse, ro, rl, TOL16)
+    finally:
+        ops.device_status()
+
+
+@pytest.mark.parametrize("shape", TC5_SHAPES)
+def test_tcgen05_fused_forward_vs_oracle_and_generic(nsa, shape):
+    from nsa_from_scratch_b200 import ops
+    B, H, Hkv, Tq, Tk, D, dt = shape
+    Q, K, V, g = make_qkv(10, B, H, Hkv, Tq, Tk, D, dt)
+    gates = torch.randn(B, H, Tq, 3, generator=g)
+    cfg = nsa.NSAConfig(block_size_c=32, stride_c=16, top_k=4, window_size=128, force_first=1, force_local=2,
+                        select_per_group=True)
+    ref = O.nsa_forward(Q, K, V, block_size_c=32, stride_c=16, top_k=4, window_size=128, gate_logits=gates,
+                        force_first=1, force_local=2, group_shared=True)
+    try:
+        ops.set_engine("tcgen05")
+        out = nsa.nsa_forward(Q.cuda(), K.cuda(), V.cuda(), cfg, gate_logits=gates.cuda())
+        out_b = nsa.nsa_forward(Q.cuda(), K.cuda(), V.cuda(), cfg, gate_logits=gates.cuda())
+        ops.device_status()
+        ops.set_engine("generic")
+        out_g = nsa.nsa_forward(Q.cuda(), K.cuda(), V.cuda(), cfg, gate_logits=gates.cuda())
+    finally:
+        ops.set_engine("auto")
+    assert max_abs(out, ref) <= TOL16, max_abs(out, ref)
+    assert max_abs(out_g, ref) <= TOL16
+    assert torch.equal(out, out_b)          # run-to-run bitwise repeatable
