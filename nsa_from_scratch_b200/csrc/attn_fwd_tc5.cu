@@ -33,6 +33,14 @@ constexpr int T5_THREADS = 384;
 
 __device__ int g_tc5_status;   // 0 ok; otherwise (1 + id of the barrier a wait gave up on)
 
+// Optional cycle-stamp trace of one block (debug builds only: -DNSA_TC5_TRACE=<block index>).
+#ifdef NSA_TC5_TRACE
+__device__ long long g_tc5_trace[8192];
+#define T5_TRACE(slot) do { if (blockIdx.x == (NSA_TC5_TRACE) && (slot) < 8192) g_tc5_trace[(slot)] = clock64(); } while (0)
+#else
+#define T5_TRACE(slot) do { } while (0)
+#endif
+
 struct Tc5Params {
   CUtensorMap tmQ, tmK, tmV, tmKc, tmVc;
   nsa_fwd_args a;
@@ -247,11 +255,14 @@ __global__ void __launch_bounds__(T5_THREADS, 1) nsa_fwd_tc5_kernel(const __grid
         locate(it, br, t);
         const Tile tl = get_tile(br, t);
         const int s = it & 1, ph = (it >> 1) & 1;
+        T5_TRACE(4096 + it * 8 + 0);
         ok = mbar_wait(bar(B_VFULL + s), ph, &abort_flag);
         if (!ok) { fail_id = B_VFULL + s + 1; break; }
+        T5_TRACE(4096 + it * 8 + 1);
         for (int X = 0; X < 2 && ok; ++X) {
           ok = mbar_wait(bar(B_PFULL + X), it & 1, &abort_flag);
           if (!ok) { fail_id = B_PFULL + X + 1; break; }
+          T5_TRACE(4096 + it * 8 + 2 + 2 * X);
           tc_fence_after();
           for (int kk = 0; kk < 4 * tl.nch; ++kk)
             mma_ts(tmem + 256 + X * 128, tmem + X * 128 + kk * 8,
@@ -259,6 +270,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) nsa_fwd_tc5_kernel(const __grid
           tc_commit(bar(B_PVDONE + X));
           if (X == 1) tc_commit(bar(B_VEMPTY + s));
           if (it + 1 < total_tiles) ok = issue_qk(X, it + 1);
+          T5_TRACE(4096 + it * 8 + 3 + 2 * X);
         }
       }
     }
@@ -321,8 +333,10 @@ __global__ void __launch_bounds__(T5_THREADS, 1) nsa_fwd_tc5_kernel(const __grid
 #pragma unroll 1
       for (int t = 0; t < nt && ok; ++t, ++it) {
         const Tile tl = get_tile(br, t);
+        if (quarter == 0 && lane == 0) T5_TRACE(X * 2048 + it * 8 + 0);
         ok = __all_sync(0xffffffffu, mbar_wait(bar(B_SFULL + X), it & 1, &abort_flag));
         if (!ok) { fail_id = B_SFULL + X + 1; break; }
+        if (quarter == 0 && lane == 0) T5_TRACE(X * 2048 + it * 8 + 1);
         tc_fence_after();
         // valid column range of each chunk for this row
         int vlo[2], vhi[2];
@@ -348,6 +362,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) nsa_fwd_tc5_kernel(const __grid
               if (base + i >= vlo[c] && base + i <= vhi[c]) mx = fmaxf(mx, __uint_as_float(v[i]));
           }
         }
+        if (quarter == 0 && lane == 0) T5_TRACE(X * 2048 + it * 8 + 2);
         mx *= p.scale_log2;                                  // scale > 0 keeps the order
         // lazy rescale: only when some row of the warp outgrows its reference maximum by 2^8
         const bool grow = mx > m_used + 8.f;
@@ -395,9 +410,11 @@ __global__ void __launch_bounds__(T5_THREADS, 1) nsa_fwd_tc5_kernel(const __grid
           tmem_st16(tS + g * 16, pk);
         }
         l += psum;
+        if (quarter == 0 && lane == 0) T5_TRACE(X * 2048 + it * 8 + 3);
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar(B_PFULL + X));
+        if (quarter == 0 && lane == 0) T5_TRACE(X * 2048 + it * 8 + 4);
       }
       if (!ok) break;
       // ---- end of the branch: O is complete once the last PV has landed ---------------------------
@@ -528,6 +545,12 @@ int attention_fwd_tc5(const nsa_fwd_args& a, cudaStream_t st) {
 #undef NSA_TC5_LAUNCH
   return launch_status("attn_fwd_tc5");
 }
+
+#ifdef NSA_TC5_TRACE
+extern "C" int nsa_debug_trace(long long* host_buf) {
+  return (int)cudaMemcpyFromSymbol(host_buf, g_tc5_trace, sizeof(long long) * 8192);
+}
+#endif
 
 // Synchronises `st`, returns and clears the status word the tcgen05 kernels set when a bounded wait gave up.
 int tc5_take_status(cudaStream_t st, int* status) {
