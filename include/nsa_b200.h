@@ -130,6 +130,23 @@ int nsa_attention_fwd(const nsa_fwd_args* args, nsa_stream_t stream);
  * No counterpart in the reference (its kernels have no device-side waits). */
 int nsa_device_status(nsa_stream_t stream);
 
+/* Compressed-branch forward that needs no scratch memory from the caller: the pooled K and V
+ * live in an array built into the library (NSA_STATIC_SCRATCH_BYTES per GPU, held until the
+ * process exits).  Meant for hosts that cannot allocate at call time -- a runtime whose device
+ * memory is fully planned up front, or code inside a region where cudaMalloc is forbidden or
+ * would stall the device.  Same results as nsa_pool_mean (K, V) followed by
+ * nsa_attention_fwd(branches = NSA_BRANCH_COMPRESSED, fused = 0): out [B,H,Tq,D], lse [B,H,Tq]
+ * (lse may be NULL).  Limit: B*Hkv*n_pooled*D*4 bytes (each half rounded up to 256) must fit the
+ * array, otherwise NSA_ERR_UNSUPPORTED with the sizes in nsa_last_error().  The first call on a
+ * device looks up the array's device address (cudaGetSymbolAddress); make that first call
+ * outside any stream capture.  All calls share the one array: calls that may run concurrently
+ * on the GPU race with each other; nothing in it needs clearing between calls.
+ * No counterpart in the reference (its wrappers allocate through torch). */
+#define NSA_STATIC_SCRATCH_BYTES (16u << 20)
+int nsa_compressed_attention_static(const void* Q, const void* K, const void* V, void* out, float* lse, int B,
+                                    int H, int Hkv, int Tq, int Tk, int D, int block, int stride, int causal,
+                                    float scale, int dtype, nsa_stream_t stream);
+
 /* The reference's native launcher, same argument list (bf16, Hkv == H folded into BH,
  * 64x64 blocks, pre-padded lengths, D in {32,64,128}); returns a status instead of void.
  * Replaces: launch_selected_attn_fwd, nsa/cuda/selected_fwd.cu:582-614
