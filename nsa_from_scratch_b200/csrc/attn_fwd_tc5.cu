@@ -5,16 +5,18 @@
 // All rows of a work item see the same KV tiles in every branch (the selected blocks are
 // shared by the heads of a GQA group), so a K/V tile staged once by TMA feeds both tiles.
 //
-// Warp roles (12 warps, one block per SM):
+// Warp roles (12 warps, one block per SM; warps 0-3 shrink to 56 registers with setmaxnreg, the
+// softmax warps grow to 224 -- each SM sub-partition then holds 56 + 2*224 registers per lane):
 //   warp 0      TMA producer: Q once, then K and V tiles (1 or 2 chunks of 64 keys) into two
 //               2-deep rings of 128-byte-swizzled shared memory; pooled K/V for the compressed
 //               branch, raw K/V for the selected and sliding branches
 //   warp 1      MMA issuer (one thread): S_X = Q_X K^T into TMEM, then O_X (+)= P_X V with P read
 //               from TMEM (it aliases S_X) and V as an MN-major shared-memory operand
-//   warps 4-7   softmax of tile 0, warps 8-11 softmax of tile 1 (one thread per row): read S from
-//               TMEM, mask, running max with lazy rescale of O (only when the max grows by > 2^8),
-//               exp2, row sum, P as 16-bit back into TMEM; at the end of a branch they read O,
-//               apply gate/l and keep the gated sum of the branches in registers
+//   warps 4-7   softmax of tile 0, warps 8-11 softmax of tile 1 (one thread per row; a warp reaches
+//               the TMEM lanes 32*(warp%4)..+31): read the whole S row from TMEM in one round trip,
+//               mask, running max with lazy rescale of O (only when the max grows by > 2^8), exp2,
+//               row sum, P as 16-bit back into TMEM; at the end of a branch they read O, apply
+//               gate/l and add it into the output row (the row itself holds the running gated sum)
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D).
 // Tile X's chain QK -> softmax -> PV is serial; the tensor pipe stays busy because the other
 // tile's MMAs run in the gaps.  Every mbarrier wait is bounded; a wait that gives up raises a
@@ -29,7 +31,7 @@ namespace nsa {
 using namespace tc5;
 
 constexpr int T5_MAX_SEL = 64;
-constexpr int T5_THREADS = 384;
+constexpr int T5_THREADS = 384;   // 12 warps; register budget rebalanced per role with setmaxnreg   // 10 warps: 65536 / 320 leaves 200 registers per thread
 
 __device__ int g_tc5_status;   // 0 ok; otherwise (1 + id of the barrier a wait gave up on)
 
@@ -59,7 +61,7 @@ struct Tile {
 enum { B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 3, B_VFULL = 5, B_VEMPTY = 7, B_SFULL = 9, B_PFULL = 11, B_PVDONE = 13, B_COUNT = 15 };
 
 template <int D, int FMT>
-__global__ void __launch_bounds__(T5_THREADS, 1) nsa_fwd_tc5_kernel(const __grid_constant__ Tc5Params p) {
+__global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_constant__ Tc5Params p) {
   using T = typename std::conditional<FMT == 1, __nv_bfloat16, __half>::type;
   constexpr int DH = D / 64;                    // 64-element (128-byte) halves of a row
   constexpr int QTILE = DH * 128 * 128;         // bytes of one 128-row Q tile
@@ -175,6 +177,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) nsa_fwd_tc5_kernel(const __grid
   int last_k_it = -1, last_v_it = -1;   // producer: last tile whose K / V copies were issued
 
   if (warp == 0) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;\n");
     // =============================== TMA producer ===============================
     if (lane == 0) {
       tma_prefetch_desc(&p.tmQ); tma_prefetch_desc(&p.tmK); tma_prefetch_desc(&p.tmV);
@@ -213,6 +216,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) nsa_fwd_tc5_kernel(const __grid
       }
     }
   } else if (warp == 1) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;\n");
     // =============================== MMA issuer ===============================
     if (lane == 0) {
       constexpr uint32_t IDESC_PV = idesc_f16(FMT, 128, D, 0, 1);
@@ -274,7 +278,10 @@ __global__ void __launch_bounds__(T5_THREADS, 1) nsa_fwd_tc5_kernel(const __grid
         }
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;\n");
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;\n");
     // =============================== softmax / epilogue ===============================
     const int X = (warp - 4) >> 2;
     const int quarter = warp & 3;
@@ -310,15 +317,11 @@ __global__ void __launch_bounds__(T5_THREADS, 1) nsa_fwd_tc5_kernel(const __grid
       }
     }
 
-    // gated sum of the finished branches, kept as packed 16-bit pairs (D/2 registers); the last
-    // branch is added in fp32 straight into the output row
-    uint32_t total[D / 2];
-#pragma unroll
-    for (int d = 0; d < D / 2; ++d) total[d] = 0u;
+    // The gated sum of the finished branches lives in the output row itself (16-bit, this thread's
+    // own 2*D bytes of HBM, read back and added to at the next branch end): that keeps the whole
+    // S row (128 registers) resident during a tile, so a tile costs ONE TMEM round trip.
     float lse_out = -INFINITY;
-    int last_br = -1;
-#pragma unroll
-    for (int br = 0; br < 3; ++br) if (nchunks[br] > 0) last_br = br;
+    bool have_partial = false;
     T* orow = reinterpret_cast<T*>(a.out) + row_index * D;
 
     int it = 0;
@@ -338,30 +341,39 @@ __global__ void __launch_bounds__(T5_THREADS, 1) nsa_fwd_tc5_kernel(const __grid
         if (!ok) { fail_id = B_SFULL + X + 1; break; }
         if (quarter == 0 && lane == 0) T5_TRACE(X * 2048 + it * 8 + 1);
         tc_fence_after();
-        // valid column range of each chunk for this row
-        int vlo[2], vhi[2];
+        // the whole S row of the tile: 64*nch columns, one wait
+        uint32_t sv[4][32];
+        tmem_ld32(tS, sv[0]);
+        tmem_ld32(tS + 32, sv[1]);
+        if (tl.nch == 2) { tmem_ld32(tS + 64, sv[2]); tmem_ld32(tS + 96, sv[3]); }
+        tc_wait_ld();
+        // valid column range of each chunk for this row; masked entries become -inf
+        bool full = true;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          vlo[c] = max(lo - tl.j0[c], 0);
-          vhi[c] = min(hi, tl.jlim[c] - 1) - tl.j0[c];
-          if (c >= tl.nch) vhi[c] = -1;
-        }
-        // pass 1: row maximum
-        float mx = -INFINITY;
-        for (int g = 0; g < 2 * tl.nch; ++g) {
-          uint32_t v[32];
-          tmem_ld32(tS + g * 32, v);
-          tc_wait_ld();
-          const int c = g >> 1, base = (g & 1) * 32;
-          if (vlo[c] <= base && vhi[c] >= base + 31) {
+          const int vlo = max(lo - tl.j0[c], 0);
+          const int vhi = c < tl.nch ? min(hi, tl.jlim[c] - 1) - tl.j0[c] : -1;
+          if (c < tl.nch && (vlo > 0 || vhi < 63)) {
+            full = false;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
-          } else {
+            for (int g = 0; g < 2; ++g)
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (base + i >= vlo[c] && base + i <= vhi[c]) mx = fmaxf(mx, __uint_as_float(v[i]));
+              for (int i = 0; i < 32; ++i)
+                if (g * 32 + i < vlo || g * 32 + i > vhi) sv[2 * c + g][i] = 0xff800000u;   // -inf
           }
         }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int g = 0; g < 2; ++g)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[g][i]));
+        if (tl.nch == 2) {
+#pragma unroll
+          for (int g = 2; g < 4; ++g)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[g][i]));
+        }
+        (void)full;
         if (quarter == 0 && lane == 0) T5_TRACE(X * 2048 + it * 8 + 2);
         mx *= p.scale_log2;                                  // scale > 0 keeps the order
         // lazy rescale: only when some row of the warp outgrows its reference maximum by 2^8
@@ -387,29 +399,24 @@ __global__ void __launch_bounds__(T5_THREADS, 1) nsa_fwd_tc5_kernel(const __grid
           m_used = m_new;
         }
         const float m_ref = m_used == -INFINITY ? 0.f : m_used;
-        // pass 2: P = exp2(S*scale - m_ref) as 16-bit into the columns S occupied
-        float psum = 0.f;
-        for (int g = 0; g < 2 * tl.nch; ++g) {
-          uint32_t v[32];
-          tmem_ld32(tS + g * 32, v);
-          tc_wait_ld();
-          const int c = g >> 1, base = (g & 1) * 32;
-          const bool full = vlo[c] <= base && vhi[c] >= base + 31;
-          uint32_t pk[16];
+        // P = exp2(S*scale - m_ref) as 16-bit into the columns S occupied (-inf -> 0)
+        float psum0 = 0.f, psum1 = 0.f;
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            float p0 = ex2(__uint_as_float(v[2 * i]) * p.scale_log2 - m_ref);
-            float p1 = ex2(__uint_as_float(v[2 * i + 1]) * p.scale_log2 - m_ref);
-            if (!full) {
-              if (base + 2 * i < vlo[c] || base + 2 * i > vhi[c]) p0 = 0.f;
-              if (base + 2 * i + 1 < vlo[c] || base + 2 * i + 1 > vhi[c]) p1 = 0.f;
+        for (int g = 0; g < 4; ++g) {
+          if (g < 2 * tl.nch) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float p0 = ex2(fmaf(__uint_as_float(sv[g][2 * i]), p.scale_log2, -m_ref));
+              const float p1 = ex2(fmaf(__uint_as_float(sv[g][2 * i + 1]), p.scale_log2, -m_ref));
+              psum0 += p0;
+              psum1 += p1;
+              pk[i] = Elem<T>::pack(p0, p1);
             }
-            psum += p0 + p1;
-            pk[i] = Elem<T>::pack(p0, p1);
+            tmem_st16(tS + g * 16, pk);
           }
-          tmem_st16(tS + g * 16, pk);
         }
-        l += psum;
+        l += psum0 + psum1;
         if (quarter == 0 && lane == 0) T5_TRACE(X * 2048 + it * 8 + 3);
         tc_wait_st();
         tc_fence_before();
@@ -429,22 +436,28 @@ __global__ void __launch_bounds__(T5_THREADS, 1) nsa_fwd_tc5_kernel(const __grid
         uint32_t v[32];
         tmem_ld32(tO + g * 32, v);
         tc_wait_ld();
+        if (row_ok) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float2 acc = Elem<T>::unpack(total[g * 16 + i]);
-          total[g * 16 + i] = Elem<T>::pack(acc.x + __uint_as_float(v[2 * i]) * coef, acc.y + __uint_as_float(v[2 * i + 1]) * coef);
-        }
-        if (br == last_br && row_ok) {
+          for (int c = 0; c < 4; ++c) {
+            uint4 prev = make_uint4(0u, 0u, 0u, 0u);
+            if (have_partial) prev = reinterpret_cast<const uint4*>(orow)[g * 4 + c];
+            const uint32_t pw[4] = {prev.x, prev.y, prev.z, prev.w};
+            uint32_t w[4];
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
-            reinterpret_cast<uint4*>(orow)[g * 4 + c] =
-                make_uint4(total[g * 16 + 4 * c], total[g * 16 + 4 * c + 1], total[g * 16 + 4 * c + 2], total[g * 16 + 4 * c + 3]);
+            for (int e = 0; e < 4; ++e) {
+              const float2 acc = Elem<T>::unpack(pw[e]);
+              w[e] = Elem<T>::pack(fmaf(__uint_as_float(v[8 * c + 2 * e]), coef, acc.x),
+                                   fmaf(__uint_as_float(v[8 * c + 2 * e + 1]), coef, acc.y));
+            }
+            reinterpret_cast<uint4*>(orow)[g * 4 + c] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
         }
       }
+      have_partial = true;
       tc_fence_before();
     }
     if (ok && row_ok) {
-      if (last_br < 0) {                      // no branch had a visible key: the row is zero
+      if (!have_partial) {                    // no branch had a visible key: the row is zero
 #pragma unroll
         for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(orow)[c] = make_uint4(0u, 0u, 0u, 0u);
       }
