@@ -5,8 +5,8 @@
 // All rows of a work item see the same KV tiles in every branch (the selected blocks are
 // shared by the heads of a GQA group), so a K/V tile staged once by TMA feeds both tiles.
 //
-// Warp roles (12 warps, one block per SM; warps 0-3 shrink to 56 registers with setmaxnreg, the
-// softmax warps grow to 224 -- each SM sub-partition then holds 56 + 2*224 registers per lane):
+// Warp roles (12 warps, one block per SM; warps 0-3 shrink to 72 registers with setmaxnreg, the
+// softmax warps grow to 216 -- each SM sub-partition then holds 72 + 2*216 = 504 of its 512 registers per lane; an exact fit must be avoided, setmaxnreg.inc blocks until the registers exist):
 //   warp 0      TMA producer: Q once, then K and V tiles (1 or 2 chunks of 64 keys) into two
 //               2-deep rings of 128-byte-swizzled shared memory; pooled K/V for the compressed
 //               branch, raw K/V for the selected and sliding branches
@@ -38,7 +38,7 @@ __device__ int g_tc5_status;   // 0 ok; otherwise (1 + id of the barrier a wait 
 // Optional cycle-stamp trace of one block (debug builds only: -DNSA_TC5_TRACE=<block index>).
 #ifdef NSA_TC5_TRACE
 __device__ long long g_tc5_trace[8192];
-#define T5_TRACE(slot) do { if (blockIdx.x == (NSA_TC5_TRACE) && (slot) < 8192) g_tc5_trace[(slot)] = clock64(); } while (0)
+#define T5_TRACE(slot) do { if (blockIdx.x == (NSA_TC5_TRACE) && (slot) < 8192 && ((slot) < 4096 || (threadIdx.x & 31) == 0)) g_tc5_trace[(slot)] = clock64(); } while (0)
 #else
 #define T5_TRACE(slot) do { } while (0)
 #endif
@@ -177,17 +177,22 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
   int last_k_it = -1, last_v_it = -1;   // producer: last tile whose K / V copies were issued
 
   if (warp == 0) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;\n");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;\n");
     // =============================== TMA producer ===============================
-    if (lane == 0) {
-      tma_prefetch_desc(&p.tmQ); tma_prefetch_desc(&p.tmK); tma_prefetch_desc(&p.tmV);
-      if (a.branches & NSA_BRANCH_COMPRESSED) { tma_prefetch_desc(&p.tmKc); tma_prefetch_desc(&p.tmVc); }
-      mbar_expect_tx(bar(B_QFULL), 2 * QTILE);
-      for (int X = 0; X < 2; ++X)
-        for (int hh = 0; hh < 2; ++hh)
-          for (int dh = 0; dh < DH; ++dh)
-            tma_load_3d(sQ + X * QTILE + dh * DHSTRIDE + hh * 8192, &p.tmQ, bar(B_QFULL), dh * 64, q0,
-                        b * a.H + h_base + 2 * X + hh);
+    // The whole warp walks the tile sequence (converged); one elected lane issues the copies.
+    {
+      const bool leader = elect_one();
+      if (leader) {
+        tma_prefetch_desc(&p.tmQ); tma_prefetch_desc(&p.tmK); tma_prefetch_desc(&p.tmV);
+        if (a.branches & NSA_BRANCH_COMPRESSED) { tma_prefetch_desc(&p.tmKc); tma_prefetch_desc(&p.tmVc); }
+        mbar_expect_tx(bar(B_QFULL), 2 * QTILE);
+        for (int X = 0; X < 2; ++X)
+          for (int hh = 0; hh < 2; ++hh)
+            for (int dh = 0; dh < DH; ++dh)
+              tma_load_3d(sQ + X * QTILE + dh * DHSTRIDE + hh * 8192, &p.tmQ, bar(B_QFULL), dh * 64, q0,
+                          b * a.H + h_base + 2 * X + hh);
+      }
+      __syncwarp();
       int it = 0;
       bool ok = true;
       for (int br = 0; br < 3 && ok; ++br) {
@@ -198,90 +203,120 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
           const Tile tl = get_tile(br, t);
           const int s = it & 1, ph = (it >> 1) & 1;
           const uint32_t bytes = (uint32_t)tl.nch * 64 * D * 2;
-          ok = mbar_wait(bar(B_KEMPTY + s), ph ^ 1, &abort_flag);
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(B_KEMPTY + s), ph ^ 1, &abort_flag));
           if (!ok) { fail_id = B_KEMPTY + s + 1; break; }
-          mbar_expect_tx(bar(B_KFULL + s), bytes);
-          for (int c = 0; c < tl.nch; ++c)
-            for (int dh = 0; dh < DH; ++dh)
-              tma_load_3d(sK + s * KVTILE + dh * DHSTRIDE + c * 8192, mk, bar(B_KFULL + s), dh * 64, tl.j0[c], kv_slab);
+          if (leader) {
+            mbar_expect_tx(bar(B_KFULL + s), bytes);
+            for (int c = 0; c < tl.nch; ++c)
+              for (int dh = 0; dh < DH; ++dh)
+                tma_load_3d(sK + s * KVTILE + dh * DHSTRIDE + c * 8192, mk, bar(B_KFULL + s), dh * 64, tl.j0[c], kv_slab);
+          }
           last_k_it = it;
-          ok = mbar_wait(bar(B_VEMPTY + s), ph ^ 1, &abort_flag);
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(B_VEMPTY + s), ph ^ 1, &abort_flag));
           if (!ok) { fail_id = B_VEMPTY + s + 1; break; }
-          mbar_expect_tx(bar(B_VFULL + s), bytes);
-          for (int c = 0; c < tl.nch; ++c)
-            for (int dh = 0; dh < DH; ++dh)
-              tma_load_3d(sV + s * KVTILE + dh * DHSTRIDE + c * 8192, mv, bar(B_VFULL + s), dh * 64, tl.j0[c], kv_slab);
+          if (leader) {
+            mbar_expect_tx(bar(B_VFULL + s), bytes);
+            for (int c = 0; c < tl.nch; ++c)
+              for (int dh = 0; dh < DH; ++dh)
+                tma_load_3d(sV + s * KVTILE + dh * DHSTRIDE + c * 8192, mv, bar(B_VFULL + s), dh * 64, tl.j0[c], kv_slab);
+          }
           last_v_it = it;
+          __syncwarp();
         }
       }
     }
   } else if (warp == 1) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;\n");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;\n");
     // =============================== MMA issuer ===============================
-    if (lane == 0) {
+    // The whole warp walks the tile sequence converged; one elected lane issues the MMAs and commits.
+    // Everything an MMA needs beyond an add is computed before the loop.
+    {
+      const bool leader = elect_one();
       constexpr uint32_t IDESC_PV = idesc_f16(FMT, 128, D, 0, 1);
-      bool ok = mbar_wait(bar(B_QFULL), 0, &abort_flag);
+      constexpr uint32_t IDESC_QK1 = idesc_f16(FMT, 128, 64, 0, 0);
+      constexpr uint32_t IDESC_QK2 = idesc_f16(FMT, 128, 128, 0, 0);
+      bool ok = __all_sync(0xffffffffu, mbar_wait(bar(B_QFULL), 0, &abort_flag));
       if (!ok) fail_id = B_QFULL + 1;
-      // flattened tile sequence over the branches
-      int br_of[3], nt_of[3], nbr = 0, total_tiles = 0;
-      for (int br = 0; br < 3; ++br) {
-        int nt = (nchunks[br] + 1) >> 1;
-        if (nt > 0) { br_of[nbr] = br; nt_of[nbr] = nt; ++nbr; total_tiles += nt; }
-      }
-      auto locate = [&](int it, int& br, int& t) {
-        int k = 0;
-        while (it >= nt_of[k]) { it -= nt_of[k]; ++k; }
-        br = br_of[k]; t = it;
-      };
-      auto issue_qk = [&](int X, int it) {
-        int br, t;
-        locate(it, br, t);
-        const Tile tl = get_tile(br, t);
-        const int s = it & 1, ph = (it >> 1) & 1;
+      // tile counts per branch and in total; (cur_br, cur_t) walk the flattened sequence
+      int nt_of[3], total_tiles = 0;
+#pragma unroll
+      for (int br = 0; br < 3; ++br) { nt_of[br] = (nchunks[br] + 1) >> 1; total_tiles += nt_of[br]; }
+      // descriptor bases: the low word carries the address field, so "+ (bytes >> 4)" moves the start
+      const uint64_t dQ[2] = {smem_desc_sw128(sQ, 16, 1024), smem_desc_sw128(sQ + QTILE, 16, 1024)};
+      const uint64_t dK[2] = {smem_desc_sw128(sK, 16, 1024), smem_desc_sw128(sK + KVTILE, 16, 1024)};
+      const uint64_t dV[2] = {smem_desc_sw128(sV, DHSTRIDE, 1024), smem_desc_sw128(sV + KVTILE, DHSTRIDE, 1024)};
+      const uint32_t tSx[2] = {tmem, tmem + 128}, tOx[2] = {tmem + 256, tmem + 384};
+
+      // position of the tile whose QK is issued next / whose PV is issued next
+      int q_br = 0, q_t = 0, p_br = 0, p_t = 0;
+      auto skip_empty = [&](int& br, int& t) { while (br < 3 && t >= nt_of[br]) { ++br; t = 0; } };
+      skip_empty(q_br, q_t);
+      skip_empty(p_br, p_t);
+
+      auto issue_qk = [&](int X, int it) {          // uses (q_br, q_t); the caller advances them after X == 1
+        const int nch = min(2, nchunks[q_br] - 2 * q_t);
+        const int s = it & 1;
         if (X == 0) {
-          if (!mbar_wait(bar(B_KFULL + s), ph, &abort_flag)) { fail_id = B_KFULL + s + 1; return false; }
+          if (!__all_sync(0xffffffffu, mbar_wait(bar(B_KFULL + s), (it >> 1) & 1, &abort_flag))) { fail_id = B_KFULL + s + 1; return false; }
           tc_fence_after();
         }
-        const uint32_t idesc = idesc_f16(FMT, 128, 64 * tl.nch, 0, 0);
+        const uint32_t idesc = nch == 2 ? IDESC_QK2 : IDESC_QK1;
+        if (leader) {
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * DHSTRIDE + (ks & 3) * 32;
-          mma_ss(tmem + X * 128, smem_desc_sw128(sQ + X * QTILE + off, 16, 1024),
-                 smem_desc_sw128(sK + s * KVTILE + off, 16, 1024), idesc, ks > 0);
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint32_t off = (uint32_t)(((ks >> 2) * DHSTRIDE + (ks & 3) * 32) >> 4);
+            if (ks == 0) mma_ss(tSx[X], dQ[X] + off, dK[s] + off, idesc, 0u);
+            else mma_ss(tSx[X], dQ[X] + off, dK[s] + off, idesc, 1u);
+          }
+          tc_commit(bar(B_SFULL + X));
+          if (X == 1) tc_commit(bar(B_KEMPTY + s));
         }
-        tc_commit(bar(B_SFULL + X));
-        if (X == 1) tc_commit(bar(B_KEMPTY + s));
+        __syncwarp();
         return true;
       };
-      if (ok && total_tiles > 0) ok = issue_qk(0, 0) && issue_qk(1, 0);
+      if (ok && total_tiles > 0) {
+        ok = issue_qk(0, 0) && issue_qk(1, 0);
+        ++q_t; skip_empty(q_br, q_t);
+      }
       for (int it = 0; it < total_tiles && ok; ++it) {
-        int br, t;
-        locate(it, br, t);
-        const Tile tl = get_tile(br, t);
-        const int s = it & 1, ph = (it >> 1) & 1;
+        const int nch = min(2, nchunks[p_br] - 2 * p_t);
+        const bool fresh = p_t == 0;                       // first tile of a branch starts a new O
+        const int s = it & 1;
         T5_TRACE(4096 + it * 8 + 0);
-        ok = mbar_wait(bar(B_VFULL + s), ph, &abort_flag);
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(B_VFULL + s), (it >> 1) & 1, &abort_flag));
         if (!ok) { fail_id = B_VFULL + s + 1; break; }
         T5_TRACE(4096 + it * 8 + 1);
-        for (int X = 0; X < 2 && ok; ++X) {
-          ok = mbar_wait(bar(B_PFULL + X), it & 1, &abort_flag);
+#pragma unroll
+        for (int X = 0; X < 2; ++X) {
+          if (!ok) break;
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(B_PFULL + X), it & 1, &abort_flag));
           if (!ok) { fail_id = B_PFULL + X + 1; break; }
           T5_TRACE(4096 + it * 8 + 2 + 2 * X);
           tc_fence_after();
-          for (int kk = 0; kk < 4 * tl.nch; ++kk)
-            mma_ts(tmem + 256 + X * 128, tmem + X * 128 + kk * 8,
-                   smem_desc_sw128(sV + s * KVTILE + kk * 2048, DHSTRIDE, 1024), IDESC_PV, (t > 0 || kk > 0) ? 1u : 0u);
-          tc_commit(bar(B_PVDONE + X));
-          if (X == 1) tc_commit(bar(B_VEMPTY + s));
+          if (leader) {
+            if (fresh) mma_ts(tOx[X], tSx[X], dV[s], IDESC_PV, 0u);
+            else mma_ts(tOx[X], tSx[X], dV[s], IDESC_PV, 1u);
+#pragma unroll
+            for (int kk = 1; kk < 4; ++kk) mma_ts(tOx[X], tSx[X] + kk * 8, dV[s] + kk * 128, IDESC_PV, 1u);
+            if (nch == 2) {
+#pragma unroll
+              for (int kk = 4; kk < 8; ++kk) mma_ts(tOx[X], tSx[X] + kk * 8, dV[s] + kk * 128, IDESC_PV, 1u);
+            }
+            tc_commit(bar(B_PVDONE + X));
+            if (X == 1) tc_commit(bar(B_VEMPTY + s));
+          }
+          __syncwarp();
           if (it + 1 < total_tiles) ok = issue_qk(X, it + 1);
           T5_TRACE(4096 + it * 8 + 3 + 2 * X);
         }
+        ++p_t; skip_empty(p_br, p_t);
+        if (it + 1 < total_tiles) { ++q_t; skip_empty(q_br, q_t); }
       }
     }
   } else if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;\n");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;\n");
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;\n");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;\n");
     // =============================== softmax / epilogue ===============================
     const int X = (warp - 4) >> 2;
     const int quarter = warp & 3;

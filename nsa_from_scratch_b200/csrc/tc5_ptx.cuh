@@ -9,6 +9,14 @@
 namespace nsa {
 namespace tc5 {
 
+// One lane of a fully converged warp (the tcgen05 / TMA instructions take warp-uniform operands: issuing
+// them from a converged warp under this predicate is several times cheaper than from a lone diverged lane).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t is_leader;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}\n" : "=r"(is_leader));
+  return is_leader != 0;
+}
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
