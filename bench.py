@@ -50,6 +50,10 @@ def parse():
     ap.add_argument("--engine", default="auto", choices=["auto", "generic", "tcgen05"])
     ap.add_argument("--select", default="group", choices=["group", "head"],
                     help="block lists shared by the query heads of a KV head (group) or one per query head (head)")
+    ap.add_argument("--layout", default="dp", choices=["dp", "cp"],
+                    help="dp: every rank runs the whole workload on its own batch element (weak scaling); "
+                         "cp: context parallel, --seq-len is the TOTAL length, queries sharded contiguously, "
+                         "K/V all-gathered over NCCL inside the timed step (strong scaling)")
     ap.add_argument("--cpu-tiles", type=int, default=40, help="64-row query tiles in the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -216,6 +220,8 @@ def run_ours(a):
                         top_k=a.top_k, window_size=a.window, force_first=1, force_local=2,
                         select_per_group=a.select == "group")
     engine = {"auto": L.ENGINE_AUTO, "generic": L.ENGINE_GENERIC, "tcgen05": L.ENGINE_TCGEN05}[a.engine]
+    if a.layout == "cp":
+        return run_cp(a, nsa, cfg, rank, world, dist, barrier)
     Qh, Kh, Vh, Gh = make_inputs(a, a.seed + rank)
     Qh, Kh, Vh, Gh = (t.pin_memory() for t in (Qh, Kh, Vh, Gh))
     Q, K, V, G = (t.cuda(non_blocking=True) for t in (Qh, Kh, Vh, Gh))
@@ -340,6 +346,57 @@ def run_ours(a):
             "gpu_launches": LAUNCHES_PER_STEP * a.steps,
         }
         ops.device_status()
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def run_cp(a, nsa, cfg, rank, world, dist, barrier):
+    """Context-parallel layout: rank r holds rows [r*Tl, (r+1)*Tl) of Q / gates / out and of K, V."""
+    import copy
+    from nsa_from_scratch_b200 import ops, parallel
+    T = a.seq_len
+    assert T % (world * 64) == 0, "--seq-len must be a multiple of 64 * ranks for the cp layout"
+    loc = copy.copy(a)
+    loc.seq_len = T // world
+    Q, K, V, G = (t.cuda() for t in make_inputs(loc, a.seed + rank))
+    group = None
+
+    def step():
+        if world > 1:
+            return parallel.nsa_forward_context_parallel(Q, K, V, cfg, gate_logits=G, group=group)
+        return nsa.nsa_forward(Q, K, V, cfg, gate_logits=G)
+    for _ in range(a.warmup):
+        out = step()
+    barrier()
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0"))) if rank == 0 else None
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    barrier()
+    ev[0].record()
+    for _ in range(a.steps):
+        out = step()
+    ev[1].record()
+    barrier()
+    ms = ev[0].elapsed_time(ev[1])
+    clocks = sampler.stop() if sampler else None
+    if dist is not None:
+        t_ = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t_, op=dist.ReduceOp.MAX)
+        ms = float(t_.item())
+    ms_step = ms / a.steps
+    ops.device_status()
+    if rank == 0:
+        kv_bytes = 2 * K.numel() * K.element_size() * (world - 1)
+        line = {
+            "metric": METRIC, "value": T / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": a.steps,
+            "warmup": a.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": workload_name(a) + " [context parallel: total T, contiguous query shards]",
+                       "global_batch": 1, "seq_len": T, "parallelism": f"cp{world}: all-gather of K/V ({kv_bytes} B received per rank per step) + local forward",
+                       "l2": "inputs exceed the 126 MB L2"},
+            "roofline": None, "cpu_baseline": None, "e2e": None, "clocks": clocks,
+            "gpu_launches": 6 * a.steps,
+        }
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()

@@ -383,13 +383,11 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
         if (tl.nch == 2) { tmem_ld32(tS + 64, sv[2]); tmem_ld32(tS + 96, sv[3]); }
         tc_wait_ld();
         // valid column range of each chunk for this row; masked entries become -inf
-        bool full = true;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           const int vlo = max(lo - tl.j0[c], 0);
           const int vhi = c < tl.nch ? min(hi, tl.jlim[c] - 1) - tl.j0[c] : -1;
           if (c < tl.nch && (vlo > 0 || vhi < 63)) {
-            full = false;
 #pragma unroll
             for (int g = 0; g < 2; ++g)
 #pragma unroll
@@ -408,7 +406,6 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
 #pragma unroll
             for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[g][i]));
         }
-        (void)full;
         if (quarter == 0 && lane == 0) T5_TRACE(X * 2048 + it * 8 + 2);
         mx *= p.scale_log2;                                  // scale > 0 keeps the order
         // lazy rescale: only when some row of the warp outgrows its reference maximum by 2^8

@@ -110,7 +110,7 @@ __global__ void __launch_bounds__(256) select_blocks_kernel(const T* __restrict_
                                                             int k_out, int bm, int bn, int offset, int causal, float scale,
                                                             int force_first, int force_local, int R) {
   constexpr int KT = 64;
-  constexpr int PITCH = D + 2;     // 16-bit elements; odd word stride -> conflict-free row reads
+  constexpr int PITCH = D + 8;     // 16-bit elements; 16-byte aligned rows, 17-chunk stride -> conflict-free 128-bit reads
   extern __shared__ __align__(16) unsigned char smem[];
   T* kt = reinterpret_cast<T*>(smem);                              // [KT][PITCH]
   const int G = H / Hkv;
@@ -145,32 +145,57 @@ __global__ void __launch_bounds__(256) select_blocks_kernel(const T* __restrict_
   for (int c0 = 0; c0 <= cmax_chunk; c0 += KT) {
     __syncthreads();
     const int nrow = min(KT, nk - c0);
-    for (int i = threadIdx.x; i < nrow * (D / 2); i += blockDim.x) {
-      int r = i / (D / 2), w = i % (D / 2);
-      reinterpret_cast<uint32_t*>(kt + r * PITCH)[w] = reinterpret_cast<const uint32_t*>(kbase + (size_t)(c0 + r) * D)[w];
+    for (int i = threadIdx.x; i < KT * (D / 8); i += blockDim.x) {
+      const int r = i / (D / 8), w = i % (D / 8);
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (r < nrow) v = reinterpret_cast<const uint4*>(kbase + (size_t)(c0 + r) * D)[w];
+      reinterpret_cast<uint4*>(kt + r * PITCH)[w] = v;
     }
     __syncthreads();
-    if (warp < rows) {
+    if (warp < rows && c0 <= my_cmax) {
+      // lane owns blocks c0+lane and c0+lane+32; heads are taken four at a time so that one 128-bit
+      // read of a K mean feeds 32 fma.  Each (head, block) dot is its own fma chain in index order and
+      // the heads are added in head order, so the value does not depend on this tiling.
+      const uint4* k0 = reinterpret_cast<const uint4*>(kt + lane * PITCH);
+      const uint4* k1 = reinterpret_cast<const uint4*>(kt + (lane + 32) * PITCH);
+      float tot0 = 0.f, tot1 = 0.f;
+      for (int g0 = 0; g0 < GS; g0 += 4) {
+        float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
+        const int ng = min(4, GS - g0);
+#pragma unroll 2
+        for (int w = 0; w < D / 8; ++w) {
+          const uint4 kv0 = k0[w], kv1 = k1[w];
+          const uint32_t kw0[4] = {kv0.x, kv0.y, kv0.z, kv0.w}, kw1[4] = {kv1.x, kv1.y, kv1.z, kv1.w};
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (g < ng) {
+              const uint4 qv = reinterpret_cast<const uint4*>(qs + (warp * GS + g0 + g) * D)[w];
+              const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 qf = Elem<T>::unpack(qw[e]);
+                const float2 f0 = Elem<T>::unpack(kw0[e]), f1 = Elem<T>::unpack(kw1[e]);
+                a0[g] = __fmaf_rn(qf.x, f0.x, a0[g]);
+                a0[g] = __fmaf_rn(qf.y, f0.y, a0[g]);
+                a1[g] = __fmaf_rn(qf.x, f1.x, a1[g]);
+                a1[g] = __fmaf_rn(qf.y, f1.y, a1[g]);
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          if (g < ng) {
+            tot0 = (g0 + g == 0) ? a0[g] : __fadd_rn(tot0, a0[g]);
+            tot1 = (g0 + g == 0) ? a1[g] : __fadd_rn(tot1, a1[g]);
+          }
+        }
+      }
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        int r = lane + half * 32;
-        int c = c0 + r;
-        if (r < nrow && c <= my_cmax) {
-          const uint32_t* kr = reinterpret_cast<const uint32_t*>(kt + r * PITCH);
-          float tot = 0.f;
-          for (int gs = 0; gs < GS; ++gs) {
-            const uint32_t* qr = reinterpret_cast<const uint32_t*>(qs + (warp * GS + gs) * D);
-            float acc = 0.f;
-#pragma unroll 8
-            for (int w = 0; w < D / 2; ++w) {
-              float2 kf = Elem<T>::unpack(kr[w]);
-              float2 qf = Elem<T>::unpack(qr[w]);
-              acc = __fmaf_rn(qf.x, kf.x, acc);
-              acc = __fmaf_rn(qf.y, kf.y, acc);
-            }
-            tot = gs == 0 ? acc : __fadd_rn(tot, acc);
-          }
-          float v = tot * scale;
+        const int c = c0 + lane + half * 32;
+        if (lane + half * 32 < nrow && c <= my_cmax) {
+          float v = (half == 0 ? tot0 : tot1) * scale;
           if (c < force_first || c > my_cmax - force_local) v = INFINITY;
           my_sc[c] = v;
         }
@@ -187,7 +212,7 @@ __global__ void __launch_bounds__(256) select_blocks_kernel(const T* __restrict_
 template <typename T>
 static int select_launch(const void* Qb, const void* Kb, int32_t* idx, int B, int H, int Hkv, int Hi, int nq, int nk, int D,
                          int k_out, int bm, int bn, int offset, int causal, float scale, int ff, int fl, cudaStream_t st) {
-  const size_t fixed = (size_t)64 * (D + 2) * 2;
+  const size_t fixed = (size_t)64 * (D + 8) * 2;
   int R = 8;
   const int GS = Hi == H ? 1 : H / Hkv;
   auto need = [&](int r) { return fixed + (size_t)r * GS * D * 2 + 4 + (size_t)r * nk * 4; };
