@@ -54,6 +54,9 @@ def parse():
                     help="dp: every rank runs the whole workload on its own batch element (weak scaling); "
                          "cp: context parallel, --seq-len is the TOTAL length, queries sharded contiguously, "
                          "K/V all-gathered over NCCL inside the timed step (strong scaling)")
+    ap.add_argument("--sweep", action="store_true",
+                    help="instead of the single contract line: one JSON line per point of the T x D sweep "
+                         "(T = 1k..64k, D = 64/128, Hq=64/Hkv=4) plus the reference's own MHA shape (H=16, D=64, 64/64)")
     ap.add_argument("--cpu-tiles", type=int, default=40, help="64-row query tiles in the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -402,8 +405,111 @@ def run_cp(a, nsa, cfg, rank, world, dist, barrier):
         dist.destroy_process_group()
 
 
+def run_sweep(a):
+    """One line per sweep point: tokens/s with inputs resident, fused-kernel time and TFLOP/s."""
+    import copy
+    import nsa_from_scratch_b200 as nsa
+    from nsa_from_scratch_b200 import forward as F, ops
+    torch.cuda.set_device(0)
+    points = [dict(seq_len=T, head_dim=D, heads=64, kv_heads=4, cmp_block=32, cmp_stride=16, select="group")
+              for D in (128, 64) for T in (1024, 2048, 4096, 8192, 16384, 32768, 65536)]
+    points += [dict(seq_len=T, head_dim=64, heads=16, kv_heads=16, cmp_block=64, cmp_stride=64, select="head")
+               for T in (4096, 16384, 65536)]
+    for pt in points:
+        b = copy.copy(a)
+        for k, v in pt.items():
+            setattr(b, k, v)
+        forced = (1, 2) if b.select == "group" else (0, 0)        # the MHA points use the reference's plain top-k
+        cfg = nsa.NSAConfig(block_size_c=b.cmp_block, stride_c=b.cmp_stride, top_k=b.top_k, window_size=b.window,
+                            force_first=forced[0], force_local=forced[1], select_per_group=b.select == "group")
+        Q, K, V, G = (t.cuda() for t in make_inputs(b, a.seed))
+        scale = b.head_dim ** -0.5
+        for _ in range(a.warmup):
+            nsa.nsa_forward(Q, K, V, cfg, gate_logits=G)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(a.steps):
+            nsa.nsa_forward(Q, K, V, cfg, gate_logits=G)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / a.steps
+        idx = F._resolve_block_indices(Q, K, block_size_m=64, block_size_n=64, top_k=b.top_k, causal=True, scale=scale,
+                                       force_first=forced[0], force_local=forced[1], shared_per_group=b.select == "group")
+        flops = algorithmic_flops(b, idx)["total"]
+        ops.device_status()
+        print(json.dumps({"metric": METRIC, "value": b.seq_len / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms,
+                          "algorithmic_tflop": flops / 1e12, "tflops_whole_step": flops / (ms * 1e-3) / 1e12,
+                          "config": {"workload": workload_name(b)}}), flush=True)
+        del Q, K, V, G
+        torch.cuda.empty_cache()
+
+    def timed(fn, n):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    # selected-branch forward + backward at the training shape (B=2, T=32768, Hq=12, Hkv=1, D=64)
+    g = torch.Generator().manual_seed(a.seed)
+    B, H, Hkv, T, D = 2, 12, 1, 32768, 64
+    Q = torch.randn(B, H, T, D, generator=g).to(torch.bfloat16).cuda()
+    K = torch.randn(B, Hkv, T, D, generator=g).to(torch.bfloat16).cuda()
+    V = torch.randn(B, Hkv, T, D, generator=g).to(torch.bfloat16).cuda()
+    dO = torch.randn(B, H, T, D, generator=g).to(torch.bfloat16).cuda()
+    for shared in (False, True):
+        idx = F._resolve_block_indices(Q, K, block_size_m=64, block_size_n=64, top_k=16, causal=True, scale=D ** -0.5,
+                                       shared_per_group=shared)
+        out, lse = nsa.selected_attention(Q, K, V, block_indices=idx)
+        nq = T // 64
+        qb = torch.arange(nq, device="cuda").view(1, 1, nq, 1)
+        pairs = (int(((idx < qb) & (idx >= 0)).sum()) * 4096 + int((idx == qb).sum()) * 2080) * (H // idx.shape[1])
+        ms_f = timed(lambda: nsa.selected_attention(Q, K, V, block_indices=idx), a.steps)
+        ms_b = timed(lambda: nsa.selected_backward(dO, Q, K, V, out, lse, idx, block_size_m=64, block_size_n=64, causal=True,
+                                                   scale=D ** -0.5, Tq=T, Tk=T, return_fp32=True), a.steps)
+        ops.device_status()
+        print(json.dumps({"metric": "selected_fwd_bwd_ms", "config": {"workload": f"selected branch B={B} T={T} Hq={H} Hkv={Hkv} D={D} bf16, "
+                          f"block lists per {'group' if shared else 'head'}"}, "fwd_ms": ms_f, "bwd_ms": ms_b,
+                          "fwd_tflops": 4 * D * pairs / (ms_f * 1e-3) / 1e12, "bwd_tflops": 10 * D * pairs / (ms_b * 1e-3) / 1e12,
+                          "tokens_per_s_fwd_bwd": B * T / ((ms_f + ms_b) * 1e-3)}), flush=True)
+    del Q, K, V, dO
+    torch.cuda.empty_cache()
+
+    # fp8 storage forward (e4m3, per-tensor absmax scales, 0.1 % outliers x20) at T=32768
+    b = copy.copy(a)
+    b.seq_len = 32768
+    Qh, Kh, Vh, Gh = make_inputs(b, a.seed)
+    gq = torch.Generator().manual_seed(a.seed + 1)
+    xs = []
+    for t in (Qh, Kh, Vh):
+        t = t.float()
+        t = torch.where(torch.rand(t.shape, generator=gq) < 1e-3, t * 20, t)
+        xs.append(t.to(torch.bfloat16).cuda())
+    q8, k8, v8 = (nsa.quantize_to_fp8(t) for t in xs)
+    cfg = nsa.NSAConfig(block_size_c=b.cmp_block, stride_c=b.cmp_stride, top_k=b.top_k, window_size=b.window,
+                        force_first=1, force_local=2, select_per_group=True)
+    Gc = Gh.cuda()
+    o8 = nsa.nsa_forward_fp8(q8[0], k8[0], v8[0], q8[1], k8[1], v8[1], cfg, gate_logits=Gc)
+    deq = [(t.to(torch.bfloat16) * sc) for t, sc in (q8, k8, v8)]
+    ob = nsa.nsa_forward(deq[0], deq[1], deq[2], cfg, gate_logits=Gc)
+    ms8 = timed(lambda: nsa.nsa_forward_fp8(q8[0], k8[0], v8[0], q8[1], k8[1], v8[1], cfg, gate_logits=Gc), max(2, a.steps // 2))
+    msb = timed(lambda: nsa.nsa_forward(deq[0], deq[1], deq[2], cfg, gate_logits=Gc), a.steps)
+    ops.device_status()
+    print(json.dumps({"metric": "nsa_fwd_fp8_tokens_per_s", "value": b.seq_len / (ms8 * 1e-3), "ms_per_step": ms8,
+                      "bf16_same_values_ms": msb, "max_abs_vs_bf16_path": float((o8.float() - ob.float()).abs().max()),
+                      "config": {"workload": workload_name(b) + " [fp8 e4m3 storage, dequantised in-kernel]"}}), flush=True)
+
+
 def main():
     a = parse()
+    if a.sweep:
+        return run_sweep(a)
     if a.impl == "reference":
         run_reference(a)
     else:

@@ -395,17 +395,21 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
                 if (g * 32 + i < vlo || g * 32 + i > vhi) sv[2 * c + g][i] = 0xff800000u;   // -inf
           }
         }
-        float mx = -INFINITY;
+        // row maximum: eight independent chains (a single chain of 128 dependent max ops is latency-bound)
+        float mxa[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) mxa[i] = -INFINITY;
 #pragma unroll
         for (int g = 0; g < 2; ++g)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[g][i]));
+          for (int i = 0; i < 32; ++i) mxa[i & 7] = fmaxf(mxa[i & 7], __uint_as_float(sv[g][i]));
         if (tl.nch == 2) {
 #pragma unroll
           for (int g = 2; g < 4; ++g)
 #pragma unroll
-            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[g][i]));
+            for (int i = 0; i < 32; ++i) mxa[i & 7] = fmaxf(mxa[i & 7], __uint_as_float(sv[g][i]));
         }
+        float mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])), fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
         if (quarter == 0 && lane == 0) T5_TRACE(X * 2048 + it * 8 + 2);
         mx *= p.scale_log2;                                  // scale > 0 keeps the order
         // lazy rescale: only when some row of the warp outgrows its reference maximum by 2^8
@@ -432,7 +436,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
         }
         const float m_ref = m_used == -INFINITY ? 0.f : m_used;
         // P = exp2(S*scale - m_ref) as 16-bit into the columns S occupied (-inf -> 0)
-        float psum0 = 0.f, psum1 = 0.f;
+        float psum0 = 0.f, psum1 = 0.f, psum2 = 0.f, psum3 = 0.f;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           if (g < 2 * tl.nch) {
@@ -441,13 +445,14 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
             for (int i = 0; i < 16; ++i) {
               const float p0 = ex2(fmaf(__uint_as_float(sv[g][2 * i]), p.scale_log2, -m_ref));
               const float p1 = ex2(fmaf(__uint_as_float(sv[g][2 * i + 1]), p.scale_log2, -m_ref));
-              psum0 += p0;
-              psum1 += p1;
+              if (i & 1) { psum2 += p0; psum3 += p1; } else { psum0 += p0; psum1 += p1; }
               pk[i] = Elem<T>::pack(p0, p1);
             }
             tmem_st16(tS + g * 16, pk);
           }
         }
+        psum0 += psum2;
+        psum1 += psum3;
         l += psum0 + psum1;
         if (quarter == 0 && lane == 0) T5_TRACE(X * 2048 + it * 8 + 3);
         tc_wait_st();
