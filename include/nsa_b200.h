@@ -73,9 +73,9 @@ int nsa_pool_mean(const void* x, void* out, int B, int H, int T, int D, int bloc
  * score = fp32 dot over D (fma in index order) * scale; block c is legal for q block q iff
  * !causal or c*bn <= q*bm + bm-1 + offset.  force_first / force_local give score +inf to
  * the first blocks and to the last legal blocks of each row (0/0 = the reference).
- * shared_per_group != 0: one index row per KV head, idx [B,Hkv,nq,k_out]; its score is the
- * sum, in head order, of the per-head scores of the H/Hkv query heads that share the KV head
- * (0 = the reference: one row per query head).
+ * shared_per_group != 0: one index row per KV head, idx [B,Hkv,nq,k_out]; its query vector is
+ * the fp32 sum, in head order, of the block means of the H/Hkv query heads that share the KV
+ * head (0 = the reference: one row per query head).
  * Replaces: _resolve_block_indices, nsa/triton/forward.py:321-359 (einsum + mask + topk). */
 int nsa_select_blocks(const void* Qb, const void* Kb, int32_t* idx, int B, int H, int Hkv, int nq,
                       int nk, int D, int top_k, int bm, int bn, int offset, int causal, float scale,

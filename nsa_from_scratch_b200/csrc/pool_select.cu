@@ -101,8 +101,10 @@ __device__ void warp_topk_row(float* s, int n_scan, int nk, int k_out, int32_t* 
 
 // ------------------------------------------------------------------ score + select
 // Thread block = (batch, index head, chunk of R query blocks); warp w owns query block row w.
-// An index head is a query head (GS = 1) or, for indices shared by a GQA group, a KV head whose
-// score is the sum over its GS = H/Hkv query heads (per-head dots added in head order).
+// An index head is a query head (GS = 1) or, for indices shared by a GQA group, a KV head; its query
+// vector is then the fp32 sum, in head order, of the block means of its GS = H/Hkv query heads (the
+// score of the group is the dot of that sum with the K block mean -- GS times less work than summing
+// per-head dots, and the definition the CPU oracle restates).
 // Kb tiles of 64 block-means are staged in shared memory once per chunk and shared by the rows.
 template <typename T, int D>
 __global__ void __launch_bounds__(256) select_blocks_kernel(const T* __restrict__ Qb, const T* __restrict__ Kb,
@@ -115,8 +117,8 @@ __global__ void __launch_bounds__(256) select_blocks_kernel(const T* __restrict_
   T* kt = reinterpret_cast<T*>(smem);                              // [KT][PITCH]
   const int G = H / Hkv;
   const int GS = Hi == H ? 1 : G;                                  // query heads summed per index head
-  T* qs = kt + KT * PITCH;                                         // [R][GS][D]
-  float* sc = reinterpret_cast<float*>(qs + R * GS * D);           // [R][nk]
+  float* qs = reinterpret_cast<float*>(kt + KT * PITCH);           // [R][D] fp32 query vectors
+  float* sc = qs + R * D;                                          // [R][nk]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh = blockIdx.y, b = bh / Hi, hi = bh % Hi;
   const int hk = Hi == H ? hi / G : hi;
@@ -125,9 +127,11 @@ __global__ void __launch_bounds__(256) select_blocks_kernel(const T* __restrict_
   const int rows = min(R, nq - qb0);
   const T* kbase = Kb + ((size_t)(b * Hkv + hk) * nk) * D;
 
-  for (int i = threadIdx.x; i < rows * GS * D; i += blockDim.x) {
-    const int r = i / (GS * D), gs = (i / D) % GS, d = i % D;
-    qs[i] = Qb[(((size_t)b * H + h0 + gs) * nq + qb0 + r) * D + d];
+  for (int i = threadIdx.x; i < rows * D; i += blockDim.x) {
+    const int r = i / D, d = i % D;
+    float acc = Elem<T>::to_f(Qb[(((size_t)b * H + h0) * nq + qb0 + r) * D + d]);
+    for (int gs = 1; gs < GS; ++gs) acc = __fadd_rn(acc, Elem<T>::to_f(Qb[(((size_t)b * H + h0 + gs) * nq + qb0 + r) * D + d]));
+    qs[i] = acc;
   }
 
   // legal range per row: blocks 0..cmax
@@ -153,42 +157,24 @@ __global__ void __launch_bounds__(256) select_blocks_kernel(const T* __restrict_
     }
     __syncthreads();
     if (warp < rows && c0 <= my_cmax) {
-      // lane owns blocks c0+lane and c0+lane+32; heads are taken four at a time so that one 128-bit
-      // read of a K mean feeds 32 fma.  Each (head, block) dot is its own fma chain in index order and
-      // the heads are added in head order, so the value does not depend on this tiling.
+      // lane owns blocks c0+lane and c0+lane+32: two independent fma chains in index order
       const uint4* k0 = reinterpret_cast<const uint4*>(kt + lane * PITCH);
       const uint4* k1 = reinterpret_cast<const uint4*>(kt + (lane + 32) * PITCH);
+      const float4* qv = reinterpret_cast<const float4*>(qs + warp * D);
       float tot0 = 0.f, tot1 = 0.f;
-      for (int g0 = 0; g0 < GS; g0 += 4) {
-        float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
-        const int ng = min(4, GS - g0);
-#pragma unroll 2
-        for (int w = 0; w < D / 8; ++w) {
-          const uint4 kv0 = k0[w], kv1 = k1[w];
-          const uint32_t kw0[4] = {kv0.x, kv0.y, kv0.z, kv0.w}, kw1[4] = {kv1.x, kv1.y, kv1.z, kv1.w};
+#pragma unroll 4
+      for (int w = 0; w < D / 8; ++w) {
+        const uint4 kv0 = k0[w], kv1 = k1[w];
+        const float4 qa = qv[2 * w], qb_ = qv[2 * w + 1];
+        const float q[8] = {qa.x, qa.y, qa.z, qa.w, qb_.x, qb_.y, qb_.z, qb_.w};
+        const uint32_t kw0[4] = {kv0.x, kv0.y, kv0.z, kv0.w}, kw1[4] = {kv1.x, kv1.y, kv1.z, kv1.w};
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            if (g < ng) {
-              const uint4 qv = reinterpret_cast<const uint4*>(qs + (warp * GS + g0 + g) * D)[w];
-              const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 qf = Elem<T>::unpack(qw[e]);
-                const float2 f0 = Elem<T>::unpack(kw0[e]), f1 = Elem<T>::unpack(kw1[e]);
-                a0[g] = __fmaf_rn(qf.x, f0.x, a0[g]);
-                a0[g] = __fmaf_rn(qf.y, f0.y, a0[g]);
-                a1[g] = __fmaf_rn(qf.x, f1.x, a1[g]);
-                a1[g] = __fmaf_rn(qf.y, f1.y, a1[g]);
-              }
-            }
-          }
-        }
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          if (g < ng) {
-            tot0 = (g0 + g == 0) ? a0[g] : __fadd_rn(tot0, a0[g]);
-            tot1 = (g0 + g == 0) ? a1[g] : __fadd_rn(tot1, a1[g]);
-          }
+        for (int e = 0; e < 4; ++e) {
+          const float2 f0 = Elem<T>::unpack(kw0[e]), f1 = Elem<T>::unpack(kw1[e]);
+          tot0 = __fmaf_rn(q[2 * e], f0.x, tot0);
+          tot0 = __fmaf_rn(q[2 * e + 1], f0.y, tot0);
+          tot1 = __fmaf_rn(q[2 * e], f1.x, tot1);
+          tot1 = __fmaf_rn(q[2 * e + 1], f1.y, tot1);
         }
       }
 #pragma unroll
@@ -215,7 +201,8 @@ static int select_launch(const void* Qb, const void* Kb, int32_t* idx, int B, in
   const size_t fixed = (size_t)64 * (D + 8) * 2;
   int R = 8;
   const int GS = Hi == H ? 1 : H / Hkv;
-  auto need = [&](int r) { return fixed + (size_t)r * GS * D * 2 + 4 + (size_t)r * nk * 4; };
+  auto need = [&](int r) { return fixed + (size_t)r * D * 4 + (size_t)r * nk * 4; };
+  (void)GS;
   while (R > 1 && need(R) > 200 * 1024) R >>= 1;
   NSA_REQUIRE(need(R) <= 200 * 1024, NSA_ERR_UNSUPPORTED, "select: %d KV blocks exceed the shared-memory score row", nk);
   dim3 grid((unsigned)((nq + R - 1) / R), (unsigned)(B * Hi));

@@ -178,21 +178,23 @@ def block_scores(Q: Tensor, K: Tensor, *, block_size_m: int = 64, block_size_n: 
                  scale: Optional[float] = None, group_shared: bool = False) -> Tensor:
     """fp32 [B,H,nq,nk] scores: block means of Q and K taken in the input
     dtype, cast to fp32, dotted, times scale (forward.py:301-318,344-347).
-    group_shared (parity unpinned): [B,Hkv,nq,nk], the per-head dots of the
-    heads sharing a KV head added in head order, then scaled."""
+    group_shared (parity unpinned): [B,Hkv,nq,nk]; the query vector of a KV
+    head is the fp32 sum, in head order, of the block means of the query heads
+    that share it."""
     B, H, Tq, D = Q.shape
     Hkv = K.shape[1]
     G = _group(H, Hkv)
     Qb = pool_mean(Q, block_size_m).float()
     Kb = pool_mean(K, block_size_n).float()
-    Kb = Kb.repeat_interleave(G, dim=1) if G > 1 else Kb
-    dots = torch.matmul(Qb, Kb.transpose(-1, -2))
     if group_shared:
-        dots = dots.view(B, Hkv, G, dots.shape[-2], dots.shape[-1])
-        acc = dots[:, :, 0].clone()
-        for g in range(1, G):
-            acc = acc + dots[:, :, g]
-        dots = acc
+        Qg = Qb.view(B, Hkv, G, Qb.shape[2], D)
+        qsum = Qg[:, :, 0].clone()
+        for g in range(1, G):                       # fp32 sum of the heads' block means, in head order
+            qsum = qsum + Qg[:, :, g]
+        dots = torch.matmul(qsum, Kb.transpose(-1, -2))
+    else:
+        Kb = Kb.repeat_interleave(G, dim=1) if G > 1 else Kb
+        dots = torch.matmul(Qb, Kb.transpose(-1, -2))
     return dots * _softmax_scale(D, scale)
 
 
