@@ -46,7 +46,8 @@ __device__ long long g_tc5_trace[8192];
 struct Tc5Params {
   CUtensorMap tmQ, tmK, tmV, tmKc, tmVc;
   nsa_fwd_args a;
-  float scale_log2;
+  float scale_log2[3];   // per branch: softmax scale * log2(e) (* the fp8 dequantisation scales of the operands)
+  float out_scale[3];    // per branch: factor on P.V (the fp8 scale of V; 1 otherwise)
   int nk_blocks;
   int G4;          // query-head quads per KV head
 };
@@ -58,9 +59,10 @@ struct Tile {
 };
 
 // barrier ids
-enum { B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 3, B_VFULL = 5, B_VEMPTY = 7, B_SFULL = 9, B_PFULL = 11, B_PVDONE = 13, B_COUNT = 15 };
+enum { B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 3, B_VFULL = 5, B_VEMPTY = 7, B_SFULL = 9, B_PFULL = 11, B_PVDONE = 13,
+       B_STGFULL = 15, B_STGEMPTY = 17, B_COUNT = 19 };   // STG*: fp8 staging buffers (0 = K side, 1 = V side)
 
-template <int D, int FMT>
+template <int D, int FMT, bool IN8>
 __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_constant__ Tc5Params p) {
   using T = typename std::conditional<FMT == 1, __nv_bfloat16, __half>::type;
   constexpr int DH = D / 64;                    // 64-element (128-byte) halves of a row
@@ -74,6 +76,10 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
   const uint32_t sQ = smem_u32(smem);
   const uint32_t sK = sQ + 2 * QTILE;
   const uint32_t sV = sK + 2 * KVTILE;
+  // fp8 storage only: two staging buffers of 128 rows x D bytes (plain row-major), filled by TMA and turned
+  // into the swizzled 16-bit tiles above by warps 2 (K side) and 3 (V side); Q goes through them first
+  constexpr int STG = 128 * D;
+  unsigned char* stg = smem + 2 * QTILE + 4 * KVTILE;
   __shared__ __align__(8) uint64_t bars[B_COUNT];
   __shared__ int sel_list[T5_MAX_SEL];
   __shared__ int sel_n;
@@ -120,7 +126,8 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
   // ---- setup: barriers, TMEM, list of selected blocks ---------------------------------------
   if (tid == 0) {
     abort_flag = 0;
-    for (int i = 0; i < B_COUNT; ++i) mbar_init(bar(i), (i == B_PFULL || i == B_PFULL + 1) ? 128 : 1);
+    for (int i = 0; i < B_COUNT; ++i)
+      mbar_init(bar(i), (i == B_PFULL || i == B_PFULL + 1) ? 128 : ((IN8 && i == B_QFULL) ? 2 : 1));
     fence_barrier_init();
   }
   if (warp == 1) { tmem_alloc(smem_u32(&tmem_base_s), 512); tmem_relinquish(); }
@@ -175,6 +182,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
   };
   int fail_id = 0;   // barrier id (+1) this thread gave up on
   int last_k_it = -1, last_v_it = -1;   // producer: last tile whose K / V copies were issued
+  int last_u8 = -1;                     // producer (fp8): last use of the staging buffers that was issued
 
   if (warp == 0) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 72;\n");
@@ -185,23 +193,51 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
       if (leader) {
         tma_prefetch_desc(&p.tmQ); tma_prefetch_desc(&p.tmK); tma_prefetch_desc(&p.tmV);
         if (a.branches & NSA_BRANCH_COMPRESSED) { tma_prefetch_desc(&p.tmKc); tma_prefetch_desc(&p.tmVc); }
-        mbar_expect_tx(bar(B_QFULL), 2 * QTILE);
-        for (int X = 0; X < 2; ++X)
-          for (int hh = 0; hh < 2; ++hh)
-            for (int dh = 0; dh < DH; ++dh)
-              tma_load_3d(sQ + X * QTILE + dh * DHSTRIDE + hh * 8192, &p.tmQ, bar(B_QFULL), dh * 64, q0,
-                          b * a.H + h_base + 2 * X + hh);
+        if constexpr (IN8) {
+          last_u8 = 0;
+          // Q tile X (2 heads x 64 positions, D bytes per row) into staging buffer X
+          for (int X = 0; X < 2; ++X) {
+            mbar_expect_tx(bar(B_STGFULL + X), STG);
+            for (int hh = 0; hh < 2; ++hh)
+              tma_load_3d(smem_u32(stg) + X * STG + hh * 64 * D, &p.tmQ, bar(B_STGFULL + X), 0, q0, b * a.H + h_base + 2 * X + hh);
+          }
+        } else {
+          mbar_expect_tx(bar(B_QFULL), 2 * QTILE);
+          for (int X = 0; X < 2; ++X)
+            for (int hh = 0; hh < 2; ++hh)
+              for (int dh = 0; dh < DH; ++dh)
+                tma_load_3d(sQ + X * QTILE + dh * DHSTRIDE + hh * 8192, &p.tmQ, bar(B_QFULL), dh * 64, q0,
+                            b * a.H + h_base + 2 * X + hh);
+        }
       }
       __syncwarp();
-      int it = 0;
+      int it = 0;          // tile counter over all branches
+      int u8 = 1;          // fp8: use counter of the staging buffers (use 0 was Q)
       bool ok = true;
       for (int br = 0; br < 3 && ok; ++br) {
         const int nt = (nchunks[br] + 1) >> 1;
         const CUtensorMap* mk = br == 0 ? &p.tmKc : &p.tmK;
         const CUtensorMap* mv = br == 0 ? &p.tmVc : &p.tmV;
+        const bool raw8 = IN8 && br != 0;      // pooled K/V of the compressed branch are already 16-bit
         for (int t = 0; t < nt && ok; ++t, ++it) {
           const Tile tl = get_tile(br, t);
           const int s = it & 1, ph = (it >> 1) & 1;
+          if (raw8) {
+            // fp8 K/V: TMA fills the staging buffers; the converter warps own the ring slots
+            for (int side = 0; side < 2 && ok; ++side) {
+              ok = __all_sync(0xffffffffu, mbar_wait(bar(B_STGEMPTY + side), (u8 - 1) & 1, &abort_flag));
+              if (!ok) { fail_id = B_STGEMPTY + side + 1; break; }
+              if (leader) {
+                mbar_expect_tx(bar(B_STGFULL + side), (uint32_t)tl.nch * 64 * D);
+                for (int c = 0; c < tl.nch; ++c)
+                  tma_load_3d(smem_u32(stg) + side * STG + c * 64 * D, side == 0 ? mk : mv, bar(B_STGFULL + side), 0, tl.j0[c], kv_slab);
+              }
+            }
+            last_u8 = u8;
+            ++u8;
+            __syncwarp();
+            continue;
+          }
           const uint32_t bytes = (uint32_t)tl.nch * 64 * D * 2;
           ok = __all_sync(0xffffffffu, mbar_wait(bar(B_KEMPTY + s), ph ^ 1, &abort_flag));
           if (!ok) { fail_id = B_KEMPTY + s + 1; break; }
@@ -315,6 +351,61 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
     }
   } else if (warp < 4) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 72;\n");
+    if constexpr (IN8) {
+      // =============================== fp8 -> 16-bit converters ===============================
+      // warp 2: K side (Q tile 0 first), warp 3: V side (Q tile 1 first).  A staged row of D fp8 bytes
+      // becomes D values bf16(fp32(x) * scale) -- the operands the reference's wrapper builds
+      // (nsa/triton/fp8.py:67-69), so the MMAs see exactly what the bf16 path sees on dequantised
+      // tensors -- written in the 128-byte swizzled layout the MMA descriptors expect.
+      const int side = warp - 2;
+      const unsigned char* src = stg + side * STG;
+      const __nv_fp8_interpretation_t kind = a.q_dtype == NSA_FP8_E5M2 ? __NV_E5M2 : __NV_E4M3;
+      auto convert_rows = [&](int nrows, unsigned char* dst_tile, float dq) {
+        constexpr int GPR = D / 16;                       // 16-element groups per row
+        for (int i = lane; i < nrows * GPR; i += 32) {
+          const int r = i / GPR, grp = i % GPR;
+          const uint4 raw = *reinterpret_cast<const uint4*>(src + r * D + grp * 16);
+          const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+          uint32_t o[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const __nv_fp8x2_storage_t two = (__nv_fp8x2_storage_t)((w[e >> 1] >> ((e & 1) * 16)) & 0xffffu);
+            const __half2_raw h2 = __nv_cvt_fp8x2_to_halfraw2(two, kind);
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+            o[e] = Elem<__nv_bfloat16>::pack(f.x * dq, f.y * dq);
+          }
+          const int e0 = grp * 16, dh = e0 >> 6, ch = (e0 & 63) >> 3;        // two consecutive 16-byte chunks
+          unsigned char* rowp = dst_tile + dh * DHSTRIDE + r * 128;
+          *reinterpret_cast<uint4*>(rowp + (((ch) ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+          *reinterpret_cast<uint4*>(rowp + (((ch + 1) ^ (r & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+        }
+      };
+      bool ok = __all_sync(0xffffffffu, mbar_wait(bar(B_STGFULL + side), 0, &abort_flag));
+      if (!ok) fail_id = B_STGFULL + side + 1;
+      if (ok) {
+        convert_rows(128, smem + side * QTILE, a.q_scale);
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) { mbar_arrive(bar(B_QFULL)); mbar_arrive(bar(B_STGEMPTY + side)); }
+      }
+      int it = 0, u8 = 1;
+      for (int br = 0; br < 3 && ok; ++br) {
+        const int nt = (nchunks[br] + 1) >> 1;
+        if (br == 0) { it += nt; continue; }              // pooled tiles come straight from TMA
+        for (int t = 0; t < nt && ok; ++t, ++it, ++u8) {
+          const Tile tl = get_tile(br, t);
+          const int s = it & 1, ph = (it >> 1) & 1;
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(B_STGFULL + side), u8 & 1, &abort_flag));
+          if (!ok) { fail_id = B_STGFULL + side + 1; break; }
+          ok = __all_sync(0xffffffffu, mbar_wait(bar((side == 0 ? B_KEMPTY : B_VEMPTY) + s), ph ^ 1, &abort_flag));
+          if (!ok) { fail_id = (side == 0 ? B_KEMPTY : B_VEMPTY) + s + 1; break; }
+          convert_rows(tl.nch * 64, smem + 2 * QTILE + (side == 0 ? 0 : 2 * KVTILE) + s * KVTILE, side == 0 ? a.k_scale : a.v_scale);
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) { mbar_arrive(bar((side == 0 ? B_KFULL : B_VFULL) + s)); mbar_arrive(bar(B_STGEMPTY + side)); }
+        }
+      }
+    }
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 216;\n");
     // =============================== softmax / epilogue ===============================
@@ -368,6 +459,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
       int lo, hi;
       bounds(br, qi, row_ok, lo, hi);
       float m_used = -INFINITY, l = 0.f;
+      const float sl2 = p.scale_log2[br];
 #pragma unroll 1
       for (int t = 0; t < nt && ok; ++t, ++it) {
         const Tile tl = get_tile(br, t);
@@ -411,7 +503,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
         }
         float mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])), fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
         if (quarter == 0 && lane == 0) T5_TRACE(X * 2048 + it * 8 + 2);
-        mx *= p.scale_log2;                                  // scale > 0 keeps the order
+        mx *= p.scale_log2[br];                              // scale > 0 keeps the order
         // lazy rescale: only when some row of the warp outgrows its reference maximum by 2^8
         const bool grow = mx > m_used + 8.f;
         if (__any_sync(0xffffffffu, grow)) {
@@ -443,8 +535,8 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
             uint32_t pk[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              const float p0 = ex2(fmaf(__uint_as_float(sv[g][2 * i]), p.scale_log2, -m_ref));
-              const float p1 = ex2(fmaf(__uint_as_float(sv[g][2 * i + 1]), p.scale_log2, -m_ref));
+              const float p0 = ex2(fmaf(__uint_as_float(sv[g][2 * i]), sl2, -m_ref));
+              const float p1 = ex2(fmaf(__uint_as_float(sv[g][2 * i + 1]), sl2, -m_ref));
               if (i & 1) { psum2 += p0; psum3 += p1; } else { psum0 += p0; psum1 += p1; }
               pk[i] = Elem<T>::pack(p0, p1);
             }
@@ -466,7 +558,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
       if (!ok) { fail_id = B_PVDONE + X + 1; break; }
       tc_fence_after();
       const bool has = l > 0.f;
-      const float coef = has ? (a.fused ? gate[br] : 1.f) / l : 0.f;
+      const float coef = has ? (a.fused ? gate[br] : 1.f) * p.out_scale[br] / l : 0.f;
       if (!a.fused) lse_out = has ? m_used * kLn2 + __logf(l) : -INFINITY;
 #pragma unroll
       for (int g = 0; g < D / 32; ++g) {
@@ -508,11 +600,15 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
   __syncthreads();
   if (abort_flag && warp == 0 && lane == 0) {
     // let copies already in flight land (bounded) before the block's shared memory is handed back
-    for (int i = 0; i < 20000 && !mbar_try_wait(bar(B_QFULL), 0); ++i) __nanosleep(100);
+    if (!IN8)
+      for (int i = 0; i < 20000 && !mbar_try_wait(bar(B_QFULL), 0); ++i) __nanosleep(100);
     if (last_k_it >= 0)
       for (int i = 0; i < 20000 && !mbar_try_wait(bar(B_KFULL + (last_k_it & 1)), (last_k_it >> 1) & 1); ++i) __nanosleep(100);
     if (last_v_it >= 0)
       for (int i = 0; i < 20000 && !mbar_try_wait(bar(B_VFULL + (last_v_it & 1)), (last_v_it >> 1) & 1); ++i) __nanosleep(100);
+    if (last_u8 >= 0)
+      for (int side = 0; side < 2; ++side)
+        for (int i = 0; i < 20000 && !mbar_try_wait(bar(B_STGFULL + side), last_u8 & 1); ++i) __nanosleep(100);
   }
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
@@ -529,6 +625,22 @@ static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
       fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
   }
   return fn;
+}
+
+// [slabs][rows][D] fp8 tensor, boxes of 64 rows x D bytes, no swizzle (the converter warps re-lay it out)
+static int make_map8(CUtensorMap* m, const void* ptr, long long slabs, long long rows, int D) {
+  auto enc = encode_fn();
+  NSA_REQUIRE(enc != nullptr, NSA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  NSA_REQUIRE((reinterpret_cast<uintptr_t>(ptr) & 15) == 0, NSA_ERR_ARG, "tensor base %p is not 16-byte aligned", ptr);
+  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)rows, (cuuint64_t)slabs};
+  cuuint64_t strides[2] = {(cuuint64_t)D, (cuuint64_t)rows * D};
+  cuuint32_t box[3] = {(cuuint32_t)D, 64, 1};
+  cuuint32_t es[3] = {1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(ptr), dims, strides, box, es,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  NSA_REQUIRE(r == CUDA_SUCCESS, NSA_ERR_CUDA, "cuTensorMapEncodeTiled (fp8) failed with %d", (int)r);
+  return NSA_OK;
 }
 
 // [slabs][rows][D] 16-bit tensor, boxes of 64 rows x 64 elements, 128-byte swizzle, zero fill outside
@@ -548,7 +660,9 @@ static int make_map(CUtensorMap* m, const void* ptr, long long slabs, long long 
 }
 
 bool attention_fwd_tc5_supports(const nsa_fwd_args& a) {
-  if (!(a.q_dtype == NSA_BF16 || a.q_dtype == NSA_FP16) || a.kv_dtype != a.q_dtype) return false;
+  const bool in8 = a.q_dtype == NSA_FP8_E4M3 || a.q_dtype == NSA_FP8_E5M2;
+  if (!(a.q_dtype == NSA_BF16 || a.q_dtype == NSA_FP16 || in8) || a.kv_dtype != a.q_dtype) return false;
+  if (in8 && !(a.q_scale > 0.f && a.k_scale > 0.f && a.v_scale > 0.f)) return false;
   if (!(a.D == 64 || a.D == 128)) return false;
   if (!(a.scale > 0.f)) return false;
   const int G = a.H / a.Hkv;
@@ -564,34 +678,47 @@ int attention_fwd_tc5(const nsa_fwd_args& a, cudaStream_t st) {
   Tc5Params p;
   p.a = a;
   if (!(a.branches & NSA_BRANCH_SELECTED)) p.a.nq = (a.Tq + 63) / 64;
-  p.scale_log2 = a.scale * kLog2e;
+  const bool in8 = a.q_dtype == NSA_FP8_E4M3 || a.q_dtype == NSA_FP8_E5M2;
+  const int cdt = in8 ? NSA_BF16 : a.q_dtype;             // type of the staged 16-bit tiles
+  for (int br = 0; br < 3; ++br) {
+    p.scale_log2[br] = a.scale * kLog2e;
+    p.out_scale[br] = 1.f;
+  }
   p.nk_blocks = (a.sel_key_limit + 63) / 64;
   p.G4 = (a.H / a.Hkv) / 4;
   int rc;
-  if ((rc = make_map(&p.tmQ, a.Q, (long long)a.B * a.H, a.Tq, a.D, a.q_dtype)) != NSA_OK) return rc;
-  if ((rc = make_map(&p.tmK, a.K, (long long)a.B * a.Hkv, a.Tk, a.D, a.q_dtype)) != NSA_OK) return rc;
-  if ((rc = make_map(&p.tmV, a.V, (long long)a.B * a.Hkv, a.Tk, a.D, a.q_dtype)) != NSA_OK) return rc;
+  if (in8) {
+    if ((rc = make_map8(&p.tmQ, a.Q, (long long)a.B * a.H, a.Tq, a.D)) != NSA_OK) return rc;
+    if ((rc = make_map8(&p.tmK, a.K, (long long)a.B * a.Hkv, a.Tk, a.D)) != NSA_OK) return rc;
+    if ((rc = make_map8(&p.tmV, a.V, (long long)a.B * a.Hkv, a.Tk, a.D)) != NSA_OK) return rc;
+  } else {
+    if ((rc = make_map(&p.tmQ, a.Q, (long long)a.B * a.H, a.Tq, a.D, cdt)) != NSA_OK) return rc;
+    if ((rc = make_map(&p.tmK, a.K, (long long)a.B * a.Hkv, a.Tk, a.D, cdt)) != NSA_OK) return rc;
+    if ((rc = make_map(&p.tmV, a.V, (long long)a.B * a.Hkv, a.Tk, a.D, cdt)) != NSA_OK) return rc;
+  }
   if (a.branches & NSA_BRANCH_COMPRESSED) {
-    if ((rc = make_map(&p.tmKc, a.Kc, (long long)a.B * a.Hkv, a.Nc, a.D, a.q_dtype)) != NSA_OK) return rc;
-    if ((rc = make_map(&p.tmVc, a.Vc, (long long)a.B * a.Hkv, a.Nc, a.D, a.q_dtype)) != NSA_OK) return rc;
+    if ((rc = make_map(&p.tmKc, a.Kc, (long long)a.B * a.Hkv, a.Nc, a.D, cdt)) != NSA_OK) return rc;
+    if ((rc = make_map(&p.tmVc, a.Vc, (long long)a.B * a.Hkv, a.Nc, a.D, cdt)) != NSA_OK) return rc;
   } else {
     p.tmKc = p.tmK;
     p.tmVc = p.tmV;
   }
   const long long blocks = (long long)p.a.nq * a.B * a.Hkv * p.G4;
   NSA_REQUIRE(blocks > 0 && blocks < 2147483647LL, NSA_ERR_ARG, "attention forward: %lld work items do not fit a grid", blocks);
-  const size_t smem = (size_t)(2 + 2 + 2) * (a.D / 64) * 128 * 128 + 1024;
-#define NSA_TC5_LAUNCH(DD, FF)                                                                              \
+  const size_t smem = (size_t)(2 + 2 + 2) * (a.D / 64) * 128 * 128 + (in8 ? (size_t)2 * 128 * a.D : 0) + 1024;
+#define NSA_TC5_LAUNCH(DD, FF, I8)                                                                         \
   {                                                                                                         \
-    auto fn = nsa_fwd_tc5_kernel<DD, FF>;                                                                   \
+    auto fn = nsa_fwd_tc5_kernel<DD, FF, I8>;                                                               \
     NSA_CUDA_OK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));         \
     fn<<<(unsigned)blocks, T5_THREADS, smem, st>>>(p);                                                     \
   }
-  const int fmt = a.q_dtype == NSA_BF16 ? 1 : 0;
-  if (a.D == 128 && fmt == 1) NSA_TC5_LAUNCH(128, 1)
-  else if (a.D == 128) NSA_TC5_LAUNCH(128, 0)
-  else if (fmt == 1) NSA_TC5_LAUNCH(64, 1)
-  else NSA_TC5_LAUNCH(64, 0)
+  const int fmt = cdt == NSA_BF16 ? 1 : 0;
+  if (in8 && a.D == 128) NSA_TC5_LAUNCH(128, 1, true)
+  else if (in8) NSA_TC5_LAUNCH(64, 1, true)
+  else if (a.D == 128 && fmt == 1) NSA_TC5_LAUNCH(128, 1, false)
+  else if (a.D == 128) NSA_TC5_LAUNCH(128, 0, false)
+  else if (fmt == 1) NSA_TC5_LAUNCH(64, 1, false)
+  else NSA_TC5_LAUNCH(64, 0, false)
 #undef NSA_TC5_LAUNCH
   return launch_status("attn_fwd_tc5");
 }

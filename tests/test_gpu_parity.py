@@ -369,3 +369,42 @@ def test_tcgen05_fused_forward_vs_oracle_and_generic(nsa, shape):
     assert max_abs(out, ref) <= TOL16, max_abs(out, ref)
     assert max_abs(out_g, ref) <= TOL16
     assert torch.equal(out, out_b)          # run-to-run bitwise repeatable
+
+
+@pytest.mark.parametrize("fmt", [torch.float8_e4m3fn, torch.float8_e5m2])
+@pytest.mark.parametrize("shape", [(1, 8, 2, 512, 512, 128), (1, 4, 1, 200, 456, 64)])
+def test_tcgen05_fp8_storage_path(nsa, shape, fmt):
+    """fp8 Q/K/V through the tcgen05 kernel (TMA fp8 staging, in-kernel conversion, scales folded into the
+    softmax): against the fp32 oracle on the dequantised values (<= 6e-2) and against the generic kernel."""
+    from nsa_from_scratch_b200 import _lib as L, ops
+    B, H, Hkv, Tq, Tk, D = shape
+    g = torch.Generator().manual_seed(11)
+    xs = []
+    for shp in ((B, H, Tq, D), (B, Hkv, Tk, D), (B, Hkv, Tk, D)):
+        x = torch.randn(shp, generator=g)
+        x = torch.where(torch.rand(shp, generator=g) < 1e-3, x * 20, x)
+        xs.append(x.to(torch.bfloat16))
+    q8, k8, v8 = (nsa.quantize_to_fp8(x.cuda(), fmt=fmt) for x in xs)
+    deq = [O.dequantize_fp8(t.cpu(), s) for t, s in (q8, k8, v8)]
+    gates = torch.randn(B, H, Tq, 3, generator=g)
+    cfg = nsa.NSAConfig(block_size_c=32, stride_c=16, top_k=4, window_size=128, select_per_group=True)
+    idx = O.select_blocks(deq[0], deq[1], top_k=4, group_shared=True)
+    ref = O.nsa_forward(deq[0], deq[1], deq[2], block_size_c=32, stride_c=16, top_k=4, window_size=128,
+                        gate_logits=gates, block_indices=idx)
+    tol = TOL8 * max(1.0, float(ref.abs().max()))
+    try:
+        ops.set_engine("tcgen05")
+        out = nsa.nsa_forward_fp8(q8[0], k8[0], v8[0], q8[1], k8[1], v8[1], cfg, gate_logits=gates.cuda())
+        o_s, l_s = nsa.selected_attention_fp8(q8[0], k8[0], v8[0], q8[1], k8[1], v8[1], top_k=4, block_indices=idx.cuda())
+        ops.device_status()
+        ops.set_engine("generic")
+        out_g = nsa.nsa_forward_fp8(q8[0], k8[0], v8[0], q8[1], k8[1], v8[1], cfg, gate_logits=gates.cuda())
+    finally:
+        ops.set_engine("auto")
+    assert max_abs(out, ref) <= tol, (max_abs(out, ref), tol)
+    assert max_abs(out_g, ref) <= tol
+    ro, rl = O.selected_attention(deq[0], deq[1], deq[2], idx)
+    check_out_lse(o_s, l_s, ro, rl, tol, tol_lse=1e-2 * max(1.0, float(rl[torch.isfinite(rl)].abs().max())))
+    # identical operands after the in-kernel dequantisation: bit-equal to the bf16 path on dequantised tensors
+    ob, lb = nsa.selected_attention(deq[0].cuda(), deq[1].cuda(), deq[2].cuda(), top_k=4, block_indices=idx.cuda())
+    assert torch.equal(o_s, ob) and torch.equal(l_s, lb)
