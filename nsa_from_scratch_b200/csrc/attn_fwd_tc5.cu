@@ -30,7 +30,8 @@ namespace nsa {
 
 using namespace tc5;
 
-constexpr int T5_MAX_SEL = 64;
+constexpr int T5_MAX_SEL = 64;            // listed blocks per query block
+constexpr int T5_MAX_ENT = 4 * T5_MAX_SEL;  // entries of the four row groups of a work item
 constexpr int T5_THREADS = 384;   // 12 warps; register budget rebalanced per role with setmaxnreg   // 10 warps: 65536 / 320 leaves 200 registers per thread
 
 __device__ int g_tc5_status;   // 0 ok; otherwise (1 + id of the barrier a wait gave up on)
@@ -49,13 +50,16 @@ struct Tc5Params {
   float scale_log2[3];   // per branch: softmax scale * log2(e) (* the fp8 dequantisation scales of the operands)
   float out_scale[3];    // per branch: factor on P.V (the fp8 scale of V; 1 otherwise)
   int nk_blocks;
-  int G4;          // query-head quads per KV head
+  int GH;          // query heads per work item (4, 2 or 1); a work item has 4/GH consecutive query blocks
+  int HG;          // head groups per KV head = (H/Hkv) / GH
+  int NQG;         // query-block groups = ceil(nq / (4/GH))
 };
 
 struct Tile {
   int nch;
   int j0[2];
   int jlim[2];
+  int mask[2];   // which of the 4 row groups attend the chunk (selected branch; 0xF otherwise)
 };
 
 // barrier ids
@@ -81,7 +85,8 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
   constexpr int STG = 128 * D;
   unsigned char* stg = smem + 2 * QTILE + 4 * KVTILE;
   __shared__ __align__(8) uint64_t bars[B_COUNT];
-  __shared__ int sel_list[T5_MAX_SEL];
+  __shared__ int sel_list[T5_MAX_ENT];            // selected branch: key blocks to visit ...
+  __shared__ unsigned char sel_mask[T5_MAX_ENT];  // ... and the row groups that listed each of them
   __shared__ int sel_n;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
@@ -89,16 +94,22 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   // ---- work item -------------------------------------------------------------------
-  const int per_q = a.B * a.Hkv * p.G4;
-  const int qb = a.nq - 1 - (int)(blockIdx.x / per_q);   // long rows first
+  // 4 row groups of 64 query positions: group g = (head h_base + g % GH, query block qb_base + g / GH);
+  // MMA tile X holds groups 2X and 2X+1.
+  const int per_q = a.B * a.Hkv * p.HG;
+  const int qbg = p.NQG - 1 - (int)(blockIdx.x / per_q);   // long rows first
   const int rem = (int)(blockIdx.x % per_q);
-  const int b = rem / (a.Hkv * p.G4);
-  const int hk = (rem / p.G4) % a.Hkv;
-  const int g4 = rem % p.G4;
+  const int b = rem / (a.Hkv * p.HG);
+  const int hk = (rem / p.HG) % a.Hkv;
+  const int hg = rem % p.HG;
   const int G = a.H / a.Hkv;
-  const int h_base = hk * G + g4 * 4;
-  const int q0 = qb * 64;
-  const int i_last = min(q0 + 64, a.Tq) - 1;
+  const int GH = p.GH, NQB = 4 / p.GH;
+  const int h_base = hk * G + hg * GH;
+  const int qb_base = qbg * NQB;
+  auto grp_head = [&](int g) { return h_base + g % GH; };
+  auto grp_qb = [&](int g) { return qb_base + g / GH; };
+  const int q_first = qb_base * 64;
+  const int i_last = min((min(qb_base + NQB, a.nq)) * 64, a.Tq) - 1;
   const int kv_slab = b * a.Hkv + hk;
 
   auto bar = [&](int id) { return smem_u32(&bars[id]); };
@@ -131,19 +142,66 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
     fence_barrier_init();
   }
   if (warp == 1) { tmem_alloc(smem_u32(&tmem_base_s), 512); tmem_relinquish(); }
+  // scratch of the list builder: the first bytes of the (not yet used) Q tile area
+  int* ent_blk = reinterpret_cast<int*>(smem);
+  unsigned char* ent_p = smem + T5_MAX_ENT * sizeof(int);
   if (warp == 2) {
+    // Selected branch: the key blocks the work item visits, each with the set of row groups that list it.
+    // Lists shared by the 4 groups (one list per KV head, GH == 4) are taken as they are.  Otherwise the
+    // 4 lists are merged: a block listed by several groups is staged once and masked per group; a block
+    // listed p times by one group is visited p times (the reference counts duplicates twice).
     int n = 0;
     if (a.branches & NSA_BRANCH_SELECTED) {
-      const int hi_ = (a.Hi == a.H) ? h_base : hk;
-      const int32_t* row = a.idx + (((size_t)b * a.Hi + hi_) * a.nq + qb) * a.top_k;
-      const int last_pos = i_last + a.offset;
-      for (int s0 = 0; s0 < a.top_k; s0 += 32) {
-        int s = s0 + lane;
-        int blk = s < a.top_k ? row[s] : -1;
-        bool ok = blk >= 0 && blk < p.nk_blocks && (!a.causal || (long long)blk * 64 <= last_pos);
-        unsigned m = __ballot_sync(0xffffffffu, ok);
-        if (ok) sel_list[n + __popc(m & ((1u << lane) - 1))] = blk;
-        n += __popc(m);
+      const bool shared = a.Hi != a.H && GH == 4;
+      const int ngrp = shared ? 1 : 4;
+      const int n_ent = ngrp * a.top_k;
+      for (int i = lane; i < n_ent; i += 32) {
+        const int g = i / a.top_k, sl = i % a.top_k;
+        const int qb = grp_qb(g);
+        int blk = -1;
+        if (qb < a.nq) {
+          const int hi_ = (a.Hi == a.H) ? grp_head(g) : hk;
+          blk = a.idx[(((size_t)b * a.Hi + hi_) * a.nq + qb) * a.top_k + sl];
+          const int last_pos = min(qb * 64 + 64, a.Tq) - 1 + a.offset;
+          if (blk < 0 || blk >= p.nk_blocks || (a.causal && (long long)blk * 64 > last_pos)) blk = -1;
+        }
+        ent_blk[i] = blk;
+      }
+      __syncwarp();
+      if (!shared) {
+        for (int i = lane; i < n_ent; i += 32) {          // p = how many earlier entries of the same group list the same block
+          int pc = 0;
+          const int blk = ent_blk[i], g0 = (i / a.top_k) * a.top_k;
+          for (int j = g0; j < i; ++j) pc += (ent_blk[j] == blk);
+          ent_p[i] = (unsigned char)pc;
+        }
+        __syncwarp();
+      }
+      for (int i0 = 0; i0 < n_ent; i0 += 32) {
+        const int i = i0 + lane;
+        bool lead = false;
+        unsigned msk = 0xFu;
+        if (i < n_ent && ent_blk[i] >= 0) {
+          lead = true;
+          if (!shared) {
+            const int blk = ent_blk[i], pi = ent_p[i], gi = i / a.top_k;
+            msk = 0;
+            for (int j = 0; j < n_ent; ++j) {
+              if (ent_blk[j] == blk && ent_p[j] == pi) {
+                const int gj = j / a.top_k;
+                msk |= 1u << gj;
+                if (gj < gi) lead = false;
+              }
+            }
+          }
+        }
+        const unsigned bal = __ballot_sync(0xffffffffu, lead);
+        if (lead) {
+          const int pos = n + __popc(bal & ((1u << lane) - 1));
+          sel_list[pos] = ent_blk[i];
+          sel_mask[pos] = (unsigned char)msk;
+        }
+        n += __popc(bal);
       }
     }
     if (lane == 0) sel_n = n;
@@ -164,7 +222,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
     }
     if (a.branches & NSA_BRANCH_SELECTED) nchunks[1] = sel_n;
     if (a.branches & NSA_BRANCH_SLIDING) {
-      bounds(2, q0, true, lo_f, hi_f);
+      bounds(2, q_first, true, lo_f, hi_f);
       bounds(2, i_last, true, lo_l, hi_l);
       if (hi_l >= lo_f) { sld_c0 = lo_f / 64; nchunks[2] = hi_l / 64 - sld_c0 + 1; }
     }
@@ -174,8 +232,9 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
     tl.nch = min(2, nchunks[br] - 2 * t);
     for (int c = 0; c < 2; ++c) {
       int ci = min(2 * t + c, nchunks[br] - 1);
+      tl.mask[c] = 0xF;
       if (br == 0) { tl.j0[c] = ci * 64; tl.jlim[c] = a.Nc; }
-      else if (br == 1) { int blk = sel_list[ci]; tl.j0[c] = blk * 64; tl.jlim[c] = min(blk * 64 + 64, a.sel_key_limit); }
+      else if (br == 1) { int blk = sel_list[ci]; tl.j0[c] = blk * 64; tl.jlim[c] = min(blk * 64 + 64, a.sel_key_limit); tl.mask[c] = sel_mask[ci]; }
       else { tl.j0[c] = (sld_c0 + ci) * 64; tl.jlim[c] = a.Tk; }
     }
     return tl;
@@ -199,15 +258,16 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
           for (int X = 0; X < 2; ++X) {
             mbar_expect_tx(bar(B_STGFULL + X), STG);
             for (int hh = 0; hh < 2; ++hh)
-              tma_load_3d(smem_u32(stg) + X * STG + hh * 64 * D, &p.tmQ, bar(B_STGFULL + X), 0, q0, b * a.H + h_base + 2 * X + hh);
+              tma_load_3d(smem_u32(stg) + X * STG + hh * 64 * D, &p.tmQ, bar(B_STGFULL + X), 0, grp_qb(2 * X + hh) * 64,
+                          b * a.H + grp_head(2 * X + hh));
           }
         } else {
           mbar_expect_tx(bar(B_QFULL), 2 * QTILE);
           for (int X = 0; X < 2; ++X)
             for (int hh = 0; hh < 2; ++hh)
               for (int dh = 0; dh < DH; ++dh)
-                tma_load_3d(sQ + X * QTILE + dh * DHSTRIDE + hh * 8192, &p.tmQ, bar(B_QFULL), dh * 64, q0,
-                            b * a.H + h_base + 2 * X + hh);
+                tma_load_3d(sQ + X * QTILE + dh * DHSTRIDE + hh * 8192, &p.tmQ, bar(B_QFULL), dh * 64, grp_qb(2 * X + hh) * 64,
+                            b * a.H + grp_head(2 * X + hh));
         }
       }
       __syncwarp();
@@ -415,9 +475,10 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const uint32_t tS = tmem + lane_addr + X * 128;
     const uint32_t tO = tmem + lane_addr + 256 + X * 128;
-    const int head = h_base + 2 * X + (r >> 6);
-    const int qi = q0 + (r & 63);
-    const bool row_ok = qi < a.Tq;
+    const int rg = 2 * X + (r >> 6);                         // row group of this row
+    const int head = grp_head(rg);
+    const int qi = grp_qb(rg) * 64 + (r & 63);
+    const bool row_ok = grp_qb(rg) < a.nq && qi < a.Tq;
     const size_t row_index = ((size_t)b * a.H + head) * a.Tq + qi;
 
     float gate[3] = {0.5f, 0.5f, 0.5f};
@@ -478,7 +539,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           const int vlo = max(lo - tl.j0[c], 0);
-          const int vhi = c < tl.nch ? min(hi, tl.jlim[c] - 1) - tl.j0[c] : -1;
+          const int vhi = (c < tl.nch && ((tl.mask[c] >> rg) & 1)) ? min(hi, tl.jlim[c] - 1) - tl.j0[c] : -1;
           if (c < tl.nch && (vlo > 0 || vhi < 63)) {
 #pragma unroll
             for (int g = 0; g < 2; ++g)
@@ -665,10 +726,8 @@ bool attention_fwd_tc5_supports(const nsa_fwd_args& a) {
   if (in8 && !(a.q_scale > 0.f && a.k_scale > 0.f && a.v_scale > 0.f)) return false;
   if (!(a.D == 64 || a.D == 128)) return false;
   if (!(a.scale > 0.f)) return false;
-  const int G = a.H / a.Hkv;
-  if (G % 4 != 0) return false;
   if (a.branches & NSA_BRANCH_SELECTED) {
-    if (a.bm != 64 || a.bn != 64 || a.Hi != a.Hkv || a.top_k > T5_MAX_SEL) return false;
+    if (a.bm != 64 || a.bn != 64 || a.top_k > T5_MAX_SEL) return false;
   }
   if ((a.branches & NSA_BRANCH_COMPRESSED) && a.Nc <= 0) return false;
   return true;
@@ -685,7 +744,11 @@ int attention_fwd_tc5(const nsa_fwd_args& a, cudaStream_t st) {
     p.out_scale[br] = 1.f;
   }
   p.nk_blocks = (a.sel_key_limit + 63) / 64;
-  p.G4 = (a.H / a.Hkv) / 4;
+  {
+    const int G = a.H / a.Hkv;
+    p.GH = G % 4 == 0 ? 4 : (G % 2 == 0 ? 2 : 1);
+    p.HG = G / p.GH;
+  }
   int rc;
   if (in8) {
     if ((rc = make_map8(&p.tmQ, a.Q, (long long)a.B * a.H, a.Tq, a.D)) != NSA_OK) return rc;
@@ -703,7 +766,8 @@ int attention_fwd_tc5(const nsa_fwd_args& a, cudaStream_t st) {
     p.tmKc = p.tmK;
     p.tmVc = p.tmV;
   }
-  const long long blocks = (long long)p.a.nq * a.B * a.Hkv * p.G4;
+  p.NQG = (p.a.nq + 4 / p.GH - 1) / (4 / p.GH);
+  const long long blocks = (long long)p.NQG * a.B * a.Hkv * p.HG;
   NSA_REQUIRE(blocks > 0 && blocks < 2147483647LL, NSA_ERR_ARG, "attention forward: %lld work items do not fit a grid", blocks);
   const size_t smem = (size_t)(2 + 2 + 2) * (a.D / 64) * 128 * 128 + (in8 ? (size_t)2 * 128 * a.D : 0) + 1024;
 #define NSA_TC5_LAUNCH(DD, FF, I8)                                                                         \

@@ -408,3 +408,28 @@ def test_tcgen05_fp8_storage_path(nsa, shape, fmt):
     # identical operands after the in-kernel dequantisation: bit-equal to the bf16 path on dequantised tensors
     ob, lb = nsa.selected_attention(deq[0].cuda(), deq[1].cuda(), deq[2].cuda(), top_k=4, block_indices=idx.cuda())
     assert torch.equal(o_s, ob) and torch.equal(l_s, lb)
+
+
+@pytest.mark.parametrize("shape", [(1, 4, 4, 512, 512, 64), (1, 4, 2, 448, 448, 128), (1, 8, 2, 320, 576, 128),
+                                   (2, 3, 3, 200, 200, 64), (1, 6, 1, 256, 256, 64)])
+def test_tcgen05_per_head_block_lists_and_any_group_size(nsa, shape):
+    """One block list per query head (the reference's semantics) on the tcgen05 kernel: MHA (4 consecutive
+    query blocks of one head per work item), 2 heads x 2 query blocks, and 4 heads with 4 different lists."""
+    from nsa_from_scratch_b200 import ops
+    B, H, Hkv, Tq, Tk, D = shape
+    Q, K, V, g = make_qkv(12, B, H, Hkv, Tq, Tk, D)
+    gates = torch.randn(B, H, Tq, 3, generator=g)
+    cfg = nsa.NSAConfig(block_size_c=64, top_k=4, window_size=100)
+    idx = O.select_blocks(Q, K, top_k=4)
+    ref = O.nsa_forward(Q, K, V, block_size_c=64, top_k=4, window_size=100, gate_logits=gates, block_indices=idx)
+    ro, rl = O.selected_attention(Q, K, V, idx)
+    try:
+        ops.set_engine("tcgen05")
+        out = nsa.nsa_forward(Q.cuda(), K.cuda(), V.cuda(), cfg, gate_logits=gates.cuda())
+        o_s, l_s = nsa.selected_attention(Q.cuda(), K.cuda(), V.cuda(), top_k=4, block_indices=idx.cuda())
+        ops.device_status()
+    finally:
+        ops.set_engine("auto")
+    fin = torch.isfinite(ref).all(-1)
+    assert max_abs(out, ref, fin) <= TOL16, max_abs(out, ref, fin)
+    check_out_lse(o_s, l_s, ro, rl, TOL16)
