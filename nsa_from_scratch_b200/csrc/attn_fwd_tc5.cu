@@ -64,7 +64,8 @@ struct Tile {
 
 // barrier ids
 enum { B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 3, B_VFULL = 5, B_VEMPTY = 7, B_SFULL = 9, B_PFULL = 11, B_PVDONE = 13,
-       B_STGFULL = 15, B_STGEMPTY = 17, B_COUNT = 19 };   // STG*: fp8 staging buffers (0 = K side, 1 = V side)
+       B_STGFULL = 15, B_STGEMPTY = 17, B_SREAD = 19, B_COUNT = 21 };
+// STG*: fp8 staging buffers (0 = K side, 1 = V side); SREAD: D=64 only, "S row is in registers"
 
 template <int D, int FMT, bool IN8>
 __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_constant__ Tc5Params p) {
@@ -73,6 +74,10 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
   constexpr int QTILE = DH * 128 * 128;         // bytes of one 128-row Q tile
   constexpr int KVTILE = DH * 128 * 128;        // bytes of one 128-key K or V tile
   constexpr int DHSTRIDE = 128 * 128;           // bytes between the halves
+  // D = 64 leaves 64 TMEM columns per tile unused: P gets columns of its own there instead of aliasing S,
+  // so the next tile's QK^T can be issued as soon as the softmax threads hold the S row in registers
+  // (not only after PV has consumed P) -- the QK -> softmax -> PV chain of a tile is broken.
+  constexpr bool EARLY = (D == 64);
   const nsa_fwd_args& a = p.a;
 
   extern __shared__ unsigned char smem_raw[];
@@ -138,7 +143,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
   if (tid == 0) {
     abort_flag = 0;
     for (int i = 0; i < B_COUNT; ++i)
-      mbar_init(bar(i), (i == B_PFULL || i == B_PFULL + 1) ? 128 : ((IN8 && i == B_QFULL) ? 2 : 1));
+      mbar_init(bar(i), (i == B_PFULL || i == B_PFULL + 1 || i == B_SREAD || i == B_SREAD + 1) ? 128 : ((IN8 && i == B_QFULL) ? 2 : 1));
     fence_barrier_init();
   }
   if (warp == 1) { tmem_alloc(smem_u32(&tmem_base_s), 512); tmem_relinquish(); }
@@ -342,6 +347,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
       const uint64_t dK[2] = {smem_desc_sw128(sK, 16, 1024), smem_desc_sw128(sK + KVTILE, 16, 1024)};
       const uint64_t dV[2] = {smem_desc_sw128(sV, DHSTRIDE, 1024), smem_desc_sw128(sV + KVTILE, DHSTRIDE, 1024)};
       const uint32_t tSx[2] = {tmem, tmem + 128}, tOx[2] = {tmem + 256, tmem + 384};
+      const uint32_t tPx[2] = {EARLY ? tmem + 320 : tmem, EARLY ? tmem + 448 : tmem + 128};
 
       // position of the tile whose QK is issued next / whose PV is issued next
       int q_br = 0, q_t = 0, p_br = 0, p_t = 0;
@@ -382,6 +388,17 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
         ok = __all_sync(0xffffffffu, mbar_wait(bar(B_VFULL + s), (it >> 1) & 1, &abort_flag));
         if (!ok) { fail_id = B_VFULL + s + 1; break; }
         T5_TRACE(4096 + it * 8 + 1);
+        if constexpr (EARLY) {
+          // next tile's QK^T as soon as this tile's S rows have been read
+#pragma unroll
+          for (int X = 0; X < 2; ++X) {
+            if (!ok || it + 1 >= total_tiles) break;
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(B_SREAD + X), it & 1, &abort_flag));
+            if (!ok) { fail_id = B_SREAD + X + 1; break; }
+            tc_fence_after();
+            ok = issue_qk(X, it + 1);
+          }
+        }
 #pragma unroll
         for (int X = 0; X < 2; ++X) {
           if (!ok) break;
@@ -390,19 +407,19 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
           T5_TRACE(4096 + it * 8 + 2 + 2 * X);
           tc_fence_after();
           if (leader) {
-            if (fresh) mma_ts(tOx[X], tSx[X], dV[s], IDESC_PV, 0u);
-            else mma_ts(tOx[X], tSx[X], dV[s], IDESC_PV, 1u);
+            if (fresh) mma_ts(tOx[X], tPx[X], dV[s], IDESC_PV, 0u);
+            else mma_ts(tOx[X], tPx[X], dV[s], IDESC_PV, 1u);
 #pragma unroll
-            for (int kk = 1; kk < 4; ++kk) mma_ts(tOx[X], tSx[X] + kk * 8, dV[s] + kk * 128, IDESC_PV, 1u);
+            for (int kk = 1; kk < 4; ++kk) mma_ts(tOx[X], tPx[X] + kk * 8, dV[s] + kk * 128, IDESC_PV, 1u);
             if (nch == 2) {
 #pragma unroll
-              for (int kk = 4; kk < 8; ++kk) mma_ts(tOx[X], tSx[X] + kk * 8, dV[s] + kk * 128, IDESC_PV, 1u);
+              for (int kk = 4; kk < 8; ++kk) mma_ts(tOx[X], tPx[X] + kk * 8, dV[s] + kk * 128, IDESC_PV, 1u);
             }
             tc_commit(bar(B_PVDONE + X));
             if (X == 1) tc_commit(bar(B_VEMPTY + s));
           }
           __syncwarp();
-          if (it + 1 < total_tiles) ok = issue_qk(X, it + 1);
+          if (!EARLY && it + 1 < total_tiles) ok = issue_qk(X, it + 1);
           T5_TRACE(4096 + it * 8 + 3 + 2 * X);
         }
         ++p_t; skip_empty(p_br, p_t);
@@ -475,6 +492,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const uint32_t tS = tmem + lane_addr + X * 128;
     const uint32_t tO = tmem + lane_addr + 256 + X * 128;
+    const uint32_t tP = EARLY ? tmem + lane_addr + 320 + X * 128 : tS;   // P: own columns at D=64, else over S
     const int rg = 2 * X + (r >> 6);                         // row group of this row
     const int head = grp_head(rg);
     const int qi = grp_qb(rg) * 64 + (r & 63);
@@ -535,6 +553,10 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
         tmem_ld32(tS + 32, sv[1]);
         if (tl.nch == 2) { tmem_ld32(tS + 64, sv[2]); tmem_ld32(tS + 96, sv[3]); }
         tc_wait_ld();
+        if constexpr (EARLY) {                             // S is in registers: the MMA warp may overwrite it
+          tc_fence_before();
+          mbar_arrive(bar(B_SREAD + X));
+        }
         // valid column range of each chunk for this row; masked entries become -inf
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -588,7 +610,14 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
           m_used = m_new;
         }
         const float m_ref = m_used == -INFINITY ? 0.f : m_used;
-        // P = exp2(S*scale - m_ref) as 16-bit into the columns S occupied (-inf -> 0)
+        if constexpr (EARLY) {
+          if (it > 0) {                                    // P's columns are free once the previous PV has read them
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(B_PVDONE + X), (it - 1) & 1, &abort_flag));
+            if (!ok) { fail_id = B_PVDONE + X + 1; break; }
+            tc_fence_after();
+          }
+        }
+        // P = exp2(S*scale - m_ref) as 16-bit (-inf -> 0)
         float psum0 = 0.f, psum1 = 0.f, psum2 = 0.f, psum3 = 0.f;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -601,7 +630,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
               if (i & 1) { psum2 += p0; psum3 += p1; } else { psum0 += p0; psum1 += p1; }
               pk[i] = Elem<T>::pack(p0, p1);
             }
-            tmem_st16(tS + g * 16, pk);
+            tmem_st16(tP + g * 16, pk);
           }
         }
         psum0 += psum2;
