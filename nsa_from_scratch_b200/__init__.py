@@ -13,9 +13,10 @@ from .forward import nsa_forward, nsa_forward_fp8, _resolve_block_indices
 from .backward import selected_backward
 from .fp8 import quantize_to_fp8, selected_attention_fp8
 from .native import selected_attention_cuda, selected_backward_cuda
+from .host import nsa_forward_host
 
 __all__ = [
     "NSAConfig", "compressed_attention", "selected_attention", "sliding_attention", "combine", "nsa_forward",
-    "nsa_forward_fp8", "selected_backward", "quantize_to_fp8", "selected_attention_fp8",
+    "nsa_forward_fp8", "nsa_forward_host", "selected_backward", "quantize_to_fp8", "selected_attention_fp8",
     "selected_attention_cuda", "selected_backward_cuda",
 ]

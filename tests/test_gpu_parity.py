@@ -433,3 +433,13 @@ def test_tcgen05_per_head_block_lists_and_any_group_size(nsa, shape):
     fin = torch.isfinite(ref).all(-1)
     assert max_abs(out, ref, fin) <= TOL16, max_abs(out, ref, fin)
     check_out_lse(o_s, l_s, ro, rl, TOL16)
+
+
+def test_host_tensor_entry_point_matches_device_path(nsa):
+    Q, K, V, g = make_qkv(13, 2, 8, 2, 512, 512, 128)
+    gates = torch.randn(2, 8, 512, 3, generator=g).to(torch.bfloat16)
+    cfg = nsa.NSAConfig(block_size_c=32, stride_c=16, top_k=4, window_size=128, select_per_group=True)
+    ref = nsa.nsa_forward(Q.cuda(), K.cuda(), V.cuda(), cfg, gate_logits=gates.cuda())
+    out = nsa.nsa_forward_host(Q.pin_memory(), K.pin_memory(), V.pin_memory(), cfg, gate_logits=gates.pin_memory())
+    torch.cuda.synchronize()
+    assert not out.is_cuda and torch.equal(out, ref.cpu())
