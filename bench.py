@@ -478,7 +478,21 @@ def run_sweep(a):
                           f"block lists per {'group' if shared else 'head'}"}, "fwd_ms": ms_f, "bwd_ms": ms_b,
                           "fwd_tflops": 4 * D * pairs / (ms_f * 1e-3) / 1e12, "bwd_tflops": 10 * D * pairs / (ms_b * 1e-3) / 1e12,
                           "tokens_per_s_fwd_bwd": B * T / ((ms_f + ms_b) * 1e-3)}), flush=True)
-    del Q, K, V, dO
+    # whole forward + backward through autograd (all three branch backward kernels + combine) at the same shape
+    cfg_t = nsa.NSAConfig(block_size_c=b.cmp_block, stride_c=b.cmp_stride, top_k=16, window_size=b.window,
+                          select_per_group=True)
+    Qr, Kr, Vr = (t.clone().requires_grad_(True) for t in (Q, K, V))
+
+    def train_step():
+        o = nsa.nsa_forward(Qr, Kr, Vr, cfg_t)
+        o.backward(dO)
+        Qr.grad = Kr.grad = Vr.grad = None
+    ms_t = timed(train_step, max(2, a.steps // 2))
+    ops.device_status()
+    print(json.dumps({"metric": "nsa_fwd_bwd_tokens_per_s", "value": B * T / (ms_t * 1e-3), "ms_per_step": ms_t,
+                      "config": {"workload": f"nsa_forward + backward (autograd, every branch on kernels) B={B} T={T} Hq={H} Hkv={Hkv} D={D} bf16"}}),
+          flush=True)
+    del Q, K, V, dO, Qr, Kr, Vr
     torch.cuda.empty_cache()
 
     # fp8 storage forward (e4m3, per-tensor absmax scales, 0.1 % outliers x20) at T=32768

@@ -160,7 +160,8 @@ int launch_selected_attn_fwd(const void* Q, const void* K, const void* V, const 
 int nsa_bwd_delta(const void* dO, const void* O, float* delta, int64_t rows, int D, int dtype,
                   nsa_stream_t stream);
 
-/* Selected-branch backward.  dQ [B,H,Tq,D] is WRITTEN (each query tile is owned by one
+/* Attention backward of ONE branch (nsa_bwd_args.branch = NSA_BRANCH_SELECTED / _SLIDING /
+ * _COMPRESSED).  dQ [B,H,Tq,D] is WRITTEN (each query tile is owned by one
  * thread block) in dq_dtype (NSA_FP32 or the 16-bit input type).  dK_f, dV_f
  * [B,Hkv,Tk,D] are fp32 and are ACCUMULATED into with fp32 atomic adds (the caller
  * zeroes them), which also forms the sum over the query heads that share a KV head.
@@ -183,10 +184,24 @@ typedef struct nsa_bwd_args {
   int32_t causal;
   int32_t dtype, dq_dtype;
   float scale;
+  int32_t branch;                               /* NSA_BRANCH_*; 0 is taken as NSA_BRANCH_SELECTED            */
+  int32_t window;                               /* sliding                                                     */
+  int32_t Nc, cmp_block, cmp_stride, cmp_offset; /* compressed: K, V, dK_f, dV_f are then [B,Hkv,Nc,D] (pooled) */
 } nsa_bwd_args;
 
-/* Replaces: selected_backward / _bwd_kernel, nsa/triton/backward.py:16-195. */
+/* Replaces: selected_backward / _bwd_kernel, nsa/triton/backward.py:16-195 (branch forced to selected). */
 int nsa_selected_bwd(const nsa_bwd_args* args, nsa_stream_t stream);
+
+/* Any branch.  lse and delta are those of the branch's own forward output.  Replaces the
+ * autograd-through-reference backward of the compressed and sliding branches,
+ * nsa/triton/forward.py:133-140 and :273-298. */
+int nsa_attention_bwd(const nsa_bwd_args* args, nsa_stream_t stream);
+
+/* Backward of nsa_pool_mean for fp32 gradients: dx [B,H,T,D] += spread(dxc [B,H,n_out,D]) / block,
+ * every row receiving the gradients of the windows that cover it.
+ * Replaces: the autograd of view(...).mean(3), nsa/reference.py:102-108. */
+int nsa_pool_mean_bwd(const float* dxc, float* dx, int B, int H, int T, int D, int block, int stride, int n_out,
+                      nsa_stream_t stream);
 
 /* The reference's native backward launcher, same argument list: dQ is bf16 and is
  * written; dK_f/dV_f are fp32 and accumulated into (zeroed by the caller, as

@@ -62,6 +62,8 @@ class BwdArgs(C.Structure):
         ("nq", C.c_int32), ("top_k", C.c_int32), ("bm", C.c_int32), ("bn", C.c_int32), ("sel_key_limit", C.c_int32),
         ("offset", C.c_int32), ("causal", C.c_int32), ("dtype", C.c_int32), ("dq_dtype", C.c_int32),
         ("scale", C.c_float),
+        ("branch", C.c_int32), ("window", C.c_int32),
+        ("Nc", C.c_int32), ("cmp_block", C.c_int32), ("cmp_stride", C.c_int32), ("cmp_offset", C.c_int32),
     ]
 
 
@@ -79,6 +81,8 @@ PROTOTYPES = {
     "launch_selected_attn_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "nsa_bwd_delta": (_i, [_vp, _vp, _vp, _i64, _i, _i, _vp]),
     "nsa_selected_bwd": (_i, [C.POINTER(BwdArgs), _vp]),
+    "nsa_attention_bwd": (_i, [C.POINTER(BwdArgs), _vp]),
+    "nsa_pool_mean_bwd": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "launch_selected_attn_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "nsa_combine": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp]),
     "nsa_fp8_absmax": (_i, [_vp, _i64, _i, _vp, _vp]),

@@ -25,7 +25,8 @@ int attention_fwd_generic(const nsa_fwd_args&, cudaStream_t);
 int attention_fwd_tc5(const nsa_fwd_args&, cudaStream_t);
 bool attention_fwd_tc5_supports(const nsa_fwd_args&);
 int tc5_take_status(cudaStream_t, int*);
-int selected_bwd(const nsa_bwd_args&, cudaStream_t);
+int attention_bwd(const nsa_bwd_args&, cudaStream_t);
+int pool_mean_bwd(const float*, float*, int, int, int, int, int, int, int, cudaStream_t);
 int combine(const void*, const void*, const void*, const void*, void*, long long, int, int, int, int, cudaStream_t);
 int fp8_absmax(const void*, long long, int, float*, cudaStream_t);
 int fp8_quantize(const void*, void*, long long, int, int, float, cudaStream_t);
@@ -145,17 +146,51 @@ int nsa_bwd_delta(const void* dO, const void* O, float* delta, int64_t rows, int
   return bwd_delta(dO, O, delta, rows, D, dtype, (cudaStream_t)stream);
 }
 
+static int check_bwd(const nsa_bwd_args* a) {
+  NSA_REQUIRE(a, NSA_ERR_ARG, "attention backward: NULL argument block");
+  NSA_REQUIRE(a->Q && a->K && a->V && a->dO && a->lse && a->delta && a->dQ && a->dK_f && a->dV_f, NSA_ERR_ARG,
+              "attention backward: NULL pointer");
+  NSA_REQUIRE(a->B > 0 && a->H > 0 && a->Hkv > 0 && a->H % a->Hkv == 0, NSA_ERR_ARG, "attention backward: heads %d/%d", a->H, a->Hkv);
+  NSA_REQUIRE(a->Tq > 0 && a->Tk > 0, NSA_ERR_ARG, "attention backward: empty problem");
+  NSA_REQUIRE(a->dq_dtype == NSA_FP32 || a->dq_dtype == a->dtype, NSA_ERR_ARG, "attention backward: dQ dtype %d", a->dq_dtype);
+  if (a->branch == NSA_BRANCH_SELECTED) {
+    NSA_REQUIRE(a->idx, NSA_ERR_ARG, "selected backward: block index pointer is NULL");
+    NSA_REQUIRE(a->Hi == a->H || a->Hi == a->Hkv, NSA_ERR_ARG, "selected backward: index heads %d", a->Hi);
+    NSA_REQUIRE(a->bm > 0 && a->bn > 0 && a->top_k > 0, NSA_ERR_ARG, "selected backward: empty problem");
+    NSA_REQUIRE(a->nq == (a->Tq + a->bm - 1) / a->bm, NSA_ERR_ARG, "selected backward: nq %d != ceil(Tq/bm)", a->nq);
+    NSA_REQUIRE(a->sel_key_limit >= a->Tk && a->sel_key_limit < a->Tk + a->bn, NSA_ERR_ARG, "selected backward: key limit %d", a->sel_key_limit);
+  } else if (a->branch == NSA_BRANCH_SLIDING) {
+    NSA_REQUIRE(a->window >= 1, NSA_ERR_ARG, "sliding backward: window %d", a->window);
+  } else if (a->branch == NSA_BRANCH_COMPRESSED) {
+    NSA_REQUIRE(a->Nc >= 0 && a->cmp_block > 0 && a->cmp_stride > 0 && a->cmp_stride <= a->cmp_block, NSA_ERR_ARG,
+                "compressed backward: Nc %d block %d stride %d", a->Nc, a->cmp_block, a->cmp_stride);
+  } else {
+    return fail(NSA_ERR_ARG, "attention backward: branch %d", a->branch);
+  }
+  return NSA_OK;
+}
+
+int nsa_attention_bwd(const nsa_bwd_args* a, nsa_stream_t stream) {
+  NSA_REQUIRE(a, NSA_ERR_ARG, "attention backward: NULL argument block");
+  nsa_bwd_args b = *a;
+  if (b.branch == 0) b.branch = NSA_BRANCH_SELECTED;
+  int rc = check_bwd(&b);
+  if (rc != NSA_OK) return rc;
+  if (b.branch == NSA_BRANCH_COMPRESSED && b.Nc == 0) return NSA_OK;
+  return attention_bwd(b, (cudaStream_t)stream);
+}
+
 int nsa_selected_bwd(const nsa_bwd_args* a, nsa_stream_t stream) {
   NSA_REQUIRE(a, NSA_ERR_ARG, "selected backward: NULL argument block");
-  NSA_REQUIRE(a->Q && a->K && a->V && a->dO && a->lse && a->delta && a->idx && a->dQ && a->dK_f && a->dV_f, NSA_ERR_ARG,
-              "selected backward: NULL pointer");
-  NSA_REQUIRE(a->B > 0 && a->H > 0 && a->Hkv > 0 && a->H % a->Hkv == 0, NSA_ERR_ARG, "selected backward: heads %d/%d", a->H, a->Hkv);
-  NSA_REQUIRE(a->Hi == a->H || a->Hi == a->Hkv, NSA_ERR_ARG, "selected backward: index heads %d", a->Hi);
-  NSA_REQUIRE(a->Tq > 0 && a->Tk > 0 && a->bm > 0 && a->bn > 0 && a->top_k > 0, NSA_ERR_ARG, "selected backward: empty problem");
-  NSA_REQUIRE(a->nq == (a->Tq + a->bm - 1) / a->bm, NSA_ERR_ARG, "selected backward: nq %d != ceil(Tq/bm)", a->nq);
-  NSA_REQUIRE(a->sel_key_limit >= a->Tk && a->sel_key_limit < a->Tk + a->bn, NSA_ERR_ARG, "selected backward: key limit %d", a->sel_key_limit);
-  NSA_REQUIRE(a->dq_dtype == NSA_FP32 || a->dq_dtype == a->dtype, NSA_ERR_ARG, "selected backward: dQ dtype %d", a->dq_dtype);
-  return selected_bwd(*a, (cudaStream_t)stream);
+  nsa_bwd_args b = *a;
+  b.branch = NSA_BRANCH_SELECTED;
+  return nsa_attention_bwd(&b, stream);
+}
+
+int nsa_pool_mean_bwd(const float* dxc, float* dx, int B, int H, int T, int D, int block, int stride, int n_out,
+                      nsa_stream_t stream) {
+  NSA_REQUIRE(dxc && dx, NSA_ERR_ARG, "pool backward: NULL pointer");
+  return pool_mean_bwd(dxc, dx, B, H, T, D, block, stride, n_out, (cudaStream_t)stream);
 }
 
 int launch_selected_attn_bwd(const void* Q, const void* K, const void* V, const void* dO, const float* LSE,

@@ -1,5 +1,7 @@
-// Selected-branch backward.  One thread block owns a tile of TM = 16*NW query rows of one
-// (batch, query head) and walks the KV blocks listed for its query block.  Per 64-key tile:
+// Attention backward for one NSA branch per launch: selected (the KV blocks listed for the query
+// block), sliding (the band of keys the tile's rows can see) or compressed (the pooled tokens; K/V are
+// then the pooled tensors and dK/dV their gradients, which nsa_pool_mean_bwd spreads back over the
+// rows).  One thread block owns a tile of TM = 16*NW query rows of one (batch, query head).  Per 64-key tile:
 //   S  = Q K^T            P  = exp(S*scale - lse)        (masked entries 0)
 //   dP = dO V^T           dS = P * (dP - delta) * scale
 //   dQ += dS K                                   (registers, written once at the end)
@@ -58,38 +60,67 @@ __global__ void __launch_bounds__(NW * 32, 2) selected_bwd_kernel(const __grid_c
   const int q0 = qt * TM;
   const int i_last = min(q0 + TM, a.Tq) - 1;
   const size_t q_slab = ((size_t)bh * a.Tq) * D;
-  const size_t kv_slab = ((size_t)(b * a.Hkv + hk) * a.Tk) * D;
+  const int key_rows = a.branch == NSA_BRANCH_COMPRESSED ? a.Nc : a.Tk;   // rows of K/V (and of dK/dV)
+  const size_t kv_slab = ((size_t)(b * a.Hkv + hk) * key_rows) * D;
   const T* Kg = reinterpret_cast<const T*>(a.K) + kv_slab;
   const T* Vg = reinterpret_cast<const T*>(a.V) + kv_slab;
 
   bstage16<T, D, NT>(smem_u32(Qs), reinterpret_cast<const T*>(a.Q) + q_slab, q0, TM, a.Tq);
   bstage16<T, D, NT>(smem_u32(dOs), reinterpret_cast<const T*>(a.dO) + q_slab, q0, TM, a.Tq);
   cp_async_commit();
+  // what the branch lets a query row see: keys lo..hi (inclusive)
+  auto bounds = [&](int i, int& lo, int& hi) {
+    lo = 0;
+    if (a.branch == NSA_BRANCH_COMPRESSED) {
+      if (a.causal) {
+        const int num = i + a.cmp_offset - (a.cmp_block - 1);
+        hi = num < 0 ? -1 : num / a.cmp_stride;
+      } else hi = a.Nc - 1;
+      hi = min(hi, a.Nc - 1);
+    } else if (a.branch == NSA_BRANCH_SLIDING) {
+      const int pos = i + a.offset;
+      if (a.causal) { lo = pos - a.window + 1; hi = pos; }
+      else { lo = pos - a.window; hi = pos + a.window; }
+      lo = max(lo, 0); hi = min(hi, a.Tk - 1);
+    } else {
+      hi = a.causal ? min(i + a.offset, a.sel_key_limit - 1) : a.sel_key_limit - 1;
+    }
+  };
   if (warp == 0) {
-    const int qb = q0 / a.bm;
-    const int hi_ = (a.Hi == a.H) ? h : hk;
-    const int32_t* row = a.idx + (((size_t)b * a.Hi + hi_) * a.nq + qb) * a.top_k;
-    const int last_pos = i_last + a.offset;
     int n = 0;
-    for (int s0 = 0; s0 < a.top_k; s0 += 32) {
-      int s = s0 + lane;
-      int blk = s < a.top_k ? row[s] : -1;
-      bool ok = blk >= 0 && blk < p.nk_blocks && (!a.causal || (long long)blk * a.bn <= last_pos);
-      unsigned m = __ballot_sync(0xffffffffu, ok);
-      if (ok) sel_list[n + __popc(m & ((1u << lane) - 1))] = blk;
-      n += __popc(m);
+    if (a.branch == NSA_BRANCH_SELECTED) {
+      const int qb = q0 / a.bm;
+      const int hi_ = (a.Hi == a.H) ? h : hk;
+      const int32_t* row = a.idx + (((size_t)b * a.Hi + hi_) * a.nq + qb) * a.top_k;
+      const int last_pos = i_last + a.offset;
+      for (int s0 = 0; s0 < a.top_k; s0 += 32) {
+        int s = s0 + lane;
+        int blk = s < a.top_k ? row[s] : -1;
+        bool ok = blk >= 0 && blk < p.nk_blocks && (!a.causal || (long long)blk * a.bn <= last_pos);
+        unsigned m = __ballot_sync(0xffffffffu, ok);
+        if (ok) sel_list[n + __popc(m & ((1u << lane) - 1))] = blk;
+        n += __popc(m);
+      }
     }
     if (lane == 0) sel_n = n;
   }
   __syncthreads();
   const int tpb = (a.bn + BTN - 1) / BTN;
-  const int ntiles = sel_n * tpb;
+  int ntiles = 0, tile0 = 0;
+  if (a.branch == NSA_BRANCH_SELECTED) ntiles = sel_n * tpb;
+  else {
+    int lo_f, hi_f, lo_l, hi_l;
+    bounds(q0, lo_f, hi_f);
+    bounds(i_last, lo_l, hi_l);
+    if (a.branch == NSA_BRANCH_COMPRESSED) ntiles = hi_l < 0 ? 0 : hi_l / BTN + 1;
+    else if (hi_l >= lo_f) { tile0 = lo_f / BTN; ntiles = hi_l / BTN - tile0 + 1; }
+  }
 
   const int g8 = lane >> 2, t4 = lane & 3, mi = lane >> 3, r8 = lane & 7;
   const int row_l[2] = {warp * 16 + g8, warp * 16 + g8 + 8};
   const int row_i[2] = {q0 + row_l[0], q0 + row_l[1]};
   float lse2[2], dl[2];
-  int hi[2];
+  int lo[2], hi[2];
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     bool ok = row_i[r] < a.Tq;
@@ -97,7 +128,8 @@ __global__ void __launch_bounds__(NW * 32, 2) selected_bwd_kernel(const __grid_c
     dl[r] = ok ? a.delta[(size_t)bh * a.Tq + row_i[r]] : 0.f;
     ok = ok && l > -INFINITY;
     lse2[r] = ok ? l * kLog2e : 0.f;
-    hi[r] = !ok ? -1 : (a.causal ? min(row_i[r] + a.offset, a.sel_key_limit - 1) : a.sel_key_limit - 1);
+    bounds(row_i[r], lo[r], hi[r]);
+    if (!ok) hi[r] = -1;
   }
 
   float dq[2 * KS][4];
@@ -105,15 +137,20 @@ __global__ void __launch_bounds__(NW * 32, 2) selected_bwd_kernel(const __grid_c
   for (int d = 0; d < 2 * KS; ++d) { dq[d][0] = dq[d][1] = dq[d][2] = dq[d][3] = 0.f; }
 
   auto tile_start = [&](int t, int& j0, int& jlim) {
-    int blk = sel_list[t / tpb];
-    j0 = blk * a.bn + (t % tpb) * BTN;
-    jlim = min(blk * a.bn + a.bn, a.sel_key_limit);
+    if (a.branch == NSA_BRANCH_SELECTED) {
+      int blk = sel_list[t / tpb];
+      j0 = blk * a.bn + (t % tpb) * BTN;
+      jlim = min(blk * a.bn + a.bn, a.sel_key_limit);
+    } else {
+      j0 = (tile0 + t) * BTN;
+      jlim = key_rows;
+    }
   };
   auto issue = [&](int t) {
     int j0, jlim;
     tile_start(t, j0, jlim);
-    bstage16<T, D, NT>(smem_u32(Ks), Kg, j0, BTN, a.Tk);
-    bstage16<T, D, NT>(smem_u32(Vs), Vg, j0, BTN, a.Tk);
+    bstage16<T, D, NT>(smem_u32(Ks), Kg, j0, BTN, key_rows);
+    bstage16<T, D, NT>(smem_u32(Vs), Vg, j0, BTN, key_rows);
     cp_async_commit();
   };
   if (ntiles > 0) issue(0);
@@ -156,7 +193,7 @@ __global__ void __launch_bounds__(NW * 32, 2) selected_bwd_kernel(const __grid_c
       for (int e = 0; e < 4; ++e) {
         const int r = e >> 1;
         const int j = j0 + n * 8 + t4 * 2 + (e & 1);
-        float pv = j <= hi_t[r] ? ex2(s[n][e] * p.scale_log2 - lse2[r]) : 0.f;
+        float pv = (j >= lo[r] && j <= hi_t[r]) ? ex2(s[n][e] * p.scale_log2 - lse2[r]) : 0.f;
         s[n][e] = pv;
         dp[n][e] = pv * (dp[n][e] - dl[r]) * a.scale;
       }
@@ -211,7 +248,7 @@ __global__ void __launch_bounds__(NW * 32, 2) selected_bwd_kernel(const __grid_c
           }
         }
         const int key0 = j0 + mt * 16 + g8, key1 = key0 + 8;
-        const int key_lim = min(jlim, a.Tk);
+        const int key_lim = min(jlim, key_rows);
 #pragma unroll
         for (int d = 0; d < 2 * KS; ++d) {
           const int col = d * 8 + t4 * 2;
@@ -259,21 +296,59 @@ static int bwd_dispatch(const BwdK& k, int nw, cudaStream_t st) {
   return fail(NSA_ERR_UNSUPPORTED, "selected backward: head dim %d not in {32,64,128}", k.a.D);
 }
 
-int selected_bwd(const nsa_bwd_args& a, cudaStream_t st) {
+int attention_bwd(const nsa_bwd_args& a, cudaStream_t st) {
   BwdK k;
   k.a = a;
   k.scale_log2 = a.scale * kLog2e;
-  k.nk_blocks = (a.sel_key_limit + a.bn - 1) / a.bn;
-  NSA_REQUIRE(a.top_k <= BMAX_SEL, NSA_ERR_UNSUPPORTED, "selected backward: top_k %d > %d", a.top_k, BMAX_SEL);
+  k.nk_blocks = 0;
   int tm = 64;
-  if (a.bm % 64 != 0) {
-    NSA_REQUIRE(a.bm == 32, NSA_ERR_UNSUPPORTED, "selected backward: block_size_m %d must be 32 or a multiple of 64", a.bm);
-    tm = 32;
+  if (a.branch == NSA_BRANCH_SELECTED) {
+    k.nk_blocks = (a.sel_key_limit + a.bn - 1) / a.bn;
+    NSA_REQUIRE(a.top_k <= BMAX_SEL, NSA_ERR_UNSUPPORTED, "selected backward: top_k %d > %d", a.top_k, BMAX_SEL);
+    if (a.bm % 64 != 0) {
+      NSA_REQUIRE(a.bm == 32, NSA_ERR_UNSUPPORTED, "selected backward: block_size_m %d must be 32 or a multiple of 64", a.bm);
+      tm = 32;
+    }
   }
   k.n_qtiles = (a.Tq + tm - 1) / tm;
   if (a.dtype == NSA_BF16) return bwd_dispatch<__nv_bfloat16>(k, tm / 16, st);
   if (a.dtype == NSA_FP16) return bwd_dispatch<__half>(k, tm / 16, st);
   return fail(NSA_ERR_UNSUPPORTED, "selected backward: dtype %d", a.dtype);
+}
+
+// ------------------------------------------------------------------ pooling backward
+// dX[j] += sum over the windows c that cover row j of dXc[c] / block  (fp32 in, fp32 accumulate into dX).
+__global__ void __launch_bounds__(256) pool_mean_bwd_kernel(const float* __restrict__ dxc, float* __restrict__ dx, int Tlen,
+                                                            int D, int block, int stride, int n_out) {
+  const int CH = D / 4;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)Tlen * CH) return;
+  const int j = (int)(i / CH), ch = (int)(i % CH);
+  // windows c with c*stride <= j <= c*stride + block - 1
+  int c_hi = j / stride;
+  int c_lo = j - (block - 1) <= 0 ? 0 : (j - (block - 1) + stride - 1) / stride;
+  c_hi = min(c_hi, n_out - 1);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float4* src = reinterpret_cast<const float4*>(dxc + (size_t)blockIdx.y * n_out * D) + ch;
+  for (int c = c_lo; c <= c_hi; ++c) {
+    const float4 v = src[(size_t)c * CH];
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  const float inv = 1.f / (float)block;
+  float4* dst = reinterpret_cast<float4*>(dx + (size_t)blockIdx.y * Tlen * D) + (size_t)j * CH + ch;
+  float4 o = *dst;
+  o.x += acc.x * inv; o.y += acc.y * inv; o.z += acc.z * inv; o.w += acc.w * inv;
+  *dst = o;
+}
+
+int pool_mean_bwd(const float* dxc, float* dx, int B, int H, int T, int D, int block, int stride, int n_out, cudaStream_t st) {
+  NSA_REQUIRE(D % 4 == 0 && D > 0, NSA_ERR_ARG, "pool backward: D %d must be a positive multiple of 4", D);
+  NSA_REQUIRE(block > 0 && stride > 0 && stride <= block, NSA_ERR_ARG, "pool backward: block %d stride %d", block, stride);
+  if (n_out == 0 || T == 0 || B * H == 0) return NSA_OK;
+  NSA_REQUIRE((long long)B * H <= 65535, NSA_ERR_ARG, "pool backward: B*H too large");
+  dim3 grid((unsigned)(((long long)T * (D / 4) + 255) / 256), (unsigned)(B * H));
+  pool_mean_bwd_kernel<<<grid, 256, 0, st>>>(dxc, dx, T, D, block, stride, n_out);
+  return launch_status("pool_mean_bwd");
 }
 
 }  // namespace nsa

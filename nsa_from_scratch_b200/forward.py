@@ -5,8 +5,9 @@
 Without autograd the whole forward is four launches: pool K/V, pool Q/K block means,
 score+top-k, and ONE fused kernel that runs the three branches per query tile and applies
 the gates in its epilogue (no branch output ever reaches HBM).  With autograd the branches
-run separately so that their outputs can be saved; the selected branch has the hand-written
-backward, the compressed and sliding branches differentiate a torch recompute."""
+run separately so that their outputs and log-sum-exps can be saved; every branch has a
+hand-written backward kernel (the reference differentiates its plain-torch functions for the
+compressed and sliding branches, nsa/triton/forward.py:133-140,273-298)."""
 from __future__ import annotations
 
 from typing import Optional
@@ -15,7 +16,7 @@ import torch
 from torch import Tensor
 
 from . import _lib as L
-from . import _recompute, ops
+from . import ops
 from .compressed import compressed_attention as _compressed_kernel
 from .gating import combine
 from .selected import selected_attention as _selected_kernel
@@ -47,31 +48,30 @@ def _resolve_block_indices(Q: Tensor, K: Tensor, *, block_size_m: int, block_siz
                                         shared_per_group=shared_per_group)
 
 
-def _grads_through(fn, Q, K, V, grad_out):
-    with torch.enable_grad():
-        Qd, Kd, Vd = (t.detach().requires_grad_(True) for t in (Q, K, V))
-        out = fn(Qd, Kd, Vd)
-        dQ, dK, dV = torch.autograd.grad(out, (Qd, Kd, Vd), grad_outputs=grad_out.to(out.dtype), allow_unused=True)
-    z = lambda g, x: torch.zeros_like(x) if g is None else torch.nan_to_num(g, nan=0.0, posinf=0.0, neginf=0.0).to(x.dtype)
-    return z(dQ, Q), z(dK, K), z(dV, V)
-
-
 class _CompressedFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, Q, K, V, block_size_c, pool, causal, scale, stride_c=None):
-        out, _ = _compressed_kernel(Q, K, V, block_size_c=block_size_c, pool=pool, causal=causal, scale=scale,
-                                    stride_c=stride_c)
-        ctx.save_for_backward(Q, K, V)
+        out, lse = _compressed_kernel(Q, K, V, block_size_c=block_size_c, pool=pool, causal=causal, scale=scale,
+                                      stride_c=stride_c)
+        ctx.save_for_backward(Q, K, V, out, lse)
         ctx.args = (block_size_c, stride_c, causal, scale)
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
-        Q, K, V = ctx.saved_tensors
+        Q, K, V, O, LSE = ctx.saved_tensors
         bc, sc, causal, scale = ctx.args
-        dQ, dK, dV = _grads_through(
-            lambda q, k, v: _recompute.compressed_torch(q, k, v, block_size_c=bc, stride_c=sc, causal=causal, scale=scale),
-            Q, K, V, grad_out)
+        D, Tq, Tk = Q.shape[-1], Q.shape[2], K.shape[2]
+        stride = bc if sc is None else int(sc)
+        Kc, Vc = ops.pool_mean(K, bc, stride), ops.pool_mean(V, bc, stride)
+        Tk_pad = Kc.shape[2] * bc if stride == bc else Tk
+        dO = grad_out.to(Q.dtype)
+        delta = ops.bwd_delta(dO, O)
+        dQ, dKc, dVc = ops.attention_bwd(dO, Q, Kc, Vc, LSE, delta, branch=L.BRANCH_COMPRESSED, causal=bool(causal),
+                                         scale=ops.softmax_scale(D, scale), offset=Tk - Tq, dq_fp32=False, cmp_block=bc,
+                                         cmp_stride=stride, cmp_offset=Tk_pad - Tq, Tk_keys=Tk)
+        dK = ops.cast_from_f32(ops.pool_mean_bwd(dKc, Tk, bc, stride), K.dtype)
+        dV = ops.cast_from_f32(ops.pool_mean_bwd(dVc, Tk, bc, stride), V.dtype)
         return dQ, dK, dV, None, None, None, None, None
 
 
@@ -102,18 +102,22 @@ class _SelectedFn(torch.autograd.Function):
 class _SlidingFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, Q, K, V, window_size, causal, scale):
-        out, _ = _sliding_kernel(Q, K, V, window_size=window_size, causal=causal, scale=scale)
-        ctx.save_for_backward(Q, K, V)
+        out, lse = _sliding_kernel(Q, K, V, window_size=window_size, causal=causal, scale=scale)
+        ctx.save_for_backward(Q, K, V, out, lse)
         ctx.args = (window_size, causal, scale)
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
-        Q, K, V = ctx.saved_tensors
+        Q, K, V, O, LSE = ctx.saved_tensors
         W, causal, scale = ctx.args
-        dQ, dK, dV = _grads_through(
-            lambda q, k, v: _recompute.sliding_torch(q, k, v, window_size=W, causal=causal, scale=scale), Q, K, V, grad_out)
-        return dQ, dK, dV, None, None, None
+        D = Q.shape[-1]
+        dO = grad_out.to(Q.dtype)
+        delta = ops.bwd_delta(dO, O)
+        dQ, dK, dV = ops.attention_bwd(dO, Q, K, V, LSE, delta, branch=L.BRANCH_SLIDING, causal=bool(causal),
+                                       scale=ops.softmax_scale(D, scale), offset=K.shape[2] - Q.shape[2], dq_fp32=False,
+                                       window=int(W))
+        return dQ, ops.cast_from_f32(dK, K.dtype), ops.cast_from_f32(dV, V.dtype), None, None, None
 
 
 class _CombineFn(torch.autograd.Function):

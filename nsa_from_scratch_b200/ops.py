@@ -158,30 +158,60 @@ def bwd_delta(dO: Tensor, O: Tensor) -> Tensor:
     return delta
 
 
+def attention_bwd(dO: Tensor, Q: Tensor, K: Tensor, V: Tensor, lse: Tensor, delta: Tensor, *, branch: int, causal: bool,
+                  scale: float, offset: int, dq_fp32: bool, idx: Optional[Tensor] = None, bm: int = 64, bn: int = 64,
+                  window: int = 0, cmp_block: int = 0, cmp_stride: int = 0, cmp_offset: int = 0,
+                  Tk_keys: Optional[int] = None) -> Tuple[Tensor, Tensor, Tensor]:
+    """Backward of one branch.  For the compressed branch K/V are the POOLED tensors [B,Hkv,Nc,D] and the
+    returned dK/dV are their fp32 gradients (Tk_keys = length of the raw key sequence).  Returns
+    (dQ in Q.dtype or fp32, dK fp32, dV fp32)."""
+    _need_cuda(dO, Q, K, V, lse, delta)
+    B, H, Tq, D = Q.shape
+    Hkv, rows = K.shape[1], K.shape[2]
+    dO, Q, K, V = dO.contiguous(), Q.contiguous(), K.contiguous(), V.contiguous()
+    lse, delta = lse.contiguous(), delta.contiguous()
+    dQ = torch.empty((B, H, Tq, D), device=Q.device, dtype=torch.float32 if dq_fp32 else Q.dtype)
+    dK = torch.zeros((B, Hkv, rows, D), device=Q.device, dtype=torch.float32)
+    dV = torch.zeros((B, Hkv, rows, D), device=Q.device, dtype=torch.float32)
+    a = L.BwdArgs()
+    a.Q, a.K, a.V, a.dO = Q.data_ptr(), K.data_ptr(), V.data_ptr(), dO.data_ptr()
+    a.lse, a.delta = lse.data_ptr(), delta.data_ptr()
+    a.dQ, a.dK_f, a.dV_f = dQ.data_ptr(), dK.data_ptr(), dV.data_ptr()
+    a.B, a.H, a.Hkv, a.Tq, a.D = B, H, Hkv, Tq, D
+    a.Tk = rows if Tk_keys is None else Tk_keys
+    a.branch, a.offset, a.causal, a.dtype = branch, offset, int(causal), L.dtype_code(Q.dtype)
+    a.dq_dtype = L.FP32 if dq_fp32 else a.dtype
+    a.scale = float(scale)
+    if branch == L.BRANCH_SELECTED:
+        idx = idx.to(torch.int32).contiguous()
+        a.idx, a.Hi, a.nq, a.top_k, a.bm, a.bn = idx.data_ptr(), idx.shape[1], (Tq + bm - 1) // bm, idx.shape[3], bm, bn
+        a.sel_key_limit = ((rows + bn - 1) // bn) * bn
+    elif branch == L.BRANCH_SLIDING:
+        a.window = int(window)
+    else:
+        a.Nc, a.cmp_block, a.cmp_stride, a.cmp_offset = rows, cmp_block, cmp_stride, cmp_offset
+    with torch.cuda.device(Q.device):
+        L.check(L.load().nsa_attention_bwd(C.byref(a), L.stream_ptr()), "nsa_attention_bwd")
+    return dQ, dK, dV
+
+
 def selected_bwd(dO: Tensor, Q: Tensor, K: Tensor, V: Tensor, lse: Tensor, delta: Tensor, idx: Tensor, *, bm: int,
                  bn: int, causal: bool, scale: float, offset: int, dq_fp32: bool) -> Tuple[Tensor, Tensor, Tensor]:
     """Returns (dQ in Q.dtype or fp32, dK fp32, dV fp32)."""
-    _need_cuda(dO, Q, K, V, lse, delta, idx)
-    B, H, Tq, D = Q.shape
-    Hkv, Tk = K.shape[1], K.shape[2]
-    dO, Q, K, V = dO.contiguous(), Q.contiguous(), K.contiguous(), V.contiguous()
-    lse, delta, idx = lse.contiguous(), delta.contiguous(), idx.to(torch.int32).contiguous()
-    dQ = torch.empty((B, H, Tq, D), device=Q.device, dtype=torch.float32 if dq_fp32 else Q.dtype)
-    dK = torch.zeros((B, Hkv, Tk, D), device=Q.device, dtype=torch.float32)
-    dV = torch.zeros((B, Hkv, Tk, D), device=Q.device, dtype=torch.float32)
-    a = L.BwdArgs()
-    a.Q, a.K, a.V, a.dO = Q.data_ptr(), K.data_ptr(), V.data_ptr(), dO.data_ptr()
-    a.lse, a.delta, a.idx = lse.data_ptr(), delta.data_ptr(), idx.data_ptr()
-    a.dQ, a.dK_f, a.dV_f = dQ.data_ptr(), dK.data_ptr(), dV.data_ptr()
-    a.B, a.H, a.Hkv, a.Hi, a.Tq, a.Tk, a.D = B, H, Hkv, idx.shape[1], Tq, Tk, D
-    a.nq, a.top_k, a.bm, a.bn = (Tq + bm - 1) // bm, idx.shape[3], bm, bn
-    a.sel_key_limit = ((Tk + bn - 1) // bn) * bn
-    a.offset, a.causal, a.dtype = offset, int(causal), L.dtype_code(Q.dtype)
-    a.dq_dtype = L.FP32 if dq_fp32 else a.dtype
-    a.scale = float(scale)
-    with torch.cuda.device(Q.device):
-        L.check(L.load().nsa_selected_bwd(C.byref(a), L.stream_ptr()), "nsa_selected_bwd")
-    return dQ, dK, dV
+    return attention_bwd(dO, Q, K, V, lse, delta, branch=L.BRANCH_SELECTED, causal=causal, scale=scale, offset=offset,
+                         dq_fp32=dq_fp32, idx=idx, bm=bm, bn=bn)
+
+
+def pool_mean_bwd(dxc: Tensor, T: int, block: int, stride: int) -> Tensor:
+    """fp32 [B,H,n,D] gradients of pooled rows -> fp32 [B,H,T,D] gradients of the rows."""
+    _need_cuda(dxc)
+    B, H, n, D = dxc.shape
+    dxc = dxc.contiguous()
+    dx = torch.zeros((B, H, T, D), device=dxc.device, dtype=torch.float32)
+    with torch.cuda.device(dxc.device):
+        L.check(L.load().nsa_pool_mean_bwd(dxc.data_ptr(), dx.data_ptr(), B, H, T, D, block, stride, n, L.stream_ptr()),
+                "nsa_pool_mean_bwd")
+    return dx
 
 
 def cast_from_f32(x: Tensor, dtype: torch.dtype) -> Tensor:

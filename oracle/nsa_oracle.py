@@ -348,6 +348,18 @@ def selected_backward(
     return z(dQ, Qd), z(dK, Kd), z(dV, Vd)
 
 
+def branch_backward(kind: str, dO: Tensor, Q: Tensor, K: Tensor, V: Tensor, **kw) -> Tuple[Tensor, Tensor, Tensor]:
+    """fp32 (dQ, dK, dV) of the compressed ("cmp") or sliding ("sld") branch by autograd through this
+    file's forward -- the reference's own backward for these branches is autograd through its
+    plain-torch functions with NaN rows zeroed (nsa/triton/forward.py:84-120,133-140,273-298)."""
+    Qd, Kd, Vd = (t.detach().float().requires_grad_(True) for t in (Q, K, V))
+    fn = compressed_attention if kind == "cmp" else sliding_attention
+    out, _ = fn(Qd, Kd, Vd, **kw)
+    grads = torch.autograd.grad(out, (Qd, Kd, Vd), grad_outputs=dO.float(), allow_unused=True)
+    return tuple(torch.zeros_like(x) if g is None else torch.nan_to_num(g, 0.0, 0.0, 0.0)
+                 for g, x in zip(grads, (Qd, Kd, Vd)))
+
+
 # --------------------------------------------------------------------------
 # sliding-window branch
 # --------------------------------------------------------------------------

@@ -126,6 +126,27 @@ def main():
                     f"{name}.out": np32(o), f"{name}.lse": np32(l)})
         meta.append((name, dict(B=B, H=H, Tq=Tq, Tk=Tk, D=D, W=W, causal=causal, dtype=str(dt))))
 
+    # ---- compressed / sliding gradients (the reference's own backward route: autograd through its
+    #      plain-torch functions with nan_to_num, nsa/triton/forward.py:84-120) ---------------------
+    for name, (B, H, Tq, Tk, D, kind, par, causal) in {
+        "gcmp_a": (1, 2, 128, 128, 32, "cmp", 32, True),
+        "gcmp_b": (1, 2, 96, 200, 32, "cmp", 64, True),
+        "gsld_a": (1, 2, 128, 128, 32, "sld", 48, True),
+        "gsld_b": (1, 2, 100, 300, 32, "sld", 64, False),
+    }.items():
+        Q, K, V, g = qkv(71, B, H, Tq, Tk, D, torch.bfloat16, 0.7)
+        dO = torch.randn(B, H, Tq, D, generator=g)
+        Qd, Kd, Vd = (t.float().requires_grad_(True) for t in (Q, K, V))
+        if kind == "cmp":
+            o, _ = R.compressed_attention_reference(Qd, Kd, Vd, block_size_c=par, causal=causal)
+        else:
+            o, _ = R.sliding_attention_reference(Qd, Kd, Vd, window_size=par, causal=causal)
+        on = torch.nan_to_num(o, nan=0.0, posinf=0.0, neginf=0.0)
+        dQ, dK, dV = (torch.nan_to_num(t) for t in torch.autograd.grad(on, (Qd, Kd, Vd), grad_outputs=dO))
+        out.update({f"{name}.Q": np32(Q), f"{name}.K": np32(K), f"{name}.V": np32(V), f"{name}.dO": np32(dO),
+                    f"{name}.dQ": np32(dQ), f"{name}.dK": np32(dK), f"{name}.dV": np32(dV)})
+        meta.append((name, dict(B=B, H=H, Tq=Tq, Tk=Tk, D=D, kind=kind, par=par, causal=causal)))
+
     # ---- combined forward with gates -----------------------------------------
     for name, (B, H, T, D, act) in {
         "nsa_a": (1, 2, 256, 32, "sigmoid"),

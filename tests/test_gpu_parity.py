@@ -443,3 +443,69 @@ def test_host_tensor_entry_point_matches_device_path(nsa):
     out = nsa.nsa_forward_host(Q.pin_memory(), K.pin_memory(), V.pin_memory(), cfg, gate_logits=gates.pin_memory())
     torch.cuda.synchronize()
     assert not out.is_cuda and torch.equal(out, ref.cpu())
+
+
+# ------------------------------------------------------------------ compressed / sliding backward kernels
+def test_golden_compressed_and_sliding_gradients(nsa, golden):
+    """Gradients through the autograd Functions against the reference's own (autograd through its torch code)."""
+    from nsa_from_scratch_b200.forward import _CompressedFn, _SlidingFn
+    for name, kind, par, causal in (("gcmp_a", "cmp", 32, True), ("gcmp_b", "cmp", 64, True),
+                                    ("gsld_a", "sld", 48, True), ("gsld_b", "sld", 64, False)):
+        Q, K, V, dO = (G(golden, f"{name}.{x}", torch.bfloat16) for x in ("Q", "K", "V", "dO"))
+        Qc, Kc, Vc = (t.cuda().requires_grad_(True) for t in (Q, K, V))
+        o = _CompressedFn.apply(Qc, Kc, Vc, par, "mean", causal, None) if kind == "cmp" else _SlidingFn.apply(Qc, Kc, Vc, par, causal, None)
+        o.backward(dO.cuda())
+        for got, key in ((Qc.grad, "dQ"), (Kc.grad, "dK"), (Vc.grad, "dV")):
+            ref = G(golden, f"{name}.{key}")
+            if name == "gcmp_a" and key == "dV":      # the reference's dV is all zero here (NaN rows poison it): use the oracle
+                ref = O.branch_backward("cmp", dO, Q, K, V, block_size_c=par, causal=causal)[2]
+            assert max_abs(got, ref) <= 3e-2 * max(1.0, float(ref.abs().max())), (name, key, max_abs(got, ref))
+
+
+@pytest.mark.parametrize("case", [(1, 4, 4, 256, 256, 64), (1, 8, 2, 192, 320, 128), (2, 2, 1, 100, 200, 32)])
+@pytest.mark.parametrize("causal", [True, False])
+def test_branch_backward_kernels_vs_oracle(nsa, case, causal):
+    from nsa_from_scratch_b200 import _lib as L, ops
+    B, H, Hkv, Tq, Tk, D = case
+    Q, K, V, g = make_qkv(14, B, H, Hkv, Tq, Tk, D, amp=0.7)
+    dO = torch.randn(B, H, Tq, D, generator=g).to(torch.bfloat16)
+    Qc, Kc, Vc, dOc = Q.cuda(), K.cuda(), V.cuda(), dO.cuda()
+    scale = D ** -0.5
+    # sliding
+    for W in (64, 100):
+        out, lse = nsa.sliding_attention(Qc, Kc, Vc, window_size=W, causal=causal)
+        dQ, dK, dV = ops.attention_bwd(dOc, Qc, Kc, Vc, lse, ops.bwd_delta(dOc, out), branch=L.BRANCH_SLIDING, causal=causal,
+                                       scale=scale, offset=Tk - Tq, dq_fp32=True, window=W)
+        for got, ref, nm in zip((dQ, dK, dV), O.branch_backward("sld", dO, Q, K, V, window_size=W, causal=causal), "QKV"):
+            assert max_abs(got, ref) <= TOL16 * max(1.0, float(ref.abs().max())), ("sld", W, nm, max_abs(got, ref))
+    # compressed, both geometries, through the pooled tensors and the pooling backward
+    for bc, st in ((64, 64), (32, 16)):
+        Kp, Vp = ops.pool_mean(Kc, bc, st), ops.pool_mean(Vc, bc, st)
+        Tk_pad = Kp.shape[2] * bc if st == bc else Tk
+        out, lse = nsa.compressed_attention(Qc, Kc, Vc, block_size_c=bc, causal=causal, stride_c=st)
+        dQ, dKp, dVp = ops.attention_bwd(dOc, Qc, Kp, Vp, lse, ops.bwd_delta(dOc, out), branch=L.BRANCH_COMPRESSED,
+                                         causal=causal, scale=scale, offset=Tk - Tq, dq_fp32=True, cmp_block=bc,
+                                         cmp_stride=st, cmp_offset=Tk_pad - Tq, Tk_keys=Tk)
+        dK, dV = ops.pool_mean_bwd(dKp, Tk, bc, st), ops.pool_mean_bwd(dVp, Tk, bc, st)
+        refs = O.branch_backward("cmp", dO, Q, K, V, block_size_c=bc, stride_c=st, causal=causal)
+        for got, ref, nm in zip((dQ, dK, dV), refs, "QKV"):
+            assert max_abs(got, ref) <= TOL16 * max(1.0, float(ref.abs().max())), ("cmp", bc, st, nm, max_abs(got, ref))
+
+
+def test_full_forward_gradients_vs_oracle(nsa):
+    """d(sum out * w)/d(Q,K,V,gates) through nsa_forward (all three branch backward kernels + combine)."""
+    B, H, Hkv, T, D = 1, 4, 2, 256, 64
+    Q, K, V, g = make_qkv(15, B, H, Hkv, T, T, D, amp=0.7)
+    gates = torch.randn(B, H, T, 3, generator=g)
+    w = torch.randn(B, H, T, D, generator=g)
+    cfg = nsa.NSAConfig(block_size_c=32, stride_c=16, top_k=3, window_size=96)
+    idx = O.select_blocks(Q, K, top_k=3)
+    Qf, Kf, Vf, Gf = (t.float().clone().requires_grad_(True) for t in (Q, K, V, gates))
+    ref = O.nsa_forward(Qf, Kf, Vf, block_size_c=32, stride_c=16, top_k=3, window_size=96, gate_logits=Gf, block_indices=idx)
+    rg = torch.autograd.grad(ref, (Qf, Kf, Vf, Gf), grad_outputs=w)
+    Qc, Kc, Vc = (t.cuda().requires_grad_(True) for t in (Q, K, V))
+    Gc = gates.cuda().requires_grad_(True)
+    out = nsa.nsa_forward(Qc, Kc, Vc, cfg, gate_logits=Gc, block_indices=idx.cuda())
+    out.backward(w.cuda().to(out.dtype))
+    for got, ref_g, nm in zip((Qc.grad, Kc.grad, Vc.grad, Gc.grad), rg, ("dQ", "dK", "dV", "dG")):
+        assert max_abs(got, ref_g) <= 3e-2 * max(1.0, float(ref_g.abs().max())), (nm, max_abs(got, ref_g), float(ref_g.abs().max()))
