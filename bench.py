@@ -479,8 +479,7 @@ def run_sweep(a):
                           "fwd_tflops": 4 * D * pairs / (ms_f * 1e-3) / 1e12, "bwd_tflops": 10 * D * pairs / (ms_b * 1e-3) / 1e12,
                           "tokens_per_s_fwd_bwd": B * T / ((ms_f + ms_b) * 1e-3)}), flush=True)
     # whole forward + backward through autograd (all three branch backward kernels + combine) at the same shape
-    cfg_t = nsa.NSAConfig(block_size_c=b.cmp_block, stride_c=b.cmp_stride, top_k=16, window_size=b.window,
-                          select_per_group=True)
+    cfg_t = nsa.NSAConfig(block_size_c=32, stride_c=16, top_k=16, window_size=512, select_per_group=True)
     Qr, Kr, Vr = (t.clone().requires_grad_(True) for t in (Q, K, V))
 
     def train_step():
