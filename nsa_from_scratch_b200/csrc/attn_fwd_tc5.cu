@@ -5,8 +5,9 @@
 // All rows of a work item see the same KV tiles in every branch (the selected blocks are
 // shared by the heads of a GQA group), so a K/V tile staged once by TMA feeds both tiles.
 //
-// Warp roles (12 warps, one block per SM; warps 0-3 shrink to 72 registers with setmaxnreg, the
-// softmax warps grow to 216 -- each SM sub-partition then holds 72 + 2*216 = 504 of its 512 registers per lane; an exact fit must be avoided, setmaxnreg.inc blocks until the registers exist):
+// Warp roles (12 warps launched at 168 registers, one block per SM; with setmaxnreg warps 0-3 shrink to
+// 72 and the 8 softmax warps grow to 216.  What the .inc calls take must have been released by .dec
+// calls of the SAME block -- 8*(216-168) <= 4*(168-72) -- otherwise setmaxnreg.inc blocks forever):
 //   warp 0      TMA producer: Q once, then K and V tiles (1 or 2 chunks of 64 keys) into two
 //               2-deep rings of 128-byte-swizzled shared memory; pooled K/V for the compressed
 //               branch, raw K/V for the selected and sliding branches
@@ -32,7 +33,7 @@ using namespace tc5;
 
 constexpr int T5_MAX_SEL = 64;            // listed blocks per query block
 constexpr int T5_MAX_ENT = 4 * T5_MAX_SEL;  // entries of the four row groups of a work item
-constexpr int T5_THREADS = 384;   // 12 warps; register budget rebalanced per role with setmaxnreg   // 10 warps: 65536 / 320 leaves 200 registers per thread
+constexpr int T5_THREADS = 384;   // 12 warps; register budget rebalanced per role with setmaxnreg
 
 __device__ int g_tc5_status;   // 0 ok; otherwise (1 + id of the barrier a wait gave up on)
 
