@@ -60,6 +60,8 @@ def parse():
     ap.add_argument("--cpu-tiles", type=int, default=40, help="64-row query tiles in the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--host-chunk", type=int, default=16384,
+                    help="query positions per pipeline unit of the host-tensor entry point (0 = whole sequences)")
     ap.add_argument("--seed", type=int, default=0)
     return ap.parse_args()
 
@@ -310,8 +312,9 @@ def run_ours(a):
         out_h = torch.empty(out.shape, dtype=out.dtype).pin_memory()
 
         def e2e_step():
-            # the public host-tensor entry point: copies in, kernels and copy out pipelined per (batch, KV head)
-            nsa.nsa_forward_host(Qh, Kh, Vh, cfg, gate_logits=Gh, out=out_h)
+            # the public host-tensor entry point: copies in, kernels and copy out pipelined per
+            # (batch, KV head, query chunk)
+            nsa.nsa_forward_host(Qh, Kh, Vh, cfg, gate_logits=Gh, out=out_h, chunk_rows=a.host_chunk or None)
         for _ in range(2):
             e2e_step()
         barrier()

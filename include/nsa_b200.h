@@ -18,6 +18,7 @@
 #ifndef NSA_B200_H
 #define NSA_B200_H
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -233,6 +234,15 @@ int nsa_fp8_quantize(const void* x, void* out8, int64_t n, int dtype, int fmt, f
 /* dst (16-bit `dtype`) = round(src fp32), n elements.
  * Replaces: dQ_f.to(Q.dtype) etc., nsa/triton/backward.py:195. */
 int nsa_cast_from_f32(const float* src, void* dst, int64_t n, int dtype, nsa_stream_t stream);
+
+/* Strided copy between host and device on `stream`: `rows` rows of `row_bytes` bytes, row r at
+ * dst + r*dst_pitch / src + r*src_pitch; to_device = 1 host->device, 0 device->host.  Asynchronous when
+ * the host side is pinned.  Lets the host-tensor entry point move the [heads, chunk, D] slab of one
+ * (batch, KV head, query chunk) unit in a single call.
+ * Replaces: the .to(device) / .cpu() copies a caller of nsa_forward does around it
+ * (nsa/bench/throughput.py:78-80 creates its inputs with torch.randn(..., device=device)). */
+int nsa_memcpy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t row_bytes,
+                  size_t rows, int to_device, nsa_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -88,6 +88,7 @@ PROTOTYPES = {
     "nsa_fp8_absmax": (_i, [_vp, _i64, _i, _vp, _vp]),
     "nsa_fp8_quantize": (_i, [_vp, _vp, _i64, _i, _i, _f, _vp]),
     "nsa_cast_from_f32": (_i, [_vp, _vp, _i64, _i, _vp]),
+    "nsa_memcpy_2d": (_i, [_vp, C.c_size_t, _vp, C.c_size_t, C.c_size_t, C.c_size_t, _i, _vp]),
 }
 
 _lib = None

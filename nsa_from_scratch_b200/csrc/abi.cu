@@ -229,4 +229,15 @@ int nsa_cast_from_f32(const float* src, void* dst, int64_t n, int dtype, nsa_str
   return cast_from_f32(src, dst, n, dtype, (cudaStream_t)stream);
 }
 
+int nsa_memcpy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t row_bytes, size_t rows,
+                  int to_device, nsa_stream_t stream) {
+  NSA_REQUIRE(dst && src, NSA_ERR_ARG, "memcpy_2d: NULL pointer");
+  NSA_REQUIRE(to_device == 0 || to_device == 1, NSA_ERR_ARG, "memcpy_2d: to_device must be 0 or 1");
+  NSA_REQUIRE(dst_pitch >= row_bytes && src_pitch >= row_bytes, NSA_ERR_ARG, "memcpy_2d: pitch smaller than a row");
+  if (row_bytes == 0 || rows == 0) return NSA_OK;
+  NSA_CUDA_OK(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, row_bytes, rows,
+                                to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  return NSA_OK;
+}
+
 }  // extern "C"

@@ -224,6 +224,28 @@ def cast_from_f32(x: Tensor, dtype: torch.dtype) -> Tensor:
     return out
 
 
+def copy_rows(dst: Tensor, src: Tensor) -> None:
+    """dst[r] = src[r] for [R, ...] views whose trailing dimensions are dense and whose rows are a fixed
+    stride apart; exactly one side on the device, the other on the host (pinned for an asynchronous
+    copy).  One strided DMA on the current stream of the device tensor's device."""
+    if dst.shape != src.shape or dst.dtype != src.dtype or dst.dim() < 2:
+        raise ValueError("copy_rows: dst and src must be [R, ...] views of equal shape and dtype")
+    if dst.is_cuda == src.is_cuda:
+        raise ValueError("copy_rows: exactly one of dst / src must be a CUDA tensor")
+    for t in (dst, src):
+        if not t[0].is_contiguous():
+            raise ValueError("copy_rows: the trailing dimensions must be dense")
+    isz = dst.element_size()
+    row_bytes = dst[0].numel() * isz
+    rows = dst.shape[0]
+    dp = (dst.stride(0) if rows > 1 else dst[0].numel()) * isz
+    sp = (src.stride(0) if rows > 1 else src[0].numel()) * isz
+    dev = dst.device if dst.is_cuda else src.device
+    with torch.cuda.device(dev):
+        L.check(L.load().nsa_memcpy_2d(dst.data_ptr(), dp, src.data_ptr(), sp, row_bytes, rows, 1 if dst.is_cuda else 0,
+                                       L.stream_ptr()), "nsa_memcpy_2d")
+
+
 def combine(out_c: Tensor, out_s: Tensor, out_w: Tensor, gate_logits: Tensor, activation: str) -> Tensor:
     _need_cuda(out_c, out_s, out_w, gate_logits)
     if activation not in ("sigmoid", "softmax"):

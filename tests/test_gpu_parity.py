@@ -445,6 +445,26 @@ def test_host_tensor_entry_point_matches_device_path(nsa):
     assert not out.is_cuda and torch.equal(out, ref.cpu())
 
 
+@pytest.mark.parametrize("Tq,Tk,chunk", [(512, 512, 128), (256, 768, 64), (500, 500, 128)])
+def test_host_entry_point_query_chunks(nsa, Tq, Tk, chunk):
+    """Units of (batch, KV head, query chunk) with the key prefix growing chunk by chunk give the rows
+    of the whole-sequence call (ragged lengths fall back to one chunk)."""
+    Q, K, V, g = make_qkv(23, 1, 8, 2, Tq, Tk, 64)
+    gates = torch.randn(1, 8, Tq, 3, generator=g)
+    cfg = nsa.NSAConfig(block_size_c=32, stride_c=16, top_k=4, window_size=96, force_first=1, force_local=2)
+    ref = nsa.nsa_forward(Q.cuda(), K.cuda(), V.cuda(), cfg, gate_logits=gates.cuda())
+    out = nsa.nsa_forward_host(Q.pin_memory(), K.pin_memory(), V.pin_memory(), cfg, gate_logits=gates.pin_memory(),
+                               chunk_rows=chunk)
+    torch.cuda.synchronize()
+    assert torch.equal(out, ref.cpu()), max_abs(out, ref.cpu())
+    # sliced (non-dense) host views work as sources and destination
+    big = torch.zeros(1, 8, Tq + 64, 64, dtype=Q.dtype).pin_memory()
+    nsa.nsa_forward_host(Q.pin_memory(), K.pin_memory(), V.pin_memory(), cfg, gate_logits=gates.pin_memory(),
+                         out=big[:, :, 64:], chunk_rows=chunk)
+    torch.cuda.synchronize()
+    assert torch.equal(big[:, :, 64:], ref.cpu()) and float(big[:, :, :64].abs().max()) == 0.0
+
+
 # ------------------------------------------------------------------ compressed / sliding backward kernels
 def test_golden_compressed_and_sliding_gradients(nsa, golden):
     """Gradients through the autograd Functions against the reference's own (autograd through its torch code)."""
