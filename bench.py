@@ -284,7 +284,26 @@ def run_ours(a):
         torch.cuda.synchronize()
         stage_ms["pool_select"].append(e[0].elapsed_time(e[1]))
         stage_ms["fused_attention"].append(e[1].elapsed_time(e[2]))
-    # the clock sampler ran through the timed region and the per-kernel timing loop (same kernels, same load)
+    # each branch alone through the same kernel (unfused: writes its own output and lse), for a
+    # per-branch share of the roofline; a few launches each, not part of the step
+    branch_ms = {}
+    Kc = ops.pool_mean(K, a.cmp_block, a.cmp_stride)
+    Vc = ops.pool_mean(V, a.cmp_block, a.cmp_stride)
+    for name, bit in (("compressed", 1), ("selected", 2), ("sliding", 4)):
+        ts = []
+        for i in range(4):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            ops.attention_fwd(Q, K, V, branches=bit, fused=False, causal=True, scale=scale, Kc=Kc, Vc=Vc,
+                              cmp_block=a.cmp_block, cmp_stride=a.cmp_stride,
+                              cmp_offset=(Kc.shape[2] * a.cmp_block if a.cmp_stride == a.cmp_block else T) - T,
+                              idx=idx, bm=64, bn=64, window=a.window, engine=engine)
+            e1.record()
+            torch.cuda.synchronize()
+            if i > 0:
+                ts.append(e0.elapsed_time(e1))
+        branch_ms[name] = statistics.mean(ts)
+    # the clock sampler ran through the timed region and the per-kernel timing loops (same kernels, same load)
     clocks = sampler.stop() if sampler else None
     fused_ms = statistics.mean(stage_ms["fused_attention"])
     peaks = {}
@@ -304,7 +323,9 @@ def run_ours(a):
                 "traffic": traffic, "peak_source": peak_src, "kernel": "fused three-branch attention",
                 "kernel_ms": fused_ms, "algorithmic_tflop": {k: v / 1e12 for k, v in flops.items()},
                 "frac_of_burst_peak": achieved / peaks["bf16_tflops"] if "bf16_tflops" in peaks else None,
-                "pool_select_ms": statistics.mean(stage_ms["pool_select"])}
+                "pool_select_ms": statistics.mean(stage_ms["pool_select"]),
+                "branches_alone": {k: {"ms": branch_ms[k], "tflops": flops[k] / (branch_ms[k] * 1e-3) / 1e12,
+                                       "frac": flops[k] / (branch_ms[k] * 1e-3) / 1e12 / peak} for k in branch_ms}}
 
     # ---- end to end: pinned host buffers in, host buffer out, copies inside the timed region ------
     e2e = None

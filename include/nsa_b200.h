@@ -95,6 +95,12 @@ int nsa_topk_from_scores(const float* scores, int32_t* idx, int BH, int nq, int 
  *               constant of zero logits when gates == NULL); lse is not written.
  * K/V may be fp8 (kv_dtype) with per-tensor scales; they are dequantised to bf16 as
  * bf16(fp32(x) * scale) while being staged, never materialised. */
+/* io_layout bits of nsa_fwd_args: the caller's token-major tensors used as they are
+ * (nsa/model/llama_nsa.py:82 permutes the gate logits to [B,H,T,3] and :94 transposes the
+ * result back to [B,T,H*D]; with these bits neither copy exists). */
+#define NSA_IO_OUT_BTHD 1   /* out is [B,Tq,H,D] (= [B,Tq,H*D]) */
+#define NSA_IO_GATES_BTHD 2 /* gates are [B,Tq,H,3] */
+
 typedef struct nsa_fwd_args {
   const void* Q;       /* [B,H,Tq,D]   q_dtype                                    */
   const void* K;       /* [B,Hkv,Tk,D] kv_dtype                                   */
@@ -117,6 +123,7 @@ typedef struct nsa_fwd_args {
   float scale;                                   /* softmax scale                                          */
   float q_scale, k_scale, v_scale;               /* fp8 dequantisation scales                              */
   int32_t engine;                                /* NSA_ENGINE_*                                           */
+  int32_t io_layout;                             /* NSA_IO_* bits; 0 = every tensor [B,H,T,.]              */
 } nsa_fwd_args;
 
 /* Replaces the kernels behind compressed_attention (nsa/triton/compressed.py:191-300),
@@ -234,6 +241,16 @@ int nsa_fp8_quantize(const void* x, void* out8, int64_t n, int dtype, int fmt, f
 /* dst (16-bit `dtype`) = round(src fp32), n elements.
  * Replaces: dQ_f.to(Q.dtype) etc., nsa/triton/backward.py:195. */
 int nsa_cast_from_f32(const float* src, void* dst, int64_t n, int dtype, nsa_stream_t stream);
+
+/* y[b,h,t,:] = rope(x[b,t,h,:]) rounded once to `y_dtype` (bf16/fp16): the head-major, 16-bit,
+ * position-encoded tensor the attention kernels read, made from the projection output
+ * x [B,T,H,D] (`x_dtype` fp32, bf16 or fp16) in one pass.  rope(x)[d] = x[d]*cos[t,d] +
+ * rot(x)[d]*sin[t,d] with rot(x) = (-x[D/2:], x[:D/2]) in fp32; cos/sin [T,D] in `cs_dtype`; with
+ * cos == NULL the values are only transposed and cast (the V path).
+ * Replaces: .view(B,T,H,D).transpose(1,2), _apply_rope and .to(bf16) of the caller,
+ * nsa/model/llama_nsa.py:77-80,91 and nsa/model/llama_dense.py:19-37. */
+int nsa_rope_to_heads(const void* x, void* y, const void* cos, const void* sin, int B, int T, int H, int D,
+                      int x_dtype, int cs_dtype, int y_dtype, nsa_stream_t stream);
 
 /* Strided copy between host and device on `stream`: `rows` rows of `row_bytes` bytes, row r at
  * dst + r*dst_pitch / src + r*src_pitch; to_device = 1 host->device, 0 device->host.  Asynchronous when

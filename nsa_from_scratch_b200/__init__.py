@@ -14,6 +14,7 @@ from .backward import selected_backward
 from .fp8 import quantize_to_fp8, selected_attention_fp8
 from .native import selected_attention_cuda, selected_backward_cuda
 from .host import nsa_forward_host
+from .layer import NSAAttention, nsa_attention_token_major, rope_cache
 
 __all__ = [
     "NSAConfig", "compressed_attention", "selected_attention", "sliding_attention", "combine", "nsa_forward",

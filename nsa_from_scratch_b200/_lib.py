@@ -19,6 +19,7 @@ BF16, FP16, FP8_E4M3, FP8_E5M2, FP32 = 0, 1, 2, 3, 4
 BRANCH_COMPRESSED, BRANCH_SELECTED, BRANCH_SLIDING = 1, 2, 4
 GATE_SIGMOID, GATE_SOFTMAX = 0, 1
 ENGINE_AUTO, ENGINE_GENERIC, ENGINE_TCGEN05 = 0, 1, 2
+IO_OUT_BTHD, IO_GATES_BTHD = 1, 2
 
 _DTYPE_CODE = {
     torch.bfloat16: BF16, torch.float16: FP16, torch.float32: FP32,
@@ -47,7 +48,7 @@ class FwdArgs(C.Structure):
         ("branches", C.c_int32), ("fused", C.c_int32), ("gate_act", C.c_int32),
         ("q_dtype", C.c_int32), ("kv_dtype", C.c_int32), ("gate_dtype", C.c_int32),
         ("scale", C.c_float), ("q_scale", C.c_float), ("k_scale", C.c_float), ("v_scale", C.c_float),
-        ("engine", C.c_int32),
+        ("engine", C.c_int32), ("io_layout", C.c_int32),
     ]
 
 
@@ -88,6 +89,7 @@ PROTOTYPES = {
     "nsa_fp8_absmax": (_i, [_vp, _i64, _i, _vp, _vp]),
     "nsa_fp8_quantize": (_i, [_vp, _vp, _i64, _i, _i, _f, _vp]),
     "nsa_cast_from_f32": (_i, [_vp, _vp, _i64, _i, _vp]),
+    "nsa_rope_to_heads": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "nsa_memcpy_2d": (_i, [_vp, C.c_size_t, _vp, C.c_size_t, C.c_size_t, C.c_size_t, _i, _vp]),
 }
 

@@ -32,6 +32,7 @@ int fp8_absmax(const void*, long long, int, float*, cudaStream_t);
 int fp8_quantize(const void*, void*, long long, int, int, float, cudaStream_t);
 int bwd_delta(const void*, const void*, float*, long long, int, int, cudaStream_t);
 int cast_from_f32(const float*, void*, long long, int, cudaStream_t);
+int rope_to_heads(const void*, void*, const void*, const void*, int, int, int, int, int, int, int, cudaStream_t);
 
 static bool is16(int dt) { return dt == NSA_BF16 || dt == NSA_FP16; }
 static bool is8(int dt) { return dt == NSA_FP8_E4M3 || dt == NSA_FP8_E5M2; }
@@ -46,6 +47,7 @@ static int check_fwd(const nsa_fwd_args& a) {
   NSA_REQUIRE(a.kv_dtype == a.q_dtype, NSA_ERR_UNSUPPORTED, "attention forward: K/V dtype %d differs from Q dtype %d", a.kv_dtype, a.q_dtype);
   const int br = a.branches;
   NSA_REQUIRE(br > 0 && br < 8, NSA_ERR_ARG, "attention forward: branch mask %d", br);
+  NSA_REQUIRE((a.io_layout & ~(NSA_IO_OUT_BTHD | NSA_IO_GATES_BTHD)) == 0, NSA_ERR_ARG, "attention forward: io_layout %d has unknown bits", a.io_layout);
   if (!a.fused) {
     NSA_REQUIRE(br == 1 || br == 2 || br == 4, NSA_ERR_ARG, "attention forward: unfused launch needs exactly one branch (mask %d)", br);
   } else {
@@ -77,7 +79,7 @@ using namespace nsa;
 extern "C" {
 
 const char* nsa_last_error(void) { return g_err; }
-int nsa_abi_version(void) { return 1; }
+int nsa_abi_version(void) { return 2; }
 
 int nsa_pool_mean(const void* x, void* out, int B, int H, int T, int D, int block, int stride, int n_out, int dtype,
                   float dequant_scale, nsa_stream_t stream) {
@@ -227,6 +229,19 @@ int nsa_fp8_quantize(const void* x, void* out8, int64_t n, int dtype, int fmt, f
 int nsa_cast_from_f32(const float* src, void* dst, int64_t n, int dtype, nsa_stream_t stream) {
   NSA_REQUIRE(src && dst, NSA_ERR_ARG, "cast: NULL pointer");
   return cast_from_f32(src, dst, n, dtype, (cudaStream_t)stream);
+}
+
+int nsa_rope_to_heads(const void* x, void* y, const void* cos, const void* sin, int B, int T, int H, int D, int x_dtype,
+                      int cs_dtype, int y_dtype, nsa_stream_t stream) {
+  NSA_REQUIRE(x && y, NSA_ERR_ARG, "rope_to_heads: NULL pointer");
+  NSA_REQUIRE((cos == nullptr) == (sin == nullptr), NSA_ERR_ARG, "rope_to_heads: cos and sin must both be given or both be NULL");
+  NSA_REQUIRE(B >= 0 && T >= 0 && H > 0 && D > 0, NSA_ERR_ARG, "rope_to_heads: bad sizes B=%d T=%d H=%d D=%d", B, T, H, D);
+  NSA_REQUIRE(D % 16 == 0, NSA_ERR_UNSUPPORTED, "rope_to_heads: D=%d must be a multiple of 16", D);
+  NSA_REQUIRE(x_dtype == NSA_FP32 || x_dtype == NSA_BF16 || x_dtype == NSA_FP16, NSA_ERR_UNSUPPORTED, "rope_to_heads: x dtype %d", x_dtype);
+  NSA_REQUIRE(y_dtype == NSA_BF16 || y_dtype == NSA_FP16, NSA_ERR_UNSUPPORTED, "rope_to_heads: y dtype %d must be 16-bit", y_dtype);
+  NSA_REQUIRE(cos == nullptr || cs_dtype == NSA_FP32 || cs_dtype == NSA_BF16 || cs_dtype == NSA_FP16, NSA_ERR_UNSUPPORTED,
+              "rope_to_heads: cos/sin dtype %d", cs_dtype);
+  return rope_to_heads(x, y, cos, sin, B, T, H, D, x_dtype, cs_dtype, y_dtype, (cudaStream_t)stream);
 }
 
 int nsa_memcpy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t row_bytes, size_t rows,

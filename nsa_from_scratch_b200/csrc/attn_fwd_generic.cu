@@ -137,7 +137,8 @@ __global__ void __launch_bounds__(NW * 32, 2) attn_fwd_generic_kernel(const __gr
     for (int r = 0; r < 2; ++r) {
       float x[3] = {0.f, 0.f, 0.f};
       if (a.gates != nullptr && row_ok[r]) {
-        size_t gi = ((size_t)bh * a.Tq + row_i[r]) * 3;
+        size_t gi = ((a.io_layout & NSA_IO_GATES_BTHD) ? ((size_t)b * a.Tq + row_i[r]) * a.H + h
+                                                       : (size_t)bh * a.Tq + row_i[r]) * 3;
 #pragma unroll
         for (int c = 0; c < 3; ++c) x[c] = gate_logit(a.gates, gi + c, a.gate_dtype);
       }
@@ -367,11 +368,13 @@ __global__ void __launch_bounds__(NW * 32, 2) attn_fwd_generic_kernel(const __gr
     *reinterpret_cast<uint32_t*>(Qs + tile_off<D>(r0 + 8, d) + (col & 7) * 2) = v1;
   }
   __syncthreads();
-  T* outp = reinterpret_cast<T*>(a.out) + q_slab;
+  const bool bthd = (a.io_layout & NSA_IO_OUT_BTHD) != 0;           // rows H*D apart instead of D
+  T* outp = reinterpret_cast<T*>(a.out) + (bthd ? ((size_t)b * a.Tq * a.H + h) * D : q_slab);
+  const size_t row_stride = bthd ? (size_t)a.H * D : (size_t)D;
   for (int i = tid; i < TM * CH; i += NT) {
     int r = i / CH, c = i % CH;
     if (q0 + r < a.Tq)
-      *reinterpret_cast<uint4*>(outp + (size_t)(q0 + r) * D + c * 8) =
+      *reinterpret_cast<uint4*>(outp + (size_t)(q0 + r) * row_stride + c * 8) =
           *reinterpret_cast<const uint4*>(Qs + tile_off<D>(r, c));
   }
 }

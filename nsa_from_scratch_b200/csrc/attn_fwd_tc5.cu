@@ -498,7 +498,8 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
     const int head = grp_head(rg);
     const int qi = grp_qb(rg) * 64 + (r & 63);
     const bool row_ok = grp_qb(rg) < a.nq && qi < a.Tq;
-    const size_t row_index = ((size_t)b * a.H + head) * a.Tq + qi;
+    const size_t row_index = ((size_t)b * a.H + head) * a.Tq + qi;       // [B,H,Tq] order (lse, default out / gates)
+    const size_t row_bthd = ((size_t)b * a.Tq + qi) * a.H + head;        // [B,Tq,H] order
 
     float gate[3] = {0.5f, 0.5f, 0.5f};
     if (a.fused) {
@@ -506,7 +507,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
       if (a.gates != nullptr && row_ok) {
 #pragma unroll
         for (int c = 0; c < 3; ++c) {
-          const size_t gi = row_index * 3 + c;
+          const size_t gi = ((a.io_layout & NSA_IO_GATES_BTHD) ? row_bthd : row_index) * 3 + c;
           x[c] = a.gate_dtype == NSA_FP32 ? reinterpret_cast<const float*>(a.gates)[gi]
                : a.gate_dtype == NSA_FP16 ? __half2float(reinterpret_cast<const __half*>(a.gates)[gi])
                                           : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.gates)[gi]);
@@ -528,7 +529,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
     // S row (128 registers) resident during a tile, so a tile costs ONE TMEM round trip.
     float lse_out = -INFINITY;
     bool have_partial = false;
-    T* orow = reinterpret_cast<T*>(a.out) + row_index * D;
+    T* orow = reinterpret_cast<T*>(a.out) + ((a.io_layout & NSA_IO_OUT_BTHD) ? row_bthd : row_index) * D;
 
     int it = 0;
     bool ok = true;

@@ -1,5 +1,6 @@
 // HBM-bound element-wise kernels: gated combine, fp8 absmax / quantise, the backward's
-// delta pre-pass and the fp32 -> 16-bit gradient cast.  All use 128-bit accesses and a
+// delta pre-pass, the fp32 -> 16-bit gradient cast and the rotary-embedding + head-major re-layout
+// of the projection outputs.  All use 128-bit accesses and a
 // grid-stride loop sized to a multiple of the SM count.
 #include "common.cuh"
 
@@ -198,6 +199,90 @@ int cast_from_f32(const float* src, void* dst, long long n, int dtype, cudaStrea
   else if (dtype == NSA_FP16) cast_kernel<__half><<<grid, 256, 0, st>>>(src, (__half*)dst, n);
   else return fail(NSA_ERR_UNSUPPORTED, "cast: dtype %d", dtype);
   return launch_status("cast_from_f32");
+}
+
+// ------------------------------------------------------------------ rotary embedding + [B,T,H,D] -> [B,H,T,D]
+// One thread = 8 consecutive columns d0..d0+7 of the first half of a row AND their partners d0+D/2..:
+// out[d] = x[d] cos[d] - x[d+D/2] sin[d],  out[d+D/2] = x[d+D/2] cos[d+D/2] + x[d] sin[d+D/2]  (fp32, one rounding).
+// Consecutive threads walk (d-chunk, h, t, b) in that order, so reads are linear in x and every
+// written row segment is 16 bytes x D/16 threads.
+template <typename X>
+__device__ __forceinline__ void load8(const X* p, float (&v)[8]) {
+  if constexpr (sizeof(X) == 4) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+    const uint4 a = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { const float2 f = Elem<X>::unpack(w[e]); v[2 * e] = f.x; v[2 * e + 1] = f.y; }
+  }
+}
+__device__ __forceinline__ void load8_any(const void* p, size_t i, int dt, float (&v)[8]) {
+  if (dt == NSA_FP32) load8(reinterpret_cast<const float*>(p) + i, v);
+  else if (dt == NSA_FP16) load8(reinterpret_cast<const __half*>(p) + i, v);
+  else load8(reinterpret_cast<const __nv_bfloat16*>(p) + i, v);
+}
+
+template <typename X, typename Y>
+__global__ void __launch_bounds__(256) rope_to_heads_kernel(const X* __restrict__ x, Y* __restrict__ y,
+                                                            const void* __restrict__ cosp, const void* __restrict__ sinp,
+                                                            int B, int T, int H, int D, int cs_dt) {
+  const int CH = D / 16;                                   // threads per row
+  const long long total = (long long)B * T * H * CH;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int ch = (int)(i % CH);
+    const long long row = i / CH;                          // (b, t, h)
+    const int h = (int)(row % H);
+    const long long bt = row / H;
+    const int t = (int)(bt % T);
+    const long long b = bt / T;
+    const int d0 = ch * 8, d1 = D / 2 + ch * 8;
+    float lo[8], hi[8];
+    load8(x + (size_t)row * D + d0, lo);
+    load8(x + (size_t)row * D + d1, hi);
+    float olo[8], ohi[8];
+    if (cosp != nullptr) {
+      float c0[8], c1[8], s0[8], s1[8];
+      load8_any(cosp, (size_t)t * D + d0, cs_dt, c0);
+      load8_any(cosp, (size_t)t * D + d1, cs_dt, c1);
+      load8_any(sinp, (size_t)t * D + d0, cs_dt, s0);
+      load8_any(sinp, (size_t)t * D + d1, cs_dt, s1);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        olo[e] = fmaf(lo[e], c0[e], -hi[e] * s0[e]);
+        ohi[e] = fmaf(hi[e], c1[e], lo[e] * s1[e]);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { olo[e] = lo[e]; ohi[e] = hi[e]; }
+    }
+    Y* dst = y + (((size_t)b * H + h) * T + t) * D;
+    *reinterpret_cast<uint4*>(dst + d0) = make_uint4(Elem<Y>::pack(olo[0], olo[1]), Elem<Y>::pack(olo[2], olo[3]),
+                                                     Elem<Y>::pack(olo[4], olo[5]), Elem<Y>::pack(olo[6], olo[7]));
+    *reinterpret_cast<uint4*>(dst + d1) = make_uint4(Elem<Y>::pack(ohi[0], ohi[1]), Elem<Y>::pack(ohi[2], ohi[3]),
+                                                     Elem<Y>::pack(ohi[4], ohi[5]), Elem<Y>::pack(ohi[6], ohi[7]));
+  }
+}
+
+int rope_to_heads(const void* x, void* y, const void* cosp, const void* sinp, int B, int T, int H, int D, int x_dt,
+                  int cs_dt, int y_dt, cudaStream_t st) {
+  const long long items = (long long)B * T * H * (D / 16);
+  if (items == 0) return NSA_OK;
+  const int grid = grid_for(items, 256);
+#define NSA_ROPE(XT, YT) \
+  rope_to_heads_kernel<XT, YT><<<grid, 256, 0, st>>>(reinterpret_cast<const XT*>(x), reinterpret_cast<YT*>(y), cosp, sinp, B, T, H, D, cs_dt)
+  if (y_dt == NSA_BF16) {
+    if (x_dt == NSA_FP32) NSA_ROPE(float, __nv_bfloat16);
+    else if (x_dt == NSA_FP16) NSA_ROPE(__half, __nv_bfloat16);
+    else NSA_ROPE(__nv_bfloat16, __nv_bfloat16);
+  } else {
+    if (x_dt == NSA_FP32) NSA_ROPE(float, __half);
+    else if (x_dt == NSA_FP16) NSA_ROPE(__half, __half);
+    else NSA_ROPE(__nv_bfloat16, __half);
+  }
+#undef NSA_ROPE
+  return launch_status("rope_to_heads");
 }
 
 }  // namespace nsa

@@ -176,7 +176,8 @@ def nsa_forward(Q: Tensor, K: Tensor, V: Tensor, cfg, *, gate_logits: Optional[T
     return _fused_forward(Q, K, V, cfg, float(scale), stride_c, gate_logits, block_indices, 1.0, 1.0, 1.0)
 
 
-def _fused_forward(Q, K, V, cfg, scale, stride_c, gate_logits, block_indices, sq, sk, sv, engine=None):
+def _fused_forward(Q, K, V, cfg, scale, stride_c, gate_logits, block_indices, sq, sk, sv, engine=None,
+                   token_major=False):
     bc = cfg.block_size_c
     stride = bc if stride_c is None else int(stride_c)
     Kc = ops.pool_mean(K, bc, stride, dequant_scale=sk)
@@ -190,7 +191,7 @@ def _fused_forward(Q, K, V, cfg, scale, stride_c, gate_logits, block_indices, sq
         causal=bool(cfg.causal), scale=scale, Kc=Kc, Vc=Vc, cmp_block=bc, cmp_stride=stride, cmp_offset=Tk_pad - Tq,
         idx=block_indices, bm=cfg.block_size_m, bn=cfg.block_size_n, window=cfg.window_size, gates=gate_logits,
         gate_act=L.GATE_SOFTMAX if cfg.gate_activation == "softmax" else L.GATE_SIGMOID,
-        q_scale=sq, k_scale=sk, v_scale=sv, engine=engine)
+        q_scale=sq, k_scale=sk, v_scale=sv, engine=engine, token_major=token_major)
     return out
 
 

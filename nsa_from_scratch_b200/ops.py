@@ -96,9 +96,11 @@ def attention_fwd(
     cmp_offset: int = 0, idx: Optional[Tensor] = None, bm: int = 64, bn: int = 64, window: int = 0,
     gates: Optional[Tensor] = None, gate_act: int = L.GATE_SIGMOID, offset: Optional[int] = None,
     q_scale: float = 1.0, k_scale: float = 1.0, v_scale: float = 1.0, engine: Optional[int] = None,
-    want_lse: bool = True,
+    want_lse: bool = True, token_major: bool = False,
 ) -> Tuple[Tensor, Optional[Tensor]]:
-    """One launch of nsa_attention_fwd.  Returns (out, lse); lse is None for fused launches."""
+    """One launch of nsa_attention_fwd.  Returns (out, lse); lse is None for fused launches.
+    `token_major`: gates are [B,Tq,H,3] and the result comes back as [B,Tq,H,D] (Q, K, V stay
+    [B,H,T,D]) -- the layouts on either side of the call in the reference's attention module."""
     _need_cuda(Q, K, V)
     B, H, Tq, D = Q.shape
     Hkv, Tk = K.shape[1], K.shape[2]
@@ -110,9 +112,10 @@ def attention_fwd(
         raise TypeError("Q, K, V must share a dtype")
     Q, K, V = Q.contiguous(), K.contiguous(), V.contiguous()
     out_dtype = torch.bfloat16 if Q.dtype in _8 else Q.dtype
-    out = torch.empty((B, H, Tq, D), device=Q.device, dtype=out_dtype)
+    out = torch.empty((B, Tq, H, D) if token_major else (B, H, Tq, D), device=Q.device, dtype=out_dtype)
     lse = torch.empty((B, H, Tq), device=Q.device, dtype=torch.float32) if (want_lse and not fused) else None
     a = L.FwdArgs()
+    a.io_layout = (L.IO_OUT_BTHD | L.IO_GATES_BTHD) if token_major else 0
     a.Q, a.K, a.V, a.out, a.lse = Q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(), L.ptr(lse)
     a.B, a.H, a.Hkv, a.Tq, a.Tk, a.D = B, H, Hkv, Tq, Tk, D
     a.offset = Tk - Tq if offset is None else offset
@@ -139,8 +142,9 @@ def attention_fwd(
     if fused and gates is not None:
         gates = gates.contiguous()
         keep.append(gates)
-        if gates.shape != (B, H, Tq, 3):
-            raise ValueError(f"gate_logits shape {tuple(gates.shape)} != {(B, H, Tq, 3)}")
+        want = (B, Tq, H, 3) if token_major else (B, H, Tq, 3)
+        if gates.shape != want:
+            raise ValueError(f"gate_logits shape {tuple(gates.shape)} != {want}")
         a.gates, a.gate_dtype = gates.data_ptr(), L.dtype_code(gates.dtype)
     with torch.cuda.device(Q.device):
         L.check(L.load().nsa_attention_fwd(C.byref(a), L.stream_ptr()), "nsa_attention_fwd")
@@ -222,6 +226,30 @@ def cast_from_f32(x: Tensor, dtype: torch.dtype) -> Tensor:
         L.check(L.load().nsa_cast_from_f32(x.data_ptr(), out.data_ptr(), x.numel(), L.dtype_code(dtype), L.stream_ptr()),
                 "nsa_cast_from_f32")
     return out
+
+
+def rope_to_heads(x: Tensor, cos: Optional[Tensor], sin: Optional[Tensor], dtype: torch.dtype = torch.bfloat16) -> Tensor:
+    """x [B,T,H,D] (fp32/bf16/fp16) -> rope(x) as [B,H,T,D] in `dtype`, one pass; cos/sin [T,D] or None (no rotation)."""
+    _need_cuda(x)
+    if x.dim() != 4:
+        raise ValueError(f"rope_to_heads: x must be [B,T,H,D], got {tuple(x.shape)}")
+    B, T, H, D = x.shape
+    x = x.contiguous()
+    if (cos is None) != (sin is None):
+        raise ValueError("rope_to_heads: give both cos and sin or neither")
+    cs_code = 0
+    if cos is not None:
+        _need_cuda(cos, sin)
+        if cos.shape != (T, D) or sin.shape != (T, D) or cos.dtype != sin.dtype:
+            raise ValueError(f"rope_to_heads: cos/sin must be [{T},{D}] of one dtype, got {tuple(cos.shape)}/{tuple(sin.shape)}")
+        cos, sin = cos.contiguous(), sin.contiguous()
+        cs_code = L.dtype_code(cos.dtype)
+    y = torch.empty((B, H, T, D), device=x.device, dtype=dtype)
+    with torch.cuda.device(x.device):
+        L.check(L.load().nsa_rope_to_heads(x.data_ptr(), y.data_ptr(), L.ptr(cos), L.ptr(sin), B, T, H, D,
+                                           L.dtype_code(x.dtype), cs_code, L.dtype_code(dtype), L.stream_ptr()),
+                "nsa_rope_to_heads")
+    return y
 
 
 def copy_rows(dst: Tensor, src: Tensor) -> None:

@@ -458,6 +458,39 @@ def nsa_forward(
 _FP8_MAX = {torch.float8_e4m3fn: 448.0, torch.float8_e5m2: 57344.0}
 
 
+def rope(x: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
+    """Rotary embedding of a head-major tensor x [B,H,T,D] with tables [T,D], fp32:
+    x*cos + rotate_half(x)*sin, rotate_half(x) = (-x[D/2:], x[:D/2])
+    (nsa/model/llama_dense.py:19-37)."""
+    x = x.float()
+    h = x.shape[-1] // 2
+    rot = torch.cat((-x[..., h:], x[..., :h]), dim=-1)
+    return x * cos.float()[None, None] + rot * sin.float()[None, None]
+
+
+def attention_layer(x: Tensor, w: dict, cos: Tensor, sin: Tensor, *, n_heads: int, head_dim: int,
+                    n_kv_heads: Optional[int] = None, round_to: Optional[torch.dtype] = None, **nsa_kw) -> Tensor:
+    """The attention module around the combined forward (nsa/model/llama_nsa.py:67-96), fp32:
+    q/k/v/gate projections of x [B,T,hidden], rotary embedding of q and k, `nsa_forward`, the
+    transpose back to [B,T,H*D] and the output projection.  `w` holds q_proj/k_proj/v_proj/o_proj/gate
+    `.weight` tensors.  `round_to` rounds q, k, v (after the rotary embedding) to a 16-bit type and back,
+    as a 16-bit kernel path sees them."""
+    B, T, _ = x.shape
+    H, D = n_heads, head_dim
+    Hkv = H if n_kv_heads is None else n_kv_heads
+    x = x.float()
+    q = (x @ w["q_proj.weight"].float().T).view(B, T, H, D).transpose(1, 2)
+    k = (x @ w["k_proj.weight"].float().T).view(B, T, Hkv, D).transpose(1, 2)
+    v = (x @ w["v_proj.weight"].float().T).view(B, T, Hkv, D).transpose(1, 2)
+    q, k = rope(q, cos, sin), rope(k, cos, sin)
+    if round_to is not None:
+        q, k, v = (t.to(round_to).float() for t in (q, k, v))
+    gates = (x @ w["gate.weight"].float().T).view(B, T, H, 3).permute(0, 2, 1, 3)
+    out = nsa_forward(q, k, v, gate_logits=gates, **nsa_kw)
+    out = out.transpose(1, 2).reshape(B, T, H * D)
+    return out @ w["o_proj.weight"].float().T
+
+
 def quantize_to_fp8(x: Tensor, *, fmt: torch.dtype = torch.float8_e4m3fn,
                     eps: float = 1e-12) -> Tuple[Tensor, float]:
     """Per-tensor absmax quantisation (fp8.py:20-40): scale = absmax/fmt_max;

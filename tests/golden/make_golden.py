@@ -36,12 +36,56 @@ def np32(t):
     return t.detach().float().numpy()
 
 
+def layer_cases():
+    """The reference's attention module (nsa/model/llama_nsa.py) on CPU: its fp32 route through
+    nsa_attention_reference, plus the rotary embedding on its own.  top_k covers every legal block so the
+    fp32 scorer and a 16-bit scorer cannot disagree on the selection."""
+    from nsa.model.config import TransformerConfig
+    from nsa.model.llama_dense import _apply_rope, _build_rope_cache
+    from nsa.model.llama_nsa import NSAAttention
+    out, meta = {}, []
+    for name, (B, T, H, D, hidden, bc, k, W, act) in {
+        "layer_a": (1, 320, 4, 64, 128, 32, 8, 96, "sigmoid"),
+        "layer_b": (1, 256, 2, 128, 64, 64, 4, 64, "softmax"),
+    }.items():
+        torch.manual_seed(71)
+        cfg = TransformerConfig(n_heads=H, head_dim=D, hidden_size=hidden, nsa_block_size_c=bc, nsa_top_k=k,
+                                nsa_window_size=W, nsa_gate_activation=act)
+        mod = NSAAttention(cfg).float()
+        g = torch.Generator().manual_seed(72)
+        x = torch.randn(B, T, hidden, generator=g)
+        cos, sin = _build_rope_cache(T, D, cfg.rope_theta, "cpu", torch.float32)
+        with torch.no_grad():
+            y = mod(x, cos, sin)
+            q = mod.q_proj(x).view(B, T, H, D)
+            kk = mod.k_proj(x).view(B, T, H, D)
+            qr, kr = _apply_rope(q.transpose(1, 2), kk.transpose(1, 2), cos, sin)
+        out.update({f"{name}.x": np32(x), f"{name}.cos": np32(cos), f"{name}.sin": np32(sin), f"{name}.y": np32(y)})
+        if name == "layer_a":      # the rotary embedding on its own: projection output in, _apply_rope out
+            out.update({f"{name}.q_bthd": np32(q), f"{name}.q_rope": np32(qr)})
+        for pn, pv in mod.state_dict().items():
+            out[f"{name}.w.{pn}"] = np32(pv)
+        meta.append((name, dict(B=B, T=T, H=H, D=D, hidden=hidden, bc=bc, top_k=k, W=W, act=act)))
+    np.savez_compressed(os.path.join(HERE, "layer_golden.npz"), **out)
+    with open(os.path.join(HERE, "layer_golden.meta.txt"), "w") as f:
+        f.write(f"torch {torch.__version__}\n")
+        for n, m in meta:
+            f.write(f"{n}: {m}\n")
+    print("wrote", len(out), "arrays (layer)")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--part", default="all", choices=["all", "kernels", "layer"],
+                    help="kernels: reference_golden.npz; layer: layer_golden.npz")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     sys.path.insert(0, os.path.join(HERE, "..", ".."))
+    if args.part in ("all", "layer"):
+        layer_cases()
+    if args.part == "layer":
+        return
     from nsa import reference as R
     from nsa.triton import forward as F_
     from nsa.triton import fp8 as FP8

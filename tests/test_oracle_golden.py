@@ -177,3 +177,24 @@ def test_unpinned_extensions_collapse_to_pinned_cases(golden):
     nq = f.shape[2]
     for q in range(2, nq):
         assert set(f[0, 0, q].tolist()) == {0, q - 1, q} if q >= 2 else True
+
+
+LAYER = {"layer_a": dict(n_heads=4, head_dim=64, block_size_c=32, top_k=8, window_size=96, gate_activation="sigmoid"),
+         "layer_b": dict(n_heads=2, head_dim=128, block_size_c=64, top_k=4, window_size=64, gate_activation="softmax")}
+
+
+def test_layer_oracle_matches_reference_module(layer_golden):
+    """The caller of the forward (projections, rotary embedding, gate logits, transposes, output
+    projection) against the reference's own module run on CPU (tests/golden/layer_golden.npz)."""
+    g = layer_golden
+    qr = O.rope(T(g, "layer_a.q_bthd").transpose(1, 2), T(g, "layer_a.cos"), T(g, "layer_a.sin"))
+    assert torch.allclose(qr, T(g, "layer_a.q_rope"), atol=1e-6)
+    for name, kw in LAYER.items():
+        w = {k[len(name) + 3:]: T(g, k) for k in g.files if k.startswith(f"{name}.w.")}
+        y = O.attention_layer(T(g, f"{name}.x"), w, T(g, f"{name}.cos"), T(g, f"{name}.sin"), **kw)
+        ref = T(g, f"{name}.y")
+        # tokens before the first complete compression block have no pooled key: the reference's fp32 route
+        # gives NaN there (the kernels' convention is a zero compressed branch), every other token is compared
+        ok = torch.isfinite(ref).all(-1)
+        assert torch.equal(ok[0], torch.arange(ref.shape[1]) >= kw["block_size_c"] - 1)
+        assert float((y - ref)[ok].abs().max()) <= 2e-5, float((y - ref)[ok].abs().max())
