@@ -541,6 +541,38 @@ def run_sweep(a):
     print(json.dumps({"metric": "nsa_fwd_fp8_tokens_per_s", "value": b.seq_len / (ms8 * 1e-3), "ms_per_step": ms8,
                       "bf16_same_values_ms": msb, "max_abs_vs_bf16_path": float((o8.float() - ob.float()).abs().max()),
                       "config": {"workload": workload_name(b) + " [fp8 e4m3 storage, dequantised in-kernel]"}}), flush=True)
+    del q8, k8, v8, deq, xs, o8, ob, Gc
+    torch.cuda.empty_cache()
+
+    # the caller path at the default workload: projection outputs [B,T,H,D] in, [B,T,H*D] out.  "steps of the
+    # reference module" = transposes, rotary embedding (fp32), casts, gate permute, nsa_forward, transpose back.
+    b = copy.copy(a)
+    T, H, Hkv, D = b.seq_len, b.heads, b.kv_heads, b.head_dim
+    g = torch.Generator().manual_seed(a.seed)
+    q = torch.randn(1, T, H, D, generator=g).to(torch.bfloat16).cuda()
+    k = torch.randn(1, T, Hkv, D, generator=g).to(torch.bfloat16).cuda()
+    v = torch.randn(1, T, Hkv, D, generator=g).to(torch.bfloat16).cuda()
+    gl = torch.randn(1, T, H, 3, generator=g).to(torch.bfloat16).cuda()
+    cos, sin = nsa.rope_cache(T, D, 10000.0, "cuda")
+
+    def module_steps():
+        qq, kk, vv = (t.transpose(1, 2) for t in (q, k, v))
+        c, s_ = cos[None, None], sin[None, None]
+        rot = lambda t: torch.cat((-t[..., D // 2:], t[..., :D // 2]), dim=-1)
+        qq, kk = qq * c + rot(qq) * s_, kk * c + rot(kk) * s_
+        o = nsa.nsa_forward(qq.to(torch.bfloat16), kk.to(torch.bfloat16), vv.to(torch.bfloat16), cfg,
+                            gate_logits=gl.permute(0, 2, 1, 3).contiguous())
+        return o.transpose(1, 2).contiguous().view(1, T, H * D)
+    ms_mod = timed(module_steps, max(2, a.steps // 2))
+    ms_tm = timed(lambda: nsa.nsa_attention_token_major(q, k, v, cos, sin, cfg, gate_logits=gl), a.steps)
+    ms_rope = timed(lambda: ops.rope_to_heads(q, cos, sin), a.steps)
+    ops.device_status()
+    rope_bytes = 2 * q.numel() * 2                       # read once, write once, 16-bit (tables stay in L2)
+    print(json.dumps({"metric": "nsa_layer_tokens_per_s", "value": T / (ms_tm * 1e-3), "ms_per_step": ms_tm,
+                      "reference_module_steps_ms": ms_mod, "rope_to_heads_q_ms": ms_rope,
+                      "rope_to_heads_q_gbs": rope_bytes / (ms_rope * 1e-3) / 1e9,
+                      "config": {"workload": workload_name(b) + " [projection outputs [B,T,H,D] in, [B,T,H*D] out, rotary embedding inside]"}}),
+          flush=True)
 
 
 def main():
