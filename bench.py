@@ -462,7 +462,20 @@ def run_sweep(a):
                                        force_first=forced[0], force_local=forced[1], shared_per_group=b.select == "group")
         flops = algorithmic_flops(b, idx)["total"]
         ops.device_status()
+        ms_graph = None
+        if b.seq_len <= 8192:                              # launch-bound sizes: the step replayed as one CUDA graph
+            graphed = nsa.GraphedForward(Q, K, V, cfg, gate_logits=G)
+            graphed()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(a.steps):
+                graphed()
+            e1.record()
+            torch.cuda.synchronize()
+            ms_graph = e0.elapsed_time(e1) / a.steps
+            del graphed
         print(json.dumps({"metric": METRIC, "value": b.seq_len / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms,
+                          "ms_per_step_cuda_graph": ms_graph,
                           "algorithmic_tflop": flops / 1e12, "tflops_whole_step": flops / (ms * 1e-3) / 1e12,
                           "config": {"workload": workload_name(b)}}), flush=True)
         del Q, K, V, G
@@ -573,6 +586,60 @@ def run_sweep(a):
                       "rope_to_heads_q_gbs": rope_bytes / (ms_rope * 1e-3) / 1e9,
                       "config": {"workload": workload_name(b) + " [projection outputs [B,T,H,D] in, [B,T,H*D] out, rotary embedding inside]"}}),
           flush=True)
+    del q, k, v, gl
+    torch.cuda.empty_cache()
+
+    # decoding against a KV cache: one new token per step (keys appended, pooled K/V and block means brought up
+    # to date, selection, split attention launch + merge), CUDA-event time per step
+    for B, Tk in ((1, 65536), (8, 65536), (1, 8192)):
+        cache = nsa.KVCache(B, Hkv, D, Tk + 64, cfg)
+        g = torch.Generator().manual_seed(a.seed)
+        for c0 in range(0, Tk - 1, 8192):
+            n = min(8192, Tk - 1 - c0)
+            cache.append(torch.randn(B, Hkv, n, D, generator=g).to(torch.bfloat16).cuda(),
+                         torch.randn(B, Hkv, n, D, generator=g).to(torch.bfloat16).cuda())
+        q1 = torch.randn(B, H, 1, D, generator=g).to(torch.bfloat16).cuda()
+        k1 = torch.randn(B, Hkv, 1, D, generator=g).to(torch.bfloat16).cuda()
+        g1 = torch.randn(B, H, 1, 3, generator=g).cuda()
+
+        def decode_step(ns=None):
+            cache.length = Tk - 1                          # the same position every time: the cache does not grow
+            cache.append(k1, k1)
+            return nsa.nsa_decode(q1, cache, gate_logits=g1, nsplit=ns)
+        big = torch.randn(8192, 8192, device="cuda", dtype=torch.bfloat16)
+
+        def device_us(fn, n=20):
+            """Device time per call with the host's launch work hidden: a few ms of matmuls go first, the host
+            queues the n calls behind them, and the events bracket only the calls."""
+            for _ in range(2):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            for _ in range(6):
+                big @ big
+            e0.record()
+            for _ in range(n):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / n * 1e3
+        us = device_us(decode_step)
+        us1 = device_us(lambda: decode_step(1))
+        import time as _time
+        torch.cuda.synchronize()
+        t0 = _time.perf_counter()
+        for _ in range(20):
+            decode_step()
+        torch.cuda.synchronize()
+        wall_us = (_time.perf_counter() - t0) / 20 * 1e6
+        ops.device_status()
+        del big
+        print(json.dumps({"metric": "nsa_decode_step_us", "value": us, "unsplit_launch_us": us1, "wall_us_python_host": wall_us,
+                          "tokens_per_s": B / (us * 1e-6),
+                          "config": {"workload": f"decode 1 token/sequence, B={B} cached={Tk} Hq={H} Hkv={Hkv} D={D} bf16, "
+                                                 f"cmp={b.cmp_block}/{b.cmp_stride} top-{b.top_k} W={b.window}"}}), flush=True)
+        del cache
+        torch.cuda.empty_cache()
 
 
 def main():

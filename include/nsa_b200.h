@@ -124,6 +124,13 @@ typedef struct nsa_fwd_args {
   float q_scale, k_scale, v_scale;               /* fp8 dequantisation scales                              */
   int32_t engine;                                /* NSA_ENGINE_*                                           */
   int32_t io_layout;                             /* NSA_IO_* bits; 0 = every tensor [B,H,T,.]              */
+  /* Decoding-sized launches (few query blocks, long key ranges): nsplit > 1 spreads each work item's key
+   * tiles over nsplit thread blocks and merges their partial results in a second kernel.  Fused launches on
+   * the tcgen05 kernel with 16-bit storage only (ignored elsewhere).  The caller supplies the scratch:
+   * B*H*Tq*nsplit*3*(D+4)*4 bytes, 16-byte aligned; its contents need not be preserved or cleared. */
+  int32_t nsplit;
+  void* split_scratch;
+  int64_t split_scratch_bytes;
 } nsa_fwd_args;
 
 /* Replaces the kernels behind compressed_attention (nsa/triton/compressed.py:191-300),

@@ -49,6 +49,7 @@ class FwdArgs(C.Structure):
         ("q_dtype", C.c_int32), ("kv_dtype", C.c_int32), ("gate_dtype", C.c_int32),
         ("scale", C.c_float), ("q_scale", C.c_float), ("k_scale", C.c_float), ("v_scale", C.c_float),
         ("engine", C.c_int32), ("io_layout", C.c_int32),
+        ("nsplit", C.c_int32), ("split_scratch", C.c_void_p), ("split_scratch_bytes", C.c_int64),
     ]
 
 

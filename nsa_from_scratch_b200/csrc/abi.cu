@@ -47,6 +47,7 @@ static int check_fwd(const nsa_fwd_args& a) {
   NSA_REQUIRE(a.kv_dtype == a.q_dtype, NSA_ERR_UNSUPPORTED, "attention forward: K/V dtype %d differs from Q dtype %d", a.kv_dtype, a.q_dtype);
   const int br = a.branches;
   NSA_REQUIRE(br > 0 && br < 8, NSA_ERR_ARG, "attention forward: branch mask %d", br);
+  NSA_REQUIRE(a.nsplit >= 0 && a.nsplit <= 64, NSA_ERR_ARG, "attention forward: nsplit %d not in [0, 64]", a.nsplit);
   NSA_REQUIRE((a.io_layout & ~(NSA_IO_OUT_BTHD | NSA_IO_GATES_BTHD)) == 0, NSA_ERR_ARG, "attention forward: io_layout %d has unknown bits", a.io_layout);
   if (!a.fused) {
     NSA_REQUIRE(br == 1 || br == 2 || br == 4, NSA_ERR_ARG, "attention forward: unfused launch needs exactly one branch (mask %d)", br);
@@ -79,7 +80,7 @@ using namespace nsa;
 extern "C" {
 
 const char* nsa_last_error(void) { return g_err; }
-int nsa_abi_version(void) { return 2; }
+int nsa_abi_version(void) { return 3; }
 
 int nsa_pool_mean(const void* x, void* out, int B, int H, int T, int D, int block, int stride, int n_out, int dtype,
                   float dequant_scale, nsa_stream_t stream) {

@@ -54,6 +54,8 @@ struct Tc5Params {
   int GH;          // query heads per work item (4, 2 or 1); a work item has 4/GH consecutive query blocks
   int HG;          // head groups per KV head = (H/Hkv) / GH
   int NQG;         // query-block groups = ceil(nq / (4/GH))
+  int nsplit;      // split launches: thread blocks per work item, each with a share of every branch's key tiles
+  float* part;     // split launches: partial results [B*H*Tq][nsplit][3][D+4] = unnormalised O, m (log2 units), l
 };
 
 struct Tile {
@@ -68,7 +70,10 @@ enum { B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 3, B_VFULL = 5, B_VEMPTY = 7, B_SFUL
        B_STGFULL = 15, B_STGEMPTY = 17, B_SREAD = 19, B_COUNT = 21 };
 // STG*: fp8 staging buffers (0 = K side, 1 = V side); SREAD: D=64 only, "S row is in registers"
 
-template <int D, int FMT, bool IN8>
+// SPLIT: decoding-sized launches (few work items, long key ranges).  nsplit thread blocks share a work item; block s
+// takes tiles [nt*s/nsplit, nt*(s+1)/nsplit) of each branch and leaves (unnormalised O, m, l) per branch and row
+// in p.part; nsa_split_combine_kernel merges them and applies the gates.
+template <int D, int FMT, bool IN8, bool SPLIT>
 __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_constant__ Tc5Params p) {
   using T = typename std::conditional<FMT == 1, __nv_bfloat16, __half>::type;
   constexpr int DH = D / 64;                    // 64-element (128-byte) halves of a row
@@ -103,8 +108,10 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
   // 4 row groups of 64 query positions: group g = (head h_base + g % GH, query block qb_base + g / GH);
   // MMA tile X holds groups 2X and 2X+1.
   const int per_q = a.B * a.Hkv * p.HG;
-  const int qbg = p.NQG - 1 - (int)(blockIdx.x / per_q);   // long rows first
-  const int rem = (int)(blockIdx.x % per_q);
+  const unsigned item = SPLIT ? blockIdx.x / (unsigned)p.nsplit : blockIdx.x;
+  const int split = SPLIT ? (int)(blockIdx.x % (unsigned)p.nsplit) : 0;
+  const int qbg = p.NQG - 1 - (int)(item / per_q);   // long rows first
+  const int rem = (int)(item % per_q);
   const int b = rem / (a.Hkv * p.HG);
   const int hk = (rem / p.HG) % a.Hkv;
   const int hg = rem % p.HG;
@@ -233,6 +240,15 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
       if (hi_l >= lo_f) { sld_c0 = lo_f / 64; nchunks[2] = hi_l / 64 - sld_c0 + 1; }
     }
   }
+  // tiles [tbeg(br), tend(br)) of each branch are this block's: all of them unless the launch is split
+  auto tbeg = [&](int br) {
+    if constexpr (SPLIT) return ((nchunks[br] + 1) >> 1) * split / p.nsplit;
+    else return 0;
+  };
+  auto tend = [&](int br) {
+    if constexpr (SPLIT) return ((nchunks[br] + 1) >> 1) * (split + 1) / p.nsplit;
+    else return (nchunks[br] + 1) >> 1;
+  };
   auto get_tile = [&](int br, int t) {
     Tile tl;
     tl.nch = min(2, nchunks[br] - 2 * t);
@@ -281,11 +297,10 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
       int u8 = 1;          // fp8: use counter of the staging buffers (use 0 was Q)
       bool ok = true;
       for (int br = 0; br < 3 && ok; ++br) {
-        const int nt = (nchunks[br] + 1) >> 1;
         const CUtensorMap* mk = br == 0 ? &p.tmKc : &p.tmK;
         const CUtensorMap* mv = br == 0 ? &p.tmVc : &p.tmV;
         const bool raw8 = IN8 && br != 0;      // pooled K/V of the compressed branch are already 16-bit
-        for (int t = 0; t < nt && ok; ++t, ++it) {
+        for (int t = tbeg(br); t < tend(br) && ok; ++t, ++it) {
           const Tile tl = get_tile(br, t);
           const int s = it & 1, ph = (it >> 1) & 1;
           if (raw8) {
@@ -342,7 +357,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
       // tile counts per branch and in total; (cur_br, cur_t) walk the flattened sequence
       int nt_of[3], total_tiles = 0;
 #pragma unroll
-      for (int br = 0; br < 3; ++br) { nt_of[br] = (nchunks[br] + 1) >> 1; total_tiles += nt_of[br]; }
+      for (int br = 0; br < 3; ++br) { nt_of[br] = tend(br) - tbeg(br); total_tiles += nt_of[br]; }
       // descriptor bases: the low word carries the address field, so "+ (bytes >> 4)" moves the start
       const uint64_t dQ[2] = {smem_desc_sw128(sQ, 16, 1024), smem_desc_sw128(sQ + QTILE, 16, 1024)};
       const uint64_t dK[2] = {smem_desc_sw128(sK, 16, 1024), smem_desc_sw128(sK + KVTILE, 16, 1024)};
@@ -350,14 +365,14 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
       const uint32_t tSx[2] = {tmem, tmem + 128}, tOx[2] = {tmem + 256, tmem + 384};
       const uint32_t tPx[2] = {EARLY ? tmem + 320 : tmem, EARLY ? tmem + 448 : tmem + 128};
 
-      // position of the tile whose QK is issued next / whose PV is issued next
+      // position of the tile whose QK is issued next / whose PV is issued next (tile tbeg(br) + t of the branch)
       int q_br = 0, q_t = 0, p_br = 0, p_t = 0;
       auto skip_empty = [&](int& br, int& t) { while (br < 3 && t >= nt_of[br]) { ++br; t = 0; } };
       skip_empty(q_br, q_t);
       skip_empty(p_br, p_t);
 
       auto issue_qk = [&](int X, int it) {          // uses (q_br, q_t); the caller advances them after X == 1
-        const int nch = min(2, nchunks[q_br] - 2 * q_t);
+        const int nch = min(2, nchunks[q_br] - 2 * (tbeg(q_br) + q_t));
         const int s = it & 1;
         if (X == 0) {
           if (!__all_sync(0xffffffffu, mbar_wait(bar(B_KFULL + s), (it >> 1) & 1, &abort_flag))) { fail_id = B_KFULL + s + 1; return false; }
@@ -382,7 +397,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
         ++q_t; skip_empty(q_br, q_t);
       }
       for (int it = 0; it < total_tiles && ok; ++it) {
-        const int nch = min(2, nchunks[p_br] - 2 * p_t);
+        const int nch = min(2, nchunks[p_br] - 2 * (tbeg(p_br) + p_t));
         const bool fresh = p_t == 0;                       // first tile of a branch starts a new O
         const int s = it & 1;
         T5_TRACE(4096 + it * 8 + 0);
@@ -468,9 +483,8 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
       }
       int it = 0, u8 = 1;
       for (int br = 0; br < 3 && ok; ++br) {
-        const int nt = (nchunks[br] + 1) >> 1;
-        if (br == 0) { it += nt; continue; }              // pooled tiles come straight from TMA
-        for (int t = 0; t < nt && ok; ++t, ++it, ++u8) {
+        if (br == 0) { it += tend(0) - tbeg(0); continue; }   // pooled tiles come straight from TMA
+        for (int t = tbeg(br); t < tend(br) && ok; ++t, ++it, ++u8) {
           const Tile tl = get_tile(br, t);
           const int s = it & 1, ph = (it >> 1) & 1;
           ok = __all_sync(0xffffffffu, mbar_wait(bar(B_STGFULL + side), u8 & 1, &abort_flag));
@@ -535,14 +549,18 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
     bool ok = true;
 #pragma unroll 1
     for (int br = 0; br < 3 && ok; ++br) {
-      const int nt = (nchunks[br] + 1) >> 1;
-      if (nt == 0) continue;
+      float* prow = nullptr;                                 // split launches: this row's partial result of the branch
+      if constexpr (SPLIT) prow = p.part + ((row_index * p.nsplit + split) * 3 + br) * (D + 4);
+      if (tend(br) == tbeg(br)) {
+        if (SPLIT && row_ok) { prow[D] = -INFINITY; prow[D + 1] = 0.f; }
+        continue;
+      }
       int lo, hi;
       bounds(br, qi, row_ok, lo, hi);
       float m_used = -INFINITY, l = 0.f;
       const float sl2 = p.scale_log2[br];
 #pragma unroll 1
-      for (int t = 0; t < nt && ok; ++t, ++it) {
+      for (int t = tbeg(br); t < tend(br) && ok; ++t, ++it) {
         const Tile tl = get_tile(br, t);
         if (quarter == 0 && lane == 0) T5_TRACE(X * 2048 + it * 8 + 0);
         ok = __all_sync(0xffffffffu, mbar_wait(bar(B_SFULL + X), it & 1, &abort_flag));
@@ -594,7 +612,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
         if (__any_sync(0xffffffffu, grow)) {
           const float m_new = fmaxf(m_used, mx);
           const float alpha = m_new == -INFINITY ? 1.f : ex2(m_used - m_new);
-          if (t > 0) {
+          if (t > tbeg(br)) {
             ok = __all_sync(0xffffffffu, mbar_wait(bar(B_PVDONE + X), (it - 1) & 1, &abort_flag));
             if (!ok) { fail_id = B_PVDONE + X + 1; break; }
             tc_fence_after();
@@ -649,6 +667,23 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
       ok = __all_sync(0xffffffffu, mbar_wait(bar(B_PVDONE + X), (it - 1) & 1, &abort_flag));
       if (!ok) { fail_id = B_PVDONE + X + 1; break; }
       tc_fence_after();
+      if constexpr (SPLIT) {
+        // unnormalised O of this block's share of the keys, with the row's reference maximum and sum
+#pragma unroll
+        for (int g = 0; g < D / 32; ++g) {
+          uint32_t v[32];
+          tmem_ld32(tO + g * 32, v);
+          tc_wait_ld();
+          if (row_ok) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+              reinterpret_cast<uint4*>(prow)[g * 8 + c] = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+          }
+        }
+        if (row_ok) { prow[D] = m_used; prow[D + 1] = l; }
+        tc_fence_before();
+        continue;
+      }
       const bool has = l > 0.f;
       const float coef = has ? (a.fused ? gate[br] : 1.f) * p.out_scale[br] / l : 0.f;
       if (!a.fused) lse_out = has ? m_used * kLn2 + __logf(l) : -INFINITY;
@@ -677,7 +712,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
       have_partial = true;
       tc_fence_before();
     }
-    if (ok && row_ok) {
+    if (!SPLIT && ok && row_ok) {
       if (!have_partial) {                    // no branch had a visible key: the row is zero
 #pragma unroll
         for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(orow)[c] = make_uint4(0u, 0u, 0u, 0u);
@@ -704,6 +739,79 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
   }
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
+// Merges the partial results of a split launch: per row and branch, the splits' (O_s, m_s, l_s) combine to
+// O = sum_s 2^(m_s - m) O_s / sum_s 2^(m_s - m) l_s with m = max_s m_s; the three branches are then added with
+// the row's gates, in fp32, and the row is rounded once.  One warp per row, D/32 columns per lane.
+template <typename T, int D>
+__global__ void __launch_bounds__(256) nsa_split_combine_kernel(const float* __restrict__ part, T* __restrict__ out,
+                                                                const void* __restrict__ gates, int gate_dtype, int gate_act,
+                                                                int io_layout, int H, int Tq, long long rows, int nsplit,
+                                                                float os0, float os1, float os2) {
+  constexpr int CPT = D / 32;
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);     // (b, h, t) order
+  if (row >= rows) return;
+  const long long bh = row / Tq;
+  const int t = (int)(row % Tq), h = (int)(bh % H);
+  const long long b = bh / H;
+  const long long row_bthd = (b * Tq + t) * H + h;
+  float gate[3] = {0.5f, 0.5f, 0.5f};
+  {
+    float x[3] = {0.f, 0.f, 0.f};
+    if (gates != nullptr) {
+      const size_t gi = (size_t)((io_layout & NSA_IO_GATES_BTHD) ? row_bthd : row) * 3;
+#pragma unroll
+      for (int c = 0; c < 3; ++c)
+        x[c] = gate_dtype == NSA_FP32 ? reinterpret_cast<const float*>(gates)[gi + c]
+             : gate_dtype == NSA_FP16 ? __half2float(reinterpret_cast<const __half*>(gates)[gi + c])
+                                      : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(gates)[gi + c]);
+    }
+    if (gate_act == NSA_GATE_SOFTMAX) {
+      const float mx = fmaxf(x[0], fmaxf(x[1], x[2]));
+      const float e0 = __expf(x[0] - mx), e1 = __expf(x[1] - mx), e2 = __expf(x[2] - mx);
+      const float inv = 1.f / (e0 + e1 + e2);
+      gate[0] = e0 * inv; gate[1] = e1 * inv; gate[2] = e2 * inv;
+    } else {
+#pragma unroll
+      for (int c = 0; c < 3; ++c) gate[c] = 1.f / (1.f + __expf(-x[c]));
+    }
+  }
+  const float os[3] = {os0, os1, os2};
+  float acc[CPT];
+#pragma unroll
+  for (int c = 0; c < CPT; ++c) acc[c] = 0.f;
+  const float* prow = part + (size_t)row * nsplit * 3 * (D + 4);
+#pragma unroll
+  for (int br = 0; br < 3; ++br) {
+    float m = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) m = fmaxf(m, prow[(s * 3 + br) * (D + 4) + D]);
+    if (m == -INFINITY) continue;
+    float l = 0.f, o[CPT];
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) o[c] = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+      const float* ps = prow + (s * 3 + br) * (D + 4);
+      const float ms = ps[D];
+      if (ms == -INFINITY) continue;
+      const float w = exp2f(ms - m);
+      l = fmaf(ps[D + 1], w, l);
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) o[c] = fmaf(ps[lane * CPT + c], w, o[c]);
+    }
+    if (l > 0.f) {
+      const float coef = gate[br] * os[br] / l;
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) acc[c] = fmaf(o[c], coef, acc[c]);
+    }
+  }
+  T* orow = out + (size_t)((io_layout & NSA_IO_OUT_BTHD) ? row_bthd : row) * D + lane * CPT;
+  if constexpr (CPT == 4) {
+    *reinterpret_cast<uint2*>(orow) = make_uint2(Elem<T>::pack(acc[0], acc[1]), Elem<T>::pack(acc[2], acc[3]));
+  } else {
+    *reinterpret_cast<uint32_t*>(orow) = Elem<T>::pack(acc[0], acc[1]);
+  }
 }
 
 // ---------------------------------------------------------------- host side
@@ -798,22 +906,54 @@ int attention_fwd_tc5(const nsa_fwd_args& a, cudaStream_t st) {
     p.tmVc = p.tmV;
   }
   p.NQG = (p.a.nq + 4 / p.GH - 1) / (4 / p.GH);
-  const long long blocks = (long long)p.NQG * a.B * a.Hkv * p.HG;
+  const long long items = (long long)p.NQG * a.B * a.Hkv * p.HG;
+  // split launch: asked for by the caller (who supplies the scratch), fused bf16/fp16 forward only
+  const bool split = a.nsplit > 1 && a.fused && !in8;
+  p.nsplit = split ? a.nsplit : 1;
+  p.part = split ? reinterpret_cast<float*>(a.split_scratch) : nullptr;
+  const long long rows = (long long)a.B * a.H * a.Tq;
+  if (split) {
+    const long long need = rows * p.nsplit * 3 * (a.D + 4) * 4;
+    NSA_REQUIRE(a.split_scratch != nullptr && a.split_scratch_bytes >= need, NSA_ERR_ARG,
+                "attention forward: a launch split %d ways needs %lld bytes of scratch, %lld given", p.nsplit, need,
+                (long long)a.split_scratch_bytes);
+    NSA_REQUIRE((reinterpret_cast<uintptr_t>(a.split_scratch) & 15) == 0, NSA_ERR_ARG, "attention forward: scratch must be 16-byte aligned");
+  }
+  const long long blocks = items * p.nsplit;
   NSA_REQUIRE(blocks > 0 && blocks < 2147483647LL, NSA_ERR_ARG, "attention forward: %lld work items do not fit a grid", blocks);
   const size_t smem = (size_t)(2 + 2 + 2) * (a.D / 64) * 128 * 128 + (in8 ? (size_t)2 * 128 * a.D : 0) + 1024;
-#define NSA_TC5_LAUNCH(DD, FF, I8)                                                                         \
+#define NSA_TC5_LAUNCH(DD, FF, I8, SP)                                                                     \
   {                                                                                                         \
-    auto fn = nsa_fwd_tc5_kernel<DD, FF, I8>;                                                               \
+    auto fn = nsa_fwd_tc5_kernel<DD, FF, I8, SP>;                                                           \
     NSA_CUDA_OK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));         \
     fn<<<(unsigned)blocks, T5_THREADS, smem, st>>>(p);                                                     \
   }
   const int fmt = cdt == NSA_BF16 ? 1 : 0;
-  if (in8 && a.D == 128) NSA_TC5_LAUNCH(128, 1, true)
-  else if (in8) NSA_TC5_LAUNCH(64, 1, true)
-  else if (a.D == 128 && fmt == 1) NSA_TC5_LAUNCH(128, 1, false)
-  else if (a.D == 128) NSA_TC5_LAUNCH(128, 0, false)
-  else if (fmt == 1) NSA_TC5_LAUNCH(64, 1, false)
-  else NSA_TC5_LAUNCH(64, 0, false)
+  if (split) {
+    if (a.D == 128 && fmt == 1) NSA_TC5_LAUNCH(128, 1, false, true)
+    else if (a.D == 128) NSA_TC5_LAUNCH(128, 0, false, true)
+    else if (fmt == 1) NSA_TC5_LAUNCH(64, 1, false, true)
+    else NSA_TC5_LAUNCH(64, 0, false, true)
+    int rc2 = launch_status("attn_fwd_tc5 (split)");
+    if (rc2 != NSA_OK) return rc2;
+    const unsigned cgrid = (unsigned)((rows + 7) / 8);
+#define NSA_TC5_COMBINE(TT, DD)                                                                                        \
+    nsa_split_combine_kernel<TT, DD><<<cgrid, 256, 0, st>>>(p.part, reinterpret_cast<TT*>(a.out), a.gates, a.gate_dtype, \
+                                                            a.gate_act, a.io_layout, a.H, a.Tq, rows, p.nsplit,       \
+                                                            p.out_scale[0], p.out_scale[1], p.out_scale[2])
+    if (a.D == 128 && fmt == 1) NSA_TC5_COMBINE(__nv_bfloat16, 128);
+    else if (a.D == 128) NSA_TC5_COMBINE(__half, 128);
+    else if (fmt == 1) NSA_TC5_COMBINE(__nv_bfloat16, 64);
+    else NSA_TC5_COMBINE(__half, 64);
+#undef NSA_TC5_COMBINE
+    return launch_status("split_combine");
+  }
+  if (in8 && a.D == 128) NSA_TC5_LAUNCH(128, 1, true, false)
+  else if (in8) NSA_TC5_LAUNCH(64, 1, true, false)
+  else if (a.D == 128 && fmt == 1) NSA_TC5_LAUNCH(128, 1, false, false)
+  else if (a.D == 128) NSA_TC5_LAUNCH(128, 0, false, false)
+  else if (fmt == 1) NSA_TC5_LAUNCH(64, 1, false, false)
+  else NSA_TC5_LAUNCH(64, 0, false, false)
 #undef NSA_TC5_LAUNCH
   return launch_status("attn_fwd_tc5");
 }

@@ -113,13 +113,18 @@ __global__ void __launch_bounds__(256) select_blocks_kernel(const T* __restrict_
                                                             int force_first, int force_local, int R) {
   constexpr int KT = 64;
   constexpr int PITCH = D + 8;     // 16-bit elements; 16-byte aligned rows, 17-chunk stride -> conflict-free 128-bit reads
+  // The block's 8 warps cover R query blocks x CW = 8/R tiles of 64 key blocks at a time: with many query
+  // blocks R = 8 and a warp owns a row; with few (decoding: one) the warps share a row and take different key
+  // tiles.  A score is always one lane's fma chain over D in index order, whichever warp computes it.
+  const int CW = 8 / R;
   extern __shared__ __align__(16) unsigned char smem[];
-  T* kt = reinterpret_cast<T*>(smem);                              // [KT][PITCH]
+  T* kt = reinterpret_cast<T*>(smem);                              // [CW*KT][PITCH]
   const int G = H / Hkv;
   const int GS = Hi == H ? 1 : G;                                  // query heads summed per index head
-  float* qs = reinterpret_cast<float*>(kt + KT * PITCH);           // [R][D] fp32 query vectors
+  float* qs = reinterpret_cast<float*>(kt + CW * KT * PITCH);      // [R][D] fp32 query vectors
   float* sc = qs + R * D;                                          // [R][nk]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wrow = warp % R, wslot = warp / R;                     // row of the block / key tile of the group
   const int bh = blockIdx.y, b = bh / Hi, hi = bh % Hi;
   const int hk = Hi == H ? hi / G : hi;
   const int h0 = Hi == H ? hi : hi * G;                            // first query head of this index head
@@ -142,25 +147,26 @@ __global__ void __launch_bounds__(256) select_blocks_kernel(const T* __restrict_
     return (int)min((long long)(nk - 1), last / bn);
   };
   const int cmax_chunk = cmax_of(qb0 + rows - 1);
-  const int my_qb = qb0 + warp;
-  const int my_cmax = warp < rows ? cmax_of(my_qb) : -1;
-  float* my_sc = sc + (size_t)warp * nk;
+  const int my_qb = qb0 + wrow;
+  const int my_cmax = wrow < rows ? cmax_of(my_qb) : -1;
+  float* my_sc = sc + (size_t)wrow * nk;
 
-  for (int c0 = 0; c0 <= cmax_chunk; c0 += KT) {
+  for (int c0 = 0; c0 <= cmax_chunk; c0 += KT * CW) {
     __syncthreads();
-    const int nrow = min(KT, nk - c0);
-    for (int i = threadIdx.x; i < KT * (D / 8); i += blockDim.x) {
+    const int nrow = min(KT * CW, nk - c0);
+    for (int i = threadIdx.x; i < KT * CW * (D / 8); i += blockDim.x) {
       const int r = i / (D / 8), w = i % (D / 8);
       uint4 v = make_uint4(0u, 0u, 0u, 0u);
       if (r < nrow) v = reinterpret_cast<const uint4*>(kbase + (size_t)(c0 + r) * D)[w];
       reinterpret_cast<uint4*>(kt + r * PITCH)[w] = v;
     }
     __syncthreads();
-    if (warp < rows && c0 <= my_cmax) {
-      // lane owns blocks c0+lane and c0+lane+32: two independent fma chains in index order
-      const uint4* k0 = reinterpret_cast<const uint4*>(kt + lane * PITCH);
-      const uint4* k1 = reinterpret_cast<const uint4*>(kt + (lane + 32) * PITCH);
-      const float4* qv = reinterpret_cast<const float4*>(qs + warp * D);
+    const int cw0 = c0 + wslot * KT;                               // this warp's tile of key blocks
+    if (wrow < rows && cw0 <= my_cmax) {
+      // lane owns blocks cw0+lane and cw0+lane+32: two independent fma chains in index order
+      const uint4* k0 = reinterpret_cast<const uint4*>(kt + (wslot * KT + lane) * PITCH);
+      const uint4* k1 = reinterpret_cast<const uint4*>(kt + (wslot * KT + lane + 32) * PITCH);
+      const float4* qv = reinterpret_cast<const float4*>(qs + wrow * D);
       float tot0 = 0.f, tot1 = 0.f;
 #pragma unroll 4
       for (int w = 0; w < D / 8; ++w) {
@@ -179,8 +185,8 @@ __global__ void __launch_bounds__(256) select_blocks_kernel(const T* __restrict_
       }
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        const int c = c0 + lane + half * 32;
-        if (lane + half * 32 < nrow && c <= my_cmax) {
+        const int c = cw0 + lane + half * 32;
+        if (c < nk && c <= my_cmax) {
           float v = (half == 0 ? tot0 : tot1) * scale;
           if (c < force_first || c > my_cmax - force_local) v = INFINITY;
           my_sc[c] = v;
@@ -188,8 +194,8 @@ __global__ void __launch_bounds__(256) select_blocks_kernel(const T* __restrict_
       }
     }
   }
-  __syncwarp();
-  if (warp < rows) {
+  __syncthreads();                                                 // a row's scores come from several warps
+  if (wrow < rows && wslot == 0) {
     int32_t* out_row = idx + ((size_t)bh * nq + my_qb) * k_out;
     warp_topk_row(my_sc, my_cmax + 1, nk, k_out, out_row, lane);
   }
@@ -198,11 +204,11 @@ __global__ void __launch_bounds__(256) select_blocks_kernel(const T* __restrict_
 template <typename T>
 static int select_launch(const void* Qb, const void* Kb, int32_t* idx, int B, int H, int Hkv, int Hi, int nq, int nk, int D,
                          int k_out, int bm, int bn, int offset, int causal, float scale, int ff, int fl, cudaStream_t st) {
-  const size_t fixed = (size_t)64 * (D + 8) * 2;
+  // R query blocks per thread block (a power of two <= 8): no more than there are, fewer if the score rows
+  // would not fit; the other 8/R warps of a row group take further key tiles
   int R = 8;
-  const int GS = Hi == H ? 1 : H / Hkv;
-  auto need = [&](int r) { return fixed + (size_t)r * D * 4 + (size_t)r * nk * 4; };
-  (void)GS;
+  while (R > 1 && R / 2 >= nq) R >>= 1;
+  auto need = [&](int r) { return (size_t)(8 / r) * 64 * (D + 8) * 2 + (size_t)r * D * 4 + (size_t)r * nk * 4; };
   while (R > 1 && need(R) > 200 * 1024) R >>= 1;
   NSA_REQUIRE(need(R) <= 200 * 1024, NSA_ERR_UNSUPPORTED, "select: %d KV blocks exceed the shared-memory score row", nk);
   dim3 grid((unsigned)((nq + R - 1) / R), (unsigned)(B * Hi));

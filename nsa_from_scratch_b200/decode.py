@@ -1,0 +1,112 @@
+"""Decoding against a KV cache: the Tq << Tk case of the forward.
+
+Every function of the path already takes Tq < Tk with the queries aligned to the tail of the keys
+(`offset = Tk - Tq`, nsa/reference.py:57-59); what a decoder adds is a cache that grows in place.  The cache
+keeps, next to K and V, the two derived tensors the forward recomputes from scratch on every call -- the
+pooled K/V of the compressed branch and the block means the selection scores against -- and brings them up
+to date from the appended rows only.  The kernels are handed the whole allocation as "the" K/V tensor
+together with the true offsets: under the causal rules no row past the filled length is ever visible, so no
+copy of the filled prefix is made.  (Rows past the filled length are still multiplied by zero weights: the
+cache starts zero-filled so that they are finite.)
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch import Tensor
+
+from . import _lib as L
+from . import ops
+from .forward import _cfg
+
+
+def _cdiv(a: int, b: int) -> int:
+    return (a + b - 1) // b
+
+
+class KVCache:
+    """K, V [B,Hkv,max_len,D] with `length` rows filled, pooled K/V and selection block means kept current."""
+
+    def __init__(self, B: int, Hkv: int, D: int, max_len: int, cfg, dtype: torch.dtype = torch.bfloat16, device="cuda"):
+        if not cfg.causal:
+            raise ValueError("KVCache: decoding needs causal=True")
+        self.cfg = cfg
+        self.bc = int(cfg.block_size_c)
+        self.stride = self.bc if getattr(cfg, "stride_c", None) is None else int(cfg.stride_c)
+        self.bn = int(cfg.block_size_n)
+        self.max_len = int(max_len)
+        z = lambda n: torch.zeros((B, Hkv, n, D), dtype=dtype, device=device)
+        self.K, self.V = z(max_len), z(max_len)
+        self.Kc, self.Vc = z(max(1, self.n_pooled(max_len))), z(max(1, self.n_pooled(max_len)))
+        self.Kb = z(_cdiv(max_len, self.bn))
+        self.length = 0
+
+    def n_pooled(self, T: int) -> int:
+        if self.stride == self.bc:
+            return _cdiv(T, self.bc)
+        return 0 if T < self.bc else (T - self.bc) // self.stride + 1
+
+    def reset(self) -> None:
+        self.length = 0
+
+    def append(self, k: Tensor, v: Tensor) -> None:
+        """k, v [B,Hkv,t,D]: the next t positions."""
+        t = k.shape[2]
+        T0, T1 = self.length, self.length + t
+        if T1 > self.max_len:
+            raise ValueError(f"KVCache: {T1} rows exceed the allocation of {self.max_len}")
+        self.K[:, :, T0:T1].copy_(k)
+        self.V[:, :, T0:T1].copy_(v)
+        # pooled windows that end in the new rows (stride == block: also the partial tail window, divided by
+        # the block size as the forward does)
+        c0 = T0 // self.bc if self.stride == self.bc else self.n_pooled(T0)
+        c1 = self.n_pooled(T1)
+        if c1 > c0:
+            r0 = c0 * self.stride
+            r1 = T1 if self.stride == self.bc else (c1 - 1) * self.stride + self.bc
+            self.Kc[:, :, c0:c1].copy_(ops.pool_mean(self.K[:, :, r0:r1], self.bc, self.stride))
+            self.Vc[:, :, c0:c1].copy_(ops.pool_mean(self.V[:, :, r0:r1], self.bc, self.stride))
+        # means of the selection blocks the new rows fall in (a partial block is divided by the block size)
+        b0, b1 = T0 // self.bn, _cdiv(T1, self.bn)
+        self.Kb[:, :, b0:b1].copy_(ops.pool_mean(self.K[:, :, b0 * self.bn:T1], self.bn, self.bn))
+        self.length = T1
+
+
+def _split_ways(B: int, H: int, Hkv: int, Tq: int, n_pooled: int) -> int:
+    """Thread blocks per work item of the attention launch: enough to reach every SM once when there are few
+    work items, but at least two 128-key tiles of the compressed branch (the long one) per block."""
+    G = H // Hkv
+    gh = 4 if G % 4 == 0 else (2 if G % 2 == 0 else 1)
+    items = B * Hkv * (G // gh) * _cdiv(_cdiv(Tq, 64), 4 // gh)
+    sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    return max(1, min(sms // max(items, 1), _cdiv(n_pooled, 128) // 2, 16))
+
+
+def nsa_decode(q: Tensor, cache: KVCache, *, gate_logits: Optional[Tensor] = None, nsplit: Optional[int] = None) -> Tensor:
+    """q [B,H,Tq,D]: the queries of the LAST Tq cached positions (append their keys first).  Returns
+    [B,H,Tq,D] -- what `nsa_forward(q, K[:, :, :length], V[:, :, :length], cfg)` returns.  `nsplit`: thread
+    blocks per work item of the attention launch (None: chosen from the sizes; 1: the ordinary launch)."""
+    cfg = cache.cfg
+    B, H, Tq, D = q.shape
+    Tk = cache.length
+    if Tq > Tk:
+        raise ValueError(f"nsa_decode: {Tq} queries but only {Tk} cached positions")
+    scale = float(cfg.scale if cfg.scale is not None else 1.0 / (D ** 0.5))
+    bm, bn = int(cfg.block_size_m), cache.bn
+    Qb = ops.pool_mean(q, bm, bm)
+    idx = ops.select_blocks_from_means(
+        Qb, cache.Kb, top_k=cfg.top_k, bm=bm, bn=bn, offset=_cdiv(Tk, bn) * bn - _cdiv(Tq, bm) * bm, causal=True, scale=scale,
+        force_first=_cfg(cfg, "force_first", 0), force_local=_cfg(cfg, "force_local", 0),
+        shared_per_group=bool(_cfg(cfg, "select_per_group", False)))
+    Tk_pad = _cdiv(Tk, cache.bc) * cache.bc if cache.stride == cache.bc else Tk
+    out, _ = ops.attention_fwd(
+        q, cache.K, cache.V, branches=L.BRANCH_COMPRESSED | L.BRANCH_SELECTED | L.BRANCH_SLIDING, fused=True, causal=True,
+        scale=scale, Kc=cache.Kc, Vc=cache.Vc, cmp_block=cache.bc, cmp_stride=cache.stride, cmp_offset=Tk_pad - Tq,
+        idx=idx, bm=bm, bn=bn, window=cfg.window_size, gates=gate_logits,
+        gate_act=L.GATE_SOFTMAX if cfg.gate_activation == "softmax" else L.GATE_SIGMOID, offset=Tk - Tq,
+        nsplit=_split_ways(B, H, cache.K.shape[1], Tq, cache.n_pooled(Tk)) if nsplit is None else int(nsplit))
+    return out
+
+
+__all__ = ["KVCache", "nsa_decode"]

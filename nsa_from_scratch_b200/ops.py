@@ -96,11 +96,13 @@ def attention_fwd(
     cmp_offset: int = 0, idx: Optional[Tensor] = None, bm: int = 64, bn: int = 64, window: int = 0,
     gates: Optional[Tensor] = None, gate_act: int = L.GATE_SIGMOID, offset: Optional[int] = None,
     q_scale: float = 1.0, k_scale: float = 1.0, v_scale: float = 1.0, engine: Optional[int] = None,
-    want_lse: bool = True, token_major: bool = False,
+    want_lse: bool = True, token_major: bool = False, nsplit: int = 1,
 ) -> Tuple[Tensor, Optional[Tensor]]:
     """One launch of nsa_attention_fwd.  Returns (out, lse); lse is None for fused launches.
     `token_major`: gates are [B,Tq,H,3] and the result comes back as [B,Tq,H,D] (Q, K, V stay
-    [B,H,T,D]) -- the layouts on either side of the call in the reference's attention module."""
+    [B,H,T,D]) -- the layouts on either side of the call in the reference's attention module.
+    `nsplit` > 1 (fused launches): each work item's key tiles are spread over that many thread blocks, for
+    launches with few query blocks and long key ranges (decoding)."""
     _need_cuda(Q, K, V)
     B, H, Tq, D = Q.shape
     Hkv, Tk = K.shape[1], K.shape[2]
@@ -146,6 +148,10 @@ def attention_fwd(
         if gates.shape != want:
             raise ValueError(f"gate_logits shape {tuple(gates.shape)} != {want}")
         a.gates, a.gate_dtype = gates.data_ptr(), L.dtype_code(gates.dtype)
+    if fused and nsplit > 1 and Q.dtype in _16:
+        scratch = torch.empty((B * H * Tq * nsplit * 3 * (D + 4),), device=Q.device, dtype=torch.float32)
+        keep.append(scratch)
+        a.nsplit, a.split_scratch, a.split_scratch_bytes = int(nsplit), scratch.data_ptr(), scratch.numel() * 4
     with torch.cuda.device(Q.device):
         L.check(L.load().nsa_attention_fwd(C.byref(a), L.stream_ptr()), "nsa_attention_fwd")
     return out, lse

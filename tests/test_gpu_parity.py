@@ -465,6 +465,23 @@ def test_host_entry_point_query_chunks(nsa, Tq, Tk, chunk):
     assert torch.equal(big[:, :, 64:], ref.cpu()) and float(big[:, :, :64].abs().max()) == 0.0
 
 
+def test_forward_as_cuda_graph(nsa):
+    """The whole forward step captured into one CUDA graph replays to the eager result, also after the
+    inputs were refilled in place."""
+    Q, K, V, g = make_qkv(29, 1, 8, 2, 640, 640, 128)
+    gates = torch.randn(1, 8, 640, 3, generator=g).cuda()
+    cfg = nsa.NSAConfig(block_size_c=32, stride_c=16, top_k=4, window_size=128, force_first=1, force_local=2, select_per_group=True)
+    Qc, Kc, Vc = Q.cuda(), K.cuda(), V.cuda()
+    graphed = nsa.GraphedForward(Qc, Kc, Vc, cfg, gate_logits=gates)
+    assert torch.equal(graphed(), nsa.nsa_forward(Qc, Kc, Vc, cfg, gate_logits=gates))
+    Q2, K2, V2, _ = make_qkv(30, 1, 8, 2, 640, 640, 128)
+    Qc.copy_(Q2.cuda()); Kc.copy_(K2.cuda()); Vc.copy_(V2.cuda())
+    out2 = graphed().clone()
+    assert torch.equal(out2, nsa.nsa_forward(Qc, Kc, Vc, cfg, gate_logits=gates))
+    from nsa_from_scratch_b200 import ops
+    ops.device_status()
+
+
 # ------------------------------------------------------------------ compressed / sliding backward kernels
 def test_golden_compressed_and_sliding_gradients(nsa, golden):
     """Gradients through the autograd Functions against the reference's own (autograd through its torch code)."""
