@@ -124,7 +124,7 @@ typedef struct nsa_fwd_args {
   float q_scale, k_scale, v_scale;               /* fp8 dequantisation scales                              */
   int32_t engine;                                /* NSA_ENGINE_*                                           */
   int32_t io_layout;                             /* NSA_IO_* bits; 0 = every tensor [B,H,T,.]              */
-  /* Decoding-sized launches (few query blocks, long key ranges): nsplit > 1 spreads each work item's key
+  /* Decoding-sized launches (few query blocks, long key ranges): nsplit > 1 (at most 16) spreads each work item's key
    * tiles over nsplit thread blocks and merges their partial results in a second kernel.  Fused launches on
    * the tcgen05 kernel with 16-bit storage only (ignored elsewhere).  The caller supplies the scratch:
    * B*H*Tq*nsplit*3*(D+4)*4 bytes, 16-byte aligned; its contents need not be preserved or cleared. */
@@ -258,6 +258,16 @@ int nsa_cast_from_f32(const float* src, void* dst, int64_t n, int dtype, nsa_str
  * nsa/model/llama_nsa.py:77-80,91 and nsa/model/llama_dense.py:19-37. */
 int nsa_rope_to_heads(const void* x, void* y, const void* cos, const void* sin, int B, int T, int H, int D,
                       int x_dtype, int cs_dtype, int y_dtype, nsa_stream_t stream);
+
+/* KV-cache append, one launch: k_new, v_new [B,Hkv,t_new,D] become rows filled..filled+t_new-1 of K, V
+ * [B,Hkv,max_len,D]; the pooled windows (cmp_block / cmp_stride, nsa_pool_mean's rules) of Kc, Vc
+ * [B,Hkv,nc_alloc,D] and the selection-block means Kb [B,Hkv,nb_alloc,D] that contain a new row are recomputed
+ * with nsa_pool_mean's arithmetic.  Afterwards Kc/Vc/Kb hold what nsa_pool_mean gives on the filled prefix.
+ * No counterpart in the reference (it recomputes the pooled tensors from scratch in every call,
+ * nsa/triton/compressed.py:25-44, nsa/triton/forward.py:344-345). */
+int nsa_cache_append(const void* k_new, const void* v_new, void* K, void* V, void* Kc, void* Vc, void* Kb, int B,
+                     int Hkv, int D, int t_new, int filled, int max_len, int nc_alloc, int nb_alloc, int cmp_block,
+                     int cmp_stride, int sel_block, int dtype, nsa_stream_t stream);
 
 /* Strided copy between host and device on `stream`: `rows` rows of `row_bytes` bytes, row r at
  * dst + r*dst_pitch / src + r*src_pitch; to_device = 1 host->device, 0 device->host.  Asynchronous when

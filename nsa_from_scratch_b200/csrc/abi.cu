@@ -32,6 +32,8 @@ int fp8_absmax(const void*, long long, int, float*, cudaStream_t);
 int fp8_quantize(const void*, void*, long long, int, int, float, cudaStream_t);
 int bwd_delta(const void*, const void*, float*, long long, int, int, cudaStream_t);
 int cast_from_f32(const float*, void*, long long, int, cudaStream_t);
+int cache_append(const void*, const void*, void*, void*, void*, void*, void*, int, int, int, int, int, int, int, int, int, int, int, int,
+                 cudaStream_t);
 int rope_to_heads(const void*, void*, const void*, const void*, int, int, int, int, int, int, int, cudaStream_t);
 
 static bool is16(int dt) { return dt == NSA_BF16 || dt == NSA_FP16; }
@@ -47,7 +49,7 @@ static int check_fwd(const nsa_fwd_args& a) {
   NSA_REQUIRE(a.kv_dtype == a.q_dtype, NSA_ERR_UNSUPPORTED, "attention forward: K/V dtype %d differs from Q dtype %d", a.kv_dtype, a.q_dtype);
   const int br = a.branches;
   NSA_REQUIRE(br > 0 && br < 8, NSA_ERR_ARG, "attention forward: branch mask %d", br);
-  NSA_REQUIRE(a.nsplit >= 0 && a.nsplit <= 64, NSA_ERR_ARG, "attention forward: nsplit %d not in [0, 64]", a.nsplit);
+  NSA_REQUIRE(a.nsplit >= 0 && a.nsplit <= 16, NSA_ERR_ARG, "attention forward: nsplit %d not in [0, 16]", a.nsplit);
   NSA_REQUIRE((a.io_layout & ~(NSA_IO_OUT_BTHD | NSA_IO_GATES_BTHD)) == 0, NSA_ERR_ARG, "attention forward: io_layout %d has unknown bits", a.io_layout);
   if (!a.fused) {
     NSA_REQUIRE(br == 1 || br == 2 || br == 4, NSA_ERR_ARG, "attention forward: unfused launch needs exactly one branch (mask %d)", br);
@@ -243,6 +245,14 @@ int nsa_rope_to_heads(const void* x, void* y, const void* cos, const void* sin, 
   NSA_REQUIRE(cos == nullptr || cs_dtype == NSA_FP32 || cs_dtype == NSA_BF16 || cs_dtype == NSA_FP16, NSA_ERR_UNSUPPORTED,
               "rope_to_heads: cos/sin dtype %d", cs_dtype);
   return rope_to_heads(x, y, cos, sin, B, T, H, D, x_dtype, cs_dtype, y_dtype, (cudaStream_t)stream);
+}
+
+int nsa_cache_append(const void* k_new, const void* v_new, void* K, void* V, void* Kc, void* Vc, void* Kb, int B, int Hkv, int D,
+                     int t_new, int filled, int max_len, int nc_alloc, int nb_alloc, int cmp_block, int cmp_stride, int sel_block,
+                     int dtype, nsa_stream_t stream) {
+  NSA_REQUIRE(k_new && v_new && K && V && Kc && Vc && Kb, NSA_ERR_ARG, "cache append: NULL pointer");
+  return cache_append(k_new, v_new, K, V, Kc, Vc, Kb, B, Hkv, D, t_new, filled, max_len, nc_alloc, nb_alloc, cmp_block, cmp_stride,
+                      sel_block, dtype, (cudaStream_t)stream);
 }
 
 int nsa_memcpy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t row_bytes, size_t rows,

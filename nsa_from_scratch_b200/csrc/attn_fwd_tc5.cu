@@ -783,22 +783,43 @@ __global__ void __launch_bounds__(256) nsa_split_combine_kernel(const float* __r
 #pragma unroll
   for (int c = 0; c < CPT; ++c) acc[c] = 0.f;
   const float* prow = part + (size_t)row * nsplit * 3 * (D + 4);
+  constexpr int MAXS = 16;                                  // nsplit <= 16: every load of a step is issued before any is used
 #pragma unroll
   for (int br = 0; br < 3; ++br) {
+    float ms[MAXS], ls[MAXS];
+#pragma unroll
+    for (int s = 0; s < MAXS; ++s) {
+      const bool in = s < nsplit;
+      const float2 ml = in ? *reinterpret_cast<const float2*>(prow + (s * 3 + br) * (D + 4) + D) : make_float2(-INFINITY, 0.f);
+      ms[s] = ml.x; ls[s] = ml.y;
+    }
     float m = -INFINITY;
-    for (int s = 0; s < nsplit; ++s) m = fmaxf(m, prow[(s * 3 + br) * (D + 4) + D]);
+#pragma unroll
+    for (int s = 0; s < MAXS; ++s) m = fmaxf(m, ms[s]);
     if (m == -INFINITY) continue;
     float l = 0.f, o[CPT];
 #pragma unroll
     for (int c = 0; c < CPT; ++c) o[c] = 0.f;
-    for (int s = 0; s < nsplit; ++s) {
-      const float* ps = prow + (s * 3 + br) * (D + 4);
-      const float ms = ps[D];
-      if (ms == -INFINITY) continue;
-      const float w = exp2f(ms - m);
-      l = fmaf(ps[D + 1], w, l);
 #pragma unroll
-      for (int c = 0; c < CPT; ++c) o[c] = fmaf(ps[lane * CPT + c], w, o[c]);
+    for (int s0 = 0; s0 < MAXS; s0 += 8) {
+      if (s0 >= nsplit) break;
+      float v[8][CPT];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const bool in = s0 + e < nsplit && ms[s0 + e] != -INFINITY;
+        const float* ps = prow + ((s0 + e) * 3 + br) * (D + 4) + lane * CPT;
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) v[e][c] = in ? ps[c] : 0.f;
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        if (s0 + e < nsplit && ms[s0 + e] != -INFINITY) {
+          const float w = exp2f(ms[s0 + e] - m);
+          l = fmaf(ls[s0 + e], w, l);
+#pragma unroll
+          for (int c = 0; c < CPT; ++c) o[c] = fmaf(v[e][c], w, o[c]);
+        }
+      }
     }
     if (l > 0.f) {
       const float coef = gate[br] * os[br] / l;

@@ -66,6 +66,97 @@ int pool_mean(const void* x, void* out, int B, int H, int T, int D, int block, i
   return launch_status("pool_mean");
 }
 
+// ------------------------------------------------------------------ KV-cache append
+// One launch brings a cache up to date with t_new appended positions: the rows go into K and V, and the pooled
+// windows and selection-block means that contain a new row are recomputed with pool_mean_kernel's arithmetic
+// (fp32 sum in row order, divide by the window size, one rounding).  Rows at or past `filled` are read from
+// the new tensors, so nothing in the launch depends on another thread's copy.
+// One thread = 8 columns of one item; items of a slab: t_new row copies, nw pooled windows, nbk block means.
+template <typename T>
+__global__ void __launch_bounds__(256) cache_append_kernel(const T* __restrict__ k_new, const T* __restrict__ v_new,
+                                                           T* __restrict__ K, T* __restrict__ V, T* __restrict__ Kc,
+                                                           T* __restrict__ Vc, T* __restrict__ Kb, int D, int t_new,
+                                                           int filled, int max_len, int nc_alloc, int nb_alloc, int cblock,
+                                                           int cstride, int c0, int nw, int sblock, int b0, int nbk) {
+  const int CH = D / 8;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long items = (long long)t_new + nw + nbk;
+  if (i >= items * CH) return;
+  const int item = (int)(i / CH), ch = (int)(i % CH);
+  const size_t slab = blockIdx.y;
+  const int T1 = filled + t_new;
+  auto row8 = [&](const T* cache, const T* fresh, int r) {
+    const T* p = r >= filled ? fresh + (slab * t_new + (r - filled)) * D : cache + (slab * max_len + r) * D;
+    return *reinterpret_cast<const uint4*>(p + ch * 8);
+  };
+  auto mean8 = [&](const T* cache, const T* fresh, int r0, int block) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    const int r1 = min(r0 + block, T1);
+    for (int rb = r0; rb < r1; rb += 8) {                  // eight rows' loads in flight, added in row order
+      uint4 raw[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) raw[j] = rb + j < r1 ? row8(cache, fresh, rb + j) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (rb + j < r1) {
+          const uint32_t w[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = Elem<T>::unpack(w[e]);
+            acc[2 * e] += f.x;
+            acc[2 * e + 1] += f.y;
+          }
+        }
+      }
+    }
+    const float n = (float)block;
+    return make_uint4(Elem<T>::pack(__fdiv_rn(acc[0], n), __fdiv_rn(acc[1], n)), Elem<T>::pack(__fdiv_rn(acc[2], n), __fdiv_rn(acc[3], n)),
+                      Elem<T>::pack(__fdiv_rn(acc[4], n), __fdiv_rn(acc[5], n)), Elem<T>::pack(__fdiv_rn(acc[6], n), __fdiv_rn(acc[7], n)));
+  };
+  if (item < t_new) {
+    const size_t dst = (slab * max_len + filled + item) * D + ch * 8, src = (slab * t_new + item) * D + ch * 8;
+    *reinterpret_cast<uint4*>(K + dst) = *reinterpret_cast<const uint4*>(k_new + src);
+    *reinterpret_cast<uint4*>(V + dst) = *reinterpret_cast<const uint4*>(v_new + src);
+  } else if (item < t_new + nw) {
+    const int c = c0 + (item - t_new);
+    const size_t dst = (slab * nc_alloc + c) * D + ch * 8;
+    *reinterpret_cast<uint4*>(Kc + dst) = mean8(K, k_new, c * cstride, cblock);
+    *reinterpret_cast<uint4*>(Vc + dst) = mean8(V, v_new, c * cstride, cblock);
+  } else {
+    const int bb = b0 + (item - t_new - nw);
+    *reinterpret_cast<uint4*>(Kb + (slab * nb_alloc + bb) * D + ch * 8) = mean8(K, k_new, bb * sblock, sblock);
+  }
+}
+
+int cache_append(const void* k_new, const void* v_new, void* K, void* V, void* Kc, void* Vc, void* Kb, int B, int Hkv, int D,
+                 int t_new, int filled, int max_len, int nc_alloc, int nb_alloc, int cblock, int cstride, int sblock, int dtype,
+                 cudaStream_t st) {
+  NSA_REQUIRE(D % 8 == 0 && D > 0, NSA_ERR_ARG, "cache append: D %d must be a positive multiple of 8", D);
+  NSA_REQUIRE(t_new >= 0 && filled >= 0 && filled + t_new <= max_len, NSA_ERR_ARG,
+              "cache append: %d filled + %d new rows exceed the allocation of %d", filled, t_new, max_len);
+  NSA_REQUIRE(cblock > 0 && cstride > 0 && cstride <= cblock && sblock > 0, NSA_ERR_ARG, "cache append: bad block sizes");
+  NSA_REQUIRE((long long)B * Hkv <= 65535 && B * Hkv > 0, NSA_ERR_ARG, "cache append: B*Hkv %lld", (long long)B * Hkv);
+  if (t_new == 0) return NSA_OK;
+  const int T0 = filled, T1 = filled + t_new;
+  auto n_pooled = [&](int T) { return cstride == cblock ? (T + cblock - 1) / cblock : (T >= cblock ? (T - cblock) / cstride + 1 : 0); };
+  // windows that contain a new row: whole windows completed by them, or (stride == block) the partial tail window
+  const int c0 = cstride == cblock ? T0 / cblock : n_pooled(T0);
+  const int nw = n_pooled(T1) - c0;
+  const int b0 = T0 / sblock, nbk = (T1 + sblock - 1) / sblock - b0;
+  NSA_REQUIRE(c0 + nw <= nc_alloc && b0 + nbk <= nb_alloc, NSA_ERR_ARG, "cache append: pooled (%d) or block-mean (%d) allocation too small",
+              nc_alloc, nb_alloc);
+  const long long threads = ((long long)t_new + nw + nbk) * (D / 8);
+  dim3 grid((unsigned)((threads + 255) / 256), (unsigned)(B * Hkv));
+#define NSA_APPEND(TT)                                                                                                  \
+  cache_append_kernel<TT><<<grid, 256, 0, st>>>((const TT*)k_new, (const TT*)v_new, (TT*)K, (TT*)V, (TT*)Kc, (TT*)Vc, (TT*)Kb, D, \
+                                                t_new, filled, max_len, nc_alloc, nb_alloc, cblock, cstride, c0, nw, sblock, b0, nbk)
+  if (dtype == NSA_BF16) NSA_APPEND(__nv_bfloat16);
+  else if (dtype == NSA_FP16) NSA_APPEND(__half);
+  else return fail(NSA_ERR_UNSUPPORTED, "cache append: dtype %d", dtype);
+#undef NSA_APPEND
+  return launch_status("cache_append");
+}
+
 // ------------------------------------------------------------------ top-k over one score row
 // Warp-level: k_out rounds of (lane-local scan, shuffle arg-max).  Order: larger score
 // first, equal scores lowest index first.  Chosen entries are overwritten with a quiet-NaN
@@ -134,8 +225,17 @@ __global__ void __launch_bounds__(256) select_blocks_kernel(const T* __restrict_
 
   for (int i = threadIdx.x; i < rows * D; i += blockDim.x) {
     const int r = i / D, d = i % D;
-    float acc = Elem<T>::to_f(Qb[(((size_t)b * H + h0) * nq + qb0 + r) * D + d]);
-    for (int gs = 1; gs < GS; ++gs) acc = __fadd_rn(acc, Elem<T>::to_f(Qb[(((size_t)b * H + h0 + gs) * nq + qb0 + r) * D + d]));
+    // sum over the group's heads in head order; the loads of a batch of 8 heads are issued together
+    float acc = 0.f;
+    for (int g0 = 0; g0 < GS; g0 += 8) {
+      float v[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        v[e] = g0 + e < GS ? Elem<T>::to_f(Qb[(((size_t)b * H + h0 + g0 + e) * nq + qb0 + r) * D + d]) : 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        if (g0 + e < GS) acc = (g0 + e == 0) ? v[e] : __fadd_rn(acc, v[e]);
+    }
     qs[i] = acc;
   }
 
@@ -154,12 +254,15 @@ __global__ void __launch_bounds__(256) select_blocks_kernel(const T* __restrict_
   for (int c0 = 0; c0 <= cmax_chunk; c0 += KT * CW) {
     __syncthreads();
     const int nrow = min(KT * CW, nk - c0);
+    // asynchronous 16-byte copies, all in flight at once (a load-then-store loop pays one memory round trip per
+    // iteration, which is what a launch with a handful of thread blocks -- decoding -- would wait on)
     for (int i = threadIdx.x; i < KT * CW * (D / 8); i += blockDim.x) {
       const int r = i / (D / 8), w = i % (D / 8);
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (r < nrow) v = reinterpret_cast<const uint4*>(kbase + (size_t)(c0 + r) * D)[w];
-      reinterpret_cast<uint4*>(kt + r * PITCH)[w] = v;
+      const bool in = r < nrow;
+      cp_async16(smem_u32(kt + r * PITCH + w * 8), kbase + (size_t)(c0 + (in ? r : 0)) * D + w * 8, in ? 16 : 0);
     }
+    cp_async_commit();
+    cp_async_wait<0>();
     __syncthreads();
     const int cw0 = c0 + wslot * KT;                               // this warp's tile of key blocks
     if (wrow < rows && cw0 <= my_cmax) {

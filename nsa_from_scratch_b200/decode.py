@@ -56,20 +56,16 @@ class KVCache:
         T0, T1 = self.length, self.length + t
         if T1 > self.max_len:
             raise ValueError(f"KVCache: {T1} rows exceed the allocation of {self.max_len}")
-        self.K[:, :, T0:T1].copy_(k)
-        self.V[:, :, T0:T1].copy_(v)
-        # pooled windows that end in the new rows (stride == block: also the partial tail window, divided by
-        # the block size as the forward does)
-        c0 = T0 // self.bc if self.stride == self.bc else self.n_pooled(T0)
-        c1 = self.n_pooled(T1)
-        if c1 > c0:
-            r0 = c0 * self.stride
-            r1 = T1 if self.stride == self.bc else (c1 - 1) * self.stride + self.bc
-            self.Kc[:, :, c0:c1].copy_(ops.pool_mean(self.K[:, :, r0:r1], self.bc, self.stride))
-            self.Vc[:, :, c0:c1].copy_(ops.pool_mean(self.V[:, :, r0:r1], self.bc, self.stride))
-        # means of the selection blocks the new rows fall in (a partial block is divided by the block size)
-        b0, b1 = T0 // self.bn, _cdiv(T1, self.bn)
-        self.Kb[:, :, b0:b1].copy_(ops.pool_mean(self.K[:, :, b0 * self.bn:T1], self.bn, self.bn))
+        k, v = k.contiguous(), v.contiguous()
+        B, Hkv, _, D = self.K.shape
+        if k.shape != (B, Hkv, t, D) or v.shape != k.shape or k.dtype != self.K.dtype or v.dtype != self.K.dtype:
+            raise ValueError(f"KVCache.append: expected [{B},{Hkv},t,{D}] {self.K.dtype} tensors, got {tuple(k.shape)} {k.dtype}")
+        # one launch: rows into K/V, and every pooled window / selection-block mean that contains a new row
+        with torch.cuda.device(self.K.device):
+            L.check(L.load().nsa_cache_append(k.data_ptr(), v.data_ptr(), self.K.data_ptr(), self.V.data_ptr(), self.Kc.data_ptr(),
+                                              self.Vc.data_ptr(), self.Kb.data_ptr(), B, Hkv, D, t, T0, self.max_len,
+                                              self.Kc.shape[2], self.Kb.shape[2], self.bc, self.stride, self.bn,
+                                              L.dtype_code(self.K.dtype), L.stream_ptr()), "nsa_cache_append")
         self.length = T1
 
 
