@@ -592,7 +592,7 @@ def run_sweep(a):
     # decoding against a KV cache: one new token per step (keys appended, pooled K/V and block means brought up
     # to date, selection, split attention launch + merge), CUDA-event time per step
     for B, Tk in ((1, 65536), (8, 65536), (1, 8192)):
-        cache = nsa.KVCache(B, Hkv, D, Tk + 64, cfg)
+        cache = nsa.KVCache(B, Hkv, D, Tk + 256, cfg)
         g = torch.Generator().manual_seed(a.seed)
         for c0 in range(0, Tk - 1, 8192):
             n = min(8192, Tk - 1 - c0)
@@ -632,9 +632,22 @@ def run_sweep(a):
             decode_step()
         torch.cuda.synchronize()
         wall_us = (_time.perf_counter() - t0) / 20 * 1e6
+        # the same step as one CUDA graph (fill count in device memory): wall time per replayed step
+        cache._set_length(Tk - 1)
+        dec = nsa.GraphedDecoder(cache, H)
+        dec.q.copy_(q1); dec.k.copy_(k1); dec.v.copy_(k1); dec.gate_logits.copy_(g1)
+        for _ in range(5):
+            dec.step()
+        torch.cuda.synchronize()
+        t0 = _time.perf_counter()
+        for _ in range(100):
+            dec.step()
+        torch.cuda.synchronize()
+        graph_us = (_time.perf_counter() - t0) / 100 * 1e6
         ops.device_status()
-        del big
+        del big, dec
         print(json.dumps({"metric": "nsa_decode_step_us", "value": us, "unsplit_launch_us": us1, "wall_us_python_host": wall_us,
+                          "wall_us_cuda_graph": graph_us, "tokens_per_s_cuda_graph": B / (graph_us * 1e-6),
                           "tokens_per_s": B / (us * 1e-6),
                           "config": {"workload": f"decode 1 token/sequence, B={B} cached={Tk} Hq={H} Hkv={Hkv} D={D} bf16, "
                                                  f"cmp={b.cmp_block}/{b.cmp_stride} top-{b.top_k} W={b.window}"}}), flush=True)

@@ -131,6 +131,12 @@ typedef struct nsa_fwd_args {
   int32_t nsplit;
   void* split_scratch;
   int64_t split_scratch_bytes;
+  /* Optional: the number of filled key positions, read from device memory when the kernel starts.  With it
+   * K/V (and Kc/Vc) are allocations longer than what is filled, Tk / Nc give the allocated lengths, and
+   * offset, cmp_offset and sel_key_limit are derived on the device from *dyn_len -- so the launch can sit in a
+   * CUDA graph that is replayed while a KV cache grows.  Needs causal = 1, fused = 1, 16-bit storage, the
+   * tcgen05 kernel and the split scratch (nsplit >= 1); NSA_ERR_UNSUPPORTED otherwise. */
+  const int32_t* dyn_len;
 } nsa_fwd_args;
 
 /* Replaces the kernels behind compressed_attention (nsa/triton/compressed.py:191-300),
@@ -268,6 +274,22 @@ int nsa_rope_to_heads(const void* x, void* y, const void* cos, const void* sin, 
 int nsa_cache_append(const void* k_new, const void* v_new, void* K, void* V, void* Kc, void* Vc, void* Kb, int B,
                      int Hkv, int D, int t_new, int filled, int max_len, int nc_alloc, int nb_alloc, int cmp_block,
                      int cmp_stride, int sel_block, int dtype, nsa_stream_t stream);
+
+/* The two launches above for a cache whose fill count lives in DEVICE memory, so that a decoding step can be
+ * captured into a CUDA graph once and replayed while the cache grows.
+ * nsa_cache_append_dev: appends at *filled, then adds t_new to *filled (a second, one-thread launch); an
+ *   append that would pass max_len writes nothing and leaves *filled alone (the host, which mirrors the
+ *   count, should refuse it first).
+ * nsa_select_blocks_cached: nsa_select_blocks with causal = 1 and the block-grid offset derived from
+ *   *filled (ceil(filled/bn)*bn - nq*bm); Kb [B,Hkv,nk_alloc,D] is the cache's whole block-mean tensor.
+ * No counterpart in the reference. */
+int nsa_cache_append_dev(const void* k_new, const void* v_new, void* K, void* V, void* Kc, void* Vc, void* Kb,
+                         int B, int Hkv, int D, int t_new, int32_t* filled, int max_len, int nc_alloc, int nb_alloc,
+                         int cmp_block, int cmp_stride, int sel_block, int dtype, nsa_stream_t stream);
+int nsa_select_blocks_cached(const void* Qb, const void* Kb, int32_t* idx, int B, int H, int Hkv, int nq,
+                             int nk_alloc, int D, int top_k, int bm, int bn, const int32_t* filled, float scale,
+                             int force_first, int force_local, int shared_per_group, int dtype,
+                             nsa_stream_t stream);
 
 /* Strided copy between host and device on `stream`: `rows` rows of `row_bytes` bytes, row r at
  * dst + r*dst_pitch / src + r*src_pitch; to_device = 1 host->device, 0 device->host.  Asynchronous when

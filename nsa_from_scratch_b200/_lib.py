@@ -50,6 +50,7 @@ class FwdArgs(C.Structure):
         ("scale", C.c_float), ("q_scale", C.c_float), ("k_scale", C.c_float), ("v_scale", C.c_float),
         ("engine", C.c_int32), ("io_layout", C.c_int32),
         ("nsplit", C.c_int32), ("split_scratch", C.c_void_p), ("split_scratch_bytes", C.c_int64),
+        ("dyn_len", C.c_void_p),
     ]
 
 
@@ -92,6 +93,8 @@ PROTOTYPES = {
     "nsa_cast_from_f32": (_i, [_vp, _vp, _i64, _i, _vp]),
     "nsa_rope_to_heads": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "nsa_cache_append": (_i, [_vp] * 7 + [_i] * 12 + [_vp]),
+    "nsa_cache_append_dev": (_i, [_vp] * 7 + [_i] * 4 + [_vp] + [_i] * 7 + [_vp]),
+    "nsa_select_blocks_cached": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _f, _i, _i, _i, _i, _vp]),
     "nsa_memcpy_2d": (_i, [_vp, C.c_size_t, _vp, C.c_size_t, C.c_size_t, C.c_size_t, _i, _vp]),
 }
 

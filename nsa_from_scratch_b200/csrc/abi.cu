@@ -19,7 +19,7 @@ int fail(int code, const char* fmt, ...) {
 // kernels (other translation units)
 int pool_mean(const void*, void*, int, int, int, int, int, int, int, int, float, cudaStream_t);
 int select_blocks(const void*, const void*, int32_t*, int, int, int, int, int, int, int, int, int, int, int, float, int,
-                  int, int, int, cudaStream_t);
+                  int, int, int, const int32_t*, cudaStream_t);
 int topk_from_scores(const float*, int32_t*, int, int, int, int, int, int, int, int, cudaStream_t);
 int attention_fwd_generic(const nsa_fwd_args&, cudaStream_t);
 int attention_fwd_tc5(const nsa_fwd_args&, cudaStream_t);
@@ -32,8 +32,8 @@ int fp8_absmax(const void*, long long, int, float*, cudaStream_t);
 int fp8_quantize(const void*, void*, long long, int, int, float, cudaStream_t);
 int bwd_delta(const void*, const void*, float*, long long, int, int, cudaStream_t);
 int cast_from_f32(const float*, void*, long long, int, cudaStream_t);
-int cache_append(const void*, const void*, void*, void*, void*, void*, void*, int, int, int, int, int, int, int, int, int, int, int, int,
-                 cudaStream_t);
+int cache_append(const void*, const void*, void*, void*, void*, void*, void*, int, int, int, int, int, int32_t*, int, int, int, int, int,
+                 int, int, cudaStream_t);
 int rope_to_heads(const void*, void*, const void*, const void*, int, int, int, int, int, int, int, cudaStream_t);
 
 static bool is16(int dt) { return dt == NSA_BF16 || dt == NSA_FP16; }
@@ -82,7 +82,7 @@ using namespace nsa;
 extern "C" {
 
 const char* nsa_last_error(void) { return g_err; }
-int nsa_abi_version(void) { return 3; }
+int nsa_abi_version(void) { return 4; }
 
 int nsa_pool_mean(const void* x, void* out, int B, int H, int T, int D, int block, int stride, int n_out, int dtype,
                   float dequant_scale, nsa_stream_t stream) {
@@ -95,7 +95,15 @@ int nsa_select_blocks(const void* Qb, const void* Kb, int32_t* idx, int B, int H
                       int shared_per_group, int dtype, nsa_stream_t stream) {
   NSA_REQUIRE(Qb && Kb && idx, NSA_ERR_ARG, "select: NULL pointer");
   return select_blocks(Qb, Kb, idx, B, H, Hkv, nq, nk, D, top_k, bm, bn, offset, causal, scale, force_first,
-                       force_local, shared_per_group, dtype, (cudaStream_t)stream);
+                       force_local, shared_per_group, dtype, nullptr, (cudaStream_t)stream);
+}
+
+int nsa_select_blocks_cached(const void* Qb, const void* Kb, int32_t* idx, int B, int H, int Hkv, int nq, int nk_alloc, int D,
+                             int top_k, int bm, int bn, const int32_t* filled, float scale, int force_first, int force_local,
+                             int shared_per_group, int dtype, nsa_stream_t stream) {
+  NSA_REQUIRE(Qb && Kb && idx && filled, NSA_ERR_ARG, "select (cached): NULL pointer");
+  return select_blocks(Qb, Kb, idx, B, H, Hkv, nq, nk_alloc, D, top_k, bm, bn, 0, 1, scale, force_first, force_local,
+                       shared_per_group, dtype, filled, (cudaStream_t)stream);
 }
 
 int nsa_topk_from_scores(const float* scores, int32_t* idx, int BH, int nq, int nk, int top_k, int bm, int bn,
@@ -120,6 +128,7 @@ int nsa_attention_fwd(const nsa_fwd_args* args, nsa_stream_t stream) {
     const bool sel_only_per_head = !args->fused && args->branches == NSA_BRANCH_SELECTED && args->Hi == args->H && args->D == 64;
     if (!sel_only_per_head) return attention_fwd_tc5(*args, (cudaStream_t)stream);
   }
+  NSA_REQUIRE(args->dyn_len == nullptr, NSA_ERR_UNSUPPORTED, "attention forward: a device-resident length needs the tcgen05 kernel");
   return attention_fwd_generic(*args, (cudaStream_t)stream);
 }
 
@@ -251,8 +260,16 @@ int nsa_cache_append(const void* k_new, const void* v_new, void* K, void* V, voi
                      int t_new, int filled, int max_len, int nc_alloc, int nb_alloc, int cmp_block, int cmp_stride, int sel_block,
                      int dtype, nsa_stream_t stream) {
   NSA_REQUIRE(k_new && v_new && K && V && Kc && Vc && Kb, NSA_ERR_ARG, "cache append: NULL pointer");
-  return cache_append(k_new, v_new, K, V, Kc, Vc, Kb, B, Hkv, D, t_new, filled, max_len, nc_alloc, nb_alloc, cmp_block, cmp_stride,
-                      sel_block, dtype, (cudaStream_t)stream);
+  return cache_append(k_new, v_new, K, V, Kc, Vc, Kb, B, Hkv, D, t_new, filled, nullptr, max_len, nc_alloc, nb_alloc, cmp_block,
+                      cmp_stride, sel_block, dtype, (cudaStream_t)stream);
+}
+
+int nsa_cache_append_dev(const void* k_new, const void* v_new, void* K, void* V, void* Kc, void* Vc, void* Kb, int B, int Hkv, int D,
+                         int t_new, int32_t* filled, int max_len, int nc_alloc, int nb_alloc, int cmp_block, int cmp_stride,
+                         int sel_block, int dtype, nsa_stream_t stream) {
+  NSA_REQUIRE(k_new && v_new && K && V && Kc && Vc && Kb && filled, NSA_ERR_ARG, "cache append: NULL pointer");
+  return cache_append(k_new, v_new, K, V, Kc, Vc, Kb, B, Hkv, D, t_new, 0, filled, max_len, nc_alloc, nb_alloc, cmp_block,
+                      cmp_stride, sel_block, dtype, (cudaStream_t)stream);
 }
 
 int nsa_memcpy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t row_bytes, size_t rows,

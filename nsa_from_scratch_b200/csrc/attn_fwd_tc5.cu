@@ -127,20 +127,36 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
 
   auto bar = [&](int id) { return smem_u32(&bars[id]); };
 
+  // Length-dependent launch parameters.  Split (decoding) launches may take the number of filled key positions
+  // from device memory (a.dyn_len), so that a captured CUDA graph of a decoding step stays valid as the cache
+  // grows; everything else reads the launch parameters as they are.
+  int dyn_off = 0, dyn_cmp_off = 0, dyn_sel_lim = 0;
+  if constexpr (SPLIT) {
+    if (a.dyn_len != nullptr) {
+      const int len = *a.dyn_len;
+      dyn_off = len - a.Tq;
+      dyn_cmp_off = (a.cmp_stride == a.cmp_block ? (len + a.cmp_block - 1) / a.cmp_block * a.cmp_block : len) - a.Tq;
+      dyn_sel_lim = (len + 63) / 64 * 64;
+    }
+  }
+  auto OFFSET = [&]() { if constexpr (SPLIT) return a.dyn_len != nullptr ? dyn_off : a.offset; else return a.offset; };
+  auto CMP_OFFSET = [&]() { if constexpr (SPLIT) return a.dyn_len != nullptr ? dyn_cmp_off : a.cmp_offset; else return a.cmp_offset; };
+  auto SEL_LIMIT = [&]() { if constexpr (SPLIT) return a.dyn_len != nullptr ? dyn_sel_lim : a.sel_key_limit; else return a.sel_key_limit; };
+
   // ---- per-branch key bounds of a query row -------------------------------------------
   auto bounds = [&](int br, int i, bool ok, int& lo, int& hi) {
     lo = 0; hi = -1;
     if (!ok) return;
     if (br == 0) {
       if (a.causal) {
-        int num = i + a.cmp_offset - (a.cmp_block - 1);
+        int num = i + CMP_OFFSET() - (a.cmp_block - 1);
         hi = num < 0 ? -1 : num / a.cmp_stride;
       } else hi = a.Nc - 1;
       hi = min(hi, a.Nc - 1);
     } else if (br == 1) {
-      hi = a.causal ? min(i + a.offset, a.sel_key_limit - 1) : a.sel_key_limit - 1;
+      hi = a.causal ? min(i + OFFSET(), SEL_LIMIT() - 1) : SEL_LIMIT() - 1;
     } else {
-      int pos = i + a.offset;
+      int pos = i + OFFSET();
       if (a.causal) { lo = pos - a.window + 1; hi = pos; }
       else { lo = pos - a.window; hi = pos + a.window; }
       lo = max(lo, 0); hi = min(hi, a.Tk - 1);
@@ -175,8 +191,8 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
         if (qb < a.nq) {
           const int hi_ = (a.Hi == a.H) ? grp_head(g) : hk;
           blk = a.idx[(((size_t)b * a.Hi + hi_) * a.nq + qb) * a.top_k + sl];
-          const int last_pos = min(qb * 64 + 64, a.Tq) - 1 + a.offset;
-          if (blk < 0 || blk >= p.nk_blocks || (a.causal && (long long)blk * 64 > last_pos)) blk = -1;
+          const int last_pos = min(qb * 64 + 64, a.Tq) - 1 + OFFSET();
+          if (blk < 0 || blk >= SEL_LIMIT() / 64 || (a.causal && (long long)blk * 64 > last_pos)) blk = -1;
         }
         ent_blk[i] = blk;
       }
@@ -256,7 +272,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
       int ci = min(2 * t + c, nchunks[br] - 1);
       tl.mask[c] = 0xF;
       if (br == 0) { tl.j0[c] = ci * 64; tl.jlim[c] = a.Nc; }
-      else if (br == 1) { int blk = sel_list[ci]; tl.j0[c] = blk * 64; tl.jlim[c] = min(blk * 64 + 64, a.sel_key_limit); tl.mask[c] = sel_mask[ci]; }
+      else if (br == 1) { int blk = sel_list[ci]; tl.j0[c] = blk * 64; tl.jlim[c] = min(blk * 64 + 64, SEL_LIMIT()); tl.mask[c] = sel_mask[ci]; }
       else { tl.j0[c] = (sld_c0 + ci) * 64; tl.jlim[c] = a.Tk; }
     }
     return tl;
@@ -929,8 +945,10 @@ int attention_fwd_tc5(const nsa_fwd_args& a, cudaStream_t st) {
   p.NQG = (p.a.nq + 4 / p.GH - 1) / (4 / p.GH);
   const long long items = (long long)p.NQG * a.B * a.Hkv * p.HG;
   // split launch: asked for by the caller (who supplies the scratch), fused bf16/fp16 forward only
-  const bool split = a.nsplit > 1 && a.fused && !in8;
-  p.nsplit = split ? a.nsplit : 1;
+  const bool split = (a.nsplit > 1 || a.dyn_len != nullptr) && a.fused && !in8;
+  NSA_REQUIRE(a.dyn_len == nullptr || (split && a.causal), NSA_ERR_UNSUPPORTED,
+              "attention forward: a device-resident length needs a fused, causal launch with 16-bit storage");
+  p.nsplit = split ? (a.nsplit > 1 ? a.nsplit : 1) : 1;
   p.part = split ? reinterpret_cast<float*>(a.split_scratch) : nullptr;
   const long long rows = (long long)a.B * a.H * a.Tq;
   if (split) {

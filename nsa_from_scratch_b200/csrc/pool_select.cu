@@ -77,9 +77,22 @@ __global__ void __launch_bounds__(256) cache_append_kernel(const T* __restrict__
                                                            T* __restrict__ K, T* __restrict__ V, T* __restrict__ Kc,
                                                            T* __restrict__ Vc, T* __restrict__ Kb, int D, int t_new,
                                                            int filled, int max_len, int nc_alloc, int nb_alloc, int cblock,
-                                                           int cstride, int c0, int nw, int sblock, int b0, int nbk) {
+                                                           int cstride, int c0, int nw, int sblock, int b0, int nbk,
+                                                           const int32_t* __restrict__ dyn_filled) {
   const int CH = D / 8;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (dyn_filled != nullptr) {
+    // fill count in device memory (a captured graph replays this launch as the cache grows): the window and block
+    // ranges are derived here; the grid was sized for the largest they can be
+    filled = *dyn_filled;
+    const int T1d = filled + t_new;
+    if (T1d > max_len) return;                             // the host refuses this before launching; never write past the end
+    auto n_pooled = [&](int T) { return cstride == cblock ? (T + cblock - 1) / cblock : (T >= cblock ? (T - cblock) / cstride + 1 : 0); };
+    c0 = cstride == cblock ? filled / cblock : n_pooled(filled);
+    nw = min(n_pooled(T1d), nc_alloc) - c0;
+    b0 = filled / sblock;
+    nbk = min((T1d + sblock - 1) / sblock, nb_alloc) - b0;
+  }
   const long long items = (long long)t_new + nw + nbk;
   if (i >= items * CH) return;
   const int item = (int)(i / CH), ch = (int)(i % CH);
@@ -128,10 +141,17 @@ __global__ void __launch_bounds__(256) cache_append_kernel(const T* __restrict__
   }
 }
 
+__global__ void cache_advance_kernel(int32_t* filled, int t_new, int max_len) {
+  if (threadIdx.x == 0 && blockIdx.x == 0 && *filled + t_new <= max_len) *filled += t_new;
+}
+
+// `filled_dev` != NULL: the fill count lives in device memory; it is read by the append launch and advanced by a
+// second, one-thread launch behind it (`filled` is then ignored).
 int cache_append(const void* k_new, const void* v_new, void* K, void* V, void* Kc, void* Vc, void* Kb, int B, int Hkv, int D,
-                 int t_new, int filled, int max_len, int nc_alloc, int nb_alloc, int cblock, int cstride, int sblock, int dtype,
-                 cudaStream_t st) {
+                 int t_new, int filled, int32_t* filled_dev, int max_len, int nc_alloc, int nb_alloc, int cblock, int cstride,
+                 int sblock, int dtype, cudaStream_t st) {
   NSA_REQUIRE(D % 8 == 0 && D > 0, NSA_ERR_ARG, "cache append: D %d must be a positive multiple of 8", D);
+  if (filled_dev != nullptr) filled = 0;
   NSA_REQUIRE(t_new >= 0 && filled >= 0 && filled + t_new <= max_len, NSA_ERR_ARG,
               "cache append: %d filled + %d new rows exceed the allocation of %d", filled, t_new, max_len);
   NSA_REQUIRE(cblock > 0 && cstride > 0 && cstride <= cblock && sblock > 0, NSA_ERR_ARG, "cache append: bad block sizes");
@@ -140,20 +160,26 @@ int cache_append(const void* k_new, const void* v_new, void* K, void* V, void* K
   const int T0 = filled, T1 = filled + t_new;
   auto n_pooled = [&](int T) { return cstride == cblock ? (T + cblock - 1) / cblock : (T >= cblock ? (T - cblock) / cstride + 1 : 0); };
   // windows that contain a new row: whole windows completed by them, or (stride == block) the partial tail window
-  const int c0 = cstride == cblock ? T0 / cblock : n_pooled(T0);
-  const int nw = n_pooled(T1) - c0;
-  const int b0 = T0 / sblock, nbk = (T1 + sblock - 1) / sblock - b0;
-  NSA_REQUIRE(c0 + nw <= nc_alloc && b0 + nbk <= nb_alloc, NSA_ERR_ARG, "cache append: pooled (%d) or block-mean (%d) allocation too small",
-              nc_alloc, nb_alloc);
+  int c0 = cstride == cblock ? T0 / cblock : n_pooled(T0);
+  int nw = n_pooled(T1) - c0;
+  int b0 = T0 / sblock, nbk = (T1 + sblock - 1) / sblock - b0;
+  if (filled_dev != nullptr) {                             // the most windows / blocks t_new rows can touch at any fill count
+    nw = (t_new + cstride - 1) / cstride + 1;
+    nbk = (t_new + sblock - 1) / sblock + 1;
+  } else {
+    NSA_REQUIRE(c0 + nw <= nc_alloc && b0 + nbk <= nb_alloc, NSA_ERR_ARG, "cache append: pooled (%d) or block-mean (%d) allocation too small",
+                nc_alloc, nb_alloc);
+  }
   const long long threads = ((long long)t_new + nw + nbk) * (D / 8);
   dim3 grid((unsigned)((threads + 255) / 256), (unsigned)(B * Hkv));
 #define NSA_APPEND(TT)                                                                                                  \
   cache_append_kernel<TT><<<grid, 256, 0, st>>>((const TT*)k_new, (const TT*)v_new, (TT*)K, (TT*)V, (TT*)Kc, (TT*)Vc, (TT*)Kb, D, \
-                                                t_new, filled, max_len, nc_alloc, nb_alloc, cblock, cstride, c0, nw, sblock, b0, nbk)
+                                                t_new, filled, max_len, nc_alloc, nb_alloc, cblock, cstride, c0, nw, sblock, b0, nbk, filled_dev)
   if (dtype == NSA_BF16) NSA_APPEND(__nv_bfloat16);
   else if (dtype == NSA_FP16) NSA_APPEND(__half);
   else return fail(NSA_ERR_UNSUPPORTED, "cache append: dtype %d", dtype);
 #undef NSA_APPEND
+  if (filled_dev != nullptr) cache_advance_kernel<<<1, 32, 0, st>>>(filled_dev, t_new, max_len);
   return launch_status("cache_append");
 }
 
@@ -201,8 +227,11 @@ template <typename T, int D>
 __global__ void __launch_bounds__(256) select_blocks_kernel(const T* __restrict__ Qb, const T* __restrict__ Kb,
                                                             int32_t* __restrict__ idx, int H, int Hkv, int Hi, int nq, int nk,
                                                             int k_out, int bm, int bn, int offset, int causal, float scale,
-                                                            int force_first, int force_local, int R) {
+                                                            int force_first, int force_local, int R,
+                                                            const int32_t* __restrict__ dyn_len) {
   constexpr int KT = 64;
+  // key length in device memory (decoding under a captured graph): the padded-length offset of the block grid
+  if (dyn_len != nullptr) offset = (*dyn_len + bn - 1) / bn * bn - ((nq * bm + bm - 1) / bm) * bm;
   constexpr int PITCH = D + 8;     // 16-bit elements; 16-byte aligned rows, 17-chunk stride -> conflict-free 128-bit reads
   // The block's 8 warps cover R query blocks x CW = 8/R tiles of 64 key blocks at a time: with many query
   // blocks R = 8 and a warp owns a row; with few (decoding: one) the warps share a row and take different key
@@ -306,7 +335,8 @@ __global__ void __launch_bounds__(256) select_blocks_kernel(const T* __restrict_
 
 template <typename T>
 static int select_launch(const void* Qb, const void* Kb, int32_t* idx, int B, int H, int Hkv, int Hi, int nq, int nk, int D,
-                         int k_out, int bm, int bn, int offset, int causal, float scale, int ff, int fl, cudaStream_t st) {
+                         int k_out, int bm, int bn, int offset, int causal, float scale, int ff, int fl, const int32_t* dyn_len,
+                         cudaStream_t st) {
   // R query blocks per thread block (a power of two <= 8): no more than there are, fewer if the score rows
   // would not fit; the other 8/R warps of a row group take further key tiles
   int R = 8;
@@ -321,7 +351,7 @@ static int select_launch(const void* Qb, const void* Kb, int32_t* idx, int B, in
     auto fn = select_blocks_kernel<T, DD>;                                                              \
     NSA_CUDA_OK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));      \
     fn<<<grid, 256, smem, st>>>((const T*)Qb, (const T*)Kb, idx, H, Hkv, Hi, nq, nk, k_out, bm, bn, offset, \
-                                causal, scale, ff, fl, R);                                              \
+                                causal, scale, ff, fl, R, dyn_len);                                     \
   }
   switch (D) {
     case 32: NSA_SEL(32) break;
@@ -335,7 +365,7 @@ static int select_launch(const void* Qb, const void* Kb, int32_t* idx, int B, in
 
 int select_blocks(const void* Qb, const void* Kb, int32_t* idx, int B, int H, int Hkv, int nq, int nk, int D, int top_k,
                   int bm, int bn, int offset, int causal, float scale, int ff, int fl, int shared, int dtype,
-                  cudaStream_t st) {
+                  const int32_t* dyn_len, cudaStream_t st) {
   const int Hi = shared ? Hkv : H;
   NSA_REQUIRE(B > 0 && H > 0 && Hkv > 0 && H % Hkv == 0, NSA_ERR_ARG, "select: heads %d/%d", H, Hkv);
   NSA_REQUIRE(nq > 0 && nk > 0 && top_k > 0 && bm > 0 && bn > 0, NSA_ERR_ARG, "select: empty problem");
@@ -343,9 +373,9 @@ int select_blocks(const void* Qb, const void* Kb, int32_t* idx, int B, int H, in
   NSA_REQUIRE(ff >= 0 && fl >= 0, NSA_ERR_ARG, "select: negative forced-block counts");
   int k_out = top_k < nk ? top_k : nk;
   if (dtype == NSA_BF16)
-    return select_launch<__nv_bfloat16>(Qb, Kb, idx, B, H, Hkv, Hi, nq, nk, D, k_out, bm, bn, offset, causal, scale, ff, fl, st);
+    return select_launch<__nv_bfloat16>(Qb, Kb, idx, B, H, Hkv, Hi, nq, nk, D, k_out, bm, bn, offset, causal, scale, ff, fl, dyn_len, st);
   if (dtype == NSA_FP16)
-    return select_launch<__half>(Qb, Kb, idx, B, H, Hkv, Hi, nq, nk, D, k_out, bm, bn, offset, causal, scale, ff, fl, st);
+    return select_launch<__half>(Qb, Kb, idx, B, H, Hkv, Hi, nq, nk, D, k_out, bm, bn, offset, causal, scale, ff, fl, dyn_len, st);
   return fail(NSA_ERR_UNSUPPORTED, "select: dtype %d", dtype);
 }
 

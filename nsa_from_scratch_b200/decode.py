@@ -41,6 +41,7 @@ class KVCache:
         self.Kc, self.Vc = z(max(1, self.n_pooled(max_len))), z(max(1, self.n_pooled(max_len)))
         self.Kb = z(_cdiv(max_len, self.bn))
         self.length = 0
+        self.filled_dev: Optional[Tensor] = None    # device copy of `length`, kept once a GraphedDecoder asks for it
 
     def n_pooled(self, T: int) -> int:
         if self.stride == self.bc:
@@ -48,7 +49,12 @@ class KVCache:
         return 0 if T < self.bc else (T - self.bc) // self.stride + 1
 
     def reset(self) -> None:
-        self.length = 0
+        self._set_length(0)
+
+    def _set_length(self, n: int) -> None:
+        self.length = n
+        if self.filled_dev is not None:
+            self.filled_dev.fill_(n)
 
     def append(self, k: Tensor, v: Tensor) -> None:
         """k, v [B,Hkv,t,D]: the next t positions."""
@@ -66,7 +72,7 @@ class KVCache:
                                               self.Vc.data_ptr(), self.Kb.data_ptr(), B, Hkv, D, t, T0, self.max_len,
                                               self.Kc.shape[2], self.Kb.shape[2], self.bc, self.stride, self.bn,
                                               L.dtype_code(self.K.dtype), L.stream_ptr()), "nsa_cache_append")
-        self.length = T1
+        self._set_length(T1)
 
 
 def _split_ways(B: int, H: int, Hkv: int, Tq: int, n_pooled: int) -> int:
@@ -105,4 +111,76 @@ def nsa_decode(q: Tensor, cache: KVCache, *, gate_logits: Optional[Tensor] = Non
     return out
 
 
-__all__ = ["KVCache", "nsa_decode"]
+class GraphedDecoder:
+    """A decoding step -- append the new keys/values, block means of the new queries, selection, split attention
+    launch and merge -- captured once into a CUDA graph and replayed for every step.  The cache's fill count
+    lives in device memory and every length-dependent quantity is derived there, so the same graph serves the
+    whole generation.  Fill `q`, `k`, `v` (and `gate_logits`) in place, call `step()`, read `out`."""
+
+    def __init__(self, cache: KVCache, n_heads: int, *, tokens_per_step: int = 1, gates: bool = True,
+                 nsplit: Optional[int] = None):
+        cfg = cache.cfg
+        B, Hkv, _, D = cache.K.shape
+        dev, dt = cache.K.device, cache.K.dtype
+        self.cache, self.t = cache, int(tokens_per_step)
+        self.q = torch.zeros((B, n_heads, self.t, D), dtype=dt, device=dev)
+        self.k = torch.zeros((B, Hkv, self.t, D), dtype=dt, device=dev)
+        self.v = torch.zeros((B, Hkv, self.t, D), dtype=dt, device=dev)
+        self.gate_logits = torch.zeros((B, n_heads, self.t, 3), dtype=torch.float32, device=dev) if gates else None
+        if cache.filled_dev is None:
+            cache.filled_dev = torch.full((1,), cache.length, dtype=torch.int32, device=dev)
+        # the grid is part of the graph: split as for a full cache
+        self.nsplit = _split_ways(B, n_heads, Hkv, self.t, cache.n_pooled(cache.max_len)) if nsplit is None else int(nsplit)
+        self.scale = float(cfg.scale if cfg.scale is not None else 1.0 / (D ** 0.5))
+        start = cache.length
+        if start + self.t > cache.max_len:
+            raise ValueError("GraphedDecoder: the cache has no room for a step")
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):                     # warm-up steps write past the filled rows; the count is put back
+                self._launches()
+                cache.filled_dev.fill_(start)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.out = self._launches()
+        cache.filled_dev.fill_(start)              # capturing runs nothing; be explicit all the same
+
+    def _launches(self) -> Tensor:
+        c, cfg = self.cache, self.cache.cfg
+        B, Hkv, _, D = c.K.shape
+        H = self.q.shape[1]
+        bm = int(cfg.block_size_m)
+        lib = L.load()
+        with torch.cuda.device(c.K.device):
+            L.check(lib.nsa_cache_append_dev(self.k.data_ptr(), self.v.data_ptr(), c.K.data_ptr(), c.V.data_ptr(), c.Kc.data_ptr(),
+                                             c.Vc.data_ptr(), c.Kb.data_ptr(), B, Hkv, D, self.t, c.filled_dev.data_ptr(), c.max_len,
+                                             c.Kc.shape[2], c.Kb.shape[2], c.bc, c.stride, c.bn, L.dtype_code(c.K.dtype),
+                                             L.stream_ptr()), "nsa_cache_append_dev")
+            Qb = ops.pool_mean(self.q, bm, bm)
+            shared = bool(_cfg(cfg, "select_per_group", False))
+            nq = Qb.shape[2]
+            idx = torch.empty((B, Hkv if shared else H, nq, min(cfg.top_k, c.Kb.shape[2])), device=c.K.device, dtype=torch.int32)
+            L.check(lib.nsa_select_blocks_cached(Qb.data_ptr(), c.Kb.data_ptr(), idx.data_ptr(), B, H, Hkv, nq, c.Kb.shape[2], D,
+                                                 cfg.top_k, bm, c.bn, c.filled_dev.data_ptr(), self.scale,
+                                                 _cfg(cfg, "force_first", 0), _cfg(cfg, "force_local", 0), int(shared),
+                                                 L.dtype_code(Qb.dtype), L.stream_ptr()), "nsa_select_blocks_cached")
+        out, _ = ops.attention_fwd(
+            self.q, c.K, c.V, branches=L.BRANCH_COMPRESSED | L.BRANCH_SELECTED | L.BRANCH_SLIDING, fused=True, causal=True,
+            scale=self.scale, Kc=c.Kc, Vc=c.Vc, cmp_block=c.bc, cmp_stride=c.stride, cmp_offset=0, idx=idx, bm=bm, bn=c.bn,
+            window=cfg.window_size, gates=self.gate_logits,
+            gate_act=L.GATE_SOFTMAX if cfg.gate_activation == "softmax" else L.GATE_SIGMOID, offset=0,
+            nsplit=self.nsplit, dyn_len=c.filled_dev)
+        return out
+
+    def step(self) -> Tensor:
+        c = self.cache
+        if c.length + self.t > c.max_len:
+            raise ValueError(f"GraphedDecoder: {c.length} + {self.t} rows exceed the allocation of {c.max_len}")
+        self.graph.replay()
+        c.length += self.t                         # the device count was advanced by the graph
+        return self.out
+
+
+__all__ = ["KVCache", "nsa_decode", "GraphedDecoder"]

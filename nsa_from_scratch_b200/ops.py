@@ -96,13 +96,14 @@ def attention_fwd(
     cmp_offset: int = 0, idx: Optional[Tensor] = None, bm: int = 64, bn: int = 64, window: int = 0,
     gates: Optional[Tensor] = None, gate_act: int = L.GATE_SIGMOID, offset: Optional[int] = None,
     q_scale: float = 1.0, k_scale: float = 1.0, v_scale: float = 1.0, engine: Optional[int] = None,
-    want_lse: bool = True, token_major: bool = False, nsplit: int = 1,
+    want_lse: bool = True, token_major: bool = False, nsplit: int = 1, dyn_len: Optional[Tensor] = None,
 ) -> Tuple[Tensor, Optional[Tensor]]:
     """One launch of nsa_attention_fwd.  Returns (out, lse); lse is None for fused launches.
     `token_major`: gates are [B,Tq,H,3] and the result comes back as [B,Tq,H,D] (Q, K, V stay
     [B,H,T,D]) -- the layouts on either side of the call in the reference's attention module.
     `nsplit` > 1 (fused launches): each work item's key tiles are spread over that many thread blocks, for
-    launches with few query blocks and long key ranges (decoding)."""
+    launches with few query blocks and long key ranges (decoding).  `dyn_len`: int32 device scalar with the
+    number of filled key positions; K/V/Kc/Vc are then allocations and every offset is derived on the device."""
     _need_cuda(Q, K, V)
     B, H, Tq, D = Q.shape
     Hkv, Tk = K.shape[1], K.shape[2]
@@ -148,10 +149,16 @@ def attention_fwd(
         if gates.shape != want:
             raise ValueError(f"gate_logits shape {tuple(gates.shape)} != {want}")
         a.gates, a.gate_dtype = gates.data_ptr(), L.dtype_code(gates.dtype)
-    if fused and nsplit > 1 and Q.dtype in _16:
+    if fused and (nsplit > 1 or dyn_len is not None) and Q.dtype in _16:
+        nsplit = max(1, int(nsplit))
         scratch = torch.empty((B * H * Tq * nsplit * 3 * (D + 4),), device=Q.device, dtype=torch.float32)
         keep.append(scratch)
-        a.nsplit, a.split_scratch, a.split_scratch_bytes = int(nsplit), scratch.data_ptr(), scratch.numel() * 4
+        a.nsplit, a.split_scratch, a.split_scratch_bytes = nsplit, scratch.data_ptr(), scratch.numel() * 4
+    if dyn_len is not None:
+        if dyn_len.dtype != torch.int32 or not dyn_len.is_cuda or dyn_len.numel() != 1:
+            raise ValueError("dyn_len must be a one-element int32 CUDA tensor")
+        keep.append(dyn_len)
+        a.dyn_len = dyn_len.data_ptr()
     with torch.cuda.device(Q.device):
         L.check(L.load().nsa_attention_fwd(C.byref(a), L.stream_ptr()), "nsa_attention_fwd")
     return out, lse

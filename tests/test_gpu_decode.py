@@ -84,6 +84,41 @@ def test_split_launch_vs_oracle_and_unsplit(nsa, D, dtype, nsplit):
     ops.device_status()
 
 
+@pytest.mark.parametrize("cfg_name", list(CFGS))
+def test_graphed_decoder_equals_eager_steps(nsa, cfg_name):
+    """The decoding step as one CUDA graph with the fill count in device memory: 70 replays (crossing
+    compression-window and selection-block boundaries) against eager steps on a second cache."""
+    kw = CFGS[cfg_name]
+    B, H, Hkv, D, T0, steps = 2, 8, 2, 128, 150, 70
+    Q, K, V, g = make_qkv(53, B, H, Hkv, T0 + steps, T0 + steps, D)
+    gates = torch.randn(B, H, T0 + steps, 3, generator=g)
+    cfg = nsa.NSAConfig(**kw)
+    Qc, Kc, Vc, Gc = Q.cuda(), K.cuda(), V.cuda(), gates.cuda()
+    ca, cb = nsa.KVCache(B, Hkv, D, 256, cfg), nsa.KVCache(B, Hkv, D, 256, cfg)
+    ca.append(Kc[:, :, :T0], Vc[:, :, :T0])
+    cb.append(Kc[:, :, :T0], Vc[:, :, :T0])
+    dec = nsa.GraphedDecoder(ca, H, nsplit=3)
+    assert ca.length == T0 and int(ca.filled_dev.item()) == T0
+    for t in range(T0, T0 + steps):
+        dec.q.copy_(Qc[:, :, t:t + 1]); dec.k.copy_(Kc[:, :, t:t + 1]); dec.v.copy_(Vc[:, :, t:t + 1])
+        dec.gate_logits.copy_(Gc[:, :, t:t + 1])
+        out = dec.step()
+        cb.append(Kc[:, :, t:t + 1], Vc[:, :, t:t + 1])
+        ref = nsa.nsa_decode(Qc[:, :, t:t + 1], cb, gate_logits=Gc[:, :, t:t + 1], nsplit=3)
+        assert torch.equal(out, ref), (t, max_abs(out, ref))
+    assert ca.length == T0 + steps == int(ca.filled_dev.item())
+    n = ca.n_pooled(ca.length)
+    assert torch.equal(ca.Kc[:, :, :n], cb.Kc[:, :, :n]) and torch.equal(ca.Kb, cb.Kb) and torch.equal(ca.K, cb.K)
+    # eager use of the same cache keeps the device count current
+    ca.reset()
+    assert int(ca.filled_dev.item()) == 0
+    with pytest.raises(ValueError):
+        ca.length = 256
+        dec.step()
+    from nsa_from_scratch_b200 import ops
+    ops.device_status()
+
+
 def test_chunked_prefill_equals_full_forward(nsa):
     """Block-aligned chunks through the cache reproduce the rows of one full-sequence forward."""
     B, H, Hkv, T, D = 1, 8, 2, 512, 128
