@@ -191,28 +191,46 @@ __device__ __forceinline__ bool better(float v, int c, float bv, int bc) { retur
 
 __device__ void warp_topk_row(float* s, int n_scan, int nk, int k_out, int32_t* out_row, int lane) {
   const uint32_t TAKEN = 0xFFFFFFFFu;
-  int filled = 0;
+  const int NONE = 0x7fffffff;
   const int n_pick = min(k_out, n_scan);
+  // Lane L owns the elements L, L+32, L+64, ... and remembers the best of them.  A round picks the best of the 32
+  // remembered candidates (shuffle arg-max); only the owner of the picked element needs a new candidate, and the
+  // whole warp finds it: one strided element per lane, another shuffle arg-max.
+  float bv = -INFINITY;
+  int bc = NONE;
+#pragma unroll 4
+  for (int c = lane; c < n_scan; c += 32) {
+    const float v = s[c];
+    if (bc == NONE || v > bv) { bv = v; bc = c; }
+  }
   for (int it = 0; it < n_pick; ++it) {
-    float bv = -INFINITY;
-    int bc = 0x7fffffff;
-    for (int c = lane; c < n_scan; c += 32) {
-      float v = s[c];
-      if (__float_as_uint(v) == TAKEN) continue;
-      if (bc == 0x7fffffff || v > bv) { bv = v; bc = c; }
+    float gv = bv;
+    int gc = bc;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, gv, off);
+      const int oc = __shfl_xor_sync(0xffffffffu, gc, off);
+      if (oc != NONE && (gc == NONE || better(ov, oc, gv, gc))) { gv = ov; gc = oc; }
+    }
+    if (lane == 0) { out_row[it] = gc; s[gc] = __uint_as_float(TAKEN); }
+    __syncwarp();
+    const int owner = gc & 31;
+    float rv = -INFINITY;
+    int rc = NONE;
+    for (int c = owner + 32 * lane; c < n_scan; c += 32 * 32) {
+      const float v = s[c];
+      if (__float_as_uint(v) != TAKEN && (rc == NONE || better(v, c, rv, rc))) { rv = v; rc = c; }
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
-      float ov = __shfl_xor_sync(0xffffffffu, bv, off);
-      int oc = __shfl_xor_sync(0xffffffffu, bc, off);
-      if (oc != 0x7fffffff && (bc == 0x7fffffff || better(ov, oc, bv, bc))) { bv = ov; bc = oc; }
+      const float ov = __shfl_xor_sync(0xffffffffu, rv, off);
+      const int oc = __shfl_xor_sync(0xffffffffu, rc, off);
+      if (oc != NONE && (rc == NONE || better(ov, oc, rv, rc))) { rv = ov; rc = oc; }
     }
-    if (lane == 0) { out_row[it] = bc; s[bc] = __uint_as_float(TAKEN); }
-    __syncwarp();
-    ++filled;
+    if (lane == owner) { bv = rv; bc = rc; }
   }
   // fewer candidates than slots: the remaining slots take the lowest block ids not scanned
-  for (int it = filled + lane; it < k_out; it += 32) out_row[it] = n_scan + (it - filled);
+  for (int it = n_pick + lane; it < k_out; it += 32) out_row[it] = n_scan + (it - n_pick);
   (void)nk;
 }
 
