@@ -73,3 +73,18 @@ def test_compat_shim_maps_reference_module_names():
     assert ns.selected_attention.__module__.startswith("nsa_from_scratch_b200")
     ext = nc._get_ext()
     assert hasattr(ext, "selected_attention_fwd_cuda") and hasattr(ext, "selected_attention_bwd_cuda")
+
+
+def test_host_pipeline_chunking_rules():
+    """Query chunks of the host-tensor entry point exist only where every block grid lines up at the chunk
+    boundaries; anything else is one chunk."""
+    from nsa_from_scratch_b200.config import NSAConfig
+    from nsa_from_scratch_b200.host import _chunk_rows
+    cfg = NSAConfig(block_size_c=32, stride_c=16, top_k=16, window_size=512)
+    assert _chunk_rows(cfg, 65536, 65536, 16384) == 16384
+    assert _chunk_rows(cfg, 65536, 65536, 10000) == 9984          # rounded down to a multiple of 64
+    assert _chunk_rows(cfg, 65536, 65536, None) == 65536
+    assert _chunk_rows(cfg, 65500, 65500, 16384) == 65500         # ragged tail: one chunk
+    assert _chunk_rows(cfg, 4096, 2048, 1024) == 4096             # more queries than keys: one chunk
+    assert _chunk_rows(NSAConfig(causal=False), 4096, 4096, 1024) == 4096
+    assert _chunk_rows(NSAConfig(block_size_c=96), 768 * 4, 768 * 4, 1000) == 960       # multiples of lcm(64, 96) = 192

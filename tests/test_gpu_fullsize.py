@@ -145,3 +145,66 @@ def test_cfg4_backward_sampled_query_blocks(nsa):
         assert float(dQ.abs().sum()) == float(sum(dQ[:, :, qb * 64:(qb + 1) * 64].abs().sum() for qb in blocks))
         assert max_abs(dK, rK) <= TOL * max(1.0, float(rK.abs().max()))
         assert max_abs(dV, rV) <= TOL * max(1.0, float(rV.abs().max()))
+
+
+@pytest.mark.parametrize("shared", [True, False])
+def test_cfg1_every_row_against_oracle(nsa, shared):
+    """The CPU-runnable configuration in full: B=1, T=4096, Hq=16 sharing Hkv=1, D=64, fp32 N(0,1) inputs
+    (rounded once to bf16 for both sides), compression 32/16, top-16 with block 0 and 2 local blocks forced,
+    window 512, gates = sigmoid of a random-init Linear(D,3) applied to Q.  Every row of every head against
+    the oracle, evaluated in bands of 512 rows; indices exact."""
+    from nsa_from_scratch_b200.forward import _resolve_block_indices
+    B, H, Hkv, T, D = 1, 16, 1, 4096, 64
+    g = torch.Generator().manual_seed(0)
+    Q = torch.randn(B, H, T, D, generator=g)
+    K = torch.randn(B, Hkv, T, D, generator=g)
+    V = torch.randn(B, Hkv, T, D, generator=g)
+    lin = torch.nn.Linear(D, 3, bias=False)
+    with torch.no_grad():
+        lin.weight.copy_((torch.rand(3, D, generator=g) * 2 - 1) / D ** 0.5)       # Linear's default init range
+        Qb, Kb, Vb = Q.to(torch.bfloat16), K.to(torch.bfloat16), V.to(torch.bfloat16)
+        gates = lin(Qb.float())                                                      # [B,H,T,3] logits, fp32
+    cfg = nsa.NSAConfig(block_size_c=32, stride_c=16, top_k=16, window_size=512, force_first=1, force_local=2,
+                        select_per_group=shared)
+    out = nsa.nsa_forward(Qb.cuda(), Kb.cuda(), Vb.cuda(), cfg, gate_logits=gates.cuda()).float().cpu()
+    idx = _resolve_block_indices(Qb.cuda(), Kb.cuda(), block_size_m=64, block_size_n=64, top_k=16, causal=True,
+                                 scale=D ** -0.5, force_first=1, force_local=2, shared_per_group=shared).cpu()
+    ref_idx = O.select_blocks(Qb.float(), Kb.float(), top_k=16, force_first=1, force_local=2, group_shared=shared)
+    assert torch.equal(idx, ref_idx.to(torch.int32))
+    worst = 0.0
+    for r0 in range(0, T, 512):
+        ref = O.nsa_forward(Qb.float(), Kb.float(), Vb.float(), block_size_c=32, stride_c=16, top_k=16, window_size=512,
+                            gate_logits=gates, block_indices=ref_idx, rows=(r0, r0 + 512))
+        worst = max(worst, max_abs(out[:, :, r0:r0 + 512], ref))
+    assert worst <= TOL, worst
+
+
+def test_cfg3_fp8_sampled_tiles_against_oracle(nsa):
+    """FP8 configuration at full length: T=32768, Hq=64, Hkv=4, D=128, N(0,1) values with 0.1 % outliers x20,
+    per-tensor absmax scales, e4m3.  Sampled query tiles against the oracle on the dequantised values
+    (<= 6e-2), indices exact, and the whole output bit-equal to the bf16 path fed the dequantised tensors."""
+    from nsa_from_scratch_b200.forward import _resolve_block_indices
+    B, H, Hkv, T, D = 1, 64, 4, 32768, 128
+    g = torch.Generator().manual_seed(3)
+
+    def noisy(*shape):
+        x = torch.randn(*shape, generator=g)
+        return torch.where(torch.rand(*shape, generator=g) < 1e-3, x * 20, x).to(torch.bfloat16)
+    Q, K, V = noisy(B, H, T, D), noisy(B, Hkv, T, D), noisy(B, Hkv, T, D)
+    gates = torch.randn(B, H, T, 3, generator=g)
+    (q8, sq), (k8, sk), (v8, sv) = (nsa.quantize_to_fp8(t.cuda()) for t in (Q, K, V))
+    cfg = nsa.NSAConfig(block_size_c=32, stride_c=16, top_k=16, window_size=512, force_first=1, force_local=2, select_per_group=True)
+    out8 = nsa.nsa_forward_fp8(q8, k8, v8, sq, sk, sv, cfg, gate_logits=gates.cuda())
+    dq, dk, dv = (t.to(torch.bfloat16) * s for t, s in ((q8, sq), (k8, sk), (v8, sv)))
+    outb = nsa.nsa_forward(dq, dk, dv, cfg, gate_logits=gates.cuda())
+    assert torch.equal(out8, outb)
+    idx = _resolve_block_indices(dq, dk, block_size_m=64, block_size_n=64, top_k=16, causal=True, scale=D ** -0.5,
+                                 force_first=1, force_local=2, shared_per_group=True).cpu()
+    Qd, Kd, Vd = dq.float().cpu(), dk.float().cpu(), dv.float().cpu()
+    out = out8.float().cpu()
+    for qb in (0, 7, 255, 511):
+        ref_idx, ref = _oracle_tile(Qd, Kd, Vd, gates, qb, True)
+        n = ref_idx.shape[-1]
+        assert torch.equal(idx[:, :, qb, :n], ref_idx[:, :, 0].to(torch.int32)), qb
+        err = max_abs(out[:, :, qb * 64:(qb + 1) * 64], ref)
+        assert err <= 6e-2, (qb, err)
