@@ -169,7 +169,8 @@ def test_cfg1_every_row_against_oracle(nsa, shared):
     out = nsa.nsa_forward(Qb.cuda(), Kb.cuda(), Vb.cuda(), cfg, gate_logits=gates.cuda()).float().cpu()
     idx = _resolve_block_indices(Qb.cuda(), Kb.cuda(), block_size_m=64, block_size_n=64, top_k=16, causal=True,
                                  scale=D ** -0.5, force_first=1, force_local=2, shared_per_group=shared).cpu()
-    ref_idx = O.select_blocks(Qb.float(), Kb.float(), top_k=16, force_first=1, force_local=2, group_shared=shared)
+    # the scorer takes its block means in the INPUT dtype (nsa/triton/forward.py:338-347): 16-bit tensors in
+    ref_idx = O.select_blocks(Qb, Kb, top_k=16, force_first=1, force_local=2, group_shared=shared)
     assert torch.equal(idx, ref_idx.to(torch.int32))
     worst = 0.0
     for r0 in range(0, T, 512):
@@ -200,11 +201,13 @@ def test_cfg3_fp8_sampled_tiles_against_oracle(nsa):
     assert torch.equal(out8, outb)
     idx = _resolve_block_indices(dq, dk, block_size_m=64, block_size_n=64, top_k=16, causal=True, scale=D ** -0.5,
                                  force_first=1, force_local=2, shared_per_group=True).cpu()
-    Qd, Kd, Vd = dq.float().cpu(), dk.float().cpu(), dv.float().cpu()
+    Qd, Kd, Vd = dq.cpu(), dk.cpu(), dv.cpu()        # 16-bit, as the scorer's block means are taken in the input dtype
     out = out8.float().cpu()
     for qb in (0, 7, 255, 511):
         ref_idx, ref = _oracle_tile(Qd, Kd, Vd, gates, qb, True)
         n = ref_idx.shape[-1]
         assert torch.equal(idx[:, :, qb, :n], ref_idx[:, :, 0].to(torch.int32)), qb
         err = max_abs(out[:, :, qb * 64:(qb + 1) * 64], ref)
-        assert err <= 6e-2, (qb, err)
+        # with x20 outliers in V single outputs reach tens in magnitude, where one bf16 ulp of the OUTPUT is
+        # already above 6e-2: the bound is 6e-2 plus one output ulp at the tile's largest magnitude
+        assert err <= 6e-2 + 2 ** -8 * float(ref.abs().max()), (qb, err, float(ref.abs().max()))
