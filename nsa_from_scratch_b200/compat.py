@@ -16,7 +16,11 @@ _MAP = {
 }
 
 
-def install() -> None:
+def install(fuse_caller: bool = False) -> None:
+    """`fuse_caller`: also give the reference's attention module (nsa/model/llama_nsa.py:67-96), when it is
+    importable, the token-major forward -- rotary embedding and head-major re-layout in one pass per tensor,
+    gate logits and output in the module's own [B,T,...] layouts -- for CUDA inputs outside autograd; every
+    other call still runs the module's own code."""
     pkg = __name__.rsplit(".", 1)[0]
     try:
         importlib.import_module("nsa")
@@ -36,3 +40,34 @@ def install() -> None:
         sys.modules[name] = mod
         parent, _, leaf = name.rpartition(".")
         setattr(sys.modules[parent], leaf, mod)
+    if fuse_caller:
+        _patch_attention_module(pkg)
+
+
+def _patch_attention_module(pkg: str) -> None:
+    try:
+        llama = importlib.import_module("nsa.model.llama_nsa")
+    except ImportError:
+        return
+    cls = llama.NSAAttention
+    if getattr(cls.forward, "_b200_token_major", False):
+        return
+    import torch
+    layer = importlib.import_module(pkg + ".layer")
+    original = cls.forward
+
+    def forward(self, x, cos, sin):
+        needs_grad = torch.is_grad_enabled() and (x.requires_grad or any(p.requires_grad for p in self.parameters()))
+        if not x.is_cuda or needs_grad or self.nsa_cfg.pool != "mean":
+            return original(self, x, cos, sin)
+        B, T, _ = x.shape
+        H, D = self.cfg.n_heads, self.cfg.head_dim
+        q = self.q_proj(x).view(B, T, H, D)
+        k = self.k_proj(x).view(B, T, H, D)
+        v = self.v_proj(x).view(B, T, H, D)
+        gates = self.gate(x).view(B, T, H, 3)
+        out = layer.nsa_attention_token_major(q, k, v, cos, sin, self.nsa_cfg, gate_logits=gates)
+        return self.o_proj(out.to(x.dtype))
+
+    forward._b200_token_major = True
+    cls.forward = forward

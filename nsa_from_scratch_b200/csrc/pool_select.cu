@@ -189,13 +189,26 @@ int cache_append(const void* k_new, const void* v_new, void* K, void* V, void* K
 // marker that no finite/inf score equals.
 __device__ __forceinline__ bool better(float v, int c, float bv, int bc) { return v > bv || (v == bv && c < bc); }
 
+// (value, index) arg-max over the warp in two redux instructions: scores map to unsigned keys that keep their
+// order (a lane without a candidate holds key 0, below every real score), the largest key wins, and among the
+// lanes holding it the lowest index.
+__device__ __forceinline__ uint32_t order_key(float v) {
+  const uint32_t u = __float_as_uint(v + 0.f);             // -0 and +0 compare equal: both become +0
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ int warp_argmax(float v, int c, int none) {
+  const uint32_t key = c == none ? 0u : order_key(v);
+  const uint32_t best = __reduce_max_sync(0xffffffffu, key);
+  return (int)__reduce_min_sync(0xffffffffu, (uint32_t)((key == best && c != none) ? c : none));
+}
+
 __device__ void warp_topk_row(float* s, int n_scan, int nk, int k_out, int32_t* out_row, int lane) {
   const uint32_t TAKEN = 0xFFFFFFFFu;
   const int NONE = 0x7fffffff;
   const int n_pick = min(k_out, n_scan);
   // Lane L owns the elements L, L+32, L+64, ... and remembers the best of them.  A round picks the best of the 32
-  // remembered candidates (shuffle arg-max); only the owner of the picked element needs a new candidate, and the
-  // whole warp finds it: one strided element per lane, another shuffle arg-max.
+  // remembered candidates; only the owner of the picked element needs a new candidate, and the whole warp
+  // finds it: one strided element per lane, another warp arg-max.
   float bv = -INFINITY;
   int bc = NONE;
 #pragma unroll 4
@@ -204,14 +217,7 @@ __device__ void warp_topk_row(float* s, int n_scan, int nk, int k_out, int32_t* 
     if (bc == NONE || v > bv) { bv = v; bc = c; }
   }
   for (int it = 0; it < n_pick; ++it) {
-    float gv = bv;
-    int gc = bc;
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, gv, off);
-      const int oc = __shfl_xor_sync(0xffffffffu, gc, off);
-      if (oc != NONE && (gc == NONE || better(ov, oc, gv, gc))) { gv = ov; gc = oc; }
-    }
+    const int gc = warp_argmax(bv, bc, NONE);
     if (lane == 0) { out_row[it] = gc; s[gc] = __uint_as_float(TAKEN); }
     __syncwarp();
     const int owner = gc & 31;
@@ -221,13 +227,8 @@ __device__ void warp_topk_row(float* s, int n_scan, int nk, int k_out, int32_t* 
       const float v = s[c];
       if (__float_as_uint(v) != TAKEN && (rc == NONE || better(v, c, rv, rc))) { rv = v; rc = c; }
     }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, rv, off);
-      const int oc = __shfl_xor_sync(0xffffffffu, rc, off);
-      if (oc != NONE && (rc == NONE || better(ov, oc, rv, rc))) { rv = ov; rc = oc; }
-    }
-    if (lane == owner) { bv = rv; bc = rc; }
+    const int nc = warp_argmax(rv, rc, NONE);
+    if (lane == owner) { bc = nc; bv = nc == NONE ? -INFINITY : s[nc]; }
   }
   // fewer candidates than slots: the remaining slots take the lowest block ids not scanned
   for (int it = n_pick + lane; it < k_out; it += 32) out_row[it] = n_scan + (it - n_pick);

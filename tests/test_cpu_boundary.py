@@ -88,3 +88,38 @@ def test_host_pipeline_chunking_rules():
     assert _chunk_rows(cfg, 4096, 2048, 1024) == 4096             # more queries than keys: one chunk
     assert _chunk_rows(NSAConfig(causal=False), 4096, 4096, 1024) == 4096
     assert _chunk_rows(NSAConfig(block_size_c=96), 768 * 4, 768 * 4, 1000) == 960       # multiples of lcm(64, 96) = 192
+
+
+def test_compat_fused_caller_keeps_the_cpu_route():
+    """compat.install(fuse_caller=True) patches the reference's attention module when it is importable; CPU
+    inputs (and anything under autograd) still run the module's own code, bit for bit."""
+    import os
+    import sys
+    ref = os.environ.get("NSA_REFERENCE_CHECKOUT", "/root/reference")
+    if not os.path.isdir(os.path.join(ref, "nsa", "model")):
+        pytest.skip("reference checkout not present")
+    sys.path.insert(0, ref)
+    saved = {k: sys.modules.pop(k) for k in list(sys.modules) if k == "nsa" or k.startswith("nsa.")}   # an earlier shim, if any
+    try:
+        import torch
+        from nsa.model.config import TransformerConfig
+        from nsa.model.llama_dense import _build_rope_cache
+        from nsa.model.llama_nsa import NSAAttention
+        torch.manual_seed(0)
+        cfg = TransformerConfig(n_heads=2, head_dim=32, hidden_size=48, nsa_block_size_c=32, nsa_top_k=2, nsa_window_size=32)
+        mod = NSAAttention(cfg)
+        x = torch.randn(1, 128, 48)
+        cos, sin = _build_rope_cache(128, 32, cfg.rope_theta, "cpu", torch.float32)
+        with torch.no_grad():
+            before = mod(x, cos, sin)
+        from nsa_from_scratch_b200 import compat
+        compat.install(fuse_caller=True)
+        assert getattr(NSAAttention.forward, "_b200_token_major", False)
+        with torch.no_grad():
+            after = mod(x, cos, sin)
+        assert torch.equal(torch.nan_to_num(before), torch.nan_to_num(after))
+    finally:
+        sys.path.remove(ref)
+        for k in [k for k in sys.modules if k == "nsa" or k.startswith("nsa.")]:
+            del sys.modules[k]
+        sys.modules.update(saved)
