@@ -249,17 +249,11 @@ __global__ void __launch_bounds__(NW * 32, 2) selected_bwd_kernel(const __grid_c
         }
         const int key0 = j0 + mt * 16 + g8, key1 = key0 + 8;
         const int key_lim = min(jlim, key_rows);
-        // 16-byte reductions: lanes t4 and t4^1 swap halves, the even one ends up with four consecutive columns
-        // of key0, the odd one with the same four columns of key1 -- half as many atomic instructions as float2
-        const bool odd = t4 & 1;
-        const int key = odd ? key1 : key0;
 #pragma unroll
         for (int d = 0; d < 2 * KS; ++d) {
-          const float sx = odd ? acc[d][0] : acc[d][2], sy = odd ? acc[d][1] : acc[d][3];
-          const float rx = __shfl_xor_sync(0xffffffffu, sx, 1), ry = __shfl_xor_sync(0xffffffffu, sy, 1);
-          const float4 v = odd ? make_float4(rx, ry, acc[d][2], acc[d][3]) : make_float4(acc[d][0], acc[d][1], rx, ry);
-          const int col = d * 8 + (t4 & 2) * 2;
-          if (key < key_lim) atomicAdd(reinterpret_cast<float4*>(dst + (size_t)key * D + col), v);
+          const int col = d * 8 + t4 * 2;
+          if (key0 < key_lim) atomicAdd(reinterpret_cast<float2*>(dst + (size_t)key0 * D + col), make_float2(acc[d][0], acc[d][1]));
+          if (key1 < key_lim) atomicAdd(reinterpret_cast<float2*>(dst + (size_t)key1 * D + col), make_float2(acc[d][2], acc[d][3]));
         }
       }
     }
