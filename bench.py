@@ -589,6 +589,20 @@ def run_sweep(a):
     del q, k, v, gl
     torch.cuda.empty_cache()
 
+    # selection scored from the compressed branch's probabilities instead of block means (default workload)
+    Qs, Ks, Vs, Gs = (t.cuda() for t in make_inputs(b, a.seed))
+    cfg_p = nsa.NSAConfig(block_size_c=b.cmp_block, stride_c=b.cmp_stride, top_k=b.top_k, window_size=b.window,
+                          force_first=1, force_local=2, select_per_group=True, scorer="compressed")
+    ms_sel = timed(lambda: nsa.select_blocks_compressed(Qs, Ks, cfg_p), max(2, a.steps // 2))
+    ms_fwd = timed(lambda: nsa.nsa_forward(Qs, Ks, Vs, cfg_p, gate_logits=Gs), max(2, a.steps // 2))
+    ops.device_status()
+    print(json.dumps({"metric": METRIC, "value": T / (ms_fwd * 1e-3), "unit": UNIT, "ms_per_step": ms_fwd,
+                      "selection_ms": ms_sel,
+                      "config": {"workload": workload_name(b) + " [selection scored from the compressed branch's probabilities]"}}),
+          flush=True)
+    del Qs, Ks, Vs, Gs
+    torch.cuda.empty_cache()
+
     # decoding against a KV cache: one new token per step (keys appended, pooled K/V and block means brought up
     # to date, selection, split attention launch + merge), CUDA-event time per step
     for B, Tk in ((1, 65536), (8, 65536), (1, 8192)):

@@ -83,6 +83,22 @@ int nsa_select_blocks(const void* Qb, const void* Kb, int32_t* idx, int B, int H
                       int force_first, int force_local, int shared_per_group, int dtype,
                       nsa_stream_t stream);
 
+/* Selection scores taken from the compressed branch's attention probabilities (the scorer of the NSA paper):
+ *   scores[b,hi,qb,j] = sum over the rows i of query block qb (64 rows; and, shared_per_group != 0, over the
+ *   H/Hkv query heads of KV head hi) of  sum_c exp(q_i . Kc_c * scale - lse[b,h,i]) * w(c,j),
+ * lse [B,H,Tq] being the compressed branch's log-sum-exp (nsa_attention_fwd, branches = COMPRESSED, fused = 0)
+ * and w(c,j) = |[c*stride, c*stride+block) intersect [j*bn, (j+1)*bn)| / block.  Compressed token c counts for
+ * row i iff c*stride + block - 1 <= i + cmp_offset (or always, causal = 0).  Illegal selection blocks
+ * (j*bn > qb*64 + 63 + sel_offset under causal) come out -inf, forced ones +inf; nsa_topk_from_scores then
+ * gives the indices.  Sums are formed in a fixed order: results repeat bit for bit.
+ * Replaces nothing in the reference, which scores with block means (nsa/triton/forward.py:321-359); the
+ * scores enter its functions through their block_scores= / block_indices= arguments
+ * (nsa/triton/selected.py:195-196). */
+int nsa_cmp_block_scores(const void* Q, const void* Kc, const float* lse, float* scores, int B, int H, int Hkv,
+                         int Tq, int Nc, int D, int nk, int cmp_block, int cmp_stride, int cmp_offset, int bn,
+                         int sel_offset, int causal, float scale, int force_first, int force_local,
+                         int shared_per_group, int dtype, nsa_stream_t stream);
+
 /* Top-k over caller-supplied fp32 scores [BH,nq,nk] with the same legality rule and order.
  * Replaces: _topk_indices_from_scores, nsa/triton/selected.py:153-185. */
 int nsa_topk_from_scores(const float* scores, int32_t* idx, int BH, int nq, int nk, int top_k,

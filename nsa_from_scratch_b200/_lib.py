@@ -77,6 +77,7 @@ PROTOTYPES = {
     "nsa_abi_version": (_i, []),
     "nsa_pool_mean": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "nsa_select_blocks": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp]),
+    "nsa_cmp_block_scores": (_i, [_vp, _vp, _vp, _vp] + [_i] * 13 + [_f, _i, _i, _i, _i, _vp]),
     "nsa_topk_from_scores": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "nsa_attention_fwd": (_i, [C.POINTER(FwdArgs), _vp]),
     "nsa_device_status": (_i, [_vp]),

@@ -25,3 +25,5 @@ class NSAConfig:
     force_local: int = 0             # always select the last n causally legal blocks
     select_per_group: bool = False   # one block list per KV head (shared by its query heads), scored by
                                      # the sum of the heads' scores; False = one list per query head
+    scorer: str = "mean"             # "mean": the reference's block-mean scores; "compressed": probability mass
+                                     # of the compressed branch per selection block (scoring.py)

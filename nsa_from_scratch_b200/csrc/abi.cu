@@ -34,6 +34,8 @@ int bwd_delta(const void*, const void*, float*, long long, int, int, cudaStream_
 int cast_from_f32(const float*, void*, long long, int, cudaStream_t);
 int cache_append(const void*, const void*, void*, void*, void*, void*, void*, int, int, int, int, int, int32_t*, int, int, int, int, int,
                  int, int, cudaStream_t);
+int cmp_block_scores(const void*, const void*, const float*, float*, int, int, int, int, int, int, int, int, int, int, int, int, int, float,
+                     int, int, int, int, cudaStream_t);
 int rope_to_heads(const void*, void*, const void*, const void*, int, int, int, int, int, int, int, cudaStream_t);
 
 static bool is16(int dt) { return dt == NSA_BF16 || dt == NSA_FP16; }
@@ -104,6 +106,15 @@ int nsa_select_blocks_cached(const void* Qb, const void* Kb, int32_t* idx, int B
   NSA_REQUIRE(Qb && Kb && idx && filled, NSA_ERR_ARG, "select (cached): NULL pointer");
   return select_blocks(Qb, Kb, idx, B, H, Hkv, nq, nk_alloc, D, top_k, bm, bn, 0, 1, scale, force_first, force_local,
                        shared_per_group, dtype, filled, (cudaStream_t)stream);
+}
+
+int nsa_cmp_block_scores(const void* Q, const void* Kc, const float* lse, float* scores, int B, int H, int Hkv, int Tq, int Nc,
+                         int D, int nk, int cmp_block, int cmp_stride, int cmp_offset, int bn, int sel_offset, int causal,
+                         float scale, int force_first, int force_local, int shared_per_group, int dtype, nsa_stream_t stream) {
+  NSA_REQUIRE(Q && Kc && lse && scores, NSA_ERR_ARG, "compressed scores: NULL pointer");
+  NSA_REQUIRE(force_first >= 0 && force_local >= 0, NSA_ERR_ARG, "compressed scores: negative forced-block counts");
+  return cmp_block_scores(Q, Kc, lse, scores, B, H, Hkv, Tq, Nc, D, nk, cmp_block, cmp_stride, cmp_offset, bn, sel_offset, causal,
+                          scale, force_first, force_local, shared_per_group, dtype, (cudaStream_t)stream);
 }
 
 int nsa_topk_from_scores(const float* scores, int32_t* idx, int BH, int nq, int nk, int top_k, int bm, int bn,

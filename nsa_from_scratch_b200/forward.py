@@ -157,7 +157,12 @@ def nsa_forward(Q: Tensor, K: Tensor, V: Tensor, cfg, *, gate_logits: Optional[T
         raise NotImplementedError("nsa_forward: only pool='mean' supported")
     stride_c = getattr(cfg, "stride_c", None)
     ff, fl = _cfg(cfg, "force_first", 0), _cfg(cfg, "force_local", 0)
-    if block_indices is None:
+    if block_indices is None and _cfg(cfg, "scorer", "mean") == "compressed":
+        from .scoring import select_blocks_compressed
+        block_indices = select_blocks_compressed(Q, K, cfg)
+    elif block_indices is None:
+        if _cfg(cfg, "scorer", "mean") != "mean":
+            raise ValueError(f"unknown scorer: {cfg.scorer}")
         block_indices = _resolve_block_indices(Q, K, block_size_m=cfg.block_size_m, block_size_n=cfg.block_size_n,
                                                top_k=cfg.top_k, causal=cfg.causal, scale=float(scale),
                                                force_first=ff, force_local=fl,

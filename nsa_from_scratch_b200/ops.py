@@ -79,6 +79,26 @@ def select_blocks_from_means(Qb: Tensor, Kb: Tensor, *, top_k: int, bm: int, bn:
     return idx
 
 
+def cmp_block_scores(Q: Tensor, Kc: Tensor, lse: Tensor, *, nk: int, cmp_block: int, cmp_stride: int, cmp_offset: int,
+                     bn: int, sel_offset: int, causal: bool, scale: float, force_first: int = 0, force_local: int = 0,
+                     shared_per_group: bool = False) -> Tensor:
+    """fp32 [B,H|Hkv,nq,nk] selection scores from the compressed branch's probabilities (lse = its log-sum-exp)."""
+    _need_cuda(Q, Kc, lse)
+    B, H, Tq, D = Q.shape
+    Hkv, Nc = Kc.shape[1], Kc.shape[2]
+    Q, Kc, lse = Q.contiguous(), Kc.contiguous(), lse.float().contiguous()
+    if Kc.dtype != Q.dtype or Q.dtype not in _16:
+        raise TypeError("cmp_block_scores: Q and the pooled K must share a 16-bit dtype")
+    nq = (Tq + 63) // 64
+    scores = torch.empty((B, Hkv if shared_per_group else H, nq, nk), device=Q.device, dtype=torch.float32)
+    with torch.cuda.device(Q.device):
+        L.check(L.load().nsa_cmp_block_scores(Q.data_ptr(), Kc.data_ptr(), lse.data_ptr(), scores.data_ptr(), B, H, Hkv, Tq, Nc, D,
+                                              nk, cmp_block, cmp_stride, cmp_offset, bn, sel_offset, int(causal), float(scale),
+                                              force_first, force_local, int(shared_per_group), L.dtype_code(Q.dtype),
+                                              L.stream_ptr()), "nsa_cmp_block_scores")
+    return scores
+
+
 def topk_from_scores(scores: Tensor, *, top_k: int, bm: int, bn: int, offset: int, causal: bool) -> Tensor:
     _need_cuda(scores)
     B, H, nq, nk = scores.shape

@@ -256,6 +256,55 @@ def select_blocks(Q: Tensor, K: Tensor, *, block_size_m: int = 64, block_size_n:
     return idx
 
 
+def overlap_weights(n_cmp: int, nk: int, block_size_c: int, stride_c: int, block_size_n: int) -> Tensor:
+    """fp32 [n_cmp, nk]: share of compressed token c's window [c*stride, c*stride + block_c) that lies in
+    selection block j = [j*bn, (j+1)*bn), i.e. |overlap| / block_c (exact in fp32 for power-of-two sizes)."""
+    c0 = torch.arange(n_cmp).view(-1, 1) * stride_c
+    j0 = torch.arange(nk).view(1, -1) * block_size_n
+    ov = (torch.minimum(c0 + block_size_c, j0 + block_size_n) - torch.maximum(c0, j0)).clamp(min=0)
+    return ov.float() / float(block_size_c)
+
+
+def compressed_block_scores(Q: Tensor, K: Tensor, *, block_size_c: int = 32, stride_c: Optional[int] = None,
+                            block_size_m: int = 64, block_size_n: int = 64, causal: bool = True,
+                            scale: Optional[float] = None, group_shared: bool = False) -> Tensor:
+    """Selection scores taken from the compressed branch's attention probabilities (the scorer of the NSA
+    paper; parity unpinned -- the reference scores with block means, forward.py:321-359).
+    p[i,c] = softmax over the compressed tokens visible to row i of (q_i . Kc_c) * scale -- the
+    probabilities `compressed_attention` uses; a compressed token hands its probability to the selection
+    blocks its window overlaps, in proportion to the overlap (`overlap_weights`); the score of (query
+    block, selection block) is the sum over the query block's rows -- and, group_shared, over the
+    query heads of the KV head.  fp32 [B,H|Hkv,nq,nk]."""
+    B, H, Tq, D = Q.shape
+    Hkv, Tk = K.shape[1], K.shape[2]
+    G = _group(H, Hkv)
+    stride = block_size_c if stride_c is None else stride_c
+    Kc = pool_mean(K, block_size_c, stride).float()
+    Nc = Kc.shape[2]
+    Tk_pad = Nc * block_size_c if stride == block_size_c else Tk
+    s = _softmax_scale(D, scale)
+    nq = (Tq + block_size_m - 1) // block_size_m
+    nk = (Tk + block_size_n - 1) // block_size_n
+    W = overlap_weights(Nc, nk, block_size_c, stride, block_size_n)
+    i = torch.arange(Tq).view(-1, 1) + (Tk_pad - Tq)
+    c = torch.arange(Nc).view(1, -1)
+    vis = (c * stride + block_size_c - 1 <= i) if causal else torch.ones((Tq, Nc), dtype=torch.bool)
+    out = torch.zeros((B, H, nq, nk), dtype=torch.float32)
+    for h in range(H):
+        sc = torch.matmul(Q[:, h].float(), Kc[:, h // G].transpose(-1, -2)) * s
+        sc = sc.masked_fill(~vis, NEG_INF)
+        p = torch.softmax(sc, dim=-1)
+        p = torch.where(vis.any(-1, keepdim=True), p, torch.zeros_like(p))      # rows without a visible token
+        ps = torch.matmul(p, W)                                                  # [B,Tq,nk]
+        pad = nq * block_size_m - Tq
+        if pad:
+            ps = torch.nn.functional.pad(ps, (0, 0, 0, pad))
+        out[:, h] = ps.view(B, nq, block_size_m, nk).sum(2)
+    if group_shared:
+        out = out.view(B, Hkv, G, nq, nk).sum(2)
+    return out
+
+
 def indices_from_scores(scores: Tensor, *, top_k: int, block_size_m: int, block_size_n: int,
                         Tq: int, Tk: int, causal: bool) -> Tensor:
     """Indices from caller-supplied scores (selected.py:153-185); here the

@@ -546,3 +546,37 @@ def test_full_forward_gradients_vs_oracle(nsa):
     out.backward(w.cuda().to(out.dtype))
     for got, ref_g, nm in zip((Qc.grad, Kc.grad, Vc.grad, Gc.grad), rg, ("dQ", "dK", "dV", "dG")):
         assert max_abs(got, ref_g) <= 3e-2 * max(1.0, float(ref_g.abs().max())), (nm, max_abs(got, ref_g), float(ref_g.abs().max()))
+
+
+# ------------------------------------------------------------------ scorer from the compressed branch's probabilities
+@pytest.mark.parametrize("case", [(1, 8, 2, 512, 512, 128, 32, 16, True), (2, 4, 4, 300, 300, 64, 32, 16, False),
+                                  (1, 4, 1, 256, 640, 64, 64, 64, True), (1, 6, 2, 384, 384, 32, 32, 32, False)])
+def test_compressed_probability_scorer_vs_oracle(nsa, case):
+    """Scores = compressed-attention probability mass per selection block (parity unpinned: the oracle's
+    restatement is the reference here).  Scores within fp32/ex2 noise of the oracle; the indices are exactly the
+    canonical top-k of the kernel's own scores; the forward with them matches the oracle given those indices."""
+    B, H, Hkv, Tq, Tk, D, bc, stride, shared = case
+    Q, K, V, g = make_qkv(61, B, H, Hkv, Tq, Tk, D)
+    cfg = nsa.NSAConfig(block_size_c=bc, stride_c=stride, top_k=3, window_size=96, force_first=1, force_local=1,
+                        select_per_group=shared, scorer="compressed")
+    Qc, Kc, Vc = Q.cuda(), K.cuda(), V.cuda()
+    sc = nsa.compressed_block_scores(Qc, Kc, cfg).cpu()
+    ref = O.compressed_block_scores(Q, K, block_size_c=bc, stride_c=stride, group_shared=shared)
+    nq, nk = ref.shape[-2], ref.shape[-1]
+    legal = O.legal_blocks(nq, nk, 64, 64, nk * 64 - nq * 64)
+    finite = torch.isfinite(sc)
+    assert torch.equal((sc == float("-inf")), (~legal).expand_as(sc))                  # illegal blocks
+    assert bool((finite | (sc == float("inf")) | ~legal).all())
+    assert bool(finite.any())
+    err = (sc - ref)[finite].abs().max()
+    assert float(err) <= 2e-3 * max(1.0, float(ref[finite].abs().max())), float(err)
+    # rows of a query block hand out one unit of probability each (rows without a visible compressed token: none)
+    idx = nsa.select_blocks_compressed(Qc, Kc, cfg).cpu()
+    want = O.topk_canonical(torch.where(legal, sc, torch.full_like(sc, float("-inf"))), 3, legal=legal)
+    assert torch.equal(idx, want)
+    sc2 = nsa.compressed_block_scores(Qc, Kc, cfg).cpu()
+    assert torch.equal(sc, sc2), "scores are not bitwise repeatable"
+    out = nsa.nsa_forward(Qc, Kc, Vc, cfg)
+    o_ref = O.nsa_forward(Q.float(), K.float(), V.float(), block_size_c=bc, stride_c=stride, top_k=3, window_size=96,
+                          block_indices=idx, group_shared=shared)
+    assert max_abs(out, o_ref) <= TOL16

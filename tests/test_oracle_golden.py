@@ -198,3 +198,27 @@ def test_layer_oracle_matches_reference_module(layer_golden):
         ok = torch.isfinite(ref).all(-1)
         assert torch.equal(ok[0], torch.arange(ref.shape[1]) >= kw["block_size_c"] - 1)
         assert float((y - ref)[ok].abs().max()) <= 2e-5, float((y - ref)[ok].abs().max())
+
+
+def test_compressed_probability_scorer_degenerate_cases():
+    """The probability-based scorer has no counterpart in the reference (parity unpinned); its restatement is
+    tied to pinned behaviour through cases that collapse onto it: every query row hands out exactly its
+    softmax mass (1, or 0 without a visible compressed token), and with compression block = stride = selection
+    block the score of a block is the compressed branch's own probability of that block's single token."""
+    g = torch.Generator().manual_seed(7)
+    Q = torch.randn(1, 4, 256, 32, generator=g).to(torch.bfloat16)
+    K = torch.randn(1, 2, 256, 32, generator=g).to(torch.bfloat16)
+    V = torch.zeros(1, 2, 256, 32)
+    V[..., :4] = torch.eye(4).repeat_interleave(64, 0)            # row r carries one-hot(block of r) in its first 4 columns
+    for bc, stride in ((32, 16), (32, 32), (64, 64)):
+        sc = O.compressed_block_scores(Q, K, block_size_c=bc, stride_c=stride)
+        rows_with_token = (torch.arange(256) >= bc - 1).view(4, 64).sum(1).float()      # per query block
+        assert torch.allclose(sc.sum(-1), rows_with_token.expand(1, 4, 4), atol=1e-4)
+        assert float(O.overlap_weights(O.n_pooled(256, bc, stride), 4, bc, stride, 64).sum(1).sub(1).abs().max()) == 0.0
+        gs = O.compressed_block_scores(Q, K, block_size_c=bc, stride_c=stride, group_shared=True)
+        assert torch.allclose(gs, sc.view(1, 2, 2, 4, 4).sum(2), atol=1e-5)
+    # block = stride = 64: pooled token j IS selection block j, and attention over V = one-hot(block) returns the
+    # per-row probabilities of the compressed branch
+    sc = O.compressed_block_scores(Q, K, block_size_c=64, stride_c=64)
+    probs = O.compressed_attention(Q, K, V, block_size_c=64)[0][..., :4]                  # [1,4,256,4]: p[i, block]
+    assert torch.allclose(sc, probs.view(1, 4, 4, 64, 4).sum(3), atol=1e-5)
