@@ -137,7 +137,10 @@ __global__ void __launch_bounds__(128, 2) cmp_scores_kernel(const CmpScoreK p) {
       // every selection block whose last visible token lies in this tile gathers its tokens, in token order; a block
       // spans at most (bn + block)/stride + 1 <= TN tokens (checked on the host), so they are all in the window
       const int tok_lo = t * TN, tok_hi = tok_lo + TN - 1, base = tok_lo - TN;
-      for (int j = tid; j < p.nk; j += NT) {
+      // only blocks touched by this tile's tokens can end in it
+      const int j_lo = (tok_lo * p.cstride) / p.bn;
+      const int j_hi = min(p.nk - 1, (min(tok_hi, p.Nc - 1) * p.cstride + p.cblock - 1) / p.bn);
+      for (int j = j_lo + tid; j <= j_hi; j += NT) {
         const int c_last = min(min(((j + 1) * p.bn - 1) / p.cstride, p.Nc - 1), n_vis - 1);   // last token starting inside the block
         const int num = j * p.bn - p.cblock + p.cstride;
         const int c_first = num < 0 ? 0 : num / p.cstride;                                     // first token whose window reaches it
