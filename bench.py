@@ -63,6 +63,9 @@ def parse():
     ap.add_argument("--host-chunk", type=int, default=16384,
                     help="query positions per pipeline unit of the host-tensor entry point (0 = whole sequences)")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--protocol", default="contract", choices=["contract", "reference"],
+                    help="reference: the reference benchmark's own protocol (25 warm-up + 100 timed iterations per seed, "
+                         "seeds 0,1,2, one event pair per iteration, pooled mean and a 95 %% percentile-bootstrap interval)")
     return ap.parse_args()
 
 
@@ -669,8 +672,44 @@ def run_sweep(a):
         torch.cuda.empty_cache()
 
 
+def run_reference_protocol(a):
+    """The reference's measurement protocol (nsa/bench/throughput.py:28-48 and its multi-seed pooling): for each of
+    seeds 0, 1, 2: 25 warm-up iterations, 100 timed ones with a CUDA-event pair and a synchronize each; the 300
+    samples are pooled; mean and the 95 % percentile bootstrap of the mean (10000 resamples, generator seed 12345)."""
+    import numpy as np
+    import nsa_from_scratch_b200 as nsa
+    torch.cuda.set_device(0)
+    cfg = nsa.NSAConfig(block_size_c=a.cmp_block, stride_c=a.cmp_stride, top_k=a.top_k, window_size=a.window, force_first=1,
+                        force_local=2, select_per_group=a.select == "group")
+    samples = []
+    for seed in (0, 1, 2):
+        Q, K, V, G = (t.cuda() for t in make_inputs(a, seed))
+        for _ in range(25):
+            nsa.nsa_forward(Q, K, V, cfg, gate_logits=G)
+        torch.cuda.synchronize()
+        for _ in range(100):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            nsa.nsa_forward(Q, K, V, cfg, gate_logits=G)
+            e1.record()
+            torch.cuda.synchronize()
+            samples.append(e0.elapsed_time(e1))
+        del Q, K, V, G
+        torch.cuda.empty_cache()
+    x = np.asarray(samples)
+    rng = np.random.default_rng(12345)
+    means = x[rng.integers(0, len(x), size=(10000, len(x)))].mean(axis=1)
+    lo, hi = np.percentile(means, [2.5, 97.5])
+    print(json.dumps({"metric": METRIC, "value": a.seq_len / (x.mean() * 1e-3), "unit": UNIT, "ms_per_step": float(x.mean()),
+                      "ms_ci95": [float(lo), float(hi)], "tokens_per_s_ci95": [a.seq_len / (hi * 1e-3), a.seq_len / (lo * 1e-3)],
+                      "samples": len(x), "protocol": "25 warm-up + 100 iterations x seeds 0,1,2; pooled mean, percentile bootstrap",
+                      "config": {"workload": workload_name(a)}}), flush=True)
+
+
 def main():
     a = parse()
+    if a.protocol == "reference" and a.impl == "ours":
+        return run_reference_protocol(a)
     if a.sweep:
         return run_sweep(a)
     if a.impl == "reference":
