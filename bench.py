@@ -57,6 +57,7 @@ def parse():
     ap.add_argument("--sweep", action="store_true",
                     help="instead of the single contract line: one JSON line per point of the T x D sweep "
                          "(T = 1k..64k, D = 64/128, Hq=64/Hkv=4) plus the reference's own MHA shape (H=16, D=64, 64/64)")
+    ap.add_argument("--decode", action="store_true", help="only the decoding measurement of --sweep (B=1, 65536 cached)")
     ap.add_argument("--cpu-tiles", type=int, default=40, help="64-row query tiles in the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -606,9 +607,20 @@ def run_sweep(a):
     del Qs, Ks, Vs, Gs
     torch.cuda.empty_cache()
 
-    # decoding against a KV cache: one new token per step (keys appended, pooled K/V and block means brought up
-    # to date, selection, split attention launch + merge), CUDA-event time per step
-    for B, Tk in ((1, 65536), (8, 65536), (1, 8192)):
+    sweep_decode(a)
+
+
+def sweep_decode(a, shapes=((1, 65536), (8, 65536), (1, 8192))):
+    """Decoding against a KV cache: one new token per step (keys appended, pooled K/V and block means brought up
+    to date, selection, split attention launch + merge); one JSON line per (batch, cached length)."""
+    import nsa_from_scratch_b200 as nsa
+    from nsa_from_scratch_b200 import ops
+    torch.cuda.set_device(0)
+    b = a
+    H, Hkv, D = a.heads, a.kv_heads, a.head_dim
+    cfg = nsa.NSAConfig(block_size_c=a.cmp_block, stride_c=a.cmp_stride, top_k=a.top_k, window_size=a.window,
+                        force_first=1, force_local=2, select_per_group=True)
+    for B, Tk in shapes:
         cache = nsa.KVCache(B, Hkv, D, Tk + 256, cfg)
         g = torch.Generator().manual_seed(a.seed)
         for c0 in range(0, Tk - 1, 8192):
@@ -710,6 +722,8 @@ def main():
     a = parse()
     if a.protocol == "reference" and a.impl == "ours":
         return run_reference_protocol(a)
+    if a.decode:
+        return sweep_decode(a, shapes=((1, 65536),))
     if a.sweep:
         return run_sweep(a)
     if a.impl == "reference":
