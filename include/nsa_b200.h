@@ -99,6 +99,17 @@ int nsa_cmp_block_scores(const void* Q, const void* Kc, const float* lse, float*
                          int sel_offset, int causal, float scale, int force_first, int force_local,
                          int shared_per_group, int dtype, nsa_stream_t stream);
 
+/* The same scores on the tcgen05 tensor cores (D in {64,128}, 16-bit storage, 64-token selection blocks' score
+ * rows must fit shared memory; NSA_ERR_UNSUPPORTED otherwise -- use nsa_cmp_block_scores then).  The product is
+ * formed transposed (compressed tokens on the TMEM lanes), so the sum over query rows is a sum over one thread's
+ * registers.  head_scratch: B*H*nq*nk floats the caller provides (per-head block sums before the group sum,
+ * legality and forcing are applied); contents need not be preserved.  Sums are in a fixed order, but not the
+ * order of nsa_cmp_block_scores: the two agree to fp32 rounding, not bit for bit. */
+int nsa_cmp_block_scores_tc(const void* Q, const void* Kc, const float* lse, float* scores, float* head_scratch,
+                            int B, int H, int Hkv, int Tq, int Nc, int D, int nk, int cmp_block, int cmp_stride,
+                            int cmp_offset, int bn, int sel_offset, int causal, float scale, int force_first,
+                            int force_local, int shared_per_group, int dtype, nsa_stream_t stream);
+
 /* Top-k over caller-supplied fp32 scores [BH,nq,nk] with the same legality rule and order.
  * Replaces: _topk_indices_from_scores, nsa/triton/selected.py:153-185. */
 int nsa_topk_from_scores(const float* scores, int32_t* idx, int BH, int nq, int nk, int top_k,
@@ -153,6 +164,11 @@ typedef struct nsa_fwd_args {
    * CUDA graph that is replayed while a KV cache grows.  Needs causal = 1, fused = 1, 16-bit storage, the
    * tcgen05 kernel and the split scratch (nsplit >= 1); NSA_ERR_UNSUPPORTED otherwise. */
   const int32_t* dyn_len;
+  /* Fused launches only.  accumulate != 0: `out` already holds a gated partial sum (an earlier fused launch with
+   * other branches) and this launch adds its branches to it -- the three branches may thus be spread over several
+   * launches, e.g. the compressed branch first when the selection is scored from its probabilities.  tcgen05 kernel
+   * only.  A fused launch of exactly ONE branch may also return that branch's lse (lse != NULL). */
+  int32_t accumulate;
 } nsa_fwd_args;
 
 /* Replaces the kernels behind compressed_attention (nsa/triton/compressed.py:191-300),

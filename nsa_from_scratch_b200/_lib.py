@@ -50,7 +50,7 @@ class FwdArgs(C.Structure):
         ("scale", C.c_float), ("q_scale", C.c_float), ("k_scale", C.c_float), ("v_scale", C.c_float),
         ("engine", C.c_int32), ("io_layout", C.c_int32),
         ("nsplit", C.c_int32), ("split_scratch", C.c_void_p), ("split_scratch_bytes", C.c_int64),
-        ("dyn_len", C.c_void_p),
+        ("dyn_len", C.c_void_p), ("accumulate", C.c_int32),
     ]
 
 
@@ -78,6 +78,7 @@ PROTOTYPES = {
     "nsa_pool_mean": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "nsa_select_blocks": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp]),
     "nsa_cmp_block_scores": (_i, [_vp, _vp, _vp, _vp] + [_i] * 13 + [_f, _i, _i, _i, _i, _vp]),
+    "nsa_cmp_block_scores_tc": (_i, [_vp, _vp, _vp, _vp, _vp] + [_i] * 13 + [_f, _i, _i, _i, _i, _vp]),
     "nsa_topk_from_scores": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "nsa_attention_fwd": (_i, [C.POINTER(FwdArgs), _vp]),
     "nsa_device_status": (_i, [_vp]),

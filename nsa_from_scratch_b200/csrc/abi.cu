@@ -36,6 +36,10 @@ int cache_append(const void*, const void*, void*, void*, void*, void*, void*, in
                  int, int, cudaStream_t);
 int cmp_block_scores(const void*, const void*, const float*, float*, int, int, int, int, int, int, int, int, int, int, int, int, int, float,
                      int, int, int, int, cudaStream_t);
+bool cmp_scores_tc5_supports(int, int, int, int, int, int);
+int cmp_block_scores_tc5(const void*, const void*, const float*, float*, float*, int, int, int, int, int, int, int, int, int, int, int, int,
+                         int, float, int, int, int, int, cudaStream_t);
+int cs5_take_status(int*);
 int rope_to_heads(const void*, void*, const void*, const void*, int, int, int, int, int, int, int, cudaStream_t);
 
 static bool is16(int dt) { return dt == NSA_BF16 || dt == NSA_FP16; }
@@ -58,7 +62,11 @@ static int check_fwd(const nsa_fwd_args& a) {
   } else {
     NSA_REQUIRE(a.gate_act == NSA_GATE_SIGMOID || a.gate_act == NSA_GATE_SOFTMAX, NSA_ERR_ARG, "attention forward: gate activation %d", a.gate_act);
     NSA_REQUIRE(!a.gates || is16(a.gate_dtype) || a.gate_dtype == NSA_FP32, NSA_ERR_UNSUPPORTED, "attention forward: gate dtype %d", a.gate_dtype);
+    NSA_REQUIRE(a.lse == nullptr || br == 1 || br == 2 || br == 4, NSA_ERR_ARG,
+                "attention forward: a fused launch returns an lse only for a single branch (mask %d)", br);
   }
+  NSA_REQUIRE(a.accumulate == 0 || (a.fused && a.nsplit <= 1 && a.dyn_len == nullptr), NSA_ERR_ARG,
+              "attention forward: accumulate needs a fused, unsplit launch");
   if (br & NSA_BRANCH_COMPRESSED) {
     NSA_REQUIRE(a.Nc >= 0 && (a.Nc == 0 || (a.Kc && a.Vc)), NSA_ERR_ARG, "compressed: pooled K/V pointer is NULL");
     NSA_REQUIRE(a.cmp_block > 0 && a.cmp_stride > 0 && a.cmp_stride <= a.cmp_block, NSA_ERR_ARG,
@@ -84,7 +92,7 @@ using namespace nsa;
 extern "C" {
 
 const char* nsa_last_error(void) { return g_err; }
-int nsa_abi_version(void) { return 4; }
+int nsa_abi_version(void) { return 5; }
 
 int nsa_pool_mean(const void* x, void* out, int B, int H, int T, int D, int block, int stride, int n_out, int dtype,
                   float dequant_scale, nsa_stream_t stream) {
@@ -117,6 +125,20 @@ int nsa_cmp_block_scores(const void* Q, const void* Kc, const float* lse, float*
                           scale, force_first, force_local, shared_per_group, dtype, (cudaStream_t)stream);
 }
 
+int nsa_cmp_block_scores_tc(const void* Q, const void* Kc, const float* lse, float* scores, float* head_scratch, int B, int H, int Hkv,
+                            int Tq, int Nc, int D, int nk, int cmp_block, int cmp_stride, int cmp_offset, int bn, int sel_offset,
+                            int causal, float scale, int force_first, int force_local, int shared_per_group, int dtype,
+                            nsa_stream_t stream) {
+  NSA_REQUIRE(Q && Kc && lse && scores && head_scratch, NSA_ERR_ARG, "compressed scores: NULL pointer");
+  NSA_REQUIRE(B > 0 && H > 0 && Hkv > 0 && H % Hkv == 0 && Tq > 0 && Nc > 0 && nk > 0, NSA_ERR_ARG, "compressed scores: sizes");
+  NSA_REQUIRE(cmp_block > 0 && cmp_stride > 0 && cmp_stride <= cmp_block && bn > 0, NSA_ERR_ARG, "compressed scores: block sizes");
+  NSA_REQUIRE(force_first >= 0 && force_local >= 0, NSA_ERR_ARG, "compressed scores: negative forced-block counts");
+  NSA_REQUIRE(cmp_scores_tc5_supports(D, dtype, cmp_block, cmp_stride, bn, nk), NSA_ERR_UNSUPPORTED,
+              "compressed scores (tcgen05): needs D in {64,128}, 16-bit storage and score rows that fit shared memory (nk=%d)", nk);
+  return cmp_block_scores_tc5(Q, Kc, lse, scores, head_scratch, B, H, Hkv, Tq, Nc, D, nk, cmp_block, cmp_stride, cmp_offset, bn,
+                              sel_offset, causal, scale, force_first, force_local, shared_per_group, dtype, (cudaStream_t)stream);
+}
+
 int nsa_topk_from_scores(const float* scores, int32_t* idx, int BH, int nq, int nk, int top_k, int bm, int bn,
                          int offset, int causal, nsa_stream_t stream) {
   NSA_REQUIRE(scores && idx, NSA_ERR_ARG, "topk: NULL pointer");
@@ -140,6 +162,8 @@ int nsa_attention_fwd(const nsa_fwd_args* args, nsa_stream_t stream) {
     if (!sel_only_per_head) return attention_fwd_tc5(*args, (cudaStream_t)stream);
   }
   NSA_REQUIRE(args->dyn_len == nullptr, NSA_ERR_UNSUPPORTED, "attention forward: a device-resident length needs the tcgen05 kernel");
+  NSA_REQUIRE(args->accumulate == 0 && !(args->fused && args->lse != nullptr), NSA_ERR_UNSUPPORTED,
+              "attention forward: accumulate / lse of a fused launch need the tcgen05 kernel");
   return attention_fwd_generic(*args, (cudaStream_t)stream);
 }
 
@@ -147,6 +171,9 @@ int nsa_device_status(nsa_stream_t stream) {
   int v = 0;
   int rc = tc5_take_status((cudaStream_t)stream, &v);
   if (rc != NSA_OK) return rc;
+  int v2 = 0;
+  if ((rc = cs5_take_status(&v2)) != NSA_OK) return rc;
+  if (v == 0 && v2 != 0) v = 100 + v2;
   if (v != 0) return fail(NSA_ERR_DEVICE, "a kernel gave up waiting on barrier %d (bounded wait expired)", v - 1);
   return NSA_OK;
 }

@@ -558,7 +558,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
     // own 2*D bytes of HBM, read back and added to at the next branch end): that keeps the whole
     // S row (128 registers) resident during a tile, so a tile costs ONE TMEM round trip.
     float lse_out = -INFINITY;
-    bool have_partial = false;
+    bool have_partial = !SPLIT && a.accumulate != 0;       // the output row already holds a gated partial sum to add to
     T* orow = reinterpret_cast<T*>(a.out) + ((a.io_layout & NSA_IO_OUT_BTHD) ? row_bthd : row_index) * D;
 
     int it = 0;
@@ -702,7 +702,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
       }
       const bool has = l > 0.f;
       const float coef = has ? (a.fused ? gate[br] : 1.f) * p.out_scale[br] / l : 0.f;
-      if (!a.fused) lse_out = has ? m_used * kLn2 + __logf(l) : -INFINITY;
+      if (a.lse != nullptr) lse_out = has ? m_used * kLn2 + __logf(l) : -INFINITY;   // one branch per launch when lse is asked for
 #pragma unroll
       for (int g = 0; g < D / 32; ++g) {
         uint32_t v[32];
@@ -733,7 +733,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
 #pragma unroll
         for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(orow)[c] = make_uint4(0u, 0u, 0u, 0u);
       }
-      if (!a.fused && a.lse != nullptr) a.lse[row_index] = lse_out;
+      if (a.lse != nullptr) a.lse[row_index] = lse_out;
     }
   }
 
@@ -881,7 +881,7 @@ static int make_map8(CUtensorMap* m, const void* ptr, long long slabs, long long
 }
 
 // [slabs][rows][D] 16-bit tensor, boxes of 64 rows x 64 elements, 128-byte swizzle, zero fill outside
-static int make_map(CUtensorMap* m, const void* ptr, long long slabs, long long rows, int D, int dtype) {
+int make_map(CUtensorMap* m, const void* ptr, long long slabs, long long rows, int D, int dtype) {
   auto enc = encode_fn();
   NSA_REQUIRE(enc != nullptr, NSA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   NSA_REQUIRE((reinterpret_cast<uintptr_t>(ptr) & 15) == 0, NSA_ERR_ARG, "tensor base %p is not 16-byte aligned", ptr);

@@ -158,7 +158,9 @@ def nsa_forward(Q: Tensor, K: Tensor, V: Tensor, cfg, *, gate_logits: Optional[T
     stride_c = getattr(cfg, "stride_c", None)
     ff, fl = _cfg(cfg, "force_first", 0), _cfg(cfg, "force_local", 0)
     if block_indices is None and _cfg(cfg, "scorer", "mean") == "compressed":
-        from .scoring import select_blocks_compressed
+        from .scoring import forward_with_compressed_scorer, select_blocks_compressed
+        if not (torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (Q, K, V, gate_logits))):
+            return forward_with_compressed_scorer(Q, K, V, cfg, gate_logits)
         block_indices = select_blocks_compressed(Q, K, cfg)
     elif block_indices is None:
         if _cfg(cfg, "scorer", "mean") != "mean":

@@ -24,6 +24,10 @@ def set_engine(name: str) -> None:
     _ENGINE = {"auto": L.ENGINE_AUTO, "generic": L.ENGINE_GENERIC, "tcgen05": L.ENGINE_TCGEN05}[name]
 
 
+def engine() -> int:
+    return _ENGINE
+
+
 def device_status() -> None:
     """Synchronise the current stream and raise if a kernel gave up on a bounded device-side wait."""
     L.check(L.load().nsa_device_status(L.stream_ptr()), "nsa_device_status")
@@ -91,6 +95,16 @@ def cmp_block_scores(Q: Tensor, Kc: Tensor, lse: Tensor, *, nk: int, cmp_block: 
         raise TypeError("cmp_block_scores: Q and the pooled K must share a 16-bit dtype")
     nq = (Tq + 63) // 64
     scores = torch.empty((B, Hkv if shared_per_group else H, nq, nk), device=Q.device, dtype=torch.float32)
+    # tcgen05 kernel where it applies: D in {64,128} and the four score rows of a work item fit shared memory
+    fixed = 4 * (D // 64) * 128 * 128 + (256 + 1024 + 4 * nk) * 4 + 1024
+    if _ENGINE != L.ENGINE_GENERIC and D in (64, 128) and (bn + cmp_block) // cmp_stride + 1 <= 64 and fixed <= 225 * 1024:
+        scratch = torch.empty((B, H, nq, nk), device=Q.device, dtype=torch.float32)
+        with torch.cuda.device(Q.device):
+            L.check(L.load().nsa_cmp_block_scores_tc(Q.data_ptr(), Kc.data_ptr(), lse.data_ptr(), scores.data_ptr(), scratch.data_ptr(),
+                                                     B, H, Hkv, Tq, Nc, D, nk, cmp_block, cmp_stride, cmp_offset, bn, sel_offset,
+                                                     int(causal), float(scale), force_first, force_local, int(shared_per_group),
+                                                     L.dtype_code(Q.dtype), L.stream_ptr()), "nsa_cmp_block_scores_tc")
+        return scores
     with torch.cuda.device(Q.device):
         L.check(L.load().nsa_cmp_block_scores(Q.data_ptr(), Kc.data_ptr(), lse.data_ptr(), scores.data_ptr(), B, H, Hkv, Tq, Nc, D,
                                               nk, cmp_block, cmp_stride, cmp_offset, bn, sel_offset, int(causal), float(scale),
@@ -117,13 +131,16 @@ def attention_fwd(
     gates: Optional[Tensor] = None, gate_act: int = L.GATE_SIGMOID, offset: Optional[int] = None,
     q_scale: float = 1.0, k_scale: float = 1.0, v_scale: float = 1.0, engine: Optional[int] = None,
     want_lse: bool = True, token_major: bool = False, nsplit: int = 1, dyn_len: Optional[Tensor] = None,
+    accumulate_into: Optional[Tensor] = None, fused_lse: bool = False,
 ) -> Tuple[Tensor, Optional[Tensor]]:
     """One launch of nsa_attention_fwd.  Returns (out, lse); lse is None for fused launches.
     `token_major`: gates are [B,Tq,H,3] and the result comes back as [B,Tq,H,D] (Q, K, V stay
     [B,H,T,D]) -- the layouts on either side of the call in the reference's attention module.
     `nsplit` > 1 (fused launches): each work item's key tiles are spread over that many thread blocks, for
     launches with few query blocks and long key ranges (decoding).  `dyn_len`: int32 device scalar with the
-    number of filled key positions; K/V/Kc/Vc are then allocations and every offset is derived on the device."""
+    number of filled key positions; K/V/Kc/Vc are then allocations and every offset is derived on the device.
+    `accumulate_into`: the output of an earlier fused launch (other branches); this launch adds its branches to it
+    and returns the same tensor.  `fused_lse`: a fused launch of ONE branch also returns that branch's lse."""
     _need_cuda(Q, K, V)
     B, H, Tq, D = Q.shape
     Hkv, Tk = K.shape[1], K.shape[2]
@@ -135,9 +152,15 @@ def attention_fwd(
         raise TypeError("Q, K, V must share a dtype")
     Q, K, V = Q.contiguous(), K.contiguous(), V.contiguous()
     out_dtype = torch.bfloat16 if Q.dtype in _8 else Q.dtype
-    out = torch.empty((B, Tq, H, D) if token_major else (B, H, Tq, D), device=Q.device, dtype=out_dtype)
-    lse = torch.empty((B, H, Tq), device=Q.device, dtype=torch.float32) if (want_lse and not fused) else None
+    if accumulate_into is not None:
+        out = accumulate_into
+        if not fused or out.shape != ((B, Tq, H, D) if token_major else (B, H, Tq, D)) or out.dtype != out_dtype or not out.is_contiguous():
+            raise ValueError("accumulate_into must be the contiguous output of a fused launch of the same problem")
+    else:
+        out = torch.empty((B, Tq, H, D) if token_major else (B, H, Tq, D), device=Q.device, dtype=out_dtype)
+    lse = torch.empty((B, H, Tq), device=Q.device, dtype=torch.float32) if ((want_lse and not fused) or (fused and fused_lse)) else None
     a = L.FwdArgs()
+    a.accumulate = int(accumulate_into is not None)
     a.io_layout = (L.IO_OUT_BTHD | L.IO_GATES_BTHD) if token_major else 0
     a.Q, a.K, a.V, a.out, a.lse = Q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(), L.ptr(lse)
     a.B, a.H, a.Hkv, a.Tq, a.Tk, a.D = B, H, Hkv, Tq, Tk, D

@@ -19,7 +19,7 @@ def test_library_exports_every_declared_symbol():
     assert declared == set(_lib.PROTOTYPES), declared ^ set(_lib.PROTOTYPES)
     for name in declared:
         assert hasattr(lib, name), name
-    assert lib.nsa_abi_version() == 4
+    assert lib.nsa_abi_version() == 5
 
 
 def _struct_fields(header, name):

@@ -576,7 +576,23 @@ def test_compressed_probability_scorer_vs_oracle(nsa, case):
     assert torch.equal(idx, want)
     sc2 = nsa.compressed_block_scores(Qc, Kc, cfg).cpu()
     assert torch.equal(sc, sc2), "scores are not bitwise repeatable"
-    out = nsa.nsa_forward(Qc, Kc, Vc, cfg)
+    from nsa_from_scratch_b200 import ops
+    ops.device_status()
+    # the mma.sync kernel (all head dims) and the tcgen05 kernel (D in {64,128}) agree to fp32 rounding
+    ops.set_engine("generic")
+    try:
+        sc_g = nsa.compressed_block_scores(Qc, Kc, cfg).cpu()
+    finally:
+        ops.set_engine("auto")
+    assert torch.equal(torch.isfinite(sc_g), finite)
+    assert float((sc_g - sc)[finite].abs().max()) <= 1e-3 * max(1.0, float(sc[finite].abs().max()))
+    gates = torch.randn(B, H, Tq, 3, generator=g)
+    out = nsa.nsa_forward(Qc, Kc, Vc, cfg, gate_logits=gates.cuda())
     o_ref = O.nsa_forward(Q.float(), K.float(), V.float(), block_size_c=bc, stride_c=stride, top_k=3, window_size=96,
-                          block_indices=idx, group_shared=shared)
+                          block_indices=idx, group_shared=shared, gate_logits=gates)
     assert max_abs(out, o_ref) <= TOL16
+    # compressed branch first, selected + sliding added to the same rows: the single-launch forward, bit for bit
+    from nsa_from_scratch_b200.forward import _fused_forward
+    one = _fused_forward(Qc, Kc, Vc, cfg, D ** -0.5, stride, gates.cuda(), idx.cuda(), 1.0, 1.0, 1.0)
+    assert torch.equal(out, one)
+    ops.device_status()
