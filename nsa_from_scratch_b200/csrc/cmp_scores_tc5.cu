@@ -10,9 +10,9 @@
 //
 // Work item as in the attention kernel: 4 row groups (query head, query block) that share one KV head = two
 // 128-row tiles X.  Warp 0: TMA producer (Q once, pooled-K tiles of 128 tokens into a ring).  Warp 1: MMA issuer.
-// Warps 4-7 / 8-11: tile 0 / tile 1 -- exponentials and row-group sums per token, then every selection block whose
-// last token lies in the tile gathers its tokens (overlap weights) from a two-tile window of token sums in shared
-// memory.  All sums are formed in a fixed order.  Every wait is bounded; a wait that gives up raises the block's
+// Warps 4-7 / 8-11: tile 0 / tile 1 -- exponentials and row-group sums per token, left in a two-tile window of token sums
+// in shared memory.  Warps 2 / 3: for tile 0 / 1, every selection block whose last token lies in the newest tile
+// gathers its tokens (overlap weights) from the ring, off the critical path.  All sums are formed in a fixed order.  Every wait is bounded; a wait that gives up raises the block's
 // abort flag and the device status word, and the block still frees its TMEM.
 #include "common.cuh"
 #include "tc5_ptx.cuh"
@@ -35,10 +35,11 @@ struct Cs5Params {
   int cblock, cstride, cmp_offset, bn, causal;
   float scale_log2;
   int GH, HG, NQG, NST;
+  int tpb, wpt;         // token starts per selection block (bn / stride), strides per compression window (block / stride)
 };
 
 enum { C_QFULL = 0, C_KFULL = 1, C_KEMPTY = 5, C_SFULL = 9, C_SFREE = 13, C_TOK = 17, C_GAT = 19, C_COUNT = 21 };
-// K*: up to 4 stages; S*: 2*X + buffer; TOK / GAT (per tile X, 128 arrivals): token sums written / blocks gathered
+// K*: up to 4 stages; S*: 2*X + buffer; TOK (per tile X, 128 arrivals): token sums written; GAT (1 arrival): blocks gathered
 
 template <int D, int FMT>
 __global__ void __launch_bounds__(384, 1) cmp_scores_tc5_kernel(const __grid_constant__ Cs5Params p) {
@@ -86,7 +87,7 @@ __global__ void __launch_bounds__(384, 1) cmp_scores_tc5_kernel(const __grid_con
 
   if (tid == 0) {
     abort_flag = 0;
-    for (int i = 0; i < C_COUNT; ++i) mbar_init(bar(i), i >= C_SFREE ? 128 : 1);
+    for (int i = 0; i < C_COUNT; ++i) mbar_init(bar(i), (i >= C_SFREE && i < C_GAT) ? 128 : 1);
     fence_barrier_init();
   }
   if (warp == 1) { tmem_alloc(smem_u32(&tmem_base_s), 512); tmem_relinquish(); }
@@ -174,7 +175,6 @@ __global__ void __launch_bounds__(384, 1) cmp_scores_tc5_kernel(const __grid_con
     const int X = (warp - 4) >> 2;
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;                       // token of the tile == TMEM lane
-    const int xt = tid - 128 - X * 128;                      // thread index within tile X's four warps
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const float sl2 = p.scale_log2;
     // the two row groups of this tile
@@ -202,67 +202,91 @@ __global__ void __launch_bounds__(384, 1) cmp_scores_tc5_kernel(const __grid_con
       tc_fence_before();
       mbar_arrive(bar(C_SFREE + 2 * X + bsel));              // S^T is in registers: the MMA warp may refill the buffer
       const int c = t * TT + r;                              // this thread's compressed token
+      float tsum[2];
 #pragma unroll
       for (int gg = 0; gg < 2; ++gg) {
         // rows of the group that see token c: positions >= c*stride + block - 1 - cmp_offset (causal), and existing
         int vlo = 0;
         if (p.causal) vlo = max(0, c * p.cstride + p.cblock - 1 - p.cmp_offset - g_qb[gg] * 64);
         const int vhi = c < p.Nc ? g_rows[gg] : 0;           // exclusive
-        const float* ls = lse2s + (2 * X + gg) * 64;
+        const float4* ls4 = reinterpret_cast<const float4*>(lse2s + (2 * X + gg) * 64);
         float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
         if (vlo == 0 && vhi == 64) {
 #pragma unroll
           for (int q = 0; q < 2; ++q)
 #pragma unroll
             for (int i = 0; i < 32; i += 4) {
-              s0 += ex2(fmaf(__uint_as_float(sv[2 * gg + q][i]), sl2, ls[q * 32 + i]));
-              s1 += ex2(fmaf(__uint_as_float(sv[2 * gg + q][i + 1]), sl2, ls[q * 32 + i + 1]));
-              s2 += ex2(fmaf(__uint_as_float(sv[2 * gg + q][i + 2]), sl2, ls[q * 32 + i + 2]));
-              s3 += ex2(fmaf(__uint_as_float(sv[2 * gg + q][i + 3]), sl2, ls[q * 32 + i + 3]));
+              const float4 l4 = ls4[q * 8 + (i >> 2)];
+              s0 += ex2(fmaf(__uint_as_float(sv[2 * gg + q][i]), sl2, l4.x));
+              s1 += ex2(fmaf(__uint_as_float(sv[2 * gg + q][i + 1]), sl2, l4.y));
+              s2 += ex2(fmaf(__uint_as_float(sv[2 * gg + q][i + 2]), sl2, l4.z));
+              s3 += ex2(fmaf(__uint_as_float(sv[2 * gg + q][i + 3]), sl2, l4.w));
             }
         } else if (vlo < vhi) {
 #pragma unroll
           for (int q = 0; q < 2; ++q)
 #pragma unroll
             for (int i = 0; i < 32; i += 4) {
+              const float4 l4 = ls4[q * 8 + (i >> 2)];
+              const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 const int col = q * 32 + i + e;
-                const float pv = (col >= vlo && col < vhi) ? ex2(fmaf(__uint_as_float(sv[2 * gg + q][i + e]), sl2, ls[col])) : 0.f;
+                const float pv = (col >= vlo && col < vhi) ? ex2(fmaf(__uint_as_float(sv[2 * gg + q][i + e]), sl2, lv[e])) : 0.f;
                 if (e == 0) s0 += pv; else if (e == 1) s1 += pv; else if (e == 2) s2 += pv; else s3 += pv;
               }
             }
         }
-        tokv[((bsel * 2 + X) * 2 + gg) * TT + r] = (s0 + s1) + (s2 + s3);
+        tsum[gg] = (s0 + s1) + (s2 + s3);
       }
-      mbar_arrive(bar(C_TOK + X));                           // the tile's token sums are all in place once 128 threads arrived
+      // slot t&1 held tile t-2, which the gather of tile t-1 still reads; that gather started when this tile's
+      // exponentials did, so the wait is over long before it is reached.  (It also keeps the TOK barrier at most one
+      // phase ahead of the gather warp, which waits on its phases by parity.)
+      if (t >= 1) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(C_GAT + X), (t - 1) & 1, &abort_flag));
+        if (!ok) { fail_id = C_GAT + X + 1; break; }
+      }
+      tokv[(((t & 1) * 2 + X) * 2 + 0) * TT + r] = tsum[0];
+      tokv[(((t & 1) * 2 + X) * 2 + 1) * TT + r] = tsum[1];
+      mbar_arrive(bar(C_TOK + X));                           // 128 arrivals: the tile's token sums are in the ring
+    }
+  } else {
+    // =============================== block gather (warp 2: tile 0, warp 3: tile 1) ===============================
+    // Selection blocks whose last token lies in tile t gather their tokens from ring slots t and t-1 (a block spans
+    // at most 64 tokens); lanes take (row group, block) tasks; sc is only ever touched by this warp.
+    const int X = warp - 2;
+    const int last_tok = ntiles * TT - 1;
+    bool ok = true;
+#pragma unroll 1
+    for (int t = 0; t < ntiles && ok; ++t) {
       ok = __all_sync(0xffffffffu, mbar_wait(bar(C_TOK + X), t & 1, &abort_flag));
       if (!ok) { fail_id = C_TOK + X + 1; break; }
-      // selection blocks whose last token lies in this tile gather their tokens from the window (tile t-1, tile t)
-      {
-        const int tok_lo = t * TT, tok_hi = tok_lo + TT - 1;
-        const int j_lo = (tok_lo * p.cstride) / p.bn;
-        const int j_hi = min(p.nk - 1, (min(tok_hi, p.Nc - 1) * p.cstride + p.cblock - 1) / p.bn);
-        const int nj = j_hi - j_lo + 1;
-        for (int task = xt; task < 2 * nj; task += 128) {
-          const int gg = task / nj, j = j_lo + task % nj;
-          const int c_last = min(min(((j + 1) * p.bn - 1) / p.cstride, p.Nc - 1), last_tok);
-          const int num = j * p.bn - p.cblock + p.cstride;
-          const int c_first = num < 0 ? 0 : num / p.cstride;
-          if (c_last < tok_lo || c_last > tok_hi || c_first > c_last) continue;
+      // In units of the stride: a selection block holds tpb token starts, a window spans wpt of them; token
+      // c = j*tpb + u (u from -(wpt-1) to tpb-1) overlaps block j by min(u + wpt, tpb) - max(u, 0) units of its wpt.
+      // Block j is gathered in the tile that holds its last token start (clipped to the last token processed).
+      const int tok_lo = t * TT, tok_hi = min(tok_lo + TT - 1, last_tok);
+      const int tpb = p.tpb, wpt = p.wpt;
+      const int j_lo = tok_lo / tpb;                                           // first block whose last token start is in the tile
+      const int j_top = t == ntiles - 1 ? min(p.nk - 1, (tok_hi + wpt - 1) / tpb)   // last tile: every block a processed token reaches
+                                        : (tok_lo + TT - tpb) / tpb;
+      const float inv_wpt = 1.f / (float)wpt;
+      for (int gg = 0; gg < 2; ++gg) {
+        for (int j = j_lo + lane; j <= j_top; j += 32) {
+          const int c_end = min(j * tpb + tpb - 1, tok_hi);                   // last token start of the block that was processed
+          if (c_end < tok_lo) continue;
           float acc = 0.f;
-          for (int cc = c_first; cc <= c_last; ++cc) {
-            const int w0 = max(cc * p.cstride, j * p.bn), w1 = min(cc * p.cstride + p.cblock, (j + 1) * p.bn);
-            if (w1 <= w0) continue;
-            const int tt = cc / TT;                           // t or t-1: a block spans at most 64 tokens
-            acc = fmaf(tokv[((((tt & 1) * 2 + X) * 2 + gg) * TT) + (cc - tt * TT)], (float)(w1 - w0) / (float)p.cblock, acc);
+          for (int u = -(wpt - 1); u < tpb; ++u) {
+            const int cc = j * tpb + u;
+            if (cc < 0 || cc > c_end) continue;
+            const int ov = min(u + wpt, tpb) - max(u, 0);
+            const int tt = cc >> 7;                                            // t or t-1
+            acc = fmaf(tokv[((((tt & 1) * 2 + X) * 2 + gg) * TT) + (cc & (TT - 1))], (float)ov * inv_wpt, acc);
           }
           sc[(2 * X + gg) * p.nk + j] += acc;
         }
       }
-      mbar_arrive(bar(C_GAT + X));                           // gathered: the older window half may be overwritten
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(C_GAT + X), t & 1, &abort_flag));
-      if (!ok) { fail_id = C_GAT + X + 1; break; }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(C_GAT + X));            // the slot of tile t-1 may be overwritten
     }
   }
 
@@ -316,6 +340,7 @@ bool cmp_scores_tc5_supports(int D, int dtype, int cblock, int cstride, int bn, 
   if (!(D == 64 || D == 128)) return false;
   if (!(dtype == NSA_BF16 || dtype == NSA_FP16)) return false;
   if ((bn + cblock) / cstride + 1 > 64) return false;
+  if (bn % cstride != 0 || cblock % cstride != 0) return false;      // the gather works in units of the stride
   // Q tiles + 2 K stages + row data + token window + 4 score rows must fit
   const size_t need = (size_t)4 * (D / 64) * 128 * 128 + (256 + 8 * 128 + (size_t)4 * nk) * 4 + 1024;
   return need <= 225 * 1024;
@@ -332,6 +357,7 @@ int cmp_block_scores_tc5(const void* Q, const void* Kc, const float* lse, float*
   p.B = B; p.H = H; p.Hkv = Hkv; p.Tq = Tq; p.Nc = Nc; p.nq = (Tq + 63) / 64; p.nk = nk;
   p.cblock = cblock; p.cstride = cstride; p.cmp_offset = cmp_offset; p.bn = bn; p.causal = causal;
   p.scale_log2 = scale * kLog2e;
+  p.tpb = bn / cstride; p.wpt = cblock / cstride;
   const int G = H / Hkv;
   p.GH = G % 4 == 0 ? 4 : (G % 2 == 0 ? 2 : 1);
   p.HG = G / p.GH;

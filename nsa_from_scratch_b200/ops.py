@@ -97,7 +97,8 @@ def cmp_block_scores(Q: Tensor, Kc: Tensor, lse: Tensor, *, nk: int, cmp_block: 
     scores = torch.empty((B, Hkv if shared_per_group else H, nq, nk), device=Q.device, dtype=torch.float32)
     # tcgen05 kernel where it applies: D in {64,128} and the four score rows of a work item fit shared memory
     fixed = 4 * (D // 64) * 128 * 128 + (256 + 1024 + 4 * nk) * 4 + 1024
-    if _ENGINE != L.ENGINE_GENERIC and D in (64, 128) and (bn + cmp_block) // cmp_stride + 1 <= 64 and fixed <= 225 * 1024:
+    if (_ENGINE != L.ENGINE_GENERIC and D in (64, 128) and (bn + cmp_block) // cmp_stride + 1 <= 64 and fixed <= 225 * 1024
+            and bn % cmp_stride == 0 and cmp_block % cmp_stride == 0):
         scratch = torch.empty((B, H, nq, nk), device=Q.device, dtype=torch.float32)
         with torch.cuda.device(Q.device):
             L.check(L.load().nsa_cmp_block_scores_tc(Q.data_ptr(), Kc.data_ptr(), lse.data_ptr(), scores.data_ptr(), scratch.data_ptr(),
