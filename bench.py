@@ -57,6 +57,7 @@ def parse():
     ap.add_argument("--sweep", action="store_true",
                     help="instead of the single contract line: one JSON line per point of the T x D sweep "
                          "(T = 1k..64k, D = 64/128, Hq=64/Hkv=4) plus the reference's own MHA shape (H=16, D=64, 64/64)")
+    ap.add_argument("--scorer", action="store_true", help="only the probability-scorer measurement of --sweep")
     ap.add_argument("--decode", action="store_true", help="only the decoding measurement of --sweep (B=1, 65536 cached)")
     ap.add_argument("--cpu-tiles", type=int, default=40, help="64-row query tiles in the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -593,21 +594,40 @@ def run_sweep(a):
     del q, k, v, gl
     torch.cuda.empty_cache()
 
-    # selection scored from the compressed branch's probabilities instead of block means (default workload)
-    Qs, Ks, Vs, Gs = (t.cuda() for t in make_inputs(b, a.seed))
-    cfg_p = nsa.NSAConfig(block_size_c=b.cmp_block, stride_c=b.cmp_stride, top_k=b.top_k, window_size=b.window,
+    sweep_scorer(a)
+    sweep_decode(a)
+
+
+def sweep_scorer(a):
+    """Selection scored from the compressed branch's probabilities instead of block means: one JSON line with the
+    whole forward and the selection alone."""
+    import nsa_from_scratch_b200 as nsa
+    from nsa_from_scratch_b200 import ops
+    torch.cuda.set_device(0)
+    Qs, Ks, Vs, Gs = (t.cuda() for t in make_inputs(a, a.seed))
+    cfg_p = nsa.NSAConfig(block_size_c=a.cmp_block, stride_c=a.cmp_stride, top_k=a.top_k, window_size=a.window,
                           force_first=1, force_local=2, select_per_group=True, scorer="compressed")
+
+    def timed(fn, n):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
     ms_sel = timed(lambda: nsa.select_blocks_compressed(Qs, Ks, cfg_p), max(2, a.steps // 2))
     ms_fwd = timed(lambda: nsa.nsa_forward(Qs, Ks, Vs, cfg_p, gate_logits=Gs), max(2, a.steps // 2))
     ops.device_status()
-    print(json.dumps({"metric": METRIC, "value": T / (ms_fwd * 1e-3), "unit": UNIT, "ms_per_step": ms_fwd,
+    print(json.dumps({"metric": METRIC, "value": a.seq_len / (ms_fwd * 1e-3), "unit": UNIT, "ms_per_step": ms_fwd,
                       "selection_ms": ms_sel,
-                      "config": {"workload": workload_name(b) + " [selection scored from the compressed branch's probabilities]"}}),
+                      "config": {"workload": workload_name(a) + " [selection scored from the compressed branch's probabilities]"}}),
           flush=True)
     del Qs, Ks, Vs, Gs
     torch.cuda.empty_cache()
-
-    sweep_decode(a)
 
 
 def sweep_decode(a, shapes=((1, 65536), (8, 65536), (1, 8192))):
@@ -724,6 +744,8 @@ def main():
         return run_reference_protocol(a)
     if a.decode:
         return sweep_decode(a, shapes=((1, 65536),))
+    if a.scorer:
+        return sweep_scorer(a)
     if a.sweep:
         return run_sweep(a)
     if a.impl == "reference":

@@ -76,7 +76,7 @@ def layer_cases():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the reference checkout")
     ap.add_argument("--part", default="all", choices=["all", "kernels", "layer"],
                     help="kernels: reference_golden.npz; layer: layer_golden.npz")
     args = ap.parse_args()

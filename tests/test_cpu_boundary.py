@@ -95,7 +95,9 @@ def test_compat_fused_caller_keeps_the_cpu_route():
     inputs (and anything under autograd) still run the module's own code, bit for bit."""
     import os
     import sys
-    ref = os.environ.get("NSA_REFERENCE_CHECKOUT", "/root/reference")
+    ref = os.environ.get("NSA_REFERENCE_CHECKOUT", "")
+    if not ref:                                   # default: a checkout named "reference" beside this repository
+        ref = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
     if not os.path.isdir(os.path.join(ref, "nsa", "model")):
         pytest.skip("reference checkout not present")
     sys.path.insert(0, ref)
