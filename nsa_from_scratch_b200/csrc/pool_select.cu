@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(256) cache_append_kernel(const T* __restrict__
     filled = *dyn_filled;
     const int T1d = filled + t_new;
     if (T1d > max_len) return;                             // the host refuses this before launching; never write past the end
-    auto n_pooled = [&](int T) { return cstride == cblock ? (T + cblock - 1) / cblock : (T >= cblock ? (T - cblock) / cstride + 1 : 0); };
+    auto n_pooled = [&](int len) { return cstride == cblock ? (len + cblock - 1) / cblock : (len >= cblock ? (len - cblock) / cstride + 1 : 0); };
     c0 = cstride == cblock ? filled / cblock : n_pooled(filled);
     nw = min(n_pooled(T1d), nc_alloc) - c0;
     b0 = filled / sblock;
@@ -158,7 +158,7 @@ int cache_append(const void* k_new, const void* v_new, void* K, void* V, void* K
   NSA_REQUIRE((long long)B * Hkv <= 65535 && B * Hkv > 0, NSA_ERR_ARG, "cache append: B*Hkv %lld", (long long)B * Hkv);
   if (t_new == 0) return NSA_OK;
   const int T0 = filled, T1 = filled + t_new;
-  auto n_pooled = [&](int T) { return cstride == cblock ? (T + cblock - 1) / cblock : (T >= cblock ? (T - cblock) / cstride + 1 : 0); };
+  auto n_pooled = [&](int len) { return cstride == cblock ? (len + cblock - 1) / cblock : (len >= cblock ? (len - cblock) / cstride + 1 : 0); };
   // windows that contain a new row: whole windows completed by them, or (stride == block) the partial tail window
   int c0 = cstride == cblock ? T0 / cblock : n_pooled(T0);
   int nw = n_pooled(T1) - c0;
