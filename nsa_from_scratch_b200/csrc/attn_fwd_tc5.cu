@@ -680,6 +680,14 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
       }
       if (!ok) break;
       // ---- end of the branch: O is complete once the last PV has landed ---------------------------
+      // The running gated sum of the earlier branches is read back from the output row NOW, before that wait: the
+      // loads fly while the last PV executes instead of costing a memory round trip per 64 bytes afterwards.
+      uint4 prevv[D / 8];
+      if constexpr (!SPLIT) {
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c)
+          prevv[c] = (have_partial && row_ok) ? reinterpret_cast<const uint4*>(orow)[c] : make_uint4(0u, 0u, 0u, 0u);
+      }
       ok = __all_sync(0xffffffffu, mbar_wait(bar(B_PVDONE + X), (it - 1) & 1, &abort_flag));
       if (!ok) { fail_id = B_PVDONE + X + 1; break; }
       tc_fence_after();
@@ -711,8 +719,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
         if (row_ok) {
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            uint4 prev = make_uint4(0u, 0u, 0u, 0u);
-            if (have_partial) prev = reinterpret_cast<const uint4*>(orow)[g * 4 + c];
+            const uint4 prev = prevv[g * 4 + c];
             const uint32_t pw[4] = {prev.x, prev.y, prev.z, prev.w};
             uint32_t w[4];
 #pragma unroll
