@@ -322,8 +322,8 @@ def run_ours(a):
         peak, peak_src = 1590.0, "fallback"
     achieved = flops["total"] / (fused_ms * 1e-3) / 1e12
     # DRAM bytes per launch of the fused kernel: dram__bytes_read + dram__bytes_write of one ncu capture at
-    # T=16384 with these heads (566.6 MB), scaled by T -- every operand of this shape family grows with T
-    traffic = 566.632704e6 * T / 16384 if (a.heads, a.kv_heads, a.head_dim) == (64, 4, 128) else None
+    # T=16384 with these heads (577.0 MB), scaled by T -- every operand of this shape family grows with T
+    traffic = 576.957696e6 * T / 16384 if (a.heads, a.kv_heads, a.head_dim) == (64, 4, 128) else None
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                 "traffic": traffic, "peak_source": peak_src, "kernel": "fused three-branch attention",
                 "kernel_ms": fused_ms, "algorithmic_tflop": {k: v / 1e12 for k, v in flops.items()},
