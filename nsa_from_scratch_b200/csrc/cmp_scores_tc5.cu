@@ -10,10 +10,11 @@
 //
 // Work item as in the attention kernel: 4 row groups (query head, query block) that share one KV head = two
 // 128-row tiles X.  Warp 0: TMA producer (Q once, pooled-K tiles of 128 tokens into a ring).  Warp 1: MMA issuer.
-// Warps 4-7 / 8-11: tile 0 / tile 1 -- exponentials and row-group sums per token, left in a two-tile window of token sums
-// in shared memory.  Warps 2 / 3: for tile 0 / 1, every selection block whose last token lies in the newest tile
-// gathers its tokens (overlap weights) from the ring, off the critical path.  All sums are formed in a fixed order.  Every wait is bounded; a wait that gives up raises the block's
-// abort flag and the device status word, and the block still frees its TMEM.
+// Warps 4-7 / 8-11: tile 0 / tile 1 -- exponentials and row-group sums per token, left in a two-tile window of
+// token sums in shared memory.  Warps 2 / 3: for tile 0 / 1, every selection block whose last token lies in the
+// newest tile gathers its tokens (overlap weights) from the window, off the critical path.  All sums are formed
+// in a fixed order.  Every wait is bounded; a wait that gives up raises the block's abort flag and the device
+// status word, and the block still frees its TMEM.
 #include "common.cuh"
 #include "tc5_ptx.cuh"
 
