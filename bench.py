@@ -57,6 +57,7 @@ def parse():
     ap.add_argument("--sweep", action="store_true",
                     help="instead of the single contract line: one JSON line per point of the T x D sweep "
                          "(T = 1k..64k, D = 64/128, Hq=64/Hkv=4) plus the reference's own MHA shape (H=16, D=64, 64/64)")
+    ap.add_argument("--train", action="store_true", help="only the training-shape measurements of --sweep (at --seq-len if given below 32768)")
     ap.add_argument("--scorer", action="store_true", help="only the probability-scorer measurement of --sweep")
     ap.add_argument("--decode", action="store_true", help="only the decoding measurement of --sweep (B=1, 65536 cached)")
     ap.add_argument("--cpu-tiles", type=int, default=40, help="64-row query tiles in the CPU-baseline sample")
@@ -498,43 +499,7 @@ def run_sweep(a):
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / n
 
-    # selected-branch forward + backward at the training shape (B=2, T=32768, Hq=12, Hkv=1, D=64)
-    g = torch.Generator().manual_seed(a.seed)
-    B, H, Hkv, T, D = 2, 12, 1, 32768, 64
-    Q = torch.randn(B, H, T, D, generator=g).to(torch.bfloat16).cuda()
-    K = torch.randn(B, Hkv, T, D, generator=g).to(torch.bfloat16).cuda()
-    V = torch.randn(B, Hkv, T, D, generator=g).to(torch.bfloat16).cuda()
-    dO = torch.randn(B, H, T, D, generator=g).to(torch.bfloat16).cuda()
-    for shared in (False, True):
-        idx = F._resolve_block_indices(Q, K, block_size_m=64, block_size_n=64, top_k=16, causal=True, scale=D ** -0.5,
-                                       shared_per_group=shared)
-        out, lse = nsa.selected_attention(Q, K, V, block_indices=idx)
-        nq = T // 64
-        qb = torch.arange(nq, device="cuda").view(1, 1, nq, 1)
-        pairs = (int(((idx < qb) & (idx >= 0)).sum()) * 4096 + int((idx == qb).sum()) * 2080) * (H // idx.shape[1])
-        ms_f = timed(lambda: nsa.selected_attention(Q, K, V, block_indices=idx), a.steps)
-        ms_b = timed(lambda: nsa.selected_backward(dO, Q, K, V, out, lse, idx, block_size_m=64, block_size_n=64, causal=True,
-                                                   scale=D ** -0.5, Tq=T, Tk=T, return_fp32=True), a.steps)
-        ops.device_status()
-        print(json.dumps({"metric": "selected_fwd_bwd_ms", "config": {"workload": f"selected branch B={B} T={T} Hq={H} Hkv={Hkv} D={D} bf16, "
-                          f"block lists per {'group' if shared else 'head'}"}, "fwd_ms": ms_f, "bwd_ms": ms_b,
-                          "fwd_tflops": 4 * D * pairs / (ms_f * 1e-3) / 1e12, "bwd_tflops": 10 * D * pairs / (ms_b * 1e-3) / 1e12,
-                          "tokens_per_s_fwd_bwd": B * T / ((ms_f + ms_b) * 1e-3)}), flush=True)
-    # whole forward + backward through autograd (all three branch backward kernels + combine) at the same shape
-    cfg_t = nsa.NSAConfig(block_size_c=32, stride_c=16, top_k=16, window_size=512, select_per_group=True)
-    Qr, Kr, Vr = (t.clone().requires_grad_(True) for t in (Q, K, V))
-
-    def train_step():
-        o = nsa.nsa_forward(Qr, Kr, Vr, cfg_t)
-        o.backward(dO)
-        Qr.grad = Kr.grad = Vr.grad = None
-    ms_t = timed(train_step, max(2, a.steps // 2))
-    ops.device_status()
-    print(json.dumps({"metric": "nsa_fwd_bwd_tokens_per_s", "value": B * T / (ms_t * 1e-3), "ms_per_step": ms_t,
-                      "config": {"workload": f"nsa_forward + backward (autograd, every branch on kernels) B={B} T={T} Hq={H} Hkv={Hkv} D={D} bf16"}}),
-          flush=True)
-    del Q, K, V, dO, Qr, Kr, Vr
-    torch.cuda.empty_cache()
+    sweep_train(a)
 
     # fp8 storage forward (e4m3, per-tensor absmax scales, 0.1 % outliers x20) at T=32768
     b = copy.copy(a)
@@ -596,6 +561,63 @@ def run_sweep(a):
 
     sweep_scorer(a)
     sweep_decode(a)
+
+
+def sweep_train(a, T=32768):
+    """Selected-branch forward + backward and the whole forward + backward through autograd at the training shape
+    (B=2, Hq=12, Hkv=1, D=64); `T` shortens it for a profiler capture."""
+    import nsa_from_scratch_b200 as nsa
+    from nsa_from_scratch_b200 import forward as F, ops
+    torch.cuda.set_device(0)
+
+    def timed(fn, n):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+    # selected-branch forward + backward at the training shape (B=2, T=32768, Hq=12, Hkv=1, D=64)
+    g = torch.Generator().manual_seed(a.seed)
+    B, H, Hkv, D = 2, 12, 1, 64
+    Q = torch.randn(B, H, T, D, generator=g).to(torch.bfloat16).cuda()
+    K = torch.randn(B, Hkv, T, D, generator=g).to(torch.bfloat16).cuda()
+    V = torch.randn(B, Hkv, T, D, generator=g).to(torch.bfloat16).cuda()
+    dO = torch.randn(B, H, T, D, generator=g).to(torch.bfloat16).cuda()
+    for shared in (False, True):
+        idx = F._resolve_block_indices(Q, K, block_size_m=64, block_size_n=64, top_k=16, causal=True, scale=D ** -0.5,
+                                       shared_per_group=shared)
+        out, lse = nsa.selected_attention(Q, K, V, block_indices=idx)
+        nq = T // 64
+        qb = torch.arange(nq, device="cuda").view(1, 1, nq, 1)
+        pairs = (int(((idx < qb) & (idx >= 0)).sum()) * 4096 + int((idx == qb).sum()) * 2080) * (H // idx.shape[1])
+        ms_f = timed(lambda: nsa.selected_attention(Q, K, V, block_indices=idx), a.steps)
+        ms_b = timed(lambda: nsa.selected_backward(dO, Q, K, V, out, lse, idx, block_size_m=64, block_size_n=64, causal=True,
+                                                   scale=D ** -0.5, Tq=T, Tk=T, return_fp32=True), a.steps)
+        ops.device_status()
+        print(json.dumps({"metric": "selected_fwd_bwd_ms", "config": {"workload": f"selected branch B={B} T={T} Hq={H} Hkv={Hkv} D={D} bf16, "
+                          f"block lists per {'group' if shared else 'head'}"}, "fwd_ms": ms_f, "bwd_ms": ms_b,
+                          "fwd_tflops": 4 * D * pairs / (ms_f * 1e-3) / 1e12, "bwd_tflops": 10 * D * pairs / (ms_b * 1e-3) / 1e12,
+                          "tokens_per_s_fwd_bwd": B * T / ((ms_f + ms_b) * 1e-3)}), flush=True)
+    # whole forward + backward through autograd (all three branch backward kernels + combine) at the same shape
+    cfg_t = nsa.NSAConfig(block_size_c=32, stride_c=16, top_k=16, window_size=512, select_per_group=True)
+    Qr, Kr, Vr = (t.clone().requires_grad_(True) for t in (Q, K, V))
+
+    def train_step():
+        o = nsa.nsa_forward(Qr, Kr, Vr, cfg_t)
+        o.backward(dO)
+        Qr.grad = Kr.grad = Vr.grad = None
+    ms_t = timed(train_step, max(2, a.steps // 2))
+    ops.device_status()
+    print(json.dumps({"metric": "nsa_fwd_bwd_tokens_per_s", "value": B * T / (ms_t * 1e-3), "ms_per_step": ms_t,
+                      "config": {"workload": f"nsa_forward + backward (autograd, every branch on kernels) B={B} T={T} Hq={H} Hkv={Hkv} D={D} bf16"}}),
+          flush=True)
+    del Q, K, V, dO, Qr, Kr, Vr
+    torch.cuda.empty_cache()
 
 
 def sweep_scorer(a):
@@ -746,6 +768,8 @@ def main():
         return sweep_decode(a, shapes=((1, 65536),))
     if a.scorer:
         return sweep_scorer(a)
+    if a.train:
+        return sweep_train(a, T=min(a.seq_len, 32768))
     if a.sweep:
         return run_sweep(a)
     if a.impl == "reference":
