@@ -52,6 +52,31 @@ def test_argument_errors_are_reported_without_a_gpu():
     assert lib.nsa_pool_mean(1, 1, 1, 1, 64, 60, 32, 32, 2, 0, 1.0, None) == -1   # D not a multiple of 8
     assert b"multiple of 8" in lib.nsa_last_error()
     assert lib.nsa_attention_fwd(None, None) == -1
+    ERR_ARG, ERR_UNSUPPORTED = -1, -2
+    # every entry point added around the path checks its arguments before it touches the device
+    assert lib.nsa_rope_to_heads(None, 1, None, None, 1, 8, 2, 64, 2, 2, 0, None) == ERR_ARG
+    assert lib.nsa_rope_to_heads(1, 1, 1, None, 1, 8, 2, 64, 2, 2, 0, None) == ERR_ARG           # cos without sin
+    assert lib.nsa_rope_to_heads(1, 1, None, None, 1, 8, 2, 24, 2, 2, 0, None) == ERR_UNSUPPORTED  # D % 16
+    assert b"multiple of 16" in lib.nsa_last_error()
+    assert lib.nsa_memcpy_2d(1, 8, 1, 16, 16, 2, 1, None) == ERR_ARG                              # pitch < row
+    assert lib.nsa_memcpy_2d(1, 16, 1, 16, 16, 2, 7, None) == ERR_ARG
+    assert lib.nsa_cache_append(1, 1, 1, 1, 1, 1, 1, 1, 1, 64, 4, 62, 64, 8, 1, 32, 16, 64, 0, None) == ERR_ARG   # 62 + 4 > 64
+    assert b"exceed the allocation" in lib.nsa_last_error()
+    assert lib.nsa_cache_append_dev(1, 1, 1, 1, 1, 1, 1, 1, 1, 64, 1, None, 64, 8, 1, 32, 16, 64, 0, None) == ERR_ARG
+    assert lib.nsa_select_blocks_cached(1, 1, 1, 1, 4, 1, 1, 8, 64, 4, 64, 64, None, 0.125, 0, 0, 0, 0, None) == ERR_ARG
+    assert lib.nsa_cmp_block_scores_tc(1, 1, 1, 1, 1, 1, 4, 1, 256, 15, 32, 4, 32, 16, 0, 64, 0, 1, 0.2, 0, 0, 0, 0, None) == ERR_UNSUPPORTED
+    assert b"tcgen05" in lib.nsa_last_error()                                                      # D = 32
+    assert lib.nsa_cmp_block_scores(1, 1, None, 1, 1, 4, 1, 256, 15, 64, 4, 32, 16, 0, 64, 0, 1, 0.125, 0, 0, 0, 0, None) == ERR_ARG
+    b = _lib.FwdArgs()
+    b.Q = b.out = b.K = b.V = 1
+    b.B, b.H, b.Hkv, b.Tq, b.Tk, b.D = 1, 4, 1, 64, 64, 64
+    b.branches, b.fused, b.window, b.q_dtype, b.kv_dtype = 4, 1, 16, 0, 0
+    b.nsplit = 17
+    assert lib.nsa_attention_fwd(C.byref(b), None) == ERR_ARG and b"nsplit" in lib.nsa_last_error()
+    b.nsplit, b.io_layout = 0, 8
+    assert lib.nsa_attention_fwd(C.byref(b), None) == ERR_ARG and b"io_layout" in lib.nsa_last_error()
+    b.io_layout, b.fused, b.accumulate = 0, 0, 1
+    assert lib.nsa_attention_fwd(C.byref(b), None) == ERR_ARG and b"accumulate" in lib.nsa_last_error()
 
 
 def test_no_cpu_fallback():
