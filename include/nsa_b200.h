@@ -120,8 +120,10 @@ int nsa_topk_from_scores(const float* scores, int32_t* idx, int BH, int nq, int 
  *   fused == 0: exactly one branch; writes out (same 16-bit type as compute) and lse.
  *   fused == 1: writes out = sum_b gate_b * branch_b (gates from gate logits, or the
  *               constant of zero logits when gates == NULL); lse is not written.
- * K/V may be fp8 (kv_dtype) with per-tensor scales; they are dequantised to bf16 as
- * bf16(fp32(x) * scale) while being staged, never materialised. */
+ * Q (and K/V) may be fp8 with per-tensor scales; they are dequantised to bf16 as
+ * bf16(fp32(x) * scale) while being staged.  kv_dtype is q_dtype, or NSA_BF16 beside an fp8 Q
+ * (tcgen05 kernel only): K/V dequantised once by nsa_fp8_dequantize, so that a K/V tile is not
+ * converted again by every query block that attends it; k_scale / v_scale are then unused. */
 /* io_layout bits of nsa_fwd_args: the caller's token-major tensors used as they are
  * (nsa/model/llama_nsa.py:82 permutes the gate logits to [B,H,T,3] and :94 transposes the
  * result back to [B,T,H*D]; with these bits neither copy exists). */
@@ -282,6 +284,12 @@ int nsa_fp8_absmax(const void* x, int64_t n, int dtype, float* absmax, nsa_strea
  * Replaces: (x/scale).clamp(-max,max).to(fmt), nsa/triton/fp8.py:39-40. */
 int nsa_fp8_quantize(const void* x, void* out8, int64_t n, int dtype, int fmt, float scale,
                      nsa_stream_t stream);
+
+/* out[i] = bf16( fp32(x8[i]) * scale ), n elements; x8 holds `fmt` (NSA_FP8_E4M3 / NSA_FP8_E5M2) bytes, both
+ * pointers 16-byte aligned.  The operands the reference's wrapper builds before it attends; with GQA, K and V
+ * are a small fraction of Q, so the forward dequantises them once here and converts only Q inside the kernel.
+ * Replaces: Q.to(torch.bfloat16) * scale_q etc., nsa/triton/fp8.py:67-69. */
+int nsa_fp8_dequantize(const void* x8, void* out, int64_t n, int fmt, float scale, nsa_stream_t stream);
 
 /* dst (16-bit `dtype`) = round(src fp32), n elements.
  * Replaces: dQ_f.to(Q.dtype) etc., nsa/triton/backward.py:195. */

@@ -92,6 +92,7 @@ PROTOTYPES = {
     "nsa_combine": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp]),
     "nsa_fp8_absmax": (_i, [_vp, _i64, _i, _vp, _vp]),
     "nsa_fp8_quantize": (_i, [_vp, _vp, _i64, _i, _i, _f, _vp]),
+    "nsa_fp8_dequantize": (_i, [_vp, _vp, _i64, _i, _f, _vp]),
     "nsa_cast_from_f32": (_i, [_vp, _vp, _i64, _i, _vp]),
     "nsa_rope_to_heads": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "nsa_cache_append": (_i, [_vp] * 7 + [_i] * 12 + [_vp]),

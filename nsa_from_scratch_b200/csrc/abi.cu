@@ -30,6 +30,7 @@ int pool_mean_bwd(const float*, float*, int, int, int, int, int, int, int, cudaS
 int combine(const void*, const void*, const void*, const void*, void*, long long, int, int, int, int, cudaStream_t);
 int fp8_absmax(const void*, long long, int, float*, cudaStream_t);
 int fp8_quantize(const void*, void*, long long, int, int, float, cudaStream_t);
+int fp8_dequantize(const void*, void*, long long, int, float, cudaStream_t);
 int bwd_delta(const void*, const void*, float*, long long, int, int, cudaStream_t);
 int cast_from_f32(const float*, void*, long long, int, cudaStream_t);
 int cache_append(const void*, const void*, void*, void*, void*, void*, void*, int, int, int, int, int, int32_t*, int, int, int, int, int,
@@ -52,7 +53,8 @@ static int check_fwd(const nsa_fwd_args& a) {
   NSA_REQUIRE(a.Tq > 0 && a.Tk > 0, NSA_ERR_ARG, "attention forward: Tq=%d Tk=%d", a.Tq, a.Tk);
   NSA_REQUIRE(a.D == 32 || a.D == 64 || a.D == 128, NSA_ERR_UNSUPPORTED, "attention forward: head dim %d not in {32,64,128}", a.D);
   NSA_REQUIRE(is16(a.q_dtype) || is8(a.q_dtype), NSA_ERR_UNSUPPORTED, "attention forward: q dtype %d", a.q_dtype);
-  NSA_REQUIRE(a.kv_dtype == a.q_dtype, NSA_ERR_UNSUPPORTED, "attention forward: K/V dtype %d differs from Q dtype %d", a.kv_dtype, a.q_dtype);
+  NSA_REQUIRE(a.kv_dtype == a.q_dtype || (is8(a.q_dtype) && a.kv_dtype == NSA_BF16), NSA_ERR_UNSUPPORTED,
+              "attention forward: K/V dtype %d with Q dtype %d (K/V share Q's type, or are bf16 beside an fp8 Q)", a.kv_dtype, a.q_dtype);
   const int br = a.branches;
   NSA_REQUIRE(br > 0 && br < 8, NSA_ERR_ARG, "attention forward: branch mask %d", br);
   NSA_REQUIRE(a.nsplit >= 0 && a.nsplit <= 16, NSA_ERR_ARG, "attention forward: nsplit %d not in [0, 16]", a.nsplit);
@@ -92,7 +94,7 @@ using namespace nsa;
 extern "C" {
 
 const char* nsa_last_error(void) { return g_err; }
-int nsa_abi_version(void) { return 5; }
+int nsa_abi_version(void) { return 6; }
 
 int nsa_pool_mean(const void* x, void* out, int B, int H, int T, int D, int block, int stride, int n_out, int dtype,
                   float dequant_scale, nsa_stream_t stream) {
@@ -158,10 +160,12 @@ int nsa_attention_fwd(const nsa_fwd_args* args, nsa_stream_t stream) {
     // One block list per query head makes the tcgen05 kernel stage the union of four lists for 256 rows of
     // which 64 use each block; measured, a selected-only launch at D=64 is then faster on the generic
     // kernel (1.36 ms against 1.90 ms at B=2, T=32768, Hq=12, Hkv=1), everything else on tcgen05.
-    const bool sel_only_per_head = !args->fused && args->branches == NSA_BRANCH_SELECTED && args->Hi == args->H && args->D == 64;
+    const bool sel_only_per_head = !args->fused && args->branches == NSA_BRANCH_SELECTED && args->Hi == args->H && args->D == 64 &&
+                                   args->kv_dtype == args->q_dtype;
     if (!sel_only_per_head) return attention_fwd_tc5(*args, (cudaStream_t)stream);
   }
   NSA_REQUIRE(args->dyn_len == nullptr, NSA_ERR_UNSUPPORTED, "attention forward: a device-resident length needs the tcgen05 kernel");
+  NSA_REQUIRE(args->kv_dtype == args->q_dtype, NSA_ERR_UNSUPPORTED, "attention forward: bf16 K/V beside an fp8 Q need the tcgen05 kernel");
   NSA_REQUIRE(args->accumulate == 0 && !(args->fused && args->lse != nullptr), NSA_ERR_UNSUPPORTED,
               "attention forward: accumulate / lse of a fused launch need the tcgen05 kernel");
   return attention_fwd_generic(*args, (cudaStream_t)stream);
@@ -274,6 +278,12 @@ int nsa_fp8_absmax(const void* x, int64_t n, int dtype, float* absmax, nsa_strea
 int nsa_fp8_quantize(const void* x, void* out8, int64_t n, int dtype, int fmt, float scale, nsa_stream_t stream) {
   NSA_REQUIRE(x && out8, NSA_ERR_ARG, "quantize: NULL pointer");
   return fp8_quantize(x, out8, n, dtype, fmt, scale, (cudaStream_t)stream);
+}
+
+int nsa_fp8_dequantize(const void* x8, void* out, int64_t n, int fmt, float scale, nsa_stream_t stream) {
+  NSA_REQUIRE(x8 && out, NSA_ERR_ARG, "dequantize: NULL pointer");
+  NSA_REQUIRE(n >= 0, NSA_ERR_ARG, "dequantize: n=%lld", (long long)n);
+  return fp8_dequantize(x8, out, n, fmt, scale, (cudaStream_t)stream);
 }
 
 int nsa_cast_from_f32(const float* src, void* dst, int64_t n, int dtype, nsa_stream_t stream) {

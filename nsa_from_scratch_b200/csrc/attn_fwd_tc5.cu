@@ -56,6 +56,7 @@ struct Tc5Params {
   int NQG;         // query-block groups = ceil(nq / (4/GH))
   int nsplit;      // split launches: thread blocks per work item, each with a share of every branch's key tiles
   float* part;     // split launches: partial results [B*H*Tq][nsplit][3][D+4] = unnormalised O, m (log2 units), l
+  int kv8;         // fp8 launches: K/V are fp8 too (converted tile by tile); 0 = K/V arrive as bf16, only Q is fp8
 };
 
 struct Tile {
@@ -315,7 +316,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
       for (int br = 0; br < 3 && ok; ++br) {
         const CUtensorMap* mk = br == 0 ? &p.tmKc : &p.tmK;
         const CUtensorMap* mv = br == 0 ? &p.tmVc : &p.tmV;
-        const bool raw8 = IN8 && br != 0;      // pooled K/V of the compressed branch are already 16-bit
+        const bool raw8 = IN8 && br != 0 && p.kv8;   // pooled K/V of the compressed branch are 16-bit already
         for (int t = tbeg(br); t < tend(br) && ok; ++t, ++it) {
           const Tile tl = get_tile(br, t);
           const int s = it & 1, ph = (it >> 1) & 1;
@@ -499,7 +500,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
       }
       int it = 0, u8 = 1;
       for (int br = 0; br < 3 && ok; ++br) {
-        if (br == 0) { it += tend(0) - tbeg(0); continue; }   // pooled tiles come straight from TMA
+        if (br == 0 || !p.kv8) { it += tend(br) - tbeg(br); continue; }   // 16-bit tiles come straight from TMA
         for (int t = tbeg(br); t < tend(br) && ok; ++t, ++it, ++u8) {
           const Tile tl = get_tile(br, t);
           const int s = it & 1, ph = (it >> 1) & 1;
@@ -905,7 +906,8 @@ int make_map(CUtensorMap* m, const void* ptr, long long slabs, long long rows, i
 
 bool attention_fwd_tc5_supports(const nsa_fwd_args& a) {
   const bool in8 = a.q_dtype == NSA_FP8_E4M3 || a.q_dtype == NSA_FP8_E5M2;
-  if (!(a.q_dtype == NSA_BF16 || a.q_dtype == NSA_FP16 || in8) || a.kv_dtype != a.q_dtype) return false;
+  if (!(a.q_dtype == NSA_BF16 || a.q_dtype == NSA_FP16 || in8)) return false;
+  if (a.kv_dtype != a.q_dtype && !(in8 && a.kv_dtype == NSA_BF16)) return false;   // fp8 Q may come with bf16 K/V
   if (in8 && !(a.q_scale > 0.f && a.k_scale > 0.f && a.v_scale > 0.f)) return false;
   if (!(a.D == 64 || a.D == 128)) return false;
   if (!(a.scale > 0.f)) return false;
@@ -933,12 +935,14 @@ int attention_fwd_tc5(const nsa_fwd_args& a, cudaStream_t st) {
     p.HG = G / p.GH;
   }
   int rc;
-  if (in8) {
-    if ((rc = make_map8(&p.tmQ, a.Q, (long long)a.B * a.H, a.Tq, a.D)) != NSA_OK) return rc;
+  p.kv8 = in8 && a.kv_dtype == a.q_dtype;
+  if (in8) rc = make_map8(&p.tmQ, a.Q, (long long)a.B * a.H, a.Tq, a.D);
+  else rc = make_map(&p.tmQ, a.Q, (long long)a.B * a.H, a.Tq, a.D, cdt);
+  if (rc != NSA_OK) return rc;
+  if (p.kv8) {
     if ((rc = make_map8(&p.tmK, a.K, (long long)a.B * a.Hkv, a.Tk, a.D)) != NSA_OK) return rc;
     if ((rc = make_map8(&p.tmV, a.V, (long long)a.B * a.Hkv, a.Tk, a.D)) != NSA_OK) return rc;
   } else {
-    if ((rc = make_map(&p.tmQ, a.Q, (long long)a.B * a.H, a.Tq, a.D, cdt)) != NSA_OK) return rc;
     if ((rc = make_map(&p.tmK, a.K, (long long)a.B * a.Hkv, a.Tk, a.D, cdt)) != NSA_OK) return rc;
     if ((rc = make_map(&p.tmV, a.V, (long long)a.B * a.Hkv, a.Tk, a.D, cdt)) != NSA_OK) return rc;
   }

@@ -204,9 +204,9 @@ def _fused_forward(Q, K, V, cfg, scale, stride_c, gate_logits, block_indices, sq
 
 def nsa_forward_fp8(Q: Tensor, K: Tensor, V: Tensor, scale_q: float, scale_k: float, scale_v: float, cfg, *,
                     gate_logits: Optional[Tensor] = None, block_indices: Optional[Tensor] = None) -> Tensor:
-    """The combined forward on fp8 (e4m3/e5m2) Q/K/V with per-tensor scales; every kernel
-    dequantises to bf16(fp32(x)*scale) as it loads, so the result equals `nsa_forward` on the
-    dequantised bf16 tensors.  Inference only.  Returns bf16."""
+    """The combined forward on fp8 (e4m3/e5m2) Q/K/V with per-tensor scales; the operands are
+    bf16(fp32(x)*scale) everywhere (Q converted as the kernel loads it, K/V once in front of it), so the
+    result equals `nsa_forward` on the dequantised bf16 tensors.  Inference only.  Returns bf16."""
     assert Q.dtype in (torch.float8_e4m3fn, torch.float8_e5m2) and K.dtype == Q.dtype and V.dtype == Q.dtype
     D = Q.shape[-1]
     scale = cfg.scale if cfg.scale is not None else 1.0 / (D ** 0.5)

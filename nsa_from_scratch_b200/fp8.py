@@ -1,6 +1,7 @@
 """FP8 storage path.  Same signatures as the reference's nsa/triton/fp8.py:20-58; the
-dequantisation bf16(fp32(x)*scale) happens inside the attention kernel while tiles are
-staged, never as a separate pass."""
+dequantisation bf16(fp32(x)*scale) of Q happens inside the attention kernel while its tiles
+are staged; K and V, whose tiles every attending query block uses again, are dequantised once
+in front of the tcgen05 kernel (ops.attention_fwd) and inside the generic kernel otherwise."""
 from __future__ import annotations
 
 from typing import Optional

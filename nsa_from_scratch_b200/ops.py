@@ -132,7 +132,7 @@ def attention_fwd(
     gates: Optional[Tensor] = None, gate_act: int = L.GATE_SIGMOID, offset: Optional[int] = None,
     q_scale: float = 1.0, k_scale: float = 1.0, v_scale: float = 1.0, engine: Optional[int] = None,
     want_lse: bool = True, token_major: bool = False, nsplit: int = 1, dyn_len: Optional[Tensor] = None,
-    accumulate_into: Optional[Tensor] = None, fused_lse: bool = False,
+    accumulate_into: Optional[Tensor] = None, fused_lse: bool = False, dequant_kv: Optional[bool] = None,
 ) -> Tuple[Tensor, Optional[Tensor]]:
     """One launch of nsa_attention_fwd.  Returns (out, lse); lse is None for fused launches.
     `token_major`: gates are [B,Tq,H,3] and the result comes back as [B,Tq,H,D] (Q, K, V stay
@@ -141,7 +141,9 @@ def attention_fwd(
     launches with few query blocks and long key ranges (decoding).  `dyn_len`: int32 device scalar with the
     number of filled key positions; K/V/Kc/Vc are then allocations and every offset is derived on the device.
     `accumulate_into`: the output of an earlier fused launch (other branches); this launch adds its branches to it
-    and returns the same tensor.  `fused_lse`: a fused launch of ONE branch also returns that branch's lse."""
+    and returns the same tensor.  `fused_lse`: a fused launch of ONE branch also returns that branch's lse.
+    `dequant_kv` (fp8 inputs): True/False forces / forbids the one-off dequantisation of K and V in front of the
+    launch; None decides by kernel (see below).  The results are identical either way."""
     _need_cuda(Q, K, V)
     B, H, Tq, D = Q.shape
     Hkv, Tk = K.shape[1], K.shape[2]
@@ -149,9 +151,19 @@ def attention_fwd(
         raise ValueError(f"K/V shapes {tuple(K.shape)}/{tuple(V.shape)} do not match Q {tuple(Q.shape)}")
     if H % Hkv:
         raise ValueError(f"query heads {H} not a multiple of KV heads {Hkv}")
-    if K.dtype != Q.dtype or V.dtype != Q.dtype:
-        raise TypeError("Q, K, V must share a dtype")
+    if V.dtype != K.dtype or (K.dtype != Q.dtype and not (Q.dtype in _8 and K.dtype == torch.bfloat16)):
+        raise TypeError("Q, K, V must share a dtype (or bf16 K/V beside an fp8 Q)")
     Q, K, V = Q.contiguous(), K.contiguous(), V.contiguous()
+    eng = _ENGINE if engine is None else engine
+    if Q.dtype in _8 and K.dtype == Q.dtype and eng != L.ENGINE_GENERIC and D in (64, 128):
+        # The tcgen05 kernel takes an fp8 Q with bf16 K/V: a K/V tile is used by every query block that attends it,
+        # so K and V are dequantised ONCE here (with GQA they are a small fraction of Q) instead of once per use
+        # inside the kernel, where the conversion, not the tensor pipe, set the pace; Q's tiles are used once and
+        # stay fp8 in HBM.  A selected-only launch with one list per head at D=64 runs on the generic kernel.
+        per_head_sel = (not fused and branches == L.BRANCH_SELECTED and idx is not None and idx.shape[1] == H and D == 64
+                        and eng == L.ENGINE_AUTO)
+        if (not per_head_sel) if dequant_kv is None else dequant_kv:
+            K, V = fp8_dequantize(K, k_scale), fp8_dequantize(V, v_scale)
     out_dtype = torch.bfloat16 if Q.dtype in _8 else Q.dtype
     if accumulate_into is not None:
         out = accumulate_into
@@ -167,9 +179,9 @@ def attention_fwd(
     a.B, a.H, a.Hkv, a.Tq, a.Tk, a.D = B, H, Hkv, Tq, Tk, D
     a.offset = Tk - Tq if offset is None else offset
     a.causal, a.branches, a.fused, a.gate_act = int(causal), branches, int(fused), gate_act
-    a.q_dtype = a.kv_dtype = L.dtype_code(Q.dtype)
+    a.q_dtype, a.kv_dtype = L.dtype_code(Q.dtype), L.dtype_code(K.dtype)
     a.scale, a.q_scale, a.k_scale, a.v_scale = float(scale), float(q_scale), float(k_scale), float(v_scale)
-    a.engine = _ENGINE if engine is None else engine
+    a.engine = eng
     keep = [Q, K, V]
     if branches & L.BRANCH_COMPRESSED:
         Kc, Vc = Kc.contiguous(), Vc.contiguous()
@@ -358,6 +370,17 @@ def fp8_absmax(x: Tensor) -> Tensor:
     with torch.cuda.device(x.device):
         L.check(L.load().nsa_fp8_absmax(x.data_ptr(), x.numel(), L.dtype_code(x.dtype), out.data_ptr(), L.stream_ptr()),
                 "nsa_fp8_absmax")
+    return out
+
+
+def fp8_dequantize(x8: Tensor, scale: float) -> Tensor:
+    """bf16(fp32(x8) * scale): the tensor the reference's wrapper attends on (nsa/triton/fp8.py:67-69)."""
+    _need_cuda(x8)
+    x8 = x8.contiguous()
+    out = torch.empty(x8.shape, device=x8.device, dtype=torch.bfloat16)
+    with torch.cuda.device(x8.device):
+        L.check(L.load().nsa_fp8_dequantize(x8.data_ptr(), out.data_ptr(), x8.numel(), L.dtype_code(x8.dtype), float(scale),
+                                            L.stream_ptr()), "nsa_fp8_dequantize")
     return out
 
 

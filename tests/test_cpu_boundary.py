@@ -19,7 +19,7 @@ def test_library_exports_every_declared_symbol():
     assert declared == set(_lib.PROTOTYPES), declared ^ set(_lib.PROTOTYPES)
     for name in declared:
         assert hasattr(lib, name), name
-    assert lib.nsa_abi_version() == 5
+    assert lib.nsa_abi_version() == 6
 
 
 def _struct_fields(header, name):
@@ -77,6 +77,16 @@ def test_argument_errors_are_reported_without_a_gpu():
     assert lib.nsa_attention_fwd(C.byref(b), None) == ERR_ARG and b"io_layout" in lib.nsa_last_error()
     b.io_layout, b.fused, b.accumulate = 0, 0, 1
     assert lib.nsa_attention_fwd(C.byref(b), None) == ERR_ARG and b"accumulate" in lib.nsa_last_error()
+    # K/V share Q's type, or are bf16 beside an fp8 Q -- nothing else
+    b.accumulate, b.q_dtype, b.kv_dtype = 0, 0, 2
+    assert lib.nsa_attention_fwd(C.byref(b), None) == ERR_UNSUPPORTED and b"K/V dtype" in lib.nsa_last_error()
+    b.q_dtype, b.kv_dtype = 2, 1
+    assert lib.nsa_attention_fwd(C.byref(b), None) == ERR_UNSUPPORTED and b"K/V dtype" in lib.nsa_last_error()
+    assert lib.nsa_fp8_dequantize(None, 16, 16, 2, 1.0, None) == ERR_ARG
+    assert lib.nsa_fp8_dequantize(16, 16, 16, 0, 1.0, None) == ERR_ARG and b"format" in lib.nsa_last_error()
+    assert lib.nsa_fp8_dequantize(16, 16, 16, 2, 0.0, None) == ERR_ARG and b"scale" in lib.nsa_last_error()
+    assert lib.nsa_fp8_dequantize(16, 24, 16, 2, 1.0, None) == ERR_ARG and b"aligned" in lib.nsa_last_error()
+    assert lib.nsa_fp8_dequantize(16, 16, -1, 2, 1.0, None) == ERR_ARG
 
 
 def test_no_cpu_fallback():

@@ -283,6 +283,31 @@ def test_fp8_paths_vs_bf16_and_oracle(nsa):
     assert max_abs(f8, ref) <= TOL8
 
 
+@pytest.mark.parametrize("fmt", [torch.float8_e4m3fn, torch.float8_e5m2])
+def test_fp8_dequantize_and_both_kv_routes_agree(nsa, fmt):
+    """nsa_fp8_dequantize gives bf16(fp32(x) * scale) bit for bit (ragged length too), and an fp8 launch gives the
+    same bits whether K/V are dequantised once in front of the kernel or tile by tile inside it."""
+    from nsa_from_scratch_b200 import _lib as L, ops
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(3, 1000 + 7, generator=g) * 3
+    x8, s = nsa.quantize_to_fp8(x.cuda(), fmt=fmt)
+    want = x8.to(torch.bfloat16) * s
+    assert torch.equal(ops.fp8_dequantize(x8, s), want)
+    assert torch.equal(ops.fp8_dequantize(x8.flatten()[:1000], 0.37), x8.flatten()[:1000].to(torch.bfloat16) * 0.37)
+    for D in (64, 128):
+        B, H, Hkv, T = 1, 8, 2, 640
+        q8, k8, v8 = (nsa.quantize_to_fp8(torch.randn(sh, generator=g).cuda(), fmt=fmt)
+                      for sh in ((B, H, T, D), (B, Hkv, T, D), (B, Hkv, T, D)))
+        idx = O.select_blocks(O.dequantize_fp8(q8[0].cpu(), q8[1]), O.dequantize_fp8(k8[0].cpu(), k8[1]), top_k=4).cuda()
+        kw = dict(branches=L.BRANCH_SELECTED | L.BRANCH_SLIDING, fused=True, causal=True, scale=D ** -0.5, idx=idx, window=128,
+                  q_scale=q8[1], k_scale=k8[1], v_scale=v8[1])
+        once, _ = ops.attention_fwd(q8[0], k8[0], v8[0], dequant_kv=True, **kw)
+        per_tile, _ = ops.attention_fwd(q8[0], k8[0], v8[0], dequant_kv=False, **kw)
+        assert torch.equal(once, per_tile)
+        ref, _ = ops.attention_fwd(*(t.to(torch.bfloat16) * s_ for t, s_ in (q8, k8, v8)), **{**kw, "q_scale": 1.0, "k_scale": 1.0, "v_scale": 1.0})
+        assert torch.equal(once, ref)
+
+
 def test_forward_is_bitwise_repeatable_and_errors_are_loud(nsa):
     Q, K, V, _ = make_qkv(8, 1, 4, 2, 512, 512, 64)
     cfg = nsa.NSAConfig(top_k=4, window_size=128)
