@@ -34,8 +34,11 @@ __device__ __forceinline__ void bstage16(uint32_t sdst, const T* src, int row0, 
   }
 }
 
+// Blocks per SM: the kernel is latency-bound (mma.sync chains, atomics), so at D <= 64 the register count is held
+// to 128 for four resident blocks (2.86 -> 2.68 ms at B=2, T=32768, Hq=12, Hkv=1, D=64); at D=128 shared memory
+// (80 KB per block) allows two.
 template <typename T, int D, int NW>
-__global__ void __launch_bounds__(NW * 32, 2) selected_bwd_kernel(const __grid_constant__ BwdK p) {
+__global__ void __launch_bounds__(NW * 32, D <= 64 ? 4 : 2) selected_bwd_kernel(const __grid_constant__ BwdK p) {
   constexpr int TM = 16 * NW;
   constexpr int NT = 32 * NW;
   constexpr int KS = D / 16;
