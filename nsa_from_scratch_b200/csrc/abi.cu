@@ -159,7 +159,7 @@ int nsa_attention_fwd(const nsa_fwd_args* args, nsa_stream_t stream) {
   if (args->engine == NSA_ENGINE_AUTO && tc5) {
     // One block list per query head makes the tcgen05 kernel stage the union of four lists for 256 rows of
     // which 64 use each block; measured, a selected-only launch at D=64 is then faster on the generic
-    // kernel (1.36 ms against 1.90 ms at B=2, T=32768, Hq=12, Hkv=1), everything else on tcgen05.
+    // kernel (0.99 ms against 1.90 ms at B=2, T=32768, Hq=12, Hkv=1), everything else on tcgen05.
     const bool sel_only_per_head = !args->fused && args->branches == NSA_BRANCH_SELECTED && args->Hi == args->H && args->D == 64 &&
                                    args->kv_dtype == args->q_dtype;
     if (!sel_only_per_head) return attention_fwd_tc5(*args, (cudaStream_t)stream);
