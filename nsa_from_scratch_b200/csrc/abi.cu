@@ -162,7 +162,14 @@ int nsa_attention_fwd(const nsa_fwd_args* args, nsa_stream_t stream) {
     // kernel (0.99 ms against 1.90 ms at B=2, T=32768, Hq=12, Hkv=1), everything else on tcgen05.
     const bool sel_only_per_head = !args->fused && args->branches == NSA_BRANCH_SELECTED && args->Hi == args->H && args->D == 64 &&
                                    args->kv_dtype == args->q_dtype;
-    if (!sel_only_per_head) return attention_fwd_tc5(*args, (cudaStream_t)stream);
+    // Multi-head attention (one KV head per query head) at D=64 with its per-head lists: a tcgen05 work item is then
+    // four query blocks of one head, whose four lists it merges and masks, so three quarters of the selected
+    // branch's MMA work is masked out; measured at B=1, T=65536, H=Hkv=16 the fused forward takes 3.47 ms on the
+    // generic kernel against 3.78 ms (equal at T=4096).
+    const bool mha_fused_d64 = args->fused && args->D == 64 && args->H == args->Hkv && (args->branches & NSA_BRANCH_SELECTED) &&
+                               is16(args->q_dtype) && args->kv_dtype == args->q_dtype && args->accumulate == 0 &&
+                               args->lse == nullptr && args->dyn_len == nullptr && args->nsplit <= 1;
+    if (!sel_only_per_head && !mha_fused_d64) return attention_fwd_tc5(*args, (cudaStream_t)stream);
   }
   NSA_REQUIRE(args->dyn_len == nullptr, NSA_ERR_UNSUPPORTED, "attention forward: a device-resident length needs the tcgen05 kernel");
   NSA_REQUIRE(args->kv_dtype == args->q_dtype, NSA_ERR_UNSUPPORTED, "attention forward: bf16 K/V beside an fp8 Q need the tcgen05 kernel");

@@ -618,6 +618,10 @@ def test_compressed_probability_scorer_vs_oracle(nsa, case):
     assert max_abs(out, o_ref) <= TOL16
     # compressed branch first, selected + sliding added to the same rows: the single-launch forward, bit for bit
     from nsa_from_scratch_b200.forward import _fused_forward
-    one = _fused_forward(Qc, Kc, Vc, cfg, D ** -0.5, stride, gates.cuda(), idx.cuda(), 1.0, 1.0, 1.0)
+    # (on the tcgen05 kernel, which the launches with `accumulate` run on; the default engine of a single launch is
+    # the generic kernel for multi-head attention at D=64)
+    from nsa_from_scratch_b200 import _lib as L
+    one = _fused_forward(Qc, Kc, Vc, cfg, D ** -0.5, stride, gates.cuda(), idx.cuda(), 1.0, 1.0, 1.0,
+                         engine=L.ENGINE_TCGEN05 if D in (64, 128) else None)
     assert torch.equal(out, one)
     ops.device_status()
