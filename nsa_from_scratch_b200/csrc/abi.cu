@@ -164,7 +164,7 @@ int nsa_attention_fwd(const nsa_fwd_args* args, nsa_stream_t stream) {
                                    args->kv_dtype == args->q_dtype;
     // Multi-head attention (one KV head per query head) at D=64 with its per-head lists: a tcgen05 work item is then
     // four query blocks of one head, whose four lists it merges and masks, so three quarters of the selected
-    // branch's MMA work is masked out; measured at B=1, T=65536, H=Hkv=16 the fused forward takes 3.47 ms on the
+    // branch's MMA work is masked out; measured at B=1, T=65536, H=Hkv=16 the fused forward takes 3.05 ms on the
     // generic kernel against 3.78 ms (equal at T=4096).
     const bool mha_fused_d64 = args->fused && args->D == 64 && args->H == args->Hkv && (args->branches & NSA_BRANCH_SELECTED) &&
                                is16(args->q_dtype) && args->kv_dtype == args->q_dtype && args->accumulate == 0 &&

@@ -79,7 +79,10 @@ __global__ void __launch_bounds__(NW * 32, D <= 64 ? 4 : 2) attn_fwd_generic_ker
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* Qs = smem;                               // TM x D, later the output staging tile
   unsigned char* KV = smem + TM * D * 2;                  // 2 stages x (K tile, V tile)
-  float* total = reinterpret_cast<float*>(KV + 4 * TN * D * 2);   // fused only: [D/2][NT] per-thread slots
+  // Fused launches: the gated sum of the finished branches, this thread's D/2 values.  Touched only at the two or
+  // three branch ends, so it lives in local memory (volatile keeps it out of the registers, which the launch bound
+  // holds to 128 at D <= 64, and out of shared memory, where its 16 KB per block cost a resident block per SM).
+  volatile float total[2 * KS * 4];
   __shared__ int sel_list[MAX_SEL];
   __shared__ int sel_n;
 
@@ -349,9 +352,8 @@ __global__ void __launch_bounds__(NW * 32, D <= 64 ? 4 : 2) attn_fwd_generic_ker
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           float v = o[d][e] * (e < 2 ? c0 : c1);
-          float* slot = total + (d * 4 + e) * NT + tid;
-          if (have_total) v += *slot;
-          if (last) o[d][e] = v; else *slot = v;
+          if (have_total) v += total[d * 4 + e];
+          if (last) o[d][e] = v; else total[d * 4 + e] = v;
         }
       }
       have_total = true;
@@ -384,7 +386,7 @@ __global__ void __launch_bounds__(NW * 32, D <= 64 ? 4 : 2) attn_fwd_generic_ker
 template <typename T, int D, int NW, bool IN8>
 static int launch_generic(const FwdK& k, cudaStream_t st) {
   constexpr int TM = 16 * NW;
-  size_t smem = (size_t)TM * D * 2 + 4 * (size_t)TN * D * 2 + (k.a.fused ? (size_t)TM * D * 4 : 0);
+  size_t smem = (size_t)TM * D * 2 + 4 * (size_t)TN * D * 2;
   auto fn = attn_fwd_generic_kernel<T, D, NW, IN8>;
   NSA_CUDA_OK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   long long blocks = (long long)k.a.B * k.a.H * k.n_qtiles;
