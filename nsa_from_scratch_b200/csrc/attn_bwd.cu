@@ -38,7 +38,7 @@ __device__ __forceinline__ void bstage16(uint32_t sdst, const T* src, int row0, 
 // to 128 for four resident blocks (2.86 -> 2.68 ms at B=2, T=32768, Hq=12, Hkv=1, D=64); at D=128 shared memory
 // (80 KB per block) allows two.
 template <typename T, int D, int NW>
-__global__ void __launch_bounds__(NW * 32, D <= 64 ? 4 : 2) selected_bwd_kernel(const __grid_constant__ BwdK p) {
+__global__ void __launch_bounds__(NW * 32, (D <= 64 ? 16 : 8) / NW) selected_bwd_kernel(const __grid_constant__ BwdK p) {
   constexpr int TM = 16 * NW;
   constexpr int NT = 32 * NW;
   constexpr int KS = D / 16;
@@ -228,13 +228,17 @@ __global__ void __launch_bounds__(NW * 32, D <= 64 ? 4 : 2) selected_bwd_kernel(
     // dV += P^T dO and dK += dS^T Q : 16 keys per pass
     float* dVg = a.dV_f + kv_slab;
     float* dKg = a.dK_f + kv_slab;
+    // Four warps cover the tile's 64 keys, 16 each.  With eight warps (128 query rows) warps 0-3 form dV while warps
+    // 4-7 form dK; with fewer, every warp does both in turn.
+    constexpr int NPASS = NW >= 8 ? 1 : 2;
 #pragma unroll 1
-    for (int pass = 0; pass < 2; ++pass) {
+    for (int pi = 0; pi < NPASS; ++pi) {
+      const int pass = NW >= 8 ? (warp >> 2) : pi;
       const uint32_t as_ = smem_u32(pass == 0 ? Ps : dSs);
       const uint32_t bs_ = pass == 0 ? dos_ : qs_;
       float* dst = pass == 0 ? dVg : dKg;
 #pragma unroll 1
-      for (int mt = warp; mt < 4; mt += NW) {
+      for (int mt = (NW >= 8 ? (warp & 3) : warp); mt < 4; mt += (NW >= 8 ? 4 : NW)) {
         float acc[2 * KS][4];
 #pragma unroll
         for (int d = 0; d < 2 * KS; ++d) { acc[d][0] = acc[d][1] = acc[d][2] = acc[d][3] = 0.f; }
@@ -293,7 +297,7 @@ template <typename T>
 static int bwd_dispatch(const BwdK& k, int nw, cudaStream_t st) {
   switch (k.a.D) {
     case 32: return nw == 4 ? launch_bwd<T, 32, 4>(k, st) : launch_bwd<T, 32, 2>(k, st);
-    case 64: return nw == 4 ? launch_bwd<T, 64, 4>(k, st) : launch_bwd<T, 64, 2>(k, st);
+    case 64: return nw == 8 ? launch_bwd<T, 64, 8>(k, st) : nw == 4 ? launch_bwd<T, 64, 4>(k, st) : launch_bwd<T, 64, 2>(k, st);
     case 128: return nw == 4 ? launch_bwd<T, 128, 4>(k, st) : launch_bwd<T, 128, 2>(k, st);
   }
   return fail(NSA_ERR_UNSUPPORTED, "selected backward: head dim %d not in {32,64,128}", k.a.D);
@@ -313,6 +317,9 @@ int attention_bwd(const nsa_bwd_args& a, cudaStream_t st) {
       tm = 32;
     }
   }
+  // Compressed and sliding branches at D=64: 128 query rows per block, so that a K/V tile is fetched, and its dK/dV
+  // partial sums are added atomically, once per 128 rows instead of once per 64.
+  else if (a.D == 64 && a.Tq >= 128) tm = 128;
   k.n_qtiles = (a.Tq + tm - 1) / tm;
   if (a.dtype == NSA_BF16) return bwd_dispatch<__nv_bfloat16>(k, tm / 16, st);
   if (a.dtype == NSA_FP16) return bwd_dispatch<__half>(k, tm / 16, st);
