@@ -218,9 +218,19 @@ int nsa_bwd_delta(const void* dO, const void* O, float* delta, int64_t rows, int
 /* Attention backward of ONE branch (nsa_bwd_args.branch = NSA_BRANCH_SELECTED / _SLIDING /
  * _COMPRESSED).  dQ [B,H,Tq,D] is WRITTEN (each query tile is owned by one
  * thread block) in dq_dtype (NSA_FP32 or the 16-bit input type).  dK_f, dV_f
- * [B,Hkv,Tk,D] are fp32 and are ACCUMULATED into with fp32 atomic adds (the caller
- * zeroes them), which also forms the sum over the query heads that share a KV head.
- * Rows with lse = -inf contribute nothing. */
+ * [B,Hkv,Tk,D] are fp32 and are ACCUMULATED into (the caller zeroes them); the sum over the
+ * query heads that share a KV head is formed here too.  Rows with lse = -inf contribute nothing.
+ *
+ * Two engines.  The tcgen05 engine (selected branch, 16-bit storage, D in {64,128}, 64x64 blocks,
+ * top_k <= 256) uses no floating-point atomics: it inverts the block lists (per key block, the
+ * query blocks that chose it), accumulates dK/dV of a key block in tensor memory over that
+ * list and writes them once, and forms dQ in a second, query-major pass; every sum has a fixed
+ * order, so dQ, dK and dV repeat bit for bit.  It needs caller-supplied scratch of
+ * nsa_attention_bwd_scratch_bytes() bytes (256-byte aligned; contents need neither be cleared nor
+ * preserved).  The generic engine (every other shape and branch; mma.sync) adds its dK/dV tiles
+ * with fp32 atomic adds, so their last bits depend on the order of arrival.
+ * engine = NSA_ENGINE_AUTO takes tcgen05 when the shape qualifies AND scratch is given, else generic;
+ * NSA_ENGINE_TCGEN05 fails with NSA_ERR_UNSUPPORTED / NSA_ERR_ARG instead of falling back. */
 typedef struct nsa_bwd_args {
   const void* Q;
   const void* K;
@@ -242,7 +252,16 @@ typedef struct nsa_bwd_args {
   int32_t branch;                               /* NSA_BRANCH_*; 0 is taken as NSA_BRANCH_SELECTED            */
   int32_t window;                               /* sliding                                                     */
   int32_t Nc, cmp_block, cmp_stride, cmp_offset; /* compressed: K, V, dK_f, dV_f are then [B,Hkv,Nc,D] (pooled) */
+  int32_t engine;                                /* NSA_ENGINE_*                                                */
+  void* scratch;                                 /* tcgen05 engine: nsa_attention_bwd_scratch_bytes() bytes      */
+  int64_t scratch_bytes;
 } nsa_bwd_args;
+
+/* Bytes of scratch the tcgen05 engine needs for this problem (0 when the shape does not qualify, so that
+ * the generic engine will run; negative NSA_ERR_* on a NULL argument).  Holds the inverted block lists, the
+ * work items and the partial dK/dV sums of key blocks whose list is split over several thread blocks.
+ * No counterpart in the reference (its kernel adds every tile atomically, nsa/triton/backward.py:98-118). */
+int64_t nsa_attention_bwd_scratch_bytes(const nsa_bwd_args* args);
 
 /* Replaces: selected_backward / _bwd_kernel, nsa/triton/backward.py:16-195 (branch forced to selected). */
 int nsa_selected_bwd(const nsa_bwd_args* args, nsa_stream_t stream);
@@ -260,7 +279,10 @@ int nsa_pool_mean_bwd(const float* dxc, float* dx, int B, int H, int T, int D, i
 
 /* The reference's native backward launcher, same argument list: dQ is bf16 and is
  * written; dK_f/dV_f are fp32 and accumulated into (zeroed by the caller, as
- * nsa/cuda/bindings.cpp:160-162 does).  Returns a status instead of void.
+ * nsa/cuda/bindings.cpp:160-162 does).  Returns a status instead of void.  The argument list has
+ * no room for scratch, so at D in {64,128} this entry point takes the tcgen05 engine's scratch
+ * from the stream-ordered allocator (cudaMallocAsync / cudaFreeAsync on `stream`): the one
+ * place in this library that allocates.
  * Replaces: launch_selected_attn_bwd, nsa/cuda/selected_bwd.cu:731-772
  * (declared at nsa/cuda/bindings.cpp:22-30). */
 int launch_selected_attn_bwd(const void* Q, const void* K, const void* V, const void* dO,

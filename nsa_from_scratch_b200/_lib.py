@@ -15,6 +15,7 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libnsa_b200.so")
 
 OK = 0
+ABI_VERSION = 7      # nsa_abi_version() of the library these struct mirrors and prototypes describe
 BF16, FP16, FP8_E4M3, FP8_E5M2, FP32 = 0, 1, 2, 3, 4
 BRANCH_COMPRESSED, BRANCH_SELECTED, BRANCH_SLIDING = 1, 2, 4
 GATE_SIGMOID, GATE_SOFTMAX = 0, 1
@@ -67,6 +68,7 @@ class BwdArgs(C.Structure):
         ("scale", C.c_float),
         ("branch", C.c_int32), ("window", C.c_int32),
         ("Nc", C.c_int32), ("cmp_block", C.c_int32), ("cmp_stride", C.c_int32), ("cmp_offset", C.c_int32),
+        ("engine", C.c_int32), ("scratch", C.c_void_p), ("scratch_bytes", C.c_int64),
     ]
 
 
@@ -87,6 +89,7 @@ PROTOTYPES = {
     "nsa_bwd_delta": (_i, [_vp, _vp, _vp, _i64, _i, _i, _vp]),
     "nsa_selected_bwd": (_i, [C.POINTER(BwdArgs), _vp]),
     "nsa_attention_bwd": (_i, [C.POINTER(BwdArgs), _vp]),
+    "nsa_attention_bwd_scratch_bytes": (_i64, [C.POINTER(BwdArgs)]),
     "nsa_pool_mean_bwd": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "launch_selected_attn_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "nsa_combine": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp]),
@@ -109,13 +112,19 @@ def load() -> C.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    if not os.path.exists(LIB_PATH):
-        from . import build as _build
-        _build.build()
+    from . import build as _build
+    try:
+        _build.build()               # returns at once when the stamp of the source hashes matches the built library
+    except RuntimeError:
+        if not os.path.exists(LIB_PATH):
+            raise                    # nothing to load; with a library present (no nvcc on this machine) the ABI check decides
     lib = C.CDLL(LIB_PATH)
     for name, (res, args) in PROTOTYPES.items():
         fn = getattr(lib, name)      # AttributeError if the symbol is missing
         fn.restype, fn.argtypes = res, args
+    if lib.nsa_abi_version() != ABI_VERSION:
+        raise RuntimeError(f"{LIB_PATH} has ABI version {lib.nsa_abi_version()}, this package expects {ABI_VERSION}: "
+                           "rebuild with `python -m nsa_from_scratch_b200.build --force`")
     _lib = lib
     return lib
 

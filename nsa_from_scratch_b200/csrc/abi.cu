@@ -26,6 +26,10 @@ int attention_fwd_tc5(const nsa_fwd_args&, cudaStream_t);
 bool attention_fwd_tc5_supports(const nsa_fwd_args&);
 int tc5_take_status(cudaStream_t, int*);
 int attention_bwd(const nsa_bwd_args&, cudaStream_t);
+bool attention_bwd_tc5_supports(const nsa_bwd_args&);
+long long attention_bwd_tc5_scratch_bytes(const nsa_bwd_args&);
+int attention_bwd_tc5(const nsa_bwd_args&, void*, long long, cudaStream_t);
+int bw5_take_status(int*);
 int pool_mean_bwd(const float*, float*, int, int, int, int, int, int, int, cudaStream_t);
 int combine(const void*, const void*, const void*, const void*, void*, long long, int, int, int, int, cudaStream_t);
 int fp8_absmax(const void*, long long, int, float*, cudaStream_t);
@@ -94,7 +98,7 @@ using namespace nsa;
 extern "C" {
 
 const char* nsa_last_error(void) { return g_err; }
-int nsa_abi_version(void) { return 6; }
+int nsa_abi_version(void) { return 7; }
 
 int nsa_pool_mean(const void* x, void* out, int B, int H, int T, int D, int block, int stride, int n_out, int dtype,
                   float dequant_scale, nsa_stream_t stream) {
@@ -185,6 +189,9 @@ int nsa_device_status(nsa_stream_t stream) {
   int v2 = 0;
   if ((rc = cs5_take_status(&v2)) != NSA_OK) return rc;
   if (v == 0 && v2 != 0) v = 100 + v2;
+  int v3 = 0;
+  if ((rc = bw5_take_status(&v3)) != NSA_OK) return rc;
+  if (v == 0 && v3 != 0) v = 200 + v3;
   if (v != 0) return fail(NSA_ERR_DEVICE, "a kernel gave up waiting on barrier %d (bounded wait expired)", v - 1);
   return NSA_OK;
 }
@@ -240,7 +247,25 @@ int nsa_attention_bwd(const nsa_bwd_args* a, nsa_stream_t stream) {
   int rc = check_bwd(&b);
   if (rc != NSA_OK) return rc;
   if (b.branch == NSA_BRANCH_COMPRESSED && b.Nc == 0) return NSA_OK;
+  NSA_REQUIRE(b.engine == NSA_ENGINE_AUTO || b.engine == NSA_ENGINE_GENERIC || b.engine == NSA_ENGINE_TCGEN05, NSA_ERR_ARG,
+              "attention backward: engine %d", b.engine);
+  const bool tc5 = attention_bwd_tc5_supports(b);
+  if (b.engine == NSA_ENGINE_TCGEN05) {
+    NSA_REQUIRE(tc5, NSA_ERR_UNSUPPORTED, "attention backward: the tcgen05 engine does not take this shape or branch");
+    return attention_bwd_tc5(b, b.scratch, b.scratch_bytes, (cudaStream_t)stream);
+  }
+  if (b.engine == NSA_ENGINE_AUTO && tc5 && b.scratch != nullptr) return attention_bwd_tc5(b, b.scratch, b.scratch_bytes, (cudaStream_t)stream);
   return attention_bwd(b, (cudaStream_t)stream);
+}
+
+int64_t nsa_attention_bwd_scratch_bytes(const nsa_bwd_args* a) {
+  NSA_REQUIRE(a, NSA_ERR_ARG, "attention backward: NULL argument block");
+  nsa_bwd_args b = *a;
+  if (b.branch == 0) b.branch = NSA_BRANCH_SELECTED;
+  // sizes only: the pointers may still be NULL when the caller asks how much to allocate
+  if (!(b.B > 0 && b.H > 0 && b.Hkv > 0 && b.H % b.Hkv == 0 && b.Tq > 0 && b.Tk > 0 && b.nq > 0 && b.top_k > 0)) return 0;
+  if (!attention_bwd_tc5_supports(b)) return 0;
+  return attention_bwd_tc5_scratch_bytes(b);
 }
 
 int nsa_selected_bwd(const nsa_bwd_args* a, nsa_stream_t stream) {
@@ -268,7 +293,16 @@ int launch_selected_attn_bwd(const void* Q, const void* K, const void* V, const 
   a.B = 1; a.H = BH; a.Hkv = BH; a.Hi = BH; a.Tq = Tq_p; a.Tk = Tk_p; a.D = D;
   a.nq = n_q_blocks; a.top_k = top_k; a.bm = 64; a.bn = 64; a.sel_key_limit = Tk_p;
   a.offset = offset; a.causal = causal; a.dtype = NSA_BF16; a.dq_dtype = NSA_BF16; a.scale = sm_scale;
-  return nsa_selected_bwd(&a, stream);
+  a.branch = NSA_BRANCH_SELECTED;
+  const int64_t need = nsa_attention_bwd_scratch_bytes(&a);
+  if (need <= 0) return nsa_selected_bwd(&a, stream);
+  void* scratch = nullptr;
+  NSA_CUDA_OK(cudaMallocAsync(&scratch, (size_t)need, (cudaStream_t)stream));
+  a.scratch = scratch;
+  a.scratch_bytes = need;
+  const int rc = nsa_selected_bwd(&a, stream);
+  NSA_CUDA_OK(cudaFreeAsync(scratch, (cudaStream_t)stream));
+  return rc;
 }
 
 int nsa_combine(const void* out_c, const void* out_s, const void* out_w, const void* gates, void* out, int64_t rows,

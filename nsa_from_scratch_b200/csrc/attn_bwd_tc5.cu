@@ -1,0 +1,720 @@
+// Selected-branch backward on the 5th-generation tensor cores (tcgen05 + TMEM + TMA), sm_100a.
+// No atomics on floating-point data anywhere: every sum is formed in a fixed order, so dQ, dK and dV
+// repeat bit for bit.
+//
+// Two passes over the same pairs (64 query rows of one head) x (one selected 64-key block):
+//
+//   key-major pass (dK, dV).  An inverted index -- per (batch, KV head, key block) the list of row
+//   groups (query head, query block) that selected it -- is built first (count, scan, ordered fill).
+//   A thread block owns one key block, or one segment of a long list.  K and V of the block stay in shared
+//   memory; the row groups stream by, two at a time (128 rows), through a TMA ring:
+//       S  = Q K^T   dP = dO V^T                      (tcgen05.mma, fp32 in TMEM)
+//       P  = exp2(S*scale*log2e - lse*log2e)  dS = P (dP - delta) scale   (softmax warps; 16-bit to shared memory)
+//       [dV | . ; . | dK] += [P^T ; dS^T] [dO | Q]      (one M=128 MMA per 16 query rows; the off-diagonal quadrants
+//                                                      are computed and dropped: the two useful products have M = 64)
+//   dV and dK of the block accumulate in TMEM over the whole list (all query heads of the GQA group included)
+//   and are written once.  Segments of a long list leave partial sums that a small kernel adds in segment order.
+//
+//   query-major pass (dQ).  A thread block owns 128 query rows: two heads of a GQA group that share a block
+//   list (64 rows of one head when every head has its own list).  Q and dO stay in shared memory, the listed
+//   K/V blocks stream by:  S, dP, dS as above, then dQ += dS K (A = dS from shared memory, B = K MN-major).
+//
+// Warp roles (12 warps; setmaxnreg moves registers from the control warps to the softmax warps):
+//   warp 0  TMA producer      warp 1  MMA issuer      warp 2  block-list builder (query-major pass)
+//   warps 4-7 and 8-11: two softmax groups, alternating steps (thread = TMEM lane = row of the 128-row tile)
+// TMEM columns: S/dP of step parity 0 at [0,64)/[64,128), of parity 1 at [128,192)/[192,256), accumulator from 256.
+// Every mbarrier wait is bounded; a wait that gives up raises a block-wide abort flag, the block drains its
+// copies (bounded), frees its TMEM, and the status word reports it.
+#include "common.cuh"
+#include "tc5_ptx.cuh"
+
+#include <cudaTypedefs.h>
+
+namespace nsa {
+
+using namespace tc5;
+
+int make_map(CUtensorMap* m, const void* ptr, long long slabs, long long rows, int D, int dtype);   // attn_fwd_tc5.cu
+
+__device__ int g_bw5_status;   // 0 ok; otherwise (1 + id of the barrier a wait gave up on)
+
+constexpr int BW5_THREADS = 384;
+constexpr int BW5_MAX_SEL = 256;      // listed blocks per query block (query-major pass)
+constexpr int BW5_QB_BITS = 20;       // row group = (head within the group << 20) | query block
+
+struct Bw5Params {
+  CUtensorMap tmQ, tmdO, tmK, tmV;
+  nsa_bwd_args a;
+  float scale_log2;
+  int nkb;                 // key blocks
+  int G;                   // query heads per KV head
+  int shared;              // one block list per KV head (1) or per query head (0)
+  // key-major pass
+  const int4* items;       // [owners][capW]: (key block, first row group, row groups, partial slot or -1)
+  const int* n_items;      // [owners]
+  int capW;
+  const uint32_t* rg_list; // [owners][cap_rg]
+  long long cap_rg;
+  float* partials;         // [owners][capP][2][64][D]
+  int capP;
+  // query-major pass
+  int NG;                  // row groups (heads) per tile: 2 or 1
+  int NGT;                 // tiles per (batch, KV head, query block)
+};
+
+enum { BW_RES = 0, BW_STFULL = 1, BW_STEMPTY = 3, BW_SFULL = 5, BW_SFREE = 7, BW_PFULL = 9, BW_PEMPTY = 11, BW_ACC = 13, BW_COUNT = 14 };
+
+__device__ __forceinline__ bool bw5_legal(int blk, int qb, int nkb, int Tq, int offset, int causal) {
+  if (blk < 0 || blk >= nkb) return false;
+  if (!causal) return true;
+  const int last_pos = min(qb * 64 + 64, Tq) - 1 + offset;
+  return (long long)blk * 64 <= (long long)last_pos;
+}
+
+// MODE 0: key-major pass (dK, dV).  MODE 1: query-major pass (dQ).
+template <int D, int FMT, int MODE>
+__global__ void __launch_bounds__(BW5_THREADS, 1) nsa_bwd_tc5_kernel(const __grid_constant__ Bw5Params p) {
+  using T = typename std::conditional<FMT == 1, __nv_bfloat16, __half>::type;
+  constexpr int DH = D / 64;                    // 64-element (128-byte) halves of a row
+  constexpr int T128 = DH * 128 * 128;          // bytes of a 128-row tile (halves 16384 bytes apart)
+  constexpr int T64 = DH * 64 * 128;            // bytes of a 64-row tile (halves 8192 bytes apart)
+  constexpr int RES_BYTES = MODE == 0 ? 2 * T64 : 2 * T128;   // resident: K,V (key-major) or Q,dO (query-major)
+  constexpr int ST_BYTES = MODE == 0 ? 2 * T128 : 2 * T64;    // one ring stage: dO,Q (key-major) or K,V (query-major)
+  constexpr int PB_BYTES = MODE == 0 ? 32768 : 16384;         // one P|dS buffer (key-major) or dS buffer (query-major)
+  const nsa_bwd_args& a = p.a;
+
+  // ---- work item (uniform over the block; blocks beyond the item count leave before anything is set up) ----
+  const int NL = a.B * a.Hkv;
+  int owner, b, hk, c = 0, n_rg = 0, slot = -1, qb = 0, h0 = 0, ng = 0;
+  const uint32_t* rgl = nullptr;
+  if constexpr (MODE == 0) {
+    owner = (int)(blockIdx.x % (unsigned)NL);
+    const int ii = (int)(blockIdx.x / (unsigned)NL);
+    if (ii >= p.n_items[owner]) return;
+    const int4 item = p.items[(size_t)owner * p.capW + ii];
+    c = item.x; n_rg = item.z; slot = item.w;
+    rgl = p.rg_list + (size_t)owner * p.cap_rg + item.y;
+  } else {
+    const int per_qb = NL * p.NGT;
+    qb = a.nq - 1 - (int)(blockIdx.x / (unsigned)per_qb);
+    const int rem = (int)(blockIdx.x % (unsigned)per_qb);
+    owner = rem / p.NGT;
+    const int ht = rem % p.NGT;
+    h0 = ht * p.NG;
+    ng = min(p.NG, p.G - h0);
+  }
+  b = owner / a.Hkv;
+  hk = owner % a.Hkv;
+  const int kv_slab = owner;
+
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sRes = smem_u32(smem);
+  const uint32_t sSt = sRes + RES_BYTES;
+  unsigned char* pb_ptr = smem + RES_BYTES + 2 * ST_BYTES;
+  const uint32_t sPb = smem_u32(pb_ptr);
+  __shared__ __align__(8) uint64_t bars[BW_COUNT];
+  __shared__ int sel_list[BW5_MAX_SEL];
+  __shared__ int sel_n;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  auto bar = [&](int id) { return smem_u32(&bars[id]); };
+
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int i = 0; i < BW_COUNT; ++i)
+      mbar_init(bar(i), (i == BW_SFREE || i == BW_SFREE + 1 || i == BW_PFULL || i == BW_PFULL + 1) ? 128 : 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(&tmem_base_s), 512); tmem_relinquish(); }
+  if (MODE == 1 && warp == 2) {
+    // the key blocks this query block lists, in list order, illegal slots dropped
+    const int hi_ = p.shared ? hk : hk * p.G + h0;
+    const int32_t* row = a.idx + (((size_t)b * a.Hi + hi_) * a.nq + qb) * a.top_k;
+    int n = 0;
+    for (int s0 = 0; s0 < a.top_k; s0 += 32) {
+      const int s = s0 + lane;
+      const int blk = s < a.top_k ? row[s] : -1;
+      const bool ok = bw5_legal(blk, qb, p.nkb, a.Tq, a.offset, a.causal);
+      const unsigned m = __ballot_sync(0xffffffffu, ok);
+      if (ok) sel_list[n + __popc(m & ((1u << lane) - 1))] = blk;
+      n += __popc(m);
+    }
+    if (lane == 0) sel_n = n;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+  const int nsteps = MODE == 0 ? (n_rg + 1) >> 1 : sel_n;
+
+  // row group g (0 or 1) of step `st`: head within the KV group and query block; valid == false: rows are zero
+  auto row_group = [&](int st, int g, int& hl, int& qblk) -> bool {
+    if constexpr (MODE == 0) {
+      const int e = 2 * st + g;
+      if (e >= n_rg) { hl = 0; qblk = 0; return false; }
+      const uint32_t v = rgl[e];
+      hl = (int)(v >> BW5_QB_BITS); qblk = (int)(v & ((1u << BW5_QB_BITS) - 1));
+      return true;
+    } else {
+      hl = h0 + g; qblk = qb;
+      return g < ng;
+    }
+  };
+  const int oob_row = (a.Tq + 63) / 64 * 64;    // a box that starts here lies outside the tensor: TMA fills it with zeros
+
+  int fail_id = 0;
+  int last_st = -1;        // producer: last step whose copies were issued
+
+  if (warp == 0) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;\n");
+    // =============================== TMA producer ===============================
+    const bool leader = elect_one();
+    if (leader) {
+      tma_prefetch_desc(&p.tmQ); tma_prefetch_desc(&p.tmdO); tma_prefetch_desc(&p.tmK); tma_prefetch_desc(&p.tmV);
+      mbar_expect_tx(bar(BW_RES), RES_BYTES);
+      if constexpr (MODE == 0) {
+        for (int dh = 0; dh < DH; ++dh) {
+          tma_load_3d(sRes + dh * 8192, &p.tmK, bar(BW_RES), dh * 64, c * 64, kv_slab);
+          tma_load_3d(sRes + T64 + dh * 8192, &p.tmV, bar(BW_RES), dh * 64, c * 64, kv_slab);
+        }
+      } else {
+        for (int g = 0; g < 2; ++g) {
+          int hl, qblk;
+          const bool ok = row_group(0, g, hl, qblk);
+          const int slab = ok ? b * a.H + hk * p.G + hl : 0, row = ok ? qblk * 64 : oob_row;
+          for (int dh = 0; dh < DH; ++dh) {
+            tma_load_3d(sRes + dh * 16384 + g * 8192, &p.tmQ, bar(BW_RES), dh * 64, row, slab);
+            tma_load_3d(sRes + T128 + dh * 16384 + g * 8192, &p.tmdO, bar(BW_RES), dh * 64, row, slab);
+          }
+        }
+      }
+    }
+    __syncwarp();
+    bool ok = true;
+    for (int st = 0; st < nsteps && ok; ++st) {
+      const int s = st & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(BW_STEMPTY + s), ((st >> 1) & 1) ^ 1, &abort_flag));
+      if (!ok) { fail_id = BW_STEMPTY + s + 1; break; }
+      const uint32_t dst = sSt + s * ST_BYTES;
+      if constexpr (MODE == 0) {
+        int hl[2], qblk[2];
+        bool okg[2];
+        for (int g = 0; g < 2; ++g) okg[g] = row_group(st, g, hl[g], qblk[g]);
+        if (leader) {
+          mbar_expect_tx(bar(BW_STFULL + s), ST_BYTES);
+          for (int g = 0; g < 2; ++g) {
+            const int slab = okg[g] ? b * a.H + hk * p.G + hl[g] : 0, row = okg[g] ? qblk[g] * 64 : oob_row;
+            for (int dh = 0; dh < DH; ++dh) {
+              tma_load_3d(dst + dh * 16384 + g * 8192, &p.tmdO, bar(BW_STFULL + s), dh * 64, row, slab);
+              tma_load_3d(dst + T128 + dh * 16384 + g * 8192, &p.tmQ, bar(BW_STFULL + s), dh * 64, row, slab);
+            }
+          }
+        }
+      } else {
+        const int blk = sel_list[st];
+        if (leader) {
+          mbar_expect_tx(bar(BW_STFULL + s), ST_BYTES);
+          for (int dh = 0; dh < DH; ++dh) {
+            tma_load_3d(dst + dh * 8192, &p.tmK, bar(BW_STFULL + s), dh * 64, blk * 64, kv_slab);
+            tma_load_3d(dst + T64 + dh * 8192, &p.tmV, bar(BW_STFULL + s), dh * 64, blk * 64, kv_slab);
+          }
+        }
+      }
+      last_st = st;
+      __syncwarp();
+    }
+  } else if (warp == 1) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;\n");
+    // =============================== MMA issuer ===============================
+    const bool leader = elect_one();
+    constexpr uint32_t IDESC_S = idesc_f16(FMT, 128, 64, 0, 0);            // [128 rows x 64 keys] = A(K-major) B(K-major)^T
+    constexpr uint32_t IDESC_ACC = MODE == 0 ? idesc_f16(FMT, 128, 2 * D, 1, 1)   // [P^T;dS^T] (MN-major) x [dO|Q] (MN-major)
+                                             : idesc_f16(FMT, 128, D, 0, 1);      // dS (K-major) x K (MN-major)
+    bool ok = __all_sync(0xffffffffu, mbar_wait(bar(BW_RES), 0, &abort_flag));
+    if (!ok) fail_id = BW_RES + 1;
+    // byte offsets of the 16-element k-step `ks` in a 128-row (A side) and a 64-row (B side) K-major tile
+    auto offA = [](int ks) { return (uint32_t)(((ks >> 2) * 16384 + (ks & 3) * 32) >> 4); };
+    auto offB = [](int ks) { return (uint32_t)(((ks >> 2) * 8192 + (ks & 3) * 32) >> 4); };
+    const uint32_t tACC = tmem + 256;
+
+    auto issue_sdp = [&](int st) -> bool {
+      const int s = st & 1, ph = (st >> 1) & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(bar(BW_STFULL + s), ph, &abort_flag))) { fail_id = BW_STFULL + s + 1; return false; }
+      if (!__all_sync(0xffffffffu, mbar_wait(bar(BW_SFREE + s), ph ^ 1, &abort_flag))) { fail_id = BW_SFREE + s + 1; return false; }
+      tc_fence_after();
+      if (leader) {
+        const uint32_t st_base = sSt + s * ST_BYTES;
+        // key-major: A = streamed Q / dO, B = resident K / V;  query-major: A = resident Q / dO, B = streamed K / V
+        const uint64_t aS = smem_desc_sw128(MODE == 0 ? st_base + T128 : sRes, 16, 1024);
+        const uint64_t aP = smem_desc_sw128(MODE == 0 ? st_base : sRes + T128, 16, 1024);
+        const uint64_t bS = smem_desc_sw128(MODE == 0 ? sRes : st_base, 16, 1024);
+        const uint64_t bP = smem_desc_sw128(MODE == 0 ? sRes + T64 : st_base + T64, 16, 1024);
+        const uint32_t tS = tmem + s * 128, tdP = tS + 64;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) mma_ss(tS, aS + offA(ks), bS + offB(ks), IDESC_S, ks == 0 ? 0u : 1u);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) mma_ss(tdP, aP + offA(ks), bP + offB(ks), IDESC_S, ks == 0 ? 0u : 1u);
+        tc_commit(bar(BW_SFULL + s));
+      }
+      __syncwarp();
+      return true;
+    };
+    auto issue_acc = [&](int st) -> bool {
+      const int s = st & 1, ph = (st >> 1) & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(bar(BW_PFULL + s), ph, &abort_flag))) { fail_id = BW_PFULL + s + 1; return false; }
+      tc_fence_after();
+      if (leader) {
+        const uint32_t st_base = sSt + s * ST_BYTES, pbuf = sPb + s * PB_BYTES;
+        if constexpr (MODE == 0) {
+          // A: [P^T ; dS^T]: M = 64 keys of P then 64 keys of dS (chunks 16384 bytes apart), K = 128 query rows
+          // B: [dO | Q]: N = 2*D in 64-element chunks 16384 bytes apart, K = the same 128 query rows
+          const uint64_t dA = smem_desc_sw128(pbuf, 16384, 1024);
+          const uint64_t dB = smem_desc_sw128(st_base, 16384, 1024);
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) mma_ss(tACC, dA + kk * 128, dB + kk * 128, IDESC_ACC, (st > 0 || kk > 0) ? 1u : 0u);
+        } else {
+          // A: dS [128 rows x 64 keys] K-major;  B: K [64 keys x D] MN-major (halves 8192 bytes apart)
+          const uint64_t dA = smem_desc_sw128(pbuf, 16, 1024);
+          const uint64_t dB = smem_desc_sw128(st_base, 8192, 1024);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) mma_ss(tACC, dA + ks * 2, dB + ks * 128, IDESC_ACC, (st > 0 || ks > 0) ? 1u : 0u);
+        }
+        tc_commit(bar(BW_PEMPTY + s));
+        tc_commit(bar(BW_STEMPTY + s));
+      }
+      __syncwarp();
+      return true;
+    };
+    for (int st = 0; st < nsteps && ok; ++st) {
+      ok = issue_sdp(st);
+      if (ok && st > 0) ok = issue_acc(st - 1);
+    }
+    if (ok && nsteps > 0) ok = issue_acc(nsteps - 1);
+    if (ok && nsteps > 0) {
+      if (leader) tc_commit(bar(BW_ACC));
+      __syncwarp();
+    }
+  } else if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;\n");
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;\n");
+    // =============================== softmax / epilogue ===============================
+    const int grp = (warp - 4) >> 2;                       // handles the steps of parity grp
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;                     // row of the 128-row tile == TMEM lane
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const int g2 = r >> 6;
+    const uint32_t tS = tmem + lane_addr + grp * 128, tdP = tS + 64;
+    unsigned char* prow = pb_ptr + grp * PB_BYTES + r * 128;           // this row of P (key-major) / dS (query-major)
+    const float sc = a.scale;
+
+    // what a query row needs: its log-sum-exp (log2 units), delta*scale, and the last key position it may see
+    float lse2 = 0.f, dls = 0.f;
+    int hi = -1;
+    auto load_row = [&](int st) {
+      int hl, qblk;
+      const bool okg = row_group(st, g2, hl, qblk);
+      const int qi = qblk * 64 + (r & 63);
+      lse2 = 0.f; dls = 0.f; hi = -1;
+      if (okg && qi < a.Tq) {
+        const size_t ri = ((size_t)b * a.H + hk * p.G + hl) * a.Tq + qi;
+        const float l = a.lse[ri];
+        if (l > -INFINITY) {
+          lse2 = l * kLog2e;
+          dls = a.delta[ri] * sc;
+          hi = a.causal ? min(qi + a.offset, a.sel_key_limit - 1) : a.sel_key_limit - 1;
+        }
+      }
+    };
+    if constexpr (MODE == 1) load_row(0);
+
+    bool ok = true;
+#pragma unroll 1
+    for (int st = grp; st < nsteps && ok; st += 2) {
+      const int ph = (st >> 1) & 1;
+      int j0;
+      if constexpr (MODE == 0) { load_row(st); j0 = c * 64; }
+      else j0 = sel_list[st] * 64;
+      const int vhi = min(hi, min(j0 + 64, a.sel_key_limit) - 1) - j0;   // columns 0..vhi of the tile count for this row
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(BW_SFULL + grp), ph, &abort_flag));
+      if (!ok) { fail_id = BW_SFULL + grp + 1; break; }
+      tc_fence_after();
+      uint32_t sv[2][32], dv[2][32];
+      tmem_ld32(tS, sv[0]);
+      tmem_ld32(tS + 32, sv[1]);
+      tmem_ld32(tdP, dv[0]);
+      tmem_ld32(tdP + 32, dv[1]);
+      tc_wait_ld();
+      tc_fence_before();
+      mbar_arrive(bar(BW_SFREE + grp));                    // S and dP are in registers: the next step may overwrite them
+      // P and dS in place (sv <- P, dv <- dS), then packed to 16 bits
+      uint32_t pk[2][16], dk[2][16];
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float p0 = ex2(fmaf(__uint_as_float(sv[g][2 * i]), p.scale_log2, -lse2));
+          float p1 = ex2(fmaf(__uint_as_float(sv[g][2 * i + 1]), p.scale_log2, -lse2));
+          if (g * 32 + 2 * i > vhi) p0 = 0.f;
+          if (g * 32 + 2 * i + 1 > vhi) p1 = 0.f;
+          const float d0 = p0 * fmaf(__uint_as_float(dv[g][2 * i]), sc, -dls);
+          const float d1 = p1 * fmaf(__uint_as_float(dv[g][2 * i + 1]), sc, -dls);
+          pk[g][i] = Elem<T>::pack(p0, p1);
+          dk[g][i] = Elem<T>::pack(d0, d1);
+        }
+      }
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(BW_PEMPTY + grp), ph ^ 1, &abort_flag));
+      if (!ok) { fail_id = BW_PEMPTY + grp + 1; break; }
+      // one 128-byte row per thread, 16-byte chunks XOR-swizzled with the row (the layout TMA's 128-byte swizzle gives)
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        const int g = ch >> 2, i = (ch & 3) * 4;
+        const uint32_t sw = (uint32_t)((ch ^ (r & 7)) << 4);
+        if constexpr (MODE == 0) {
+          *reinterpret_cast<uint4*>(prow + sw) = make_uint4(pk[g][i], pk[g][i + 1], pk[g][i + 2], pk[g][i + 3]);
+          *reinterpret_cast<uint4*>(prow + 16384 + sw) = make_uint4(dk[g][i], dk[g][i + 1], dk[g][i + 2], dk[g][i + 3]);
+        } else {
+          *reinterpret_cast<uint4*>(prow + sw) = make_uint4(dk[g][i], dk[g][i + 1], dk[g][i + 2], dk[g][i + 3]);
+        }
+      }
+      fence_proxy_async();
+      mbar_arrive(bar(BW_PFULL + grp));
+    }
+
+    // ---- epilogue: the accumulator is complete once the last MMA has landed ----
+    if (ok && nsteps > 0) {
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(BW_ACC), 0, &abort_flag));
+      if (!ok) fail_id = BW_ACC + 1;
+      tc_fence_after();
+    }
+    if (ok) {
+      constexpr int HC = D / 2;                            // each softmax group handles half of the columns
+      if constexpr (MODE == 0) {
+        // lanes 0-63: dV of key (lane), columns [0,D);  lanes 64-127: dK of key (lane-64), columns [D,2D)
+        const int which = g2, kr = r & 63;
+        const int key = c * 64 + kr;
+        const uint32_t tA = tmem + lane_addr + 256 + which * D + grp * HC;
+        float* dst;
+        const bool direct = slot < 0;
+        if (direct) dst = (which ? a.dK_f : a.dV_f) + ((size_t)kv_slab * a.Tk + key) * D + grp * HC;
+        else dst = p.partials + ((((size_t)owner * p.capP + slot) * 2 + which) * 64 + kr) * D + grp * HC;
+        const bool wr = !direct || key < a.Tk;
+#pragma unroll
+        for (int g = 0; g < HC / 32; ++g) {
+          uint32_t v[32];
+          tmem_ld32(tA + g * 32, v);
+          tc_wait_ld();
+          if (wr) {
+#pragma unroll
+            for (int q4 = 0; q4 < 8; ++q4) {
+              float4 o = make_float4(__uint_as_float(v[4 * q4]), __uint_as_float(v[4 * q4 + 1]), __uint_as_float(v[4 * q4 + 2]),
+                                     __uint_as_float(v[4 * q4 + 3]));
+              float4* dp4 = reinterpret_cast<float4*>(dst + g * 32) + q4;
+              if (direct) { const float4 old = *dp4; o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w; }
+              *dp4 = o;
+            }
+          }
+        }
+      } else {
+        int hl, qblk;
+        const bool okg = row_group(0, g2, hl, qblk);
+        const int qi = qblk * 64 + (r & 63);
+        const bool wr = okg && qi < a.Tq;
+        const size_t base = (((size_t)b * a.H + hk * p.G + hl) * a.Tq + qi) * D + grp * HC;
+        const uint32_t tA = tmem + lane_addr + 256 + grp * HC;
+#pragma unroll
+        for (int g = 0; g < HC / 32; ++g) {
+          uint32_t v[32];
+          if (nsteps > 0) { tmem_ld32(tA + g * 32, v); tc_wait_ld(); }
+          else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0u;
+          }
+          if (wr) {
+            if (a.dq_dtype == NSA_FP32) {
+              float4* dp4 = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.dQ) + base + g * 32);
+#pragma unroll
+              for (int q4 = 0; q4 < 8; ++q4)
+                dp4[q4] = make_float4(__uint_as_float(v[4 * q4]), __uint_as_float(v[4 * q4 + 1]), __uint_as_float(v[4 * q4 + 2]),
+                                      __uint_as_float(v[4 * q4 + 3]));
+            } else {
+              uint4* dp4 = reinterpret_cast<uint4*>(reinterpret_cast<T*>(a.dQ) + base + g * 32);
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4)
+                dp4[q4] = make_uint4(Elem<T>::pack(__uint_as_float(v[8 * q4]), __uint_as_float(v[8 * q4 + 1])),
+                                     Elem<T>::pack(__uint_as_float(v[8 * q4 + 2]), __uint_as_float(v[8 * q4 + 3])),
+                                     Elem<T>::pack(__uint_as_float(v[8 * q4 + 4]), __uint_as_float(v[8 * q4 + 5])),
+                                     Elem<T>::pack(__uint_as_float(v[8 * q4 + 6]), __uint_as_float(v[8 * q4 + 7])));
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ---- teardown (every path reaches it) ----
+  if (fail_id != 0) atomicCAS(&g_bw5_status, 0, fail_id);
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag && warp == 0 && lane == 0) {
+    // let copies already in flight land (bounded) before the block's shared memory is handed back
+    for (int i = 0; i < 20000 && !mbar_try_wait(bar(BW_RES), 0); ++i) __nanosleep(100);
+    if (last_st >= 0)
+      for (int i = 0; i < 20000 && !mbar_try_wait(bar(BW_STFULL + (last_st & 1)), (last_st >> 1) & 1); ++i) __nanosleep(100);
+  }
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
+// ---------------------------------------------------------------- inverted index
+// cnt[owner][c] += row groups that list key block c (G per entry of a list shared by the group).
+__global__ void __launch_bounds__(256) bw5_count_kernel(const int32_t* __restrict__ idx, int* __restrict__ cnt, int B, int Hi, int Hkv,
+                                                        int nq, int top_k, int nkb, int Tq, int offset, int causal, int gx) {
+  const long long n = (long long)B * Hi * nq * top_k;
+  const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= n) return;
+  const int qb = (int)((e / top_k) % nq);
+  const long long bh = e / ((long long)top_k * nq);
+  const int hi = (int)(bh % Hi), b = (int)(bh / Hi);
+  const int hk = hi / (Hi / Hkv);
+  const int blk = idx[e];
+  if (bw5_legal(blk, qb, nkb, Tq, offset, causal)) atomicAdd(&cnt[((size_t)b * Hkv + hk) * nkb + blk], gx);
+}
+
+// Per owner (batch, KV head): exclusive scans over the key blocks of (row groups, segments, partial slots); writes the
+// list offsets and the work items of the key-major pass.  One block of 1024 threads per owner.
+__global__ void __launch_bounds__(1024) bw5_plan_kernel(const int* __restrict__ cnt, int* __restrict__ off, int2* __restrict__ seginfo,
+                                                        int4* __restrict__ items, int* __restrict__ n_items, int nkb, int L, int capW) {
+  __shared__ int wsum[3][32];
+  __shared__ int run[3];
+  const int owner = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid < 3) run[tid] = 0;
+  __syncthreads();
+  for (int c0 = 0; c0 < nkb; c0 += 1024) {
+    const int c = c0 + tid;
+    const int n = c < nkb ? cnt[(size_t)owner * nkb + c] : 0;
+    const int ns = (n + L - 1) / L;
+    const int np = ns >= 2 ? ns : 0;
+    int v[3] = {n, ns, np}, inc[3];
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+      int x = v[k];
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) { const int y = __shfl_up_sync(0xffffffffu, x, d); if (lane >= d) x += y; }
+      inc[k] = x;
+      if (lane == 31) wsum[k][warp] = x;
+    }
+    __syncthreads();
+    if (warp == 0) {
+#pragma unroll
+      for (int k = 0; k < 3; ++k) {
+        int x = wsum[k][lane];
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) { const int y = __shfl_up_sync(0xffffffffu, x, d); if (lane >= d) x += y; }
+        wsum[k][lane] = x;                                   // inclusive over warps
+      }
+    }
+    __syncthreads();
+    int ex[3];
+#pragma unroll
+    for (int k = 0; k < 3; ++k) ex[k] = run[k] + (warp > 0 ? wsum[k][warp - 1] : 0) + inc[k] - v[k];
+    if (c < nkb) {
+      off[(size_t)owner * nkb + c] = ex[0];
+      seginfo[(size_t)owner * nkb + c] = make_int2(np ? ex[2] : -1, ns);
+      for (int s = 0; s < ns; ++s)
+        items[(size_t)owner * capW + ex[1] + s] = make_int4(c, ex[0] + s * L, min(L, n - s * L), np ? ex[2] + s : -1);
+    }
+    __syncthreads();
+    if (tid < 3) run[tid] += wsum[tid][31];
+    __syncthreads();
+  }
+  if (tid == 0) n_items[owner] = run[1];
+}
+
+// One warp per (owner, key block): walks the block lists in (head, query block, slot) order and appends the row
+// groups that list the key block -- a fixed order, so the sums of the key-major pass are formed in a fixed order.
+__global__ void __launch_bounds__(256) bw5_fill_kernel(const int32_t* __restrict__ idx, const int* __restrict__ cnt, const int* __restrict__ off,
+                                                       uint32_t* __restrict__ rg_list, long long cap_rg, int B, int Hi, int Hkv, int nq,
+                                                       int top_k, int nkb, int Tq, int offset, int causal, int G, int shared) {
+  const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= (long long)B * Hkv * nkb) return;
+  const int owner = (int)(w / nkb), c = (int)(w % nkb);
+  if (cnt[(size_t)owner * nkb + c] == 0) return;
+  const int b = owner / Hkv, hk = owner % Hkv;
+  uint32_t* dst = rg_list + (size_t)owner * cap_rg + off[(size_t)owner * nkb + c];
+  // first query block that can list key block c under the causal rule (legality is checked again per entry)
+  int qb0 = 0;
+  if (causal) qb0 = max(0, (c * 64 - offset) / 64 - 1);
+  int pos = 0;
+  const int nlists = shared ? 1 : G;
+  const long long n_ent = (long long)nq * top_k;
+  for (int hl = 0; hl < nlists; ++hl) {
+    const int hi = shared ? hk : hk * G + hl;
+    const int32_t* row = idx + ((size_t)b * Hi + hi) * n_ent;
+    for (long long e0 = (long long)qb0 * top_k; e0 < n_ent; e0 += 32) {
+      const long long e = e0 + lane;
+      bool m = false;
+      int qb = 0;
+      if (e < n_ent) {
+        qb = (int)(e / top_k);
+        const int blk = row[e];
+        m = blk == c && bw5_legal(blk, qb, nkb, Tq, offset, causal);
+      }
+      const unsigned bal = __ballot_sync(0xffffffffu, m);
+      if (m) {
+        const int at = pos + __popc(bal & ((1u << lane) - 1));
+        if (shared) { for (int g = 0; g < G; ++g) dst[(size_t)at * G + g] = ((uint32_t)g << BW5_QB_BITS) | (uint32_t)qb; }
+        else dst[at] = ((uint32_t)hl << BW5_QB_BITS) | (uint32_t)qb;
+      }
+      pos += __popc(bal);
+    }
+  }
+}
+
+// dK/dV of key blocks whose list was split: the segments' partial sums are added in segment order.
+template <int D>
+__global__ void __launch_bounds__(256) bw5_reduce_kernel(const float* __restrict__ partials, const int2* __restrict__ seginfo, float* __restrict__ dK,
+                                                         float* __restrict__ dV, int nkb, int capP, int Tk) {
+  const int owner = blockIdx.y, c = blockIdx.x;
+  const int2 si = seginfo[(size_t)owner * nkb + c];
+  if (si.x < 0) return;
+  constexpr int N4 = 64 * D / 4;
+  for (int which = 0; which < 2; ++which) {
+    float* out = (which ? dK : dV) + ((size_t)owner * Tk + (size_t)c * 64) * D;
+    for (int i = threadIdx.x; i < N4; i += 256) {
+      const int key = c * 64 + i / (D / 4);
+      if (key >= Tk) continue;
+      float4 acc = reinterpret_cast<const float4*>(out)[i];
+      for (int s = 0; s < si.y; ++s) {
+        const float4 v = reinterpret_cast<const float4*>(partials + (((size_t)owner * capP + si.x + s) * 2 + which) * 64 * D)[i];
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      reinterpret_cast<float4*>(out)[i] = acc;
+    }
+  }
+}
+
+// ---------------------------------------------------------------- host side
+struct Bw5Plan {
+  int nkb, G, shared, L, capW, capP;
+  long long cap_rg, owners;
+  size_t o_cnt, o_off, o_seg, o_nitems, o_items, o_list, o_part, total;
+};
+
+bool attention_bwd_tc5_supports(const nsa_bwd_args& a) {
+  if (a.branch != NSA_BRANCH_SELECTED) return false;
+  if (!(a.dtype == NSA_BF16 || a.dtype == NSA_FP16)) return false;
+  if (!(a.D == 64 || a.D == 128)) return false;
+  if (a.bm != 64 || a.bn != 64 || a.top_k > BW5_MAX_SEL) return false;
+  if (a.nq >= (1 << BW5_QB_BITS) || a.H / a.Hkv >= (1 << (32 - BW5_QB_BITS))) return false;
+  if (!(a.scale > 0.f)) return false;
+  return true;
+}
+
+static Bw5Plan bw5_plan(const nsa_bwd_args& a) {
+  Bw5Plan pl;
+  pl.nkb = (a.sel_key_limit + 63) / 64;
+  pl.G = a.H / a.Hkv;
+  pl.shared = a.Hi != a.H ? 1 : 0;
+  pl.owners = (long long)a.B * a.Hkv;
+  pl.cap_rg = (long long)pl.G * a.nq * a.top_k;
+  // segment length (row groups, even): about 16 work items per SM over the whole launch, between 128 and 1024
+  long long L = (pl.cap_rg * pl.owners / 2400 + 1) / 2 * 2;
+  pl.L = (int)(L < 128 ? 128 : (L > 1024 ? 1024 : L));
+  pl.capW = (int)(pl.nkb + pl.cap_rg / pl.L + 1);
+  pl.capP = (int)(2 * pl.cap_rg / pl.L + 2);
+  auto up = [](size_t x) { return (x + 255) & ~size_t(255); };
+  size_t o = 0;
+  pl.o_cnt = o; o = up(o + (size_t)pl.owners * pl.nkb * 4);
+  pl.o_nitems = o; o = up(o + (size_t)pl.owners * 4);
+  pl.o_off = o; o = up(o + (size_t)pl.owners * pl.nkb * 4);
+  pl.o_seg = o; o = up(o + (size_t)pl.owners * pl.nkb * 8);
+  pl.o_items = o; o = up(o + (size_t)pl.owners * pl.capW * 16);
+  pl.o_list = o; o = up(o + (size_t)pl.owners * pl.cap_rg * 4);
+  pl.o_part = o; o = up(o + (size_t)pl.owners * pl.capP * 2 * 64 * a.D * 4);
+  pl.total = o;
+  return pl;
+}
+
+long long attention_bwd_tc5_scratch_bytes(const nsa_bwd_args& a) { return (long long)bw5_plan(a).total; }
+
+int attention_bwd_tc5(const nsa_bwd_args& a, void* scratch, long long scratch_bytes, cudaStream_t st) {
+  const Bw5Plan pl = bw5_plan(a);
+  NSA_REQUIRE(scratch != nullptr && scratch_bytes >= (long long)pl.total, NSA_ERR_ARG,
+              "selected backward (tcgen05): needs %lld bytes of scratch, %lld given", (long long)pl.total, scratch_bytes);
+  NSA_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 255) == 0, NSA_ERR_ARG, "selected backward (tcgen05): scratch must be 256-byte aligned");
+  unsigned char* sc = reinterpret_cast<unsigned char*>(scratch);
+  int* cnt = reinterpret_cast<int*>(sc + pl.o_cnt);
+  int* n_items = reinterpret_cast<int*>(sc + pl.o_nitems);
+  int* off = reinterpret_cast<int*>(sc + pl.o_off);
+  int2* seginfo = reinterpret_cast<int2*>(sc + pl.o_seg);
+  int4* items = reinterpret_cast<int4*>(sc + pl.o_items);
+  uint32_t* rg_list = reinterpret_cast<uint32_t*>(sc + pl.o_list);
+  float* partials = reinterpret_cast<float*>(sc + pl.o_part);
+
+  Bw5Params p;
+  p.a = a;
+  p.scale_log2 = a.scale * kLog2e;
+  p.nkb = pl.nkb; p.G = pl.G; p.shared = pl.shared;
+  p.items = items; p.n_items = n_items; p.capW = pl.capW; p.rg_list = rg_list; p.cap_rg = pl.cap_rg;
+  p.partials = partials; p.capP = pl.capP;
+  p.NG = (pl.shared && pl.G >= 2) ? 2 : 1;
+  p.NGT = (pl.G + p.NG - 1) / p.NG;
+  int rc;
+  if ((rc = make_map(&p.tmQ, a.Q, (long long)a.B * a.H, a.Tq, a.D, a.dtype)) != NSA_OK) return rc;
+  if ((rc = make_map(&p.tmdO, a.dO, (long long)a.B * a.H, a.Tq, a.D, a.dtype)) != NSA_OK) return rc;
+  if ((rc = make_map(&p.tmK, a.K, (long long)a.B * a.Hkv, a.Tk, a.D, a.dtype)) != NSA_OK) return rc;
+  if ((rc = make_map(&p.tmV, a.V, (long long)a.B * a.Hkv, a.Tk, a.D, a.dtype)) != NSA_OK) return rc;
+
+  // inverted index
+  NSA_CUDA_OK(cudaMemsetAsync(sc + pl.o_cnt, 0, pl.o_off - pl.o_cnt, st));     // counts and item counts
+  const long long n_ent = (long long)a.B * a.Hi * a.nq * a.top_k;
+  NSA_REQUIRE(n_ent < (1LL << 40) && (long long)pl.owners * pl.capW < 2147483647LL, NSA_ERR_ARG, "selected backward: problem too large");
+  bw5_count_kernel<<<(unsigned)((n_ent + 255) / 256), 256, 0, st>>>(a.idx, cnt, a.B, a.Hi, a.Hkv, a.nq, a.top_k, pl.nkb, a.Tq, a.offset,
+                                                                   a.causal, pl.shared ? pl.G : 1);
+  bw5_plan_kernel<<<(unsigned)pl.owners, 1024, 0, st>>>(cnt, off, seginfo, items, n_items, pl.nkb, pl.L, pl.capW);
+  const long long warps = pl.owners * pl.nkb;
+  bw5_fill_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(a.idx, cnt, off, rg_list, pl.cap_rg, a.B, a.Hi, a.Hkv, a.nq, a.top_k, pl.nkb,
+                                                              a.Tq, a.offset, a.causal, pl.G, pl.shared);
+  if ((rc = launch_status("selected backward index")) != NSA_OK) return rc;
+
+  const int DHh = a.D / 64;
+  const size_t smem0 = (size_t)2 * DHh * 64 * 128 + (size_t)4 * DHh * 128 * 128 + 2 * 32768 + 1024;
+  const size_t smem1 = (size_t)2 * DHh * 128 * 128 + (size_t)4 * DHh * 64 * 128 + 2 * 16384 + 1024;
+  const unsigned grid0 = (unsigned)(pl.owners * pl.capW);
+  const long long tiles1 = pl.owners * p.NGT * a.nq;
+  NSA_REQUIRE(tiles1 < 2147483647LL, NSA_ERR_ARG, "selected backward: %lld query tiles do not fit a grid", tiles1);
+#define NSA_BW5_LAUNCH(DD, FF)                                                                                   \
+  {                                                                                                               \
+    auto f0 = nsa_bwd_tc5_kernel<DD, FF, 0>;                                                                      \
+    auto f1 = nsa_bwd_tc5_kernel<DD, FF, 1>;                                                                      \
+    NSA_CUDA_OK(cudaFuncSetAttribute(f0, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem0));              \
+    NSA_CUDA_OK(cudaFuncSetAttribute(f1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1));              \
+    f0<<<grid0, BW5_THREADS, smem0, st>>>(p);                                                                     \
+    bw5_reduce_kernel<DD><<<dim3((unsigned)pl.nkb, (unsigned)pl.owners), 256, 0, st>>>(partials, seginfo, a.dK_f, a.dV_f, pl.nkb, \
+                                                                                       pl.capP, a.Tk);           \
+    f1<<<(unsigned)tiles1, BW5_THREADS, smem1, st>>>(p);                                                          \
+  }
+  const int fmt = a.dtype == NSA_BF16 ? 1 : 0;
+  if (a.D == 128 && fmt == 1) NSA_BW5_LAUNCH(128, 1)
+  else if (a.D == 128) NSA_BW5_LAUNCH(128, 0)
+  else if (fmt == 1) NSA_BW5_LAUNCH(64, 1)
+  else NSA_BW5_LAUNCH(64, 0)
+#undef NSA_BW5_LAUNCH
+  return launch_status("selected backward (tcgen05)");
+}
+
+// Returns and clears the status word of the backward kernels (the stream has been synchronised by the caller).
+int bw5_take_status(int* status) {
+  int v = 0, zero = 0;
+  NSA_CUDA_OK(cudaMemcpyFromSymbol(&v, g_bw5_status, sizeof(int)));
+  if (v != 0) NSA_CUDA_OK(cudaMemcpyToSymbol(g_bw5_status, &zero, sizeof(int)));
+  *status = v;
+  return NSA_OK;
+}
+
+}  // namespace nsa

@@ -28,6 +28,16 @@ def engine() -> int:
     return _ENGINE
 
 
+_BWD_ENGINE = L.ENGINE_AUTO
+
+
+def set_bwd_engine(name: str) -> None:
+    """Which engine nsa_attention_bwd uses: "auto" (tcgen05 for the selected branch when the shape qualifies,
+    else generic), "generic" (mma.sync with fp32 atomic adds) or "tcgen05" (error when the shape does not qualify)."""
+    global _BWD_ENGINE
+    _BWD_ENGINE = {"auto": L.ENGINE_AUTO, "generic": L.ENGINE_GENERIC, "tcgen05": L.ENGINE_TCGEN05}[name]
+
+
 def device_status() -> None:
     """Synchronise the current stream and raise if a kernel gave up on a bounded device-side wait."""
     L.check(L.load().nsa_device_status(L.stream_ptr()), "nsa_device_status")
@@ -263,8 +273,16 @@ def attention_bwd(dO: Tensor, Q: Tensor, K: Tensor, V: Tensor, lse: Tensor, delt
         a.window = int(window)
     else:
         a.Nc, a.cmp_block, a.cmp_stride, a.cmp_offset = rows, cmp_block, cmp_stride, cmp_offset
+    a.engine = _BWD_ENGINE
     with torch.cuda.device(Q.device):
-        L.check(L.load().nsa_attention_bwd(C.byref(a), L.stream_ptr()), "nsa_attention_bwd")
+        lib = L.load()
+        scratch = None
+        if _BWD_ENGINE != L.ENGINE_GENERIC:
+            need = int(lib.nsa_attention_bwd_scratch_bytes(C.byref(a)))
+            if need > 0:      # the tcgen05 engine takes this shape: give it its scratch (inverted lists, partial sums)
+                scratch = torch.empty(need, device=Q.device, dtype=torch.uint8)
+                a.scratch, a.scratch_bytes = scratch.data_ptr(), need
+        L.check(lib.nsa_attention_bwd(C.byref(a), L.stream_ptr()), "nsa_attention_bwd")
     return dQ, dK, dV
 
 

@@ -14,12 +14,12 @@ def test_library_exports_every_declared_symbol():
     from nsa_from_scratch_b200 import _lib
     lib = _lib.load()
     header = open(os.path.join(ROOT, "include", "nsa_b200.h")).read()
-    declared = set(re.findall(r"^(?:int|const char\*)\s+(\w+)\s*\(", header, flags=re.M))
+    declared = set(re.findall(r"^(?:int|int64_t|const char\*)\s+(\w+)\s*\(", header, flags=re.M))
     assert declared, "no declarations parsed"
     assert declared == set(_lib.PROTOTYPES), declared ^ set(_lib.PROTOTYPES)
     for name in declared:
         assert hasattr(lib, name), name
-    assert lib.nsa_abi_version() == 6
+    assert lib.nsa_abi_version() == 7
 
 
 def _struct_fields(header, name):
