@@ -5,7 +5,8 @@
 // Two passes over the same pairs (64 query rows of one head) x (one selected 64-key block):
 //
 //   key-major pass (dK, dV).  An inverted index -- per (batch, KV head, key block) the list of row
-//   groups (query head, query block) that selected it -- is built first (count, scan, ordered fill).
+//   groups (query head, query block) that selected it -- is built first (a stable counting sort: per-chunk
+//   histograms, prefix sums, ordered fill).
 //   A thread block owns one key block, or one segment of a long list.  K and V of the block stay in shared
 //   memory; the row groups stream by, two at a time (128 rows), through a TMA ring:
 //       S  = Q K^T   dP = dO V^T                      (tcgen05.mma, fp32 in TMEM)
@@ -62,7 +63,11 @@ struct Bw5Params {
   int NGT;                 // tiles per (batch, KV head, query block)
 };
 
-enum { BW_RES = 0, BW_STFULL = 1, BW_STEMPTY = 3, BW_SFULL = 5, BW_SFREE = 7, BW_PFULL = 9, BW_PEMPTY = 11, BW_ACC = 13, BW_COUNT = 14 };
+// barrier ids (the ring of streamed tiles has up to 4 stages)
+enum { BW_RES = 0, BW_STFULL = 1, BW_STEMPTY = 5, BW_SFULL = 9, BW_SFREE = 11, BW_PFULL = 13, BW_PEMPTY = 15, BW_ACC = 17, BW_COUNT = 18 };
+
+// Stages of the ring of streamed tiles.  Key-major at D=128 has room for two (64 KB each) only.
+__host__ __device__ constexpr int bw5_stages(int D, int mode) { return mode == 0 ? (D == 64 ? 4 : 2) : 4; }
 
 __device__ __forceinline__ bool bw5_legal(int blk, int qb, int nkb, int Tq, int offset, int causal) {
   if (blk < 0 || blk >= nkb) return false;
@@ -81,6 +86,10 @@ __global__ void __launch_bounds__(BW5_THREADS, 1) nsa_bwd_tc5_kernel(const __gri
   constexpr int RES_BYTES = MODE == 0 ? 2 * T64 : 2 * T128;   // resident: K,V (key-major) or Q,dO (query-major)
   constexpr int ST_BYTES = MODE == 0 ? 2 * T128 : 2 * T64;    // one ring stage: dO,Q (key-major) or K,V (query-major)
   constexpr int PB_BYTES = MODE == 0 ? 32768 : 16384;         // one P|dS buffer (key-major) or dS buffer (query-major)
+  constexpr int NST = bw5_stages(D, MODE);
+  // S/dP of step i+LA are issued before the accumulate MMA of step i, so that a softmax group finds its next S waiting
+  // when it finishes a step (the accumulate of step i frees ring stage i % NST, which step i+LA must not need)
+  constexpr int LA = NST >= 3 ? 2 : 1;
   const nsa_bwd_args& a = p.a;
 
   // ---- work item (uniform over the block; blocks beyond the item count leave before anything is set up) ----
@@ -111,7 +120,7 @@ __global__ void __launch_bounds__(BW5_THREADS, 1) nsa_bwd_tc5_kernel(const __gri
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sRes = smem_u32(smem);
   const uint32_t sSt = sRes + RES_BYTES;
-  unsigned char* pb_ptr = smem + RES_BYTES + 2 * ST_BYTES;
+  unsigned char* pb_ptr = smem + RES_BYTES + NST * ST_BYTES;
   const uint32_t sPb = smem_u32(pb_ptr);
   __shared__ __align__(8) uint64_t bars[BW_COUNT];
   __shared__ int sel_list[BW5_MAX_SEL];
@@ -195,8 +204,8 @@ __global__ void __launch_bounds__(BW5_THREADS, 1) nsa_bwd_tc5_kernel(const __gri
     __syncwarp();
     bool ok = true;
     for (int st = 0; st < nsteps && ok; ++st) {
-      const int s = st & 1;
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(BW_STEMPTY + s), ((st >> 1) & 1) ^ 1, &abort_flag));
+      const int s = st % NST;
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(BW_STEMPTY + s), ((st / NST) & 1) ^ 1, &abort_flag));
       if (!ok) { fail_id = BW_STEMPTY + s + 1; break; }
       const uint32_t dst = sSt + s * ST_BYTES;
       if constexpr (MODE == 0) {
@@ -241,9 +250,9 @@ __global__ void __launch_bounds__(BW5_THREADS, 1) nsa_bwd_tc5_kernel(const __gri
     const uint32_t tACC = tmem + 256;
 
     auto issue_sdp = [&](int st) -> bool {
-      const int s = st & 1, ph = (st >> 1) & 1;
-      if (!__all_sync(0xffffffffu, mbar_wait(bar(BW_STFULL + s), ph, &abort_flag))) { fail_id = BW_STFULL + s + 1; return false; }
-      if (!__all_sync(0xffffffffu, mbar_wait(bar(BW_SFREE + s), ph ^ 1, &abort_flag))) { fail_id = BW_SFREE + s + 1; return false; }
+      const int s = st % NST, sb = st & 1, ph = (st >> 1) & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(bar(BW_STFULL + s), (st / NST) & 1, &abort_flag))) { fail_id = BW_STFULL + s + 1; return false; }
+      if (!__all_sync(0xffffffffu, mbar_wait(bar(BW_SFREE + sb), ph ^ 1, &abort_flag))) { fail_id = BW_SFREE + sb + 1; return false; }
       tc_fence_after();
       if (leader) {
         const uint32_t st_base = sSt + s * ST_BYTES;
@@ -252,22 +261,22 @@ __global__ void __launch_bounds__(BW5_THREADS, 1) nsa_bwd_tc5_kernel(const __gri
         const uint64_t aP = smem_desc_sw128(MODE == 0 ? st_base : sRes + T128, 16, 1024);
         const uint64_t bS = smem_desc_sw128(MODE == 0 ? sRes : st_base, 16, 1024);
         const uint64_t bP = smem_desc_sw128(MODE == 0 ? sRes + T64 : st_base + T64, 16, 1024);
-        const uint32_t tS = tmem + s * 128, tdP = tS + 64;
+        const uint32_t tS = tmem + sb * 128, tdP = tS + 64;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) mma_ss(tS, aS + offA(ks), bS + offB(ks), IDESC_S, ks == 0 ? 0u : 1u);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) mma_ss(tdP, aP + offA(ks), bP + offB(ks), IDESC_S, ks == 0 ? 0u : 1u);
-        tc_commit(bar(BW_SFULL + s));
+        tc_commit(bar(BW_SFULL + sb));
       }
       __syncwarp();
       return true;
     };
     auto issue_acc = [&](int st) -> bool {
-      const int s = st & 1, ph = (st >> 1) & 1;
-      if (!__all_sync(0xffffffffu, mbar_wait(bar(BW_PFULL + s), ph, &abort_flag))) { fail_id = BW_PFULL + s + 1; return false; }
+      const int s = st % NST, sb = st & 1, ph = (st >> 1) & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(bar(BW_PFULL + sb), ph, &abort_flag))) { fail_id = BW_PFULL + sb + 1; return false; }
       tc_fence_after();
       if (leader) {
-        const uint32_t st_base = sSt + s * ST_BYTES, pbuf = sPb + s * PB_BYTES;
+        const uint32_t st_base = sSt + s * ST_BYTES, pbuf = sPb + sb * PB_BYTES;
         if constexpr (MODE == 0) {
           // A: [P^T ; dS^T]: M = 64 keys of P then 64 keys of dS (chunks 16384 bytes apart), K = 128 query rows
           // B: [dO | Q]: N = 2*D in 64-element chunks 16384 bytes apart, K = the same 128 query rows
@@ -282,17 +291,17 @@ __global__ void __launch_bounds__(BW5_THREADS, 1) nsa_bwd_tc5_kernel(const __gri
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) mma_ss(tACC, dA + ks * 2, dB + ks * 128, IDESC_ACC, (st > 0 || ks > 0) ? 1u : 0u);
         }
-        tc_commit(bar(BW_PEMPTY + s));
+        tc_commit(bar(BW_PEMPTY + sb));
         tc_commit(bar(BW_STEMPTY + s));
       }
       __syncwarp();
       return true;
     };
+    for (int st = 0; st < LA && st < nsteps && ok; ++st) ok = issue_sdp(st);
     for (int st = 0; st < nsteps && ok; ++st) {
-      ok = issue_sdp(st);
-      if (ok && st > 0) ok = issue_acc(st - 1);
+      if (st + LA < nsteps) ok = issue_sdp(st + LA);
+      if (ok) ok = issue_acc(st);
     }
-    if (ok && nsteps > 0) ok = issue_acc(nsteps - 1);
     if (ok && nsteps > 0) {
       if (leader) tc_commit(bar(BW_ACC));
       __syncwarp();
@@ -462,26 +471,82 @@ __global__ void __launch_bounds__(BW5_THREADS, 1) nsa_bwd_tc5_kernel(const __gri
   if (abort_flag && warp == 0 && lane == 0) {
     // let copies already in flight land (bounded) before the block's shared memory is handed back
     for (int i = 0; i < 20000 && !mbar_try_wait(bar(BW_RES), 0); ++i) __nanosleep(100);
-    if (last_st >= 0)
-      for (int i = 0; i < 20000 && !mbar_try_wait(bar(BW_STFULL + (last_st & 1)), (last_st >> 1) & 1); ++i) __nanosleep(100);
+    for (int k = 0; k < NST && last_st - k >= 0; ++k) {
+      const int st = last_st - k;
+      for (int i = 0; i < 20000 && !mbar_try_wait(bar(BW_STFULL + st % NST), (st / NST) & 1); ++i) __nanosleep(100);
+    }
   }
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
 }
 
 // ---------------------------------------------------------------- inverted index
-// cnt[owner][c] += row groups that list key block c (G per entry of a list shared by the group).
-__global__ void __launch_bounds__(256) bw5_count_kernel(const int32_t* __restrict__ idx, int* __restrict__ cnt, int B, int Hi, int Hkv,
-                                                        int nq, int top_k, int nkb, int Tq, int offset, int causal, int gx) {
-  const long long n = (long long)B * Hi * nq * top_k;
-  const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (e >= n) return;
-  const int qb = (int)((e / top_k) % nq);
-  const long long bh = e / ((long long)top_k * nq);
-  const int hi = (int)(bh % Hi), b = (int)(bh / Hi);
-  const int hk = hi / (Hi / Hkv);
-  const int blk = idx[e];
-  if (bw5_legal(blk, qb, nkb, Tq, offset, causal)) atomicAdd(&cnt[((size_t)b * Hkv + hk) * nkb + blk], gx);
+// A stable counting sort of the list entries (list, query block, slot) by key block, in three steps whose work is
+// linear in the number of entries: per-chunk histograms, prefix sums over (list, chunk) per key block, ordered fill.
+constexpr int BW5_QC = 32;            // query blocks per chunk
+constexpr int BW5_MAX_NKB = 12288;    // key blocks a histogram in shared memory can hold
+
+// hist[(list*nchunks + chunk)*nkb + c] = legal entries of the chunk's query blocks that name key block c
+__global__ void __launch_bounds__(256) bw5_hist_kernel(const int32_t* __restrict__ idx, int* __restrict__ hist, int nq, int top_k, int nkb,
+                                                       int nchunks, int Tq, int offset, int causal) {
+  extern __shared__ int h_s[];
+  const int chunk = blockIdx.x, list = blockIdx.y;
+  for (int i = threadIdx.x; i < nkb; i += blockDim.x) h_s[i] = 0;
+  __syncthreads();
+  const int qb0 = chunk * BW5_QC, qb1 = min(qb0 + BW5_QC, nq);
+  const int32_t* row = idx + (size_t)list * nq * top_k;
+  for (int e = qb0 * top_k + threadIdx.x; e < qb1 * top_k; e += blockDim.x) {
+    const int blk = row[e];
+    if (bw5_legal(blk, e / top_k, nkb, Tq, offset, causal)) atomicAdd(&h_s[blk], 1);
+  }
+  __syncthreads();
+  int* out = hist + ((size_t)list * nchunks + chunk) * nkb;
+  for (int i = threadIdx.x; i < nkb; i += blockDim.x) out[i] = h_s[i];
+}
+
+// Per (owner, key block c): the histogram entries of the owner's lists, in (list, chunk) order, become exclusive prefix
+// sums (the position of the chunk's first entry in c's list); cnt[owner][c] = row groups in the list.  A thread block
+// takes 32 key blocks (one per lane); its 8 warps split the (list, chunk) sequence and combine through shared memory.
+__global__ void __launch_bounds__(256) bw5_prefix_kernel(int* __restrict__ hist, int* __restrict__ cnt, int nkb, int nchunks, int Hi,
+                                                         int Hkv, int G, int shared) {
+  __shared__ int part[8][32];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int owner = blockIdx.y, b = owner / Hkv, hk = owner % Hkv;
+  const int c = blockIdx.x * 32 + lane;
+  const bool in = c < nkb;
+  const int nlists = shared ? 1 : G;
+  const int nseq = nlists * nchunks;
+  const int per = (nseq + 7) / 8;
+  const int s0 = min(w * per, nseq), s1 = min(s0 + per, nseq);
+  auto at = [&](int s) {
+    const int l = s / nchunks, ch = s % nchunks;
+    const int list = b * Hi + (shared ? hk : hk * G + l);
+    return hist + ((size_t)list * nchunks + ch) * nkb + c;
+  };
+  int sum = 0;
+  for (int sb = s0; sb < s1; sb += 8) {
+    int v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = (in && sb + k < s1) ? __ldcg(at(sb + k)) : 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) sum += v[k];
+  }
+  part[w][lane] = sum;
+  __syncthreads();
+  int run = 0, total = 0;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) { if (k < w) run += part[k][lane]; total += part[k][lane]; }
+  for (int sb = s0; sb < s1; sb += 8) {
+    int v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = (in && sb + k < s1) ? __ldcg(at(sb + k)) : 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (in && sb + k < s1) __stcg(at(sb + k), run);
+      run += v[k];
+    }
+  }
+  if (w == 0 && in) cnt[(size_t)owner * nkb + c] = total * (shared ? G : 1);
 }
 
 // Per owner (batch, KV head): exclusive scans over the key blocks of (row groups, segments, partial slots); writes the
@@ -534,43 +599,43 @@ __global__ void __launch_bounds__(1024) bw5_plan_kernel(const int* __restrict__ 
   if (tid == 0) n_items[owner] = run[1];
 }
 
-// One warp per (owner, key block): walks the block lists in (head, query block, slot) order and appends the row
-// groups that list the key block -- a fixed order, so the sums of the key-major pass are formed in a fixed order.
-__global__ void __launch_bounds__(256) bw5_fill_kernel(const int32_t* __restrict__ idx, const int* __restrict__ cnt, const int* __restrict__ off,
-                                                       uint32_t* __restrict__ rg_list, long long cap_rg, int B, int Hi, int Hkv, int nq,
-                                                       int top_k, int nkb, int Tq, int offset, int causal, int G, int shared) {
+// One warp per (list, chunk): walks the chunk's query blocks in order and writes each legal entry at its position in
+// the key block's list -- (head, query block, slot) order, so the sums of the key-major pass are formed in a fixed
+// order.  hist holds the chunk's starting positions (bw5_prefix_kernel) and serves as the running cursor.
+__global__ void __launch_bounds__(256) bw5_fill_kernel(const int32_t* __restrict__ idx, int* __restrict__ hist, const int* __restrict__ off,
+                                                       uint32_t* __restrict__ rg_list, long long cap_rg, int n_lists, int Hi, int Hkv, int nq,
+                                                       int top_k, int nkb, int nchunks, int Tq, int offset, int causal, int G, int shared) {
   const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
-  if (w >= (long long)B * Hkv * nkb) return;
-  const int owner = (int)(w / nkb), c = (int)(w % nkb);
-  if (cnt[(size_t)owner * nkb + c] == 0) return;
-  const int b = owner / Hkv, hk = owner % Hkv;
-  uint32_t* dst = rg_list + (size_t)owner * cap_rg + off[(size_t)owner * nkb + c];
-  // first query block that can list key block c under the causal rule (legality is checked again per entry)
-  int qb0 = 0;
-  if (causal) qb0 = max(0, (c * 64 - offset) / 64 - 1);
-  int pos = 0;
-  const int nlists = shared ? 1 : G;
-  const long long n_ent = (long long)nq * top_k;
-  for (int hl = 0; hl < nlists; ++hl) {
-    const int hi = shared ? hk : hk * G + hl;
-    const int32_t* row = idx + ((size_t)b * Hi + hi) * n_ent;
-    for (long long e0 = (long long)qb0 * top_k; e0 < n_ent; e0 += 32) {
-      const long long e = e0 + lane;
-      bool m = false;
-      int qb = 0;
-      if (e < n_ent) {
-        qb = (int)(e / top_k);
-        const int blk = row[e];
-        m = blk == c && bw5_legal(blk, qb, nkb, Tq, offset, causal);
+  if (w >= (long long)n_lists * nchunks) return;
+  const int list = (int)(w / nchunks), chunk = (int)(w % nchunks);
+  const int b = list / Hi, hi = list % Hi;
+  const int hk = hi / (Hi / Hkv), hl = shared ? 0 : hi % G;
+  const int owner = b * Hkv + hk;
+  int* cur = hist + ((size_t)list * nchunks + chunk) * nkb;
+  const int* off_o = off + (size_t)owner * nkb;
+  uint32_t* dst = rg_list + (size_t)owner * cap_rg;
+  const int32_t* row = idx + (size_t)list * nq * top_k;
+  const int qb0 = chunk * BW5_QC, qb1 = min(qb0 + BW5_QC, nq);
+  for (int qb = qb0; qb < qb1; ++qb) {
+    for (int sl0 = 0; sl0 < top_k; sl0 += 32) {
+      const int sl = sl0 + lane;
+      const int blk = sl < top_k ? row[(size_t)qb * top_k + sl] : -1;
+      const bool ok = bw5_legal(blk, qb, nkb, Tq, offset, causal);
+      // lanes that name the same key block (a list may repeat a block) take consecutive positions in slot order
+      const unsigned same = __match_any_sync(0xffffffffu, ok ? blk : -1 - lane);
+      const int rank = __popc(same & ((1u << lane) - 1));
+      int base = 0;
+      if (ok) {
+        base = __ldcg(cur + blk);
+        const int at = base + rank;
+        const int o = off_o[blk];
+        if (shared) { for (int g = 0; g < G; ++g) dst[(size_t)o + (size_t)at * G + g] = ((uint32_t)g << BW5_QB_BITS) | (uint32_t)qb; }
+        else dst[(size_t)o + at] = ((uint32_t)hl << BW5_QB_BITS) | (uint32_t)qb;
       }
-      const unsigned bal = __ballot_sync(0xffffffffu, m);
-      if (m) {
-        const int at = pos + __popc(bal & ((1u << lane) - 1));
-        if (shared) { for (int g = 0; g < G; ++g) dst[(size_t)at * G + g] = ((uint32_t)g << BW5_QB_BITS) | (uint32_t)qb; }
-        else dst[at] = ((uint32_t)hl << BW5_QB_BITS) | (uint32_t)qb;
-      }
-      pos += __popc(bal);
+      __syncwarp();
+      if (ok && rank == 0) __stcg(cur + blk, base + __popc(same));
+      __syncwarp();
     }
   }
 }
@@ -600,9 +665,9 @@ __global__ void __launch_bounds__(256) bw5_reduce_kernel(const float* __restrict
 
 // ---------------------------------------------------------------- host side
 struct Bw5Plan {
-  int nkb, G, shared, L, capW, capP;
-  long long cap_rg, owners;
-  size_t o_cnt, o_off, o_seg, o_nitems, o_items, o_list, o_part, total;
+  int nkb, G, shared, L, capW, capP, nchunks;
+  long long cap_rg, owners, n_lists;
+  size_t o_cnt, o_off, o_seg, o_nitems, o_items, o_list, o_hist, o_part, total;
 };
 
 bool attention_bwd_tc5_supports(const nsa_bwd_args& a) {
@@ -611,6 +676,7 @@ bool attention_bwd_tc5_supports(const nsa_bwd_args& a) {
   if (!(a.D == 64 || a.D == 128)) return false;
   if (a.bm != 64 || a.bn != 64 || a.top_k > BW5_MAX_SEL) return false;
   if (a.nq >= (1 << BW5_QB_BITS) || a.H / a.Hkv >= (1 << (32 - BW5_QB_BITS))) return false;
+  if ((a.sel_key_limit + 63) / 64 > BW5_MAX_NKB || (long long)a.B * a.H > 65535) return false;
   if (!(a.scale > 0.f)) return false;
   return true;
 }
@@ -622,6 +688,8 @@ static Bw5Plan bw5_plan(const nsa_bwd_args& a) {
   pl.shared = a.Hi != a.H ? 1 : 0;
   pl.owners = (long long)a.B * a.Hkv;
   pl.cap_rg = (long long)pl.G * a.nq * a.top_k;
+  pl.n_lists = (long long)a.B * a.Hi;
+  pl.nchunks = (a.nq + BW5_QC - 1) / BW5_QC;
   // segment length (row groups, even): about 16 work items per SM over the whole launch, between 128 and 1024
   long long L = (pl.cap_rg * pl.owners / 2400 + 1) / 2 * 2;
   pl.L = (int)(L < 128 ? 128 : (L > 1024 ? 1024 : L));
@@ -635,6 +703,7 @@ static Bw5Plan bw5_plan(const nsa_bwd_args& a) {
   pl.o_seg = o; o = up(o + (size_t)pl.owners * pl.nkb * 8);
   pl.o_items = o; o = up(o + (size_t)pl.owners * pl.capW * 16);
   pl.o_list = o; o = up(o + (size_t)pl.owners * pl.cap_rg * 4);
+  pl.o_hist = o; o = up(o + (size_t)pl.n_lists * pl.nchunks * pl.nkb * 4);
   pl.o_part = o; o = up(o + (size_t)pl.owners * pl.capP * 2 * 64 * a.D * 4);
   pl.total = o;
   return pl;
@@ -654,6 +723,7 @@ int attention_bwd_tc5(const nsa_bwd_args& a, void* scratch, long long scratch_by
   int2* seginfo = reinterpret_cast<int2*>(sc + pl.o_seg);
   int4* items = reinterpret_cast<int4*>(sc + pl.o_items);
   uint32_t* rg_list = reinterpret_cast<uint32_t*>(sc + pl.o_list);
+  int* hist = reinterpret_cast<int*>(sc + pl.o_hist);
   float* partials = reinterpret_cast<float*>(sc + pl.o_part);
 
   Bw5Params p;
@@ -671,20 +741,21 @@ int attention_bwd_tc5(const nsa_bwd_args& a, void* scratch, long long scratch_by
   if ((rc = make_map(&p.tmV, a.V, (long long)a.B * a.Hkv, a.Tk, a.D, a.dtype)) != NSA_OK) return rc;
 
   // inverted index
-  NSA_CUDA_OK(cudaMemsetAsync(sc + pl.o_cnt, 0, pl.o_off - pl.o_cnt, st));     // counts and item counts
-  const long long n_ent = (long long)a.B * a.Hi * a.nq * a.top_k;
-  NSA_REQUIRE(n_ent < (1LL << 40) && (long long)pl.owners * pl.capW < 2147483647LL, NSA_ERR_ARG, "selected backward: problem too large");
-  bw5_count_kernel<<<(unsigned)((n_ent + 255) / 256), 256, 0, st>>>(a.idx, cnt, a.B, a.Hi, a.Hkv, a.nq, a.top_k, pl.nkb, a.Tq, a.offset,
-                                                                   a.causal, pl.shared ? pl.G : 1);
+  NSA_REQUIRE((long long)pl.owners * pl.capW < 2147483647LL && pl.n_lists * pl.nchunks < (1LL << 31) / 32, NSA_ERR_ARG,
+              "selected backward: problem too large");
+  bw5_hist_kernel<<<dim3((unsigned)pl.nchunks, (unsigned)pl.n_lists), 256, (size_t)pl.nkb * 4, st>>>(a.idx, hist, a.nq, a.top_k, pl.nkb,
+                                                                                                  pl.nchunks, a.Tq, a.offset, a.causal);
+  bw5_prefix_kernel<<<dim3((unsigned)((pl.nkb + 31) / 32), (unsigned)pl.owners), 256, 0, st>>>(hist, cnt, pl.nkb, pl.nchunks, a.Hi, a.Hkv,
+                                                                                             pl.G, pl.shared);
   bw5_plan_kernel<<<(unsigned)pl.owners, 1024, 0, st>>>(cnt, off, seginfo, items, n_items, pl.nkb, pl.L, pl.capW);
-  const long long warps = pl.owners * pl.nkb;
-  bw5_fill_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(a.idx, cnt, off, rg_list, pl.cap_rg, a.B, a.Hi, a.Hkv, a.nq, a.top_k, pl.nkb,
-                                                              a.Tq, a.offset, a.causal, pl.G, pl.shared);
+  const long long warps = pl.n_lists * pl.nchunks;
+  bw5_fill_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(a.idx, hist, off, rg_list, pl.cap_rg, (int)pl.n_lists, a.Hi, a.Hkv, a.nq,
+                                                              a.top_k, pl.nkb, pl.nchunks, a.Tq, a.offset, a.causal, pl.G, pl.shared);
   if ((rc = launch_status("selected backward index")) != NSA_OK) return rc;
 
   const int DHh = a.D / 64;
-  const size_t smem0 = (size_t)2 * DHh * 64 * 128 + (size_t)4 * DHh * 128 * 128 + 2 * 32768 + 1024;
-  const size_t smem1 = (size_t)2 * DHh * 128 * 128 + (size_t)4 * DHh * 64 * 128 + 2 * 16384 + 1024;
+  const size_t smem0 = (size_t)2 * DHh * 64 * 128 + (size_t)bw5_stages(a.D, 0) * 2 * DHh * 128 * 128 + 2 * 32768 + 1024;
+  const size_t smem1 = (size_t)2 * DHh * 128 * 128 + (size_t)bw5_stages(a.D, 1) * 2 * DHh * 64 * 128 + 2 * 16384 + 1024;
   const unsigned grid0 = (unsigned)(pl.owners * pl.capW);
   const long long tiles1 = pl.owners * p.NGT * a.nq;
   NSA_REQUIRE(tiles1 < 2147483647LL, NSA_ERR_ARG, "selected backward: %lld query tiles do not fit a grid", tiles1);
