@@ -30,6 +30,7 @@
 #include "tc5_ptx.cuh"
 
 #include <cudaTypedefs.h>
+#include <type_traits>
 
 namespace nsa {
 
@@ -63,11 +64,13 @@ struct Bw5Params {
   int NGT;                 // tiles per (batch, KV head, query block)
 };
 
-// barrier ids (the ring of streamed tiles has up to 4 stages)
-enum { BW_RES = 0, BW_STFULL = 1, BW_STEMPTY = 5, BW_SFULL = 9, BW_SFREE = 11, BW_PFULL = 13, BW_PEMPTY = 15, BW_ACC = 17, BW_COUNT = 18 };
+// barrier ids (the ring of streamed tiles has up to 8 stages)
+enum { BW_RES = 0, BW_STFULL = 1, BW_STEMPTY = 9, BW_SFULL = 17, BW_SFREE = 19, BW_PFULL = 21, BW_PEMPTY = 23, BW_ACC = 25, BW_COUNT = 26 };
 
-// Stages of the ring of streamed tiles.  Key-major at D=128 has room for two (64 KB each) only.
-__host__ __device__ constexpr int bw5_stages(int D, int mode) { return mode == 0 ? (D == 64 ? 4 : 2) : 4; }
+// Stages of the ring of streamed tiles.  A stage is held from the issue of its copy until the accumulate MMA of its step
+// has read it, i.e. across the whole softmax of the step, so the ring is as deep as shared memory allows: key-major
+// 4 x 32 KB at D=64 and 2 x 64 KB at D=128, query-major 8 x 16 KB at D=64 and 4 x 32 KB at D=128.
+__host__ __device__ constexpr int bw5_stages(int D, int mode) { return mode == 0 ? (D == 64 ? 4 : 2) : (D == 64 ? 8 : 4); }
 
 __device__ __forceinline__ bool bw5_legal(int blk, int qb, int nkb, int Tq, int offset, int causal) {
   if (blk < 0 || blk >= nkb) return false;
@@ -87,9 +90,6 @@ __global__ void __launch_bounds__(BW5_THREADS, 1) nsa_bwd_tc5_kernel(const __gri
   constexpr int ST_BYTES = MODE == 0 ? 2 * T128 : 2 * T64;    // one ring stage: dO,Q (key-major) or K,V (query-major)
   constexpr int PB_BYTES = MODE == 0 ? 32768 : 16384;         // one P|dS buffer (key-major) or dS buffer (query-major)
   constexpr int NST = bw5_stages(D, MODE);
-  // S/dP of step i+LA are issued before the accumulate MMA of step i, so that a softmax group finds its next S waiting
-  // when it finishes a step (the accumulate of step i frees ring stage i % NST, which step i+LA must not need)
-  constexpr int LA = NST >= 3 ? 2 : 1;
   const nsa_bwd_args& a = p.a;
 
   // ---- work item (uniform over the block; blocks beyond the item count leave before anything is set up) ----
@@ -202,9 +202,31 @@ __global__ void __launch_bounds__(BW5_THREADS, 1) nsa_bwd_tc5_kernel(const __gri
       }
     }
     __syncwarp();
+    // Key-major: the streamed Q/dO tiles come from HBM (each is read by few thread blocks), about 1800 clocks per copy,
+    // more than the ring hides; the tiles of step st+PF are therefore pulled into L2 ahead of their copy.
+    constexpr int PF = NST + 3;
+    auto prefetch_step = [&](int st) {
+      if constexpr (MODE == 0) {
+        if (st < nsteps) {
+          for (int g = 0; g < 2; ++g) {
+            int hl, qblk;
+            if (!row_group(st, g, hl, qblk)) continue;
+            if (leader) {
+              const int slab = b * a.H + hk * p.G + hl;
+              for (int dh = 0; dh < DH; ++dh) {
+                tma_prefetch_3d(&p.tmdO, dh * 64, qblk * 64, slab);
+                tma_prefetch_3d(&p.tmQ, dh * 64, qblk * 64, slab);
+              }
+            }
+          }
+        }
+      }
+    };
+    for (int st = NST; st < PF; ++st) prefetch_step(st);
     bool ok = true;
     for (int st = 0; st < nsteps && ok; ++st) {
       const int s = st % NST;
+      prefetch_step(st + PF);
       ok = __all_sync(0xffffffffu, mbar_wait(bar(BW_STEMPTY + s), ((st / NST) & 1) ^ 1, &abort_flag));
       if (!ok) { fail_id = BW_STEMPTY + s + 1; break; }
       const uint32_t dst = sSt + s * ST_BYTES;
@@ -249,10 +271,9 @@ __global__ void __launch_bounds__(BW5_THREADS, 1) nsa_bwd_tc5_kernel(const __gri
     auto offB = [](int ks) { return (uint32_t)(((ks >> 2) * 8192 + (ks & 3) * 32) >> 4); };
     const uint32_t tACC = tmem + 256;
 
-    auto issue_sdp = [&](int st) -> bool {
-      const int s = st % NST, sb = st & 1, ph = (st >> 1) & 1;
-      if (!__all_sync(0xffffffffu, mbar_wait(bar(BW_STFULL + s), (st / NST) & 1, &abort_flag))) { fail_id = BW_STFULL + s + 1; return false; }
-      if (!__all_sync(0xffffffffu, mbar_wait(bar(BW_SFREE + sb), ph ^ 1, &abort_flag))) { fail_id = BW_SFREE + sb + 1; return false; }
+    // S = Q K^T and dP = dO V^T of step st into the TMEM buffer of its parity
+    auto issue_sdp = [&](int st) {
+      const int s = st % NST, sb = st & 1;
       tc_fence_after();
       if (leader) {
         const uint32_t st_base = sSt + s * ST_BYTES;
@@ -269,11 +290,10 @@ __global__ void __launch_bounds__(BW5_THREADS, 1) nsa_bwd_tc5_kernel(const __gri
         tc_commit(bar(BW_SFULL + sb));
       }
       __syncwarp();
-      return true;
     };
-    auto issue_acc = [&](int st) -> bool {
-      const int s = st % NST, sb = st & 1, ph = (st >> 1) & 1;
-      if (!__all_sync(0xffffffffu, mbar_wait(bar(BW_PFULL + sb), ph, &abort_flag))) { fail_id = BW_PFULL + sb + 1; return false; }
+    // the accumulate MMA of step st (reads P/dS of its parity and ring stage st % NST; frees both)
+    auto issue_acc = [&](int st) {
+      const int s = st % NST, sb = st & 1;
       tc_fence_after();
       if (leader) {
         const uint32_t st_base = sSt + s * ST_BYTES, pbuf = sPb + sb * PB_BYTES;
@@ -295,12 +315,29 @@ __global__ void __launch_bounds__(BW5_THREADS, 1) nsa_bwd_tc5_kernel(const __gri
         tc_commit(bar(BW_STEMPTY + s));
       }
       __syncwarp();
-      return true;
     };
-    for (int st = 0; st < LA && st < nsteps && ok; ++st) ok = issue_sdp(st);
-    for (int st = 0; st < nsteps && ok; ++st) {
-      if (st + LA < nsteps) ok = issue_sdp(st + LA);
-      if (ok) ok = issue_acc(st);
+    // Whatever is ready is issued: S/dP of step ns as soon as its tiles have landed and the softmax group of its
+    // parity holds the previous S/dP of that buffer in registers; the accumulate of step na as soon as its P/dS are in
+    // shared memory.  (A fixed order makes one of the two softmax groups wait for the other through this warp.)
+    int ns = 0, na = 0;
+    long long idle = 0;
+    while (na < nsteps && ok) {
+      bool did = false;
+      if (ns < nsteps) {
+        const bool rdy = mbar_test_wait(bar(BW_STFULL + ns % NST), (ns / NST) & 1) && mbar_test_wait(bar(BW_SFREE + (ns & 1)), ((ns >> 1) & 1) ^ 1);
+        if (__all_sync(0xffffffffu, rdy)) { issue_sdp(ns); ++ns; did = true; }
+      }
+      if (na < ns) {
+        const bool rdy = mbar_test_wait(bar(BW_PFULL + (na & 1)), (na >> 1) & 1);
+        if (__all_sync(0xffffffffu, rdy)) { issue_acc(na); ++na; did = true; }
+      }
+      if (did) { idle = 0; continue; }
+      ++idle;                                                // bounded: about a second, or until another warp gives up
+      __nanosleep(20);                                       // leave the issue slots to the softmax warps of this scheduler
+      if (idle > 65536) {
+        if (abort_flag || idle > (1 << 23)) { abort_flag = 1; fail_id = (na < ns ? BW_PFULL + (na & 1) : BW_STFULL + ns % NST) + 1; ok = false; break; }
+        __nanosleep(100);
+      }
     }
     if (ok && nsteps > 0) {
       if (leader) tc_commit(bar(BW_ACC));
@@ -320,33 +357,53 @@ __global__ void __launch_bounds__(BW5_THREADS, 1) nsa_bwd_tc5_kernel(const __gri
     unsigned char* prow = pb_ptr + grp * PB_BYTES + r * 128;           // this row of P (key-major) / dS (query-major)
     const float sc = a.scale;
 
-    // what a query row needs: its log-sum-exp (log2 units), delta*scale, and the last key position it may see
+    // What a query row needs: its log-sum-exp (log2 units), delta*scale, and the last key position it may see.
+    // Query-major: the row is fixed.  Key-major: the rows change every step and come through two dependent loads
+    // (list entry, then lse/delta), a couple of thousand clocks when taken in line -- so they are fetched ahead: in
+    // the iteration of step st the loads of lse/delta for step st+2 (this group's next) and of the list entry for
+    // step st+4 are issued, and their results are first touched one iteration later.
     float lse2 = 0.f, dls = 0.f;
     int hi = -1;
-    auto load_row = [&](int st) {
-      int hl, qblk;
-      const bool okg = row_group(st, g2, hl, qblk);
-      const int qi = qblk * 64 + (r & 63);
+    auto entry = [&](int st) -> uint32_t {                   // list entry of this thread's row group at step st, or ~0
+      if constexpr (MODE == 0) { const int e = 2 * st + g2; return e < n_rg ? rgl[e] : 0xffffffffu; }
+      else return g2 < ng ? (((uint32_t)(h0 + g2) << BW5_QB_BITS) | (uint32_t)qb) : 0xffffffffu;   // the same rows at every step
+    };
+    struct RowRaw { float l, d; int qi; bool ok; };
+    auto fetch = [&](uint32_t ent) -> RowRaw {               // issues the loads (unconditionally, from a safe address, so that
+      RowRaw rr;                                             // nothing has to wait for them before `adopt`)
+      const int hl = (int)(ent >> BW5_QB_BITS), qblk = (int)(ent & ((1u << BW5_QB_BITS) - 1));
+      rr.qi = qblk * 64 + (r & 63);
+      rr.ok = ent != 0xffffffffu && rr.qi < a.Tq;
+      const size_t ri = rr.ok ? ((size_t)b * a.H + hk * p.G + hl) * a.Tq + rr.qi : 0;
+      rr.l = a.lse[ri];
+      rr.d = a.delta[ri];
+      return rr;
+    };
+    auto adopt = [&](const RowRaw& rr) {
       lse2 = 0.f; dls = 0.f; hi = -1;
-      if (okg && qi < a.Tq) {
-        const size_t ri = ((size_t)b * a.H + hk * p.G + hl) * a.Tq + qi;
-        const float l = a.lse[ri];
-        if (l > -INFINITY) {
-          lse2 = l * kLog2e;
-          dls = a.delta[ri] * sc;
-          hi = a.causal ? min(qi + a.offset, a.sel_key_limit - 1) : a.sel_key_limit - 1;
-        }
+      if (rr.ok && rr.l > -INFINITY) {
+        lse2 = rr.l * kLog2e;
+        dls = rr.d * sc;
+        hi = a.causal ? min(rr.qi + a.offset, a.sel_key_limit - 1) : a.sel_key_limit - 1;
       }
     };
-    if constexpr (MODE == 1) load_row(0);
+    RowRaw nxt = fetch(entry(grp));                          // rows of this group's first step
+    uint32_t ent_nn = MODE == 0 ? entry(grp + 2) : 0xffffffffu;
 
     bool ok = true;
 #pragma unroll 1
     for (int st = grp; st < nsteps && ok; st += 2) {
       const int ph = (st >> 1) & 1;
       int j0;
-      if constexpr (MODE == 0) { load_row(st); j0 = c * 64; }
-      else j0 = sel_list[st] * 64;
+      if constexpr (MODE == 0) {
+        adopt(nxt);
+        nxt = fetch(ent_nn);
+        ent_nn = entry(st + 4);
+        j0 = c * 64;
+      } else {
+        if (st == grp) adopt(nxt);
+        j0 = sel_list[st] * 64;
+      }
       const int vhi = min(hi, min(j0 + 64, a.sel_key_limit) - 1) - j0;   // columns 0..vhi of the tile count for this row
       ok = __all_sync(0xffffffffu, mbar_wait(bar(BW_SFULL + grp), ph, &abort_flag));
       if (!ok) { fail_id = BW_SFULL + grp + 1; break; }
@@ -359,22 +416,29 @@ __global__ void __launch_bounds__(BW5_THREADS, 1) nsa_bwd_tc5_kernel(const __gri
       tc_wait_ld();
       tc_fence_before();
       mbar_arrive(bar(BW_SFREE + grp));                    // S and dP are in registers: the next step may overwrite them
-      // P and dS in place (sv <- P, dv <- dS), then packed to 16 bits
+      // P and dS, packed to 16 bits.  Only tiles on the causal diagonal (or with rows that take no part) need the
+      // per-element mask; the other tiles of a warp skip its compare and select.
       uint32_t pk[2][16], dk[2][16];
+      auto compute = [&](auto masked) {
 #pragma unroll
-      for (int g = 0; g < 2; ++g) {
+        for (int g = 0; g < 2; ++g) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float p0 = ex2(fmaf(__uint_as_float(sv[g][2 * i]), p.scale_log2, -lse2));
-          float p1 = ex2(fmaf(__uint_as_float(sv[g][2 * i + 1]), p.scale_log2, -lse2));
-          if (g * 32 + 2 * i > vhi) p0 = 0.f;
-          if (g * 32 + 2 * i + 1 > vhi) p1 = 0.f;
-          const float d0 = p0 * fmaf(__uint_as_float(dv[g][2 * i]), sc, -dls);
-          const float d1 = p1 * fmaf(__uint_as_float(dv[g][2 * i + 1]), sc, -dls);
-          pk[g][i] = Elem<T>::pack(p0, p1);
-          dk[g][i] = Elem<T>::pack(d0, d1);
+          for (int i = 0; i < 16; ++i) {
+            float p0 = ex2(fmaf(__uint_as_float(sv[g][2 * i]), p.scale_log2, -lse2));
+            float p1 = ex2(fmaf(__uint_as_float(sv[g][2 * i + 1]), p.scale_log2, -lse2));
+            if constexpr (decltype(masked)::value) {
+              if (g * 32 + 2 * i > vhi) p0 = 0.f;
+              if (g * 32 + 2 * i + 1 > vhi) p1 = 0.f;
+            }
+            const float d0 = p0 * fmaf(__uint_as_float(dv[g][2 * i]), sc, -dls);
+            const float d1 = p1 * fmaf(__uint_as_float(dv[g][2 * i + 1]), sc, -dls);
+            pk[g][i] = Elem<T>::pack(p0, p1);
+            dk[g][i] = Elem<T>::pack(d0, d1);
+          }
         }
-      }
+      };
+      if (__all_sync(0xffffffffu, vhi >= 63)) compute(std::false_type{});
+      else compute(std::true_type{});
       ok = __all_sync(0xffffffffu, mbar_wait(bar(BW_PEMPTY + grp), ph ^ 1, &abort_flag));
       if (!ok) { fail_id = BW_PEMPTY + grp + 1; break; }
       // one 128-byte row per thread, 16-byte chunks XOR-swizzled with the row (the layout TMA's 128-byte swizzle gives)
