@@ -20,9 +20,11 @@
 //   list (64 rows of one head when every head has its own list).  Q and dO stay in shared memory, the listed
 //   K/V blocks stream by:  S, dP, dS as above, then dQ += dS K (A = dS from shared memory, B = K MN-major).
 //
-// Warp roles (12 warps; setmaxnreg moves registers from the control warps to the softmax warps):
-//   warp 0  TMA producer      warp 1  MMA issuer      warp 2  block-list builder (query-major pass)
-//   warps 4-7 and 8-11: two softmax groups, alternating steps (thread = TMEM lane = row of the 128-row tile)
+// Warp roles (18 warps at 112 registers):
+//   warp 0  TMA producer      warp 1  MMA issuer (issues whatever is ready: S/dP of a later step or an accumulate)
+//   warps 2-9 and 10-17: two softmax groups that alternate steps.  A row of the 128-row tile (= TMEM lane) is
+//   shared by two threads, 32 of its 64 columns each -- the log-sum-exp is an input, so the halves of a row need
+//   nothing from each other -- which puts four softmax warps on every scheduler to hide each other's waits.
 // TMEM columns: S/dP of step parity 0 at [0,64)/[64,128), of parity 1 at [128,192)/[192,256), accumulator from 256.
 // Every mbarrier wait is bounded; a wait that gives up raises a block-wide abort flag, the block drains its
 // copies (bounded), frees its TMEM, and the status word reports it.
@@ -40,7 +42,7 @@ int make_map(CUtensorMap* m, const void* ptr, long long slabs, long long rows, i
 
 __device__ int g_bw5_status;   // 0 ok; otherwise (1 + id of the barrier a wait gave up on)
 
-constexpr int BW5_THREADS = 384;
+constexpr int BW5_THREADS = 576;      // 18 warps: TMA producer, MMA issuer, 2 softmax groups of 8 warps
 constexpr int BW5_MAX_SEL = 256;      // listed blocks per query block (query-major pass)
 constexpr int BW5_QB_BITS = 20;       // row group = (head within the group << 20) | query block
 
@@ -65,7 +67,7 @@ struct Bw5Params {
 };
 
 // barrier ids (the ring of streamed tiles has up to 8 stages)
-enum { BW_RES = 0, BW_STFULL = 1, BW_STEMPTY = 9, BW_SFULL = 17, BW_SFREE = 19, BW_PFULL = 21, BW_PEMPTY = 23, BW_ACC = 25, BW_COUNT = 26 };
+enum { BW_RES = 0, BW_STFULL = 1, BW_STEMPTY = 9, BW_SFULL = 17, BW_SFREE = 19, BW_PFULL = 21, BW_PEMPTY = 23, BW_ACC = 25, BW_QTMEM = 26, BW_COUNT = 27 };
 
 // Stages of the ring of streamed tiles.  A stage is held from the issue of its copy until the accumulate MMA of its step
 // has read it, i.e. across the whole softmax of the step, so the ring is as deep as shared memory allows: key-major
@@ -90,6 +92,12 @@ __global__ void __launch_bounds__(BW5_THREADS, 1) nsa_bwd_tc5_kernel(const __gri
   constexpr int ST_BYTES = MODE == 0 ? 2 * T128 : 2 * T64;    // one ring stage: dO,Q (key-major) or K,V (query-major)
   constexpr int PB_BYTES = MODE == 0 ? 32768 : 16384;         // one P|dS buffer (key-major) or dS buffer (query-major)
   constexpr int NST = bw5_stages(D, MODE);
+  // Query-major pass: the A operands that change slowly or are made by the softmax threads live in TMEM instead of shared
+  // memory -- the MMAs of a step then read only their B operands (K, V tiles) from shared memory, whose bandwidth is what
+  // bounds these small (N = 64) MMAs.  dS (16-bit, 32 columns per buffer) always; Q and dO (32 columns each) at D=64,
+  // where the columns are there: S/dP [0,256)  dQ [256,256+D)  dS [384,448)  Q [448,480)  dO [480,512).
+  constexpr bool DS_TMEM = MODE == 1;
+  constexpr bool Q_TMEM = MODE == 1 && D == 64;
   const nsa_bwd_args& a = p.a;
 
   // ---- work item (uniform over the block; blocks beyond the item count leave before anything is set up) ----
@@ -134,7 +142,7 @@ __global__ void __launch_bounds__(BW5_THREADS, 1) nsa_bwd_tc5_kernel(const __gri
   if (tid == 0) {
     abort_flag = 0;
     for (int i = 0; i < BW_COUNT; ++i)
-      mbar_init(bar(i), (i == BW_SFREE || i == BW_SFREE + 1 || i == BW_PFULL || i == BW_PFULL + 1) ? 128 : 1);
+      mbar_init(bar(i), (i == BW_SFREE || i == BW_SFREE + 1 || i == BW_PFULL || i == BW_PFULL + 1) ? 256 : (i == BW_QTMEM ? 512 : 1));
     fence_barrier_init();
   }
   if (warp == 1) { tmem_alloc(smem_u32(&tmem_base_s), 512); tmem_relinquish(); }
@@ -178,7 +186,6 @@ __global__ void __launch_bounds__(BW5_THREADS, 1) nsa_bwd_tc5_kernel(const __gri
   int last_st = -1;        // producer: last step whose copies were issued
 
   if (warp == 0) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;\n");
     // =============================== TMA producer ===============================
     const bool leader = elect_one();
     if (leader) {
@@ -258,7 +265,6 @@ __global__ void __launch_bounds__(BW5_THREADS, 1) nsa_bwd_tc5_kernel(const __gri
       __syncwarp();
     }
   } else if (warp == 1) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;\n");
     // =============================== MMA issuer ===============================
     const bool leader = elect_one();
     constexpr uint32_t IDESC_S = idesc_f16(FMT, 128, 64, 0, 0);            // [128 rows x 64 keys] = A(K-major) B(K-major)^T
@@ -270,6 +276,13 @@ __global__ void __launch_bounds__(BW5_THREADS, 1) nsa_bwd_tc5_kernel(const __gri
     auto offA = [](int ks) { return (uint32_t)(((ks >> 2) * 16384 + (ks & 3) * 32) >> 4); };
     auto offB = [](int ks) { return (uint32_t)(((ks >> 2) * 8192 + (ks & 3) * 32) >> 4); };
     const uint32_t tACC = tmem + 256;
+    if constexpr (Q_TMEM) {
+      if (ok) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(BW_QTMEM), 0, &abort_flag));
+        if (!ok) fail_id = BW_QTMEM + 1;
+        tc_fence_after();
+      }
+    }
 
     // S = Q K^T and dP = dO V^T of step st into the TMEM buffer of its parity
     auto issue_sdp = [&](int st) {
@@ -283,10 +296,17 @@ __global__ void __launch_bounds__(BW5_THREADS, 1) nsa_bwd_tc5_kernel(const __gri
         const uint64_t bS = smem_desc_sw128(MODE == 0 ? sRes : st_base, 16, 1024);
         const uint64_t bP = smem_desc_sw128(MODE == 0 ? sRes + T64 : st_base + T64, 16, 1024);
         const uint32_t tS = tmem + sb * 128, tdP = tS + 64;
+        if constexpr (Q_TMEM) {
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) mma_ss(tS, aS + offA(ks), bS + offB(ks), IDESC_S, ks == 0 ? 0u : 1u);
+          for (int ks = 0; ks < D / 16; ++ks) mma_ts(tS, tmem + 448 + ks * 8, bS + offB(ks), IDESC_S, ks == 0 ? 0u : 1u);
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) mma_ss(tdP, aP + offA(ks), bP + offB(ks), IDESC_S, ks == 0 ? 0u : 1u);
+          for (int ks = 0; ks < D / 16; ++ks) mma_ts(tdP, tmem + 480 + ks * 8, bP + offB(ks), IDESC_S, ks == 0 ? 0u : 1u);
+        } else {
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ++ks) mma_ss(tS, aS + offA(ks), bS + offB(ks), IDESC_S, ks == 0 ? 0u : 1u);
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ++ks) mma_ss(tdP, aP + offA(ks), bP + offB(ks), IDESC_S, ks == 0 ? 0u : 1u);
+        }
         tc_commit(bar(BW_SFULL + sb));
       }
       __syncwarp();
@@ -305,11 +325,11 @@ __global__ void __launch_bounds__(BW5_THREADS, 1) nsa_bwd_tc5_kernel(const __gri
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) mma_ss(tACC, dA + kk * 128, dB + kk * 128, IDESC_ACC, (st > 0 || kk > 0) ? 1u : 0u);
         } else {
-          // A: dS [128 rows x 64 keys] K-major;  B: K [64 keys x D] MN-major (halves 8192 bytes apart)
-          const uint64_t dA = smem_desc_sw128(pbuf, 16, 1024);
+          // A: dS [128 rows x 64 keys] from TMEM (16-bit pairs, 8 columns per 16 keys);  B: K [64 keys x D] MN-major (halves 8192 bytes apart)
           const uint64_t dB = smem_desc_sw128(st_base, 8192, 1024);
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) mma_ss(tACC, dA + ks * 2, dB + ks * 128, IDESC_ACC, (st > 0 || ks > 0) ? 1u : 0u);
+          for (int ks = 0; ks < 4; ++ks) mma_ts(tACC, tmem + 384 + sb * 32 + ks * 8, dB + ks * 128, IDESC_ACC, (st > 0 || ks > 0) ? 1u : 0u);
+          (void)pbuf;
         }
         tc_commit(bar(BW_PEMPTY + sb));
         tc_commit(bar(BW_STEMPTY + s));
@@ -343,17 +363,15 @@ __global__ void __launch_bounds__(BW5_THREADS, 1) nsa_bwd_tc5_kernel(const __gri
       if (leader) tc_commit(bar(BW_ACC));
       __syncwarp();
     }
-  } else if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;\n");
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;\n");
     // =============================== softmax / epilogue ===============================
-    const int grp = (warp - 4) >> 2;                       // handles the steps of parity grp
-    const int quarter = warp & 3;
+    const int grp = (warp - 2) >> 3;                       // handles the steps of parity grp
+    const int quarter = warp & 3;                          // the TMEM lanes a warp may touch: 32*(warp % 4) ..
+    const int hf = ((warp - 2) >> 2) & 1;                  // which 32 of the row's 64 columns
     const int r = quarter * 32 + lane;                     // row of the 128-row tile == TMEM lane
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const int g2 = r >> 6;
-    const uint32_t tS = tmem + lane_addr + grp * 128, tdP = tS + 64;
+    const uint32_t tS = tmem + lane_addr + grp * 128 + hf * 32, tdP = tS + 64;
     unsigned char* prow = pb_ptr + grp * PB_BYTES + r * 128;           // this row of P (key-major) / dS (query-major)
     const float sc = a.scale;
 
@@ -387,10 +405,29 @@ __global__ void __launch_bounds__(BW5_THREADS, 1) nsa_bwd_tc5_kernel(const __gri
         hi = a.causal ? min(rr.qi + a.offset, a.sel_key_limit - 1) : a.sel_key_limit - 1;
       }
     };
+    bool ok = true;
+    if constexpr (Q_TMEM) {
+      // Q (softmax group 0) and dO (group 1) from their swizzled shared-memory tiles into TMEM: a thread moves its 64
+      // bytes of its row (32 elements = 16 columns of 16-bit pairs)
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(BW_RES), 0, &abort_flag));
+      if (!ok) fail_id = BW_RES + 1;
+      if (ok) {
+        const unsigned char* src = smem + grp * T128 + r * 128;
+        uint32_t w[16];
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+          const uint4 v = *reinterpret_cast<const uint4*>(src + (((hf * 4 + c4) ^ (r & 7)) << 4));
+          w[4 * c4] = v.x; w[4 * c4 + 1] = v.y; w[4 * c4 + 2] = v.z; w[4 * c4 + 3] = v.w;
+        }
+        tmem_st16(tmem + lane_addr + 448 + grp * 32 + hf * 16, w);
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar(BW_QTMEM));
+      }
+    }
     RowRaw nxt = fetch(entry(grp));                          // rows of this group's first step
     uint32_t ent_nn = MODE == 0 ? entry(grp + 2) : 0xffffffffu;
 
-    bool ok = true;
 #pragma unroll 1
     for (int st = grp; st < nsteps && ok; st += 2) {
       const int ph = (st >> 1) & 1;
@@ -408,52 +445,50 @@ __global__ void __launch_bounds__(BW5_THREADS, 1) nsa_bwd_tc5_kernel(const __gri
       ok = __all_sync(0xffffffffu, mbar_wait(bar(BW_SFULL + grp), ph, &abort_flag));
       if (!ok) { fail_id = BW_SFULL + grp + 1; break; }
       tc_fence_after();
-      uint32_t sv[2][32], dv[2][32];
-      tmem_ld32(tS, sv[0]);
-      tmem_ld32(tS + 32, sv[1]);
-      tmem_ld32(tdP, dv[0]);
-      tmem_ld32(tdP + 32, dv[1]);
+      uint32_t sv[32], dv[32];
+      tmem_ld32(tS, sv);
+      tmem_ld32(tdP, dv);
       tc_wait_ld();
       tc_fence_before();
       mbar_arrive(bar(BW_SFREE + grp));                    // S and dP are in registers: the next step may overwrite them
       // P and dS, packed to 16 bits.  Only tiles on the causal diagonal (or with rows that take no part) need the
       // per-element mask; the other tiles of a warp skip its compare and select.
-      uint32_t pk[2][16], dk[2][16];
+      uint32_t pk[16], dk[16];
       auto compute = [&](auto masked) {
 #pragma unroll
-        for (int g = 0; g < 2; ++g) {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            float p0 = ex2(fmaf(__uint_as_float(sv[g][2 * i]), p.scale_log2, -lse2));
-            float p1 = ex2(fmaf(__uint_as_float(sv[g][2 * i + 1]), p.scale_log2, -lse2));
-            if constexpr (decltype(masked)::value) {
-              if (g * 32 + 2 * i > vhi) p0 = 0.f;
-              if (g * 32 + 2 * i + 1 > vhi) p1 = 0.f;
-            }
-            const float d0 = p0 * fmaf(__uint_as_float(dv[g][2 * i]), sc, -dls);
-            const float d1 = p1 * fmaf(__uint_as_float(dv[g][2 * i + 1]), sc, -dls);
-            pk[g][i] = Elem<T>::pack(p0, p1);
-            dk[g][i] = Elem<T>::pack(d0, d1);
+        for (int i = 0; i < 16; ++i) {
+          float p0 = ex2(fmaf(__uint_as_float(sv[2 * i]), p.scale_log2, -lse2));
+          float p1 = ex2(fmaf(__uint_as_float(sv[2 * i + 1]), p.scale_log2, -lse2));
+          if constexpr (decltype(masked)::value) {
+            if (hf * 32 + 2 * i > vhi) p0 = 0.f;
+            if (hf * 32 + 2 * i + 1 > vhi) p1 = 0.f;
           }
+          const float d0 = p0 * fmaf(__uint_as_float(dv[2 * i]), sc, -dls);
+          const float d1 = p1 * fmaf(__uint_as_float(dv[2 * i + 1]), sc, -dls);
+          pk[i] = Elem<T>::pack(p0, p1);
+          dk[i] = Elem<T>::pack(d0, d1);
         }
       };
       if (__all_sync(0xffffffffu, vhi >= 63)) compute(std::false_type{});
       else compute(std::true_type{});
       ok = __all_sync(0xffffffffu, mbar_wait(bar(BW_PEMPTY + grp), ph ^ 1, &abort_flag));
       if (!ok) { fail_id = BW_PEMPTY + grp + 1; break; }
-      // one 128-byte row per thread, 16-byte chunks XOR-swizzled with the row (the layout TMA's 128-byte swizzle gives)
+      if constexpr (DS_TMEM) {
+        // dS as the accumulate MMA's A operand in TMEM: 16 columns of 16-bit pairs for this thread's 32 keys
+        tmem_st16(tmem + lane_addr + 384 + grp * 32 + hf * 16, dk);
+        tc_wait_st();
+        tc_fence_before();
+      } else {
+        // this thread's 64 bytes of the 128-byte row; 16-byte chunks XOR-swizzled with the row (the layout TMA's 128-byte swizzle gives)
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
-        const int g = ch >> 2, i = (ch & 3) * 4;
-        const uint32_t sw = (uint32_t)((ch ^ (r & 7)) << 4);
-        if constexpr (MODE == 0) {
-          *reinterpret_cast<uint4*>(prow + sw) = make_uint4(pk[g][i], pk[g][i + 1], pk[g][i + 2], pk[g][i + 3]);
-          *reinterpret_cast<uint4*>(prow + 16384 + sw) = make_uint4(dk[g][i], dk[g][i + 1], dk[g][i + 2], dk[g][i + 3]);
-        } else {
-          *reinterpret_cast<uint4*>(prow + sw) = make_uint4(dk[g][i], dk[g][i + 1], dk[g][i + 2], dk[g][i + 3]);
+        for (int c4 = 0; c4 < 4; ++c4) {
+          const int ch = hf * 4 + c4, i = c4 * 4;
+          const uint32_t sw = (uint32_t)((ch ^ (r & 7)) << 4);
+          *reinterpret_cast<uint4*>(prow + sw) = make_uint4(pk[i], pk[i + 1], pk[i + 2], pk[i + 3]);
+          *reinterpret_cast<uint4*>(prow + 16384 + sw) = make_uint4(dk[i], dk[i + 1], dk[i + 2], dk[i + 3]);
         }
+        fence_proxy_async();
       }
-      fence_proxy_async();
       mbar_arrive(bar(BW_PFULL + grp));
     }
 
@@ -464,64 +499,61 @@ __global__ void __launch_bounds__(BW5_THREADS, 1) nsa_bwd_tc5_kernel(const __gri
       tc_fence_after();
     }
     if (ok) {
-      constexpr int HC = D / 2;                            // each softmax group handles half of the columns
+      constexpr int HC = D / 4;                            // the four warps that share a lane quarter split the columns
+      const int part = grp * 2 + hf;
+      auto load_part = [&](uint32_t taddr, uint32_t (&v)[HC]) {
+        if constexpr (HC == 32) tmem_ld32(taddr, v);
+        else tmem_ld16(taddr, v);
+        tc_wait_ld();
+      };
       if constexpr (MODE == 0) {
         // lanes 0-63: dV of key (lane), columns [0,D);  lanes 64-127: dK of key (lane-64), columns [D,2D)
         const int which = g2, kr = r & 63;
         const int key = c * 64 + kr;
-        const uint32_t tA = tmem + lane_addr + 256 + which * D + grp * HC;
         float* dst;
         const bool direct = slot < 0;
-        if (direct) dst = (which ? a.dK_f : a.dV_f) + ((size_t)kv_slab * a.Tk + key) * D + grp * HC;
-        else dst = p.partials + ((((size_t)owner * p.capP + slot) * 2 + which) * 64 + kr) * D + grp * HC;
+        if (direct) dst = (which ? a.dK_f : a.dV_f) + ((size_t)kv_slab * a.Tk + key) * D + part * HC;
+        else dst = p.partials + ((((size_t)owner * p.capP + slot) * 2 + which) * 64 + kr) * D + part * HC;
         const bool wr = !direct || key < a.Tk;
+        uint32_t v[HC];
+        load_part(tmem + lane_addr + 256 + which * D + part * HC, v);
+        if (wr) {
 #pragma unroll
-        for (int g = 0; g < HC / 32; ++g) {
-          uint32_t v[32];
-          tmem_ld32(tA + g * 32, v);
-          tc_wait_ld();
-          if (wr) {
-#pragma unroll
-            for (int q4 = 0; q4 < 8; ++q4) {
-              float4 o = make_float4(__uint_as_float(v[4 * q4]), __uint_as_float(v[4 * q4 + 1]), __uint_as_float(v[4 * q4 + 2]),
-                                     __uint_as_float(v[4 * q4 + 3]));
-              float4* dp4 = reinterpret_cast<float4*>(dst + g * 32) + q4;
-              if (direct) { const float4 old = *dp4; o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w; }
-              *dp4 = o;
-            }
+          for (int q4 = 0; q4 < HC / 4; ++q4) {
+            float4 o = make_float4(__uint_as_float(v[4 * q4]), __uint_as_float(v[4 * q4 + 1]), __uint_as_float(v[4 * q4 + 2]),
+                                   __uint_as_float(v[4 * q4 + 3]));
+            float4* dp4 = reinterpret_cast<float4*>(dst) + q4;
+            if (direct) { const float4 old = *dp4; o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w; }
+            *dp4 = o;
           }
         }
       } else {
-        int hl, qblk;
-        const bool okg = row_group(0, g2, hl, qblk);
-        const int qi = qblk * 64 + (r & 63);
-        const bool wr = okg && qi < a.Tq;
-        const size_t base = (((size_t)b * a.H + hk * p.G + hl) * a.Tq + qi) * D + grp * HC;
-        const uint32_t tA = tmem + lane_addr + 256 + grp * HC;
+        const uint32_t ent = entry(0);
+        const int hl = (int)(ent >> BW5_QB_BITS);
+        const int qi = qb * 64 + (r & 63);
+        const bool wr = ent != 0xffffffffu && qi < a.Tq;
+        const size_t base = (((size_t)b * a.H + hk * p.G + hl) * a.Tq + qi) * D + part * HC;
+        uint32_t v[HC];
+        if (nsteps > 0) load_part(tmem + lane_addr + 256 + part * HC, v);
+        else {
 #pragma unroll
-        for (int g = 0; g < HC / 32; ++g) {
-          uint32_t v[32];
-          if (nsteps > 0) { tmem_ld32(tA + g * 32, v); tc_wait_ld(); }
-          else {
+          for (int i = 0; i < HC; ++i) v[i] = 0u;
+        }
+        if (wr) {
+          if (a.dq_dtype == NSA_FP32) {
+            float4* dp4 = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.dQ) + base);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = 0u;
-          }
-          if (wr) {
-            if (a.dq_dtype == NSA_FP32) {
-              float4* dp4 = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.dQ) + base + g * 32);
+            for (int q4 = 0; q4 < HC / 4; ++q4)
+              dp4[q4] = make_float4(__uint_as_float(v[4 * q4]), __uint_as_float(v[4 * q4 + 1]), __uint_as_float(v[4 * q4 + 2]),
+                                    __uint_as_float(v[4 * q4 + 3]));
+          } else {
+            uint4* dp4 = reinterpret_cast<uint4*>(reinterpret_cast<T*>(a.dQ) + base);
 #pragma unroll
-              for (int q4 = 0; q4 < 8; ++q4)
-                dp4[q4] = make_float4(__uint_as_float(v[4 * q4]), __uint_as_float(v[4 * q4 + 1]), __uint_as_float(v[4 * q4 + 2]),
-                                      __uint_as_float(v[4 * q4 + 3]));
-            } else {
-              uint4* dp4 = reinterpret_cast<uint4*>(reinterpret_cast<T*>(a.dQ) + base + g * 32);
-#pragma unroll
-              for (int q4 = 0; q4 < 4; ++q4)
-                dp4[q4] = make_uint4(Elem<T>::pack(__uint_as_float(v[8 * q4]), __uint_as_float(v[8 * q4 + 1])),
-                                     Elem<T>::pack(__uint_as_float(v[8 * q4 + 2]), __uint_as_float(v[8 * q4 + 3])),
-                                     Elem<T>::pack(__uint_as_float(v[8 * q4 + 4]), __uint_as_float(v[8 * q4 + 5])),
-                                     Elem<T>::pack(__uint_as_float(v[8 * q4 + 6]), __uint_as_float(v[8 * q4 + 7])));
-            }
+            for (int q4 = 0; q4 < HC / 8; ++q4)
+              dp4[q4] = make_uint4(Elem<T>::pack(__uint_as_float(v[8 * q4]), __uint_as_float(v[8 * q4 + 1])),
+                                   Elem<T>::pack(__uint_as_float(v[8 * q4 + 2]), __uint_as_float(v[8 * q4 + 3])),
+                                   Elem<T>::pack(__uint_as_float(v[8 * q4 + 4]), __uint_as_float(v[8 * q4 + 5])),
+                                   Elem<T>::pack(__uint_as_float(v[8 * q4 + 6]), __uint_as_float(v[8 * q4 + 7])));
           }
         }
       }
