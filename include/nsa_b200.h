@@ -185,6 +185,12 @@ int nsa_attention_fwd(const nsa_fwd_args* args, nsa_stream_t stream);
  * No counterpart in the reference (its kernels have no device-side waits). */
 int nsa_device_status(nsa_stream_t stream);
 
+/* Test hook: writes `value` into the device status word of a kernel family (0 = attention forward,
+ * 2 = attention backward) from the host, as a kernel does when one of its bounded waits expires; the
+ * next nsa_device_status() must then report NSA_ERR_DEVICE and clear it.  Lets the error path be
+ * exercised without making any kernel wait.  No counterpart in the reference. */
+int nsa_debug_set_device_status(int kernel_family, int value);
+
 /* Compressed-branch forward that needs no scratch memory from the caller: the pooled K and V
  * live in an array built into the library (NSA_STATIC_SCRATCH_BYTES per GPU, held until the
  * process exits).  Meant for hosts that cannot allocate at call time -- a runtime whose device

@@ -84,6 +84,7 @@ PROTOTYPES = {
     "nsa_topk_from_scores": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "nsa_attention_fwd": (_i, [C.POINTER(FwdArgs), _vp]),
     "nsa_device_status": (_i, [_vp]),
+    "nsa_debug_set_device_status": (_i, [_i, _i]),
     "nsa_compressed_attention_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp]),
     "launch_selected_attn_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "nsa_bwd_delta": (_i, [_vp, _vp, _vp, _i64, _i, _i, _vp]),

@@ -30,6 +30,8 @@ bool attention_bwd_tc5_supports(const nsa_bwd_args&);
 long long attention_bwd_tc5_scratch_bytes(const nsa_bwd_args&);
 int attention_bwd_tc5(const nsa_bwd_args&, void*, long long, cudaStream_t);
 int bw5_take_status(int*);
+int tc5_set_status(int);
+int bw5_set_status(int);
 int pool_mean_bwd(const float*, float*, int, int, int, int, int, int, int, cudaStream_t);
 int combine(const void*, const void*, const void*, const void*, void*, long long, int, int, int, int, cudaStream_t);
 int fp8_absmax(const void*, long long, int, float*, cudaStream_t);
@@ -194,6 +196,11 @@ int nsa_device_status(nsa_stream_t stream) {
   if (v == 0 && v3 != 0) v = 200 + v3;
   if (v != 0) return fail(NSA_ERR_DEVICE, "a kernel gave up waiting on barrier %d (bounded wait expired)", v - 1);
   return NSA_OK;
+}
+
+int nsa_debug_set_device_status(int kernel_family, int value) {
+  NSA_REQUIRE(kernel_family == 0 || kernel_family == 2, NSA_ERR_ARG, "debug status: kernel family %d (0 = forward, 2 = backward)", kernel_family);
+  return kernel_family == 0 ? tc5_set_status(value) : bw5_set_status(value);
 }
 
 int launch_selected_attn_fwd(const void* Q, const void* K, const void* V, const int* Idx, void* Out, float* Lse, int BH,

@@ -884,4 +884,9 @@ int bw5_take_status(int* status) {
   return NSA_OK;
 }
 
+int bw5_set_status(int v) {
+  NSA_CUDA_OK(cudaMemcpyToSymbol(g_bw5_status, &v, sizeof(int)));
+  return NSA_OK;
+}
+
 }  // namespace nsa

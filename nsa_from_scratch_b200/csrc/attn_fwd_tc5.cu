@@ -37,14 +37,6 @@ constexpr int T5_THREADS = 384;   // 12 warps; register budget rebalanced per ro
 
 __device__ int g_tc5_status;   // 0 ok; otherwise (1 + id of the barrier a wait gave up on)
 
-// Optional cycle-stamp trace of one block (debug builds only: -DNSA_TC5_TRACE=<block index>).
-#ifdef NSA_TC5_TRACE
-__device__ long long g_tc5_trace[8192];
-#define T5_TRACE(slot) do { if (blockIdx.x == (NSA_TC5_TRACE) && (slot) < 8192 && ((slot) < 4096 || (threadIdx.x & 31) == 0)) g_tc5_trace[(slot)] = clock64(); } while (0)
-#else
-#define T5_TRACE(slot) do { } while (0)
-#endif
-
 struct Tc5Params {
   CUtensorMap tmQ, tmK, tmV, tmKc, tmVc;
   nsa_fwd_args a;
@@ -417,10 +409,8 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
         const int nch = min(2, nchunks[p_br] - 2 * (tbeg(p_br) + p_t));
         const bool fresh = p_t == 0;                       // first tile of a branch starts a new O
         const int s = it & 1;
-        T5_TRACE(4096 + it * 8 + 0);
         ok = __all_sync(0xffffffffu, mbar_wait(bar(B_VFULL + s), (it >> 1) & 1, &abort_flag));
         if (!ok) { fail_id = B_VFULL + s + 1; break; }
-        T5_TRACE(4096 + it * 8 + 1);
         if constexpr (EARLY) {
           // next tile's QK^T as soon as this tile's S rows have been read
 #pragma unroll
@@ -437,7 +427,6 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
           if (!ok) break;
           ok = __all_sync(0xffffffffu, mbar_wait(bar(B_PFULL + X), it & 1, &abort_flag));
           if (!ok) { fail_id = B_PFULL + X + 1; break; }
-          T5_TRACE(4096 + it * 8 + 2 + 2 * X);
           tc_fence_after();
           if (leader) {
             if (fresh) mma_ts(tOx[X], tPx[X], dV[s], IDESC_PV, 0u);
@@ -453,7 +442,6 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
           }
           __syncwarp();
           if (!EARLY && it + 1 < total_tiles) ok = issue_qk(X, it + 1);
-          T5_TRACE(4096 + it * 8 + 3 + 2 * X);
         }
         ++p_t; skip_empty(p_br, p_t);
         if (it + 1 < total_tiles) { ++q_t; skip_empty(q_br, q_t); }
@@ -579,10 +567,8 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
 #pragma unroll 1
       for (int t = tbeg(br); t < tend(br) && ok; ++t, ++it) {
         const Tile tl = get_tile(br, t);
-        if (quarter == 0 && lane == 0) T5_TRACE(X * 2048 + it * 8 + 0);
         ok = __all_sync(0xffffffffu, mbar_wait(bar(B_SFULL + X), it & 1, &abort_flag));
         if (!ok) { fail_id = B_SFULL + X + 1; break; }
-        if (quarter == 0 && lane == 0) T5_TRACE(X * 2048 + it * 8 + 1);
         tc_fence_after();
         // the whole S row of the tile: 64*nch columns, one wait
         uint32_t sv[4][32];
@@ -622,7 +608,6 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
             for (int i = 0; i < 32; ++i) mxa[i & 7] = fmaxf(mxa[i & 7], __uint_as_float(sv[g][i]));
         }
         float mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])), fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
-        if (quarter == 0 && lane == 0) T5_TRACE(X * 2048 + it * 8 + 2);
         mx *= p.scale_log2[br];                              // scale > 0 keeps the order
         // lazy rescale: only when some row of the warp outgrows its reference maximum by 2^8
         const bool grow = mx > m_used + 8.f;
@@ -673,11 +658,9 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
         psum0 += psum2;
         psum1 += psum3;
         l += psum0 + psum1;
-        if (quarter == 0 && lane == 0) T5_TRACE(X * 2048 + it * 8 + 3);
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar(B_PFULL + X));
-        if (quarter == 0 && lane == 0) T5_TRACE(X * 2048 + it * 8 + 4);
       }
       if (!ok) break;
       // ---- end of the branch: O is complete once the last PV has landed ---------------------------
@@ -1008,12 +991,6 @@ int attention_fwd_tc5(const nsa_fwd_args& a, cudaStream_t st) {
   return launch_status("attn_fwd_tc5");
 }
 
-#ifdef NSA_TC5_TRACE
-extern "C" int nsa_debug_trace(long long* host_buf) {
-  return (int)cudaMemcpyFromSymbol(host_buf, g_tc5_trace, sizeof(long long) * 8192);
-}
-#endif
-
 // Synchronises `st`, returns and clears the status word the tcgen05 kernels set when a bounded wait gave up.
 int tc5_take_status(cudaStream_t st, int* status) {
   NSA_CUDA_OK(cudaStreamSynchronize(st));
@@ -1021,6 +998,11 @@ int tc5_take_status(cudaStream_t st, int* status) {
   NSA_CUDA_OK(cudaMemcpyFromSymbol(&v, g_tc5_status, sizeof(int)));
   if (v != 0) NSA_CUDA_OK(cudaMemcpyToSymbol(g_tc5_status, &zero, sizeof(int)));
   *status = v;
+  return NSA_OK;
+}
+
+int tc5_set_status(int v) {
+  NSA_CUDA_OK(cudaMemcpyToSymbol(g_tc5_status, &v, sizeof(int)));
   return NSA_OK;
 }
 

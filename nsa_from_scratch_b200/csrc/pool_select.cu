@@ -216,8 +216,12 @@ __device__ void warp_topk_row(float* s, int n_scan, int nk, int k_out, int32_t* 
     const float v = s[c];
     if (bc == NONE || v > bv) { bv = v; bc = c; }
   }
+  int picked = n_pick;
   for (int it = 0; it < n_pick; ++it) {
     const int gc = warp_argmax(bv, bc, NONE);
+    // no candidate left: caller-supplied scores may carry the bit pattern that marks a taken entry (an all-ones NaN);
+    // such entries are never offered, so fewer than n_pick can be picked -- the rest is filled like the tail below
+    if (gc == NONE) { picked = it; break; }
     if (lane == 0) { out_row[it] = gc; s[gc] = __uint_as_float(TAKEN); }
     __syncwarp();
     const int owner = gc & 31;
@@ -231,7 +235,7 @@ __device__ void warp_topk_row(float* s, int n_scan, int nk, int k_out, int32_t* 
     if (lane == owner) { bc = nc; bv = nc == NONE ? -INFINITY : s[nc]; }
   }
   // fewer candidates than slots: the remaining slots take the lowest block ids not scanned
-  for (int it = n_pick + lane; it < k_out; it += 32) out_row[it] = n_scan + (it - n_pick);
+  for (int it = picked + lane; it < k_out; it += 32) out_row[it] = n_scan + (it - picked);
   (void)nk;
 }
 

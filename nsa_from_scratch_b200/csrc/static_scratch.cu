@@ -14,6 +14,8 @@
 // pooled rows it later reads, so stale contents of an earlier call are harmless.
 #include "common.cuh"
 
+#include <atomic>
+
 namespace nsa {
 
 int pool_mean(const void*, void*, int, int, int, int, int, int, int, int, float, cudaStream_t);
@@ -23,19 +25,26 @@ static __device__ __align__(256) unsigned char g_static_scratch[NSA_STATIC_SCRAT
 // Device address of the array on the current device.  In host code the symbol's name is only a
 // handle, not a pointer a kernel could use; the address comes from cudaGetSymbolAddress, asked
 // once per device with that device current.
-static int scratch_address(unsigned char** out) {
+static int scratch_address(unsigned char** out, cudaStream_t st) {
   constexpr int kMaxDevices = 64;
-  static unsigned char* cached[kMaxDevices] = {};
+  static std::atomic<unsigned char*> cached[kMaxDevices];   // zero-initialised; racing first calls store the same address
   int dev = -1;
   NSA_CUDA_OK(cudaGetDevice(&dev));
   NSA_REQUIRE(dev >= 0 && dev < kMaxDevices, NSA_ERR_UNSUPPORTED, "static scratch: device index %d out of range", dev);
-  if (cached[dev] == nullptr) {
-    void* p = nullptr;
-    NSA_CUDA_OK(cudaGetSymbolAddress(&p, g_static_scratch));
-    NSA_REQUIRE(p != nullptr, NSA_ERR_CUDA, "static scratch: cudaGetSymbolAddress returned NULL");
-    cached[dev] = static_cast<unsigned char*>(p);
+  unsigned char* p = cached[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
+    // the look-up is not a stream operation: made while `st` is being captured it could invalidate the capture
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    NSA_CUDA_OK(cudaStreamIsCapturing(st, &cap));
+    NSA_REQUIRE(cap == cudaStreamCaptureStatusNone, NSA_ERR_UNSUPPORTED,
+                "static scratch: the first call on a device looks up the array's address and must come before any stream capture");
+    void* q = nullptr;
+    NSA_CUDA_OK(cudaGetSymbolAddress(&q, g_static_scratch));
+    NSA_REQUIRE(q != nullptr, NSA_ERR_CUDA, "static scratch: cudaGetSymbolAddress returned NULL");
+    p = static_cast<unsigned char*>(q);
+    cached[dev].store(p, std::memory_order_release);
   }
-  *out = cached[dev];
+  *out = p;
   return NSA_OK;
 }
 
@@ -57,11 +66,11 @@ extern "C" int nsa_compressed_attention_static(const void* Q, const void* K, con
               "(B*Hkv*n_pooled*D*4 must not exceed it); use nsa_pool_mean + nsa_attention_fwd with your own buffers",
               2 * one, (unsigned)NSA_STATIC_SCRATCH_BYTES);
   unsigned char* base = nullptr;
-  int rc = scratch_address(&base);
+  cudaStream_t st = (cudaStream_t)stream;
+  int rc = scratch_address(&base, st);
   if (rc != NSA_OK) return rc;
   void* Kc = base;
   void* Vc = base + one;
-  cudaStream_t st = (cudaStream_t)stream;
   if ((rc = pool_mean(K, Kc, B, Hkv, Tk, D, block, stride, (int)n_out, dtype, 1.f, st)) != NSA_OK) return rc;
   if ((rc = pool_mean(V, Vc, B, Hkv, Tk, D, block, stride, (int)n_out, dtype, 1.f, st)) != NSA_OK) return rc;
   nsa_fwd_args a = {};

@@ -148,8 +148,10 @@ def nsa_forward(Q: Tensor, K: Tensor, V: Tensor, cfg, *, gate_logits: Optional[T
     """NSA combined forward.  Q [B,H,Tq,D], K/V [B,H|Hkv,Tk,D] fp16/bf16; `cfg` is any object with
     the reference's NSAConfig fields (optional extras: stride_c, force_first, force_local);
     gate_logits [B,H,Tq,3] (None = zero logits); block_indices [B,H|Hkv,nq,k] int32 (None =
-    mean-pool scoring + top-k).  Returns [B,H,Tq,D] in Q's dtype; differentiable wrt Q, K, V
-    and gate_logits."""
+    mean-pool scoring + top-k).  Returns [B,H,Tq,D] in Q's dtype on every route (the reference's
+    tensor expression would promote to fp32 for fp32 gate logits, nsa/triton/gating.py:38-40; its model casts the
+    logits to Q's dtype first, nsa/model/llama_nsa.py:86, so callers of the module see Q's dtype there too);
+    differentiable wrt Q, K, V and gate_logits."""
     assert Q.dtype in (torch.float16, torch.bfloat16), "Q must be fp16 or bf16"
     D = Q.shape[-1]
     scale = cfg.scale if cfg.scale is not None else 1.0 / (D ** 0.5)
@@ -179,7 +181,8 @@ def nsa_forward(Q: Tensor, K: Tensor, V: Tensor, cfg, *, gate_logits: Optional[T
         if gate_logits is None:
             B, H, Tq, _ = Q.shape
             gate_logits = Q.new_full((B, H, Tq, 3), 0.0)
-        return _CombineFn.apply(out_c, out_s, out_w, gate_logits, cfg.gate_activation)
+        out = _CombineFn.apply(out_c, out_s, out_w, gate_logits, cfg.gate_activation)
+        return out if out.dtype == Q.dtype else out.to(Q.dtype)     # fp32 gate logits: same dtype as the fused route
     return _fused_forward(Q, K, V, cfg, float(scale), stride_c, gate_logits, block_indices, 1.0, 1.0, 1.0)
 
 

@@ -47,9 +47,13 @@ def _side_streams(dev):
 
 
 def nsa_forward_host(Q: Tensor, K: Tensor, V: Tensor, cfg, *, gate_logits: Optional[Tensor] = None,
-                     out: Optional[Tensor] = None, device=None, chunk_rows: Optional[int] = 16384) -> Tensor:
+                     out: Optional[Tensor] = None, device=None, chunk_rows: Optional[int] = 16384,
+                     non_blocking: bool = False):
     """Q [B,H,Tq,D], K/V [B,Hkv,Tk,D], gate_logits [B,H,Tq,3] on the HOST (ideally pinned); returns the
     output [B,H,Tq,D] on the host (`out` if given, else a new pinned tensor).  Inference only.
+    The call returns when the last device -> host copy has landed, so the result can be read on the CPU at once.
+    With non_blocking=True it returns (out, event) as soon as everything is queued; the caller must
+    event.synchronize() (or synchronize the device) before reading `out`.
     `chunk_rows`: query positions per pipeline unit (None = whole sequences).  Smaller chunks shorten the
     unhidden head and tail of the pipeline but cost a fixed host-side launch sequence each; 16384 was the
     fastest at 64k tokens x 64 heads on a B200 over PCIe (29.9 ms; 8192: 31.7, whole sequences: 32.3)."""
@@ -113,7 +117,12 @@ def nsa_forward_host(Q: Tensor, K: Tensor, V: Tensor, cfg, *, gate_logits: Optio
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev2)
                 ops.copy_rows(out[b, hs, c0:c1], o[0])
+    done = torch.cuda.Event()
+    done.record(s_out)          # after the last copy out
     cur.wait_stream(s_out)
+    if non_blocking:
+        return out, done
+    done.synchronize()
     return out
 
 

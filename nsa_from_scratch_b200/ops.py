@@ -43,6 +43,33 @@ def device_status() -> None:
     L.check(L.load().nsa_device_status(L.stream_ptr()), "nsa_device_status")
 
 
+_STRICT_LAYOUT = False
+_warned_layout = set()
+
+
+def set_strict_layout(flag: bool) -> None:
+    """The kernels read dense row-major tensors.  The reference's wrappers call .contiguous() on whatever they are
+    given (nsa/triton/selected.py:239-241, compressed.py:243-245), which copies a strided operand in full; so do these
+    wrappers by default, with one warning per operand name, because such a copy on the hot path is rarely intended.
+    set_strict_layout(True) turns it into an error."""
+    global _STRICT_LAYOUT
+    _STRICT_LAYOUT = bool(flag)
+
+
+def _dense(t: Tensor, name: str) -> Tensor:
+    if t.is_contiguous():
+        return t
+    if _STRICT_LAYOUT:
+        raise ValueError(f"{name} is not contiguous (shape {tuple(t.shape)}, strides {t.stride()}); the kernels take dense "
+                         "row-major tensors and strict layout checking is on")
+    if name not in _warned_layout:
+        _warned_layout.add(name)
+        import warnings
+        warnings.warn(f"nsa_from_scratch_b200: {name} is not contiguous and is being copied ({t.numel() * t.element_size()} bytes) "
+                      "before the launch; pass a dense tensor, or ops.set_strict_layout(True) to make this an error", stacklevel=3)
+    return t.contiguous()
+
+
 _16 = (torch.float16, torch.bfloat16)
 _8 = (torch.float8_e4m3fn, torch.float8_e5m2)
 
@@ -70,7 +97,7 @@ def pool_mean(x: Tensor, block: int, stride: Optional[int] = None, dequant_scale
     B, H, T, D = x.shape
     stride = block if stride is None else stride
     n = n_pooled(T, block, stride)
-    x = x.contiguous()
+    x = _dense(x, "x")
     out = torch.empty((B, H, n, D), device=x.device, dtype=torch.bfloat16 if x.dtype in _8 else x.dtype)
     with torch.cuda.device(x.device):
         L.check(L.load().nsa_pool_mean(x.data_ptr(), out.data_ptr(), B, H, T, D, block, stride, n,
@@ -100,7 +127,7 @@ def cmp_block_scores(Q: Tensor, Kc: Tensor, lse: Tensor, *, nk: int, cmp_block: 
     _need_cuda(Q, Kc, lse)
     B, H, Tq, D = Q.shape
     Hkv, Nc = Kc.shape[1], Kc.shape[2]
-    Q, Kc, lse = Q.contiguous(), Kc.contiguous(), lse.float().contiguous()
+    Q, Kc, lse = _dense(Q, "Q"), _dense(Kc, "Kc"), lse.float().contiguous()
     if Kc.dtype != Q.dtype or Q.dtype not in _16:
         raise TypeError("cmp_block_scores: Q and the pooled K must share a 16-bit dtype")
     nq = (Tq + 63) // 64
@@ -163,7 +190,7 @@ def attention_fwd(
         raise ValueError(f"query heads {H} not a multiple of KV heads {Hkv}")
     if V.dtype != K.dtype or (K.dtype != Q.dtype and not (Q.dtype in _8 and K.dtype == torch.bfloat16)):
         raise TypeError("Q, K, V must share a dtype (or bf16 K/V beside an fp8 Q)")
-    Q, K, V = Q.contiguous(), K.contiguous(), V.contiguous()
+    Q, K, V = _dense(Q, "Q"), _dense(K, "K"), _dense(V, "V")
     eng = _ENGINE if engine is None else engine
     if Q.dtype in _8 and K.dtype == Q.dtype and eng != L.ENGINE_GENERIC and D in (64, 128):
         # The tcgen05 kernel takes an fp8 Q with bf16 K/V: a K/V tile is used by every query block that attends it,
@@ -194,7 +221,7 @@ def attention_fwd(
     a.engine = eng
     keep = [Q, K, V]
     if branches & L.BRANCH_COMPRESSED:
-        Kc, Vc = Kc.contiguous(), Vc.contiguous()
+        Kc, Vc = _dense(Kc, "Kc"), _dense(Vc, "Vc")
         keep += [Kc, Vc]
         a.Kc, a.Vc, a.Nc = Kc.data_ptr(), Vc.data_ptr(), Kc.shape[2]
         a.cmp_block, a.cmp_stride, a.cmp_offset = cmp_block, cmp_stride, cmp_offset
@@ -209,7 +236,7 @@ def attention_fwd(
     if branches & L.BRANCH_SLIDING:
         a.window = int(window)
     if fused and gates is not None:
-        gates = gates.contiguous()
+        gates = _dense(gates, "gates")
         keep.append(gates)
         want = (B, Tq, H, 3) if token_major else (B, H, Tq, 3)
         if gates.shape != want:
@@ -232,7 +259,7 @@ def attention_fwd(
 
 def bwd_delta(dO: Tensor, O: Tensor) -> Tensor:
     _need_cuda(dO, O)
-    dO, O = dO.contiguous(), O.contiguous()
+    dO, O = _dense(dO, "dO"), _dense(O, "O")
     D = dO.shape[-1]
     delta = torch.empty(dO.shape[:-1], device=dO.device, dtype=torch.float32)
     with torch.cuda.device(dO.device):
@@ -251,8 +278,8 @@ def attention_bwd(dO: Tensor, Q: Tensor, K: Tensor, V: Tensor, lse: Tensor, delt
     _need_cuda(dO, Q, K, V, lse, delta)
     B, H, Tq, D = Q.shape
     Hkv, rows = K.shape[1], K.shape[2]
-    dO, Q, K, V = dO.contiguous(), Q.contiguous(), K.contiguous(), V.contiguous()
-    lse, delta = lse.contiguous(), delta.contiguous()
+    dO, Q, K, V = _dense(dO, "dO"), _dense(Q, "Q"), _dense(K, "K"), _dense(V, "V")
+    lse, delta = _dense(lse, "lse"), _dense(delta, "delta")
     dQ = torch.empty((B, H, Tq, D), device=Q.device, dtype=torch.float32 if dq_fp32 else Q.dtype)
     dK = torch.zeros((B, Hkv, rows, D), device=Q.device, dtype=torch.float32)
     dV = torch.zeros((B, Hkv, rows, D), device=Q.device, dtype=torch.float32)
@@ -297,7 +324,7 @@ def pool_mean_bwd(dxc: Tensor, T: int, block: int, stride: int) -> Tensor:
     """fp32 [B,H,n,D] gradients of pooled rows -> fp32 [B,H,T,D] gradients of the rows."""
     _need_cuda(dxc)
     B, H, n, D = dxc.shape
-    dxc = dxc.contiguous()
+    dxc = _dense(dxc, "dxc")
     dx = torch.zeros((B, H, T, D), device=dxc.device, dtype=torch.float32)
     with torch.cuda.device(dxc.device):
         L.check(L.load().nsa_pool_mean_bwd(dxc.data_ptr(), dx.data_ptr(), B, H, T, D, block, stride, n, L.stream_ptr()),
@@ -307,7 +334,7 @@ def pool_mean_bwd(dxc: Tensor, T: int, block: int, stride: int) -> Tensor:
 
 def cast_from_f32(x: Tensor, dtype: torch.dtype) -> Tensor:
     _need_cuda(x)
-    x = x.contiguous()
+    x = _dense(x, "x")
     out = torch.empty(x.shape, device=x.device, dtype=dtype)
     with torch.cuda.device(x.device):
         L.check(L.load().nsa_cast_from_f32(x.data_ptr(), out.data_ptr(), x.numel(), L.dtype_code(dtype), L.stream_ptr()),
@@ -321,7 +348,7 @@ def rope_to_heads(x: Tensor, cos: Optional[Tensor], sin: Optional[Tensor], dtype
     if x.dim() != 4:
         raise ValueError(f"rope_to_heads: x must be [B,T,H,D], got {tuple(x.shape)}")
     B, T, H, D = x.shape
-    x = x.contiguous()
+    x = _dense(x, "x")
     if (cos is None) != (sin is None):
         raise ValueError("rope_to_heads: give both cos and sin or neither")
     cs_code = 0
@@ -329,7 +356,7 @@ def rope_to_heads(x: Tensor, cos: Optional[Tensor], sin: Optional[Tensor], dtype
         _need_cuda(cos, sin)
         if cos.shape != (T, D) or sin.shape != (T, D) or cos.dtype != sin.dtype:
             raise ValueError(f"rope_to_heads: cos/sin must be [{T},{D}] of one dtype, got {tuple(cos.shape)}/{tuple(sin.shape)}")
-        cos, sin = cos.contiguous(), sin.contiguous()
+        cos, sin = _dense(cos, "cos"), _dense(sin, "sin")
         cs_code = L.dtype_code(cos.dtype)
     y = torch.empty((B, H, T, D), device=x.device, dtype=dtype)
     with torch.cuda.device(x.device):
@@ -372,7 +399,7 @@ def combine(out_c: Tensor, out_s: Tensor, out_w: Tensor, gate_logits: Tensor, ac
     B, H, Tq, D = out_c.shape
     if gate_logits.shape != (B, H, Tq, 3):
         raise ValueError(f"gate_logits shape {tuple(gate_logits.shape)} != {(B, H, Tq, 3)}")
-    out_c, out_s, out_w, g = out_c.contiguous(), out_s.contiguous(), out_w.contiguous(), gate_logits.contiguous()
+    out_c, out_s, out_w, g = _dense(out_c, "out_c"), _dense(out_s, "out_s"), _dense(out_w, "out_w"), _dense(gate_logits, "gate_logits")
     out = torch.empty((B, H, Tq, D), device=out_c.device, dtype=torch.float32 if g.dtype == torch.float32 else out_c.dtype)
     with torch.cuda.device(out_c.device):
         L.check(L.load().nsa_combine(out_c.data_ptr(), out_s.data_ptr(), out_w.data_ptr(), g.data_ptr(), out.data_ptr(),
@@ -383,7 +410,7 @@ def combine(out_c: Tensor, out_s: Tensor, out_w: Tensor, gate_logits: Tensor, ac
 
 def fp8_absmax(x: Tensor) -> Tensor:
     _need_cuda(x)
-    x = x.contiguous()
+    x = _dense(x, "x")
     out = torch.zeros(1, device=x.device, dtype=torch.float32)
     with torch.cuda.device(x.device):
         L.check(L.load().nsa_fp8_absmax(x.data_ptr(), x.numel(), L.dtype_code(x.dtype), out.data_ptr(), L.stream_ptr()),
@@ -394,7 +421,7 @@ def fp8_absmax(x: Tensor) -> Tensor:
 def fp8_dequantize(x8: Tensor, scale: float) -> Tensor:
     """bf16(fp32(x8) * scale): the tensor the reference's wrapper attends on (nsa/triton/fp8.py:67-69)."""
     _need_cuda(x8)
-    x8 = x8.contiguous()
+    x8 = _dense(x8, "x8")
     out = torch.empty(x8.shape, device=x8.device, dtype=torch.bfloat16)
     with torch.cuda.device(x8.device):
         L.check(L.load().nsa_fp8_dequantize(x8.data_ptr(), out.data_ptr(), x8.numel(), L.dtype_code(x8.dtype), float(scale),
@@ -404,7 +431,7 @@ def fp8_dequantize(x8: Tensor, scale: float) -> Tensor:
 
 def fp8_quantize(x: Tensor, fmt: torch.dtype, scale: float) -> Tensor:
     _need_cuda(x)
-    x = x.contiguous()
+    x = _dense(x, "x")
     out = torch.empty(x.shape, device=x.device, dtype=torch.uint8)
     with torch.cuda.device(x.device):
         L.check(L.load().nsa_fp8_quantize(x.data_ptr(), out.data_ptr(), x.numel(), L.dtype_code(x.dtype),

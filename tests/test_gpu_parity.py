@@ -12,6 +12,10 @@ pytestmark = pytest.mark.gpu
 
 TOL16 = 2e-2
 TOL8 = 6e-2
+# Gradients: max-abs <= 2e-2 relative to the largest reference entry (never below 2e-2 absolute).  Gradient entries
+# reach tens in magnitude (sums over hundreds of rows), and the kernels return them rounded to bf16 where the caller's
+# tensors are bf16 (one part in 2^9 of the entry), so an absolute 2e-2 cannot hold for the large entries.
+GRAD_TOL = 2e-2
 DT = {"torch.float32": torch.float32, "torch.bfloat16": torch.bfloat16, "torch.float16": torch.float16}
 
 
@@ -78,7 +82,7 @@ def test_golden_selected_fwd_bwd(nsa, golden):
         o.backward(dO.cuda())
         for got, key in ((Qc.grad, "dQ"), (Kc.grad, "dK"), (Vc.grad, "dV")):
             ref = G(golden, f"{name}.{key}")
-            assert max_abs(got, ref) <= 5e-2 + 1e-2 * float(ref.abs().max()), (name, key, max_abs(got, ref))
+            assert max_abs(got, ref) <= GRAD_TOL * max(1.0, float(ref.abs().max())), (name, key, max_abs(got, ref))
 
 
 def test_golden_sliding(nsa, golden):
@@ -465,9 +469,15 @@ def test_host_tensor_entry_point_matches_device_path(nsa):
     gates = torch.randn(2, 8, 512, 3, generator=g).to(torch.bfloat16)
     cfg = nsa.NSAConfig(block_size_c=32, stride_c=16, top_k=4, window_size=128, select_per_group=True)
     ref = nsa.nsa_forward(Q.cuda(), K.cuda(), V.cuda(), cfg, gate_logits=gates.cuda())
+    ref_h = ref.cpu()
+    # the call returns only when the last copy out has landed: the result is read with no synchronisation of ours
     out = nsa.nsa_forward_host(Q.pin_memory(), K.pin_memory(), V.pin_memory(), cfg, gate_logits=gates.pin_memory())
-    torch.cuda.synchronize()
-    assert not out.is_cuda and torch.equal(out, ref.cpu())
+    assert not out.is_cuda and torch.equal(out, ref_h)
+    # non_blocking: everything queued, the event says when `out` may be read
+    out2, done = nsa.nsa_forward_host(Q.pin_memory(), K.pin_memory(), V.pin_memory(), cfg, gate_logits=gates.pin_memory(),
+                                      non_blocking=True)
+    done.synchronize()
+    assert torch.equal(out2, ref_h)
 
 
 @pytest.mark.parametrize("Tq,Tk,chunk", [(512, 512, 128), (256, 768, 64), (500, 500, 128)])
@@ -521,7 +531,7 @@ def test_golden_compressed_and_sliding_gradients(nsa, golden):
             ref = G(golden, f"{name}.{key}")
             if name == "gcmp_a" and key == "dV":      # the reference's dV is all zero here (NaN rows poison it): use the oracle
                 ref = O.branch_backward("cmp", dO, Q, K, V, block_size_c=par, causal=causal)[2]
-            assert max_abs(got, ref) <= 3e-2 * max(1.0, float(ref.abs().max())), (name, key, max_abs(got, ref))
+            assert max_abs(got, ref) <= GRAD_TOL * max(1.0, float(ref.abs().max())), (name, key, max_abs(got, ref))
 
 
 @pytest.mark.parametrize("case", [(1, 4, 4, 256, 256, 64), (1, 8, 2, 192, 320, 128), (2, 2, 1, 100, 200, 32)])
@@ -570,7 +580,7 @@ def test_full_forward_gradients_vs_oracle(nsa):
     out = nsa.nsa_forward(Qc, Kc, Vc, cfg, gate_logits=Gc, block_indices=idx.cuda())
     out.backward(w.cuda().to(out.dtype))
     for got, ref_g, nm in zip((Qc.grad, Kc.grad, Vc.grad, Gc.grad), rg, ("dQ", "dK", "dV", "dG")):
-        assert max_abs(got, ref_g) <= 3e-2 * max(1.0, float(ref_g.abs().max())), (nm, max_abs(got, ref_g), float(ref_g.abs().max()))
+        assert max_abs(got, ref_g) <= GRAD_TOL * max(1.0, float(ref_g.abs().max())), (nm, max_abs(got, ref_g), float(ref_g.abs().max()))
 
 
 # ------------------------------------------------------------------ scorer from the compressed branch's probabilities
@@ -625,3 +635,54 @@ def test_compressed_probability_scorer_vs_oracle(nsa, case):
                          engine=L.ENGINE_TCGEN05 if D in (64, 128) else None)
     assert torch.equal(out, one)
     ops.device_status()
+
+
+def test_device_status_error_path(nsa):
+    """nsa_device_status reports NSA_ERR_DEVICE when a kernel family's status word is non-zero, names the barrier,
+    and clears the word.  The word is written from the host through the test hook: no kernel waits for anything."""
+    from nsa_from_scratch_b200 import _lib as L, ops
+    lib = L.load()
+    ops.device_status()                                        # clean before
+    for family, base in ((0, 0), (2, 200)):
+        assert lib.nsa_debug_set_device_status(family, 5) == 0
+        assert lib.nsa_device_status(L.stream_ptr()) == -4     # NSA_ERR_DEVICE
+        assert f"barrier {base + 4}".encode() in lib.nsa_last_error()
+        assert lib.nsa_device_status(L.stream_ptr()) == 0      # cleared by the report
+        lib.nsa_debug_set_device_status(family, 9)
+        with pytest.raises(RuntimeError, match="bounded wait"):
+            ops.device_status()
+        ops.device_status()
+    assert lib.nsa_debug_set_device_status(7, 1) == -1
+
+
+def test_nsa_forward_dtype_is_q_dtype_on_both_routes(nsa):
+    """fp32 gate logits: the fused (no-grad) route and the autograd route both return Q's dtype."""
+    Q, K, V, g = make_qkv(31, 1, 4, 2, 256, 256, 64)
+    gates = torch.randn(1, 4, 256, 3, generator=g)
+    cfg = nsa.NSAConfig(block_size_c=32, stride_c=16, top_k=3, window_size=64)
+    with torch.no_grad():
+        o1 = nsa.nsa_forward(Q.cuda(), K.cuda(), V.cuda(), cfg, gate_logits=gates.cuda())
+    Qg = Q.cuda().requires_grad_(True)
+    o2 = nsa.nsa_forward(Qg, K.cuda(), V.cuda(), cfg, gate_logits=gates.cuda())
+    assert o1.dtype == torch.bfloat16 and o2.dtype == torch.bfloat16
+    assert max_abs(o1, o2.detach()) <= 2e-2
+    o2.float().sum().backward()
+    assert Qg.grad is not None and Qg.grad.dtype == torch.bfloat16
+
+
+def test_strided_operands_warn_or_raise(nsa):
+    from nsa_from_scratch_b200 import ops
+    Q, K, V, _ = make_qkv(32, 1, 4, 2, 256, 256, 64)
+    Qs = torch.empty(1, 4, 256, 128, dtype=torch.bfloat16, device="cuda")[..., :64]
+    Qs.copy_(Q)
+    ref, _ = nsa.sliding_attention(Q.cuda(), K.cuda(), V.cuda(), window_size=64)
+    ops._warned_layout.discard("Q")
+    with pytest.warns(UserWarning, match="not contiguous"):
+        out, _ = nsa.sliding_attention(Qs, K.cuda(), V.cuda(), window_size=64)
+    assert torch.equal(out, ref)
+    ops.set_strict_layout(True)
+    try:
+        with pytest.raises(ValueError, match="not contiguous"):
+            nsa.sliding_attention(Qs, K.cuda(), V.cuda(), window_size=64)
+    finally:
+        ops.set_strict_layout(False)
