@@ -3,11 +3,15 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--seq-len T] ...
 
 One "step" is one NSA forward (pool K/V, pool block means, score + top-k, fused three-branch
-attention with the gated combine) over one synthetic batch.  Default workload: bf16, B=1 per GPU,
+attention with the gated combine) over one synthetic batch.  Default workload: bf16, B=1,
 T=65536 causal, Hq=64, Hkv=4, D=128, compression block 32 / stride 16, selection block 64 with
 top-16 (block 0 and the 2 local blocks forced), window 512, sigmoid gates from a random
-Linear(D,3) applied to Q.  With N GPUs every rank runs the same workload on its own batch
-element (batch x KV-head partitioning, no collective): weak scaling, value = N*T / max-rank time.
+Linear(D,3) applied to Q.  With N GPUs (--layout heads, the default) that ONE problem is split by
+(batch, KV head) units -- whole KV heads per rank up to 4 GPUs, no collective; on 8 GPUs the 16 query heads of a
+KV head are split over two ranks, which all-gather their query block means (2 MB) so that the group-shared
+block lists stay bit-exact -- strong scaling, value = T / max-rank time.  With N > 1 the line also carries a
+`context_parallel` block: T=262144 sharded contiguously by query position, K/V all-gathered over NCCL.
+--layout replicas gives every rank its own batch element instead (weak scaling, no collective).
 
 Prints ONE JSON line (rank 0).  `--impl reference` times the CPU oracle port (the reference's
 plain-torch algorithm) on a bounded sample of the same workload on the host cores.
@@ -50,10 +54,13 @@ def parse():
     ap.add_argument("--engine", default="auto", choices=["auto", "generic", "tcgen05"])
     ap.add_argument("--select", default="group", choices=["group", "head"],
                     help="block lists shared by the query heads of a KV head (group) or one per query head (head)")
-    ap.add_argument("--layout", default="dp", choices=["dp", "cp"],
-                    help="dp: every rank runs the whole workload on its own batch element (weak scaling); "
-                         "cp: context parallel, --seq-len is the TOTAL length, queries sharded contiguously, "
-                         "K/V all-gathered over NCCL inside the timed step (strong scaling)")
+    ap.add_argument("--layout", default="heads", choices=["heads", "replicas", "cp"],
+                    help="heads: ONE B=1 problem split over the ranks by (batch, KV head) units and, beyond that, by query "
+                         "heads inside a group (strong scaling); replicas: every rank runs the whole workload on its own "
+                         "batch element (weak scaling); cp: context parallel, --seq-len is the TOTAL length, queries sharded "
+                         "contiguously, K/V all-gathered over NCCL inside the timed step (strong scaling)")
+    ap.add_argument("--cp-seq-len", type=int, default=262144,
+                    help="total length of the context-parallel measurement appended to the line when N > 1 (0 = leave it out)")
     ap.add_argument("--sweep", action="store_true",
                     help="instead of the single contract line: one JSON line per point of the T x D sweep "
                          "(T = 1k..64k, D = 64/128, Hq=64/Hkv=4) plus the reference's own MHA shape (H=16, D=64, 64/64)")
@@ -73,20 +80,33 @@ def parse():
 
 
 def workload_name(a):
-    return (f"nsa_fwd bf16 B=1/gpu T={a.seq_len} Hq={a.heads} Hkv={a.kv_heads} D={a.head_dim} "
+    return (f"nsa_fwd bf16 B=1 T={a.seq_len} Hq={a.heads} Hkv={a.kv_heads} D={a.head_dim} "
             f"cmp={a.cmp_block}/{a.cmp_stride} sel=64x{a.top_k}(forced 1+2, per {a.select}) win={a.window} sigmoid-gates")
 
 
-def make_inputs(a, seed):
-    """Q, K, V ~ N(0,1) bf16 and gate logits = Linear(D,3)(Q) from a CPU generator (order Q, K, V, W)."""
-    g = torch.Generator().manual_seed(seed)
-    B, H, Hkv, T, D = 1, a.heads, a.kv_heads, a.seq_len, a.head_dim
-    Q = torch.randn(B, H, T, D, generator=g).to(torch.bfloat16)
-    K = torch.randn(B, Hkv, T, D, generator=g).to(torch.bfloat16)
-    V = torch.randn(B, Hkv, T, D, generator=g).to(torch.bfloat16)
+def make_inputs(a, seed, heads=None, kv_heads=None, rows=None):
+    """Q, K, V ~ N(0,1) bf16 and gate logits = Linear(D,3)(Q) from CPU generators.  Every query head and every KV
+    head has a generator of its own (seeded by `seed` and the head's number), so a rank that holds some heads of the
+    problem builds exactly the values the whole problem has; the gate weights come from `seed` alone.
+    `heads` / `kv_heads`: the global head numbers wanted (default: all); `rows`: (first, last+1) of the sequence."""
+    B, T, D = 1, a.seq_len, a.head_dim
+    heads = list(range(a.heads)) if heads is None else list(heads)
+    kv_heads = list(range(a.kv_heads)) if kv_heads is None else list(kv_heads)
+    r0, r1 = (0, T) if rows is None else rows
     bound = 1.0 / D ** 0.5                                           # torch.nn.Linear default init range
-    Wg = (torch.rand(3, D, generator=g) * 2 - 1) * bound
-    gates = torch.einsum("bhtd,cd->bhtc", Q.float(), Wg).to(torch.bfloat16)
+    Wg = (torch.rand(3, D, generator=torch.Generator().manual_seed(seed * 1000003 + 7)) * 2 - 1) * bound
+    Q = torch.empty(B, len(heads), r1 - r0, D, dtype=torch.bfloat16)
+    gates = torch.empty(B, len(heads), r1 - r0, 3, dtype=torch.bfloat16)
+    for i, h in enumerate(heads):
+        q = torch.randn(T, D, generator=torch.Generator().manual_seed(seed * 1000003 + 1000 + h))[r0:r1].to(torch.bfloat16)
+        Q[0, i] = q
+        gates[0, i] = (q.float() @ Wg.t()).to(torch.bfloat16)
+    K = torch.empty(B, len(kv_heads), r1 - r0, D, dtype=torch.bfloat16)
+    V = torch.empty(B, len(kv_heads), r1 - r0, D, dtype=torch.bfloat16)
+    for i, h in enumerate(kv_heads):
+        g = torch.Generator().manual_seed(seed * 1000003 + 500000 + h)
+        K[0, i] = torch.randn(T, D, generator=g)[r0:r1].to(torch.bfloat16)
+        V[0, i] = torch.randn(T, D, generator=g)[r0:r1].to(torch.bfloat16)
     return Q, K, V, gates
 
 
@@ -131,10 +151,11 @@ def run_reference(a):
     cores = torch.get_num_threads()
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": a.gpus, "steps": len(times),
-        "warmup": 1, "ms_per_step": 1e3 * min(times), "higher_is_better": True, "scaling": "weak",
+        "warmup": 1, "ms_per_step": 1e3 * min(times), "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload_name(a), "note": "CPU oracle port of the reference's plain-torch path"},
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
+        "cpu_baseline_reference_native": native_reference_cpu(a.seed),
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -208,9 +229,51 @@ def algorithmic_flops(a, idx):
             "total": f(cmp_pairs + sel_pairs + sld_pairs)}
 
 
+def measured_peaks():
+    try:
+        return json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        return {}
+
+
+def native_reference_cpu(seed):
+    """The reference's own plain-torch forward (nsa_attention_reference), unmodified, on its CPU-runnable case:
+    fp32, B=1, T=4096, Hq=16 query heads sharing one KV head (expanded to 16: it has no grouped heads), D=64,
+    its own geometry (64-token compression blocks, plain top-16, window 512), gates = sigmoid(Linear(D,3)(Q)).
+    Needs oracle/_ref (made by oracle/make_ref.py where a checkout exists); returns None without it."""
+    path = os.path.join(ROOT, "oracle", "_ref", "nsa_reference.py")
+    if not os.path.isfile(path):
+        return None
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("nsa_reference_native", path)
+    ref = importlib.util.module_from_spec(spec)
+    sys.modules["nsa_reference_native"] = ref      # dataclasses look their module up by name
+    spec.loader.exec_module(ref)
+    torch.set_num_threads(os.cpu_count() or 1)
+    g = torch.Generator().manual_seed(seed)
+    T, H, D = 4096, 16, 64
+    Q = torch.randn(1, H, T, D, generator=g)
+    K = torch.randn(1, 1, T, D, generator=g).expand(1, H, T, D).contiguous()
+    V = torch.randn(1, 1, T, D, generator=g).expand(1, H, T, D).contiguous()
+    Wg = (torch.rand(3, D, generator=g) * 2 - 1) / D ** 0.5
+    gates = torch.einsum("bhtd,cd->bhtc", Q, Wg)
+    cfg = ref.NSAConfig()
+    ts, out = [], None
+    for i in range(4):
+        t0 = time.perf_counter()
+        out = ref.nsa_attention_reference(Q, K, V, cfg, gates=gates)
+        if i > 0:
+            ts.append(time.perf_counter() - t0)
+    med = statistics.median(ts)
+    return {"value": T / med, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "reference",
+            "sample": f"nsa_attention_reference, fp32, B=1 T={T} H={H} (one KV head expanded) D={D}, 64/64 compression, top-16, "
+                      f"window 512; median of {len(ts)} runs after 1 warm-up",
+            "seconds": med, "rows_without_any_key_nan": int((~torch.isfinite(out).all(-1)).sum())}
+
+
 def run_ours(a):
     import nsa_from_scratch_b200 as nsa
-    from nsa_from_scratch_b200 import _lib as L, forward as F, ops
+    from nsa_from_scratch_b200 import _lib as L, forward as F, ops, parallel
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -227,25 +290,54 @@ def run_ours(a):
             dist.barrier()
         torch.cuda.synchronize()
 
+    def max_over_ranks(ms):
+        if dist is None:
+            return ms
+        t_ = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t_, op=dist.ReduceOp.MAX)
+        return float(t_.item())
+
     cfg = nsa.NSAConfig(block_size_c=a.cmp_block, stride_c=a.cmp_stride, block_size_n=64, block_size_m=64,
                         top_k=a.top_k, window_size=a.window, force_first=1, force_local=2,
                         select_per_group=a.select == "group")
     engine = {"auto": L.ENGINE_AUTO, "generic": L.ENGINE_GENERIC, "tcgen05": L.ENGINE_TCGEN05}[a.engine]
+    ops.set_engine(a.engine)
     if a.layout == "cp":
-        return run_cp(a, nsa, cfg, rank, world, dist, barrier)
-    Qh, Kh, Vh, Gh = make_inputs(a, a.seed + rank)
+        line = run_cp(a, a.seq_len, nsa, cfg, rank, world, dist, barrier, max_over_ranks, a.steps, a.warmup)
+        if rank == 0:
+            print(json.dumps(line), flush=True)
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+    T, D, H, Hkv = a.seq_len, a.head_dim, a.heads, a.kv_heads
+    scale = D ** -0.5
+    shared = a.select == "group"
+    group = None
+    if a.layout == "heads":
+        # ONE problem: this rank's (batch, KV head) units, or its share of the query heads of one unit
+        part = parallel.head_partition(1, H, Hkv, world, rank)
+        if world > 1:
+            group = parallel.head_groups(1, H, Hkv, world, rank)
+        G_ = H // Hkv
+        q_heads = [u * G_ + h for u in range(part.u0, part.u1) for h in range(part.h0, part.h1)]
+        kv_list = list(range(part.u0, part.u1))
+        Qh, Kh, Vh, Gh = make_inputs(a, a.seed, heads=q_heads, kv_heads=kv_list)
+        tokens_total, scaling = T, "strong"
+        par = (f"one B=1 problem over {world} rank(s): {len(kv_list)} KV head(s) x {part.h1 - part.h0} query heads per rank"
+               + (f", query block means all-gathered among the {part.split} ranks of a KV head" if part.split > 1 and shared else ", no collective"))
+    else:
+        Qh, Kh, Vh, Gh = make_inputs(a, a.seed + rank)
+        tokens_total, scaling = world * T, "weak"
+        par = f"replicas: every rank its own batch element, {world} rank(s), no collective"
     Qh, Kh, Vh, Gh = (t.pin_memory() for t in (Qh, Kh, Vh, Gh))
     Q, K, V, G = (t.cuda(non_blocking=True) for t in (Qh, Kh, Vh, Gh))
     torch.cuda.synchronize()
-    T, D = a.seq_len, a.head_dim
-    scale = D ** -0.5
-
-    shared = a.select == "group"
 
     def step():
-        idx = F._resolve_block_indices(Q, K, block_size_m=64, block_size_n=64, top_k=a.top_k, causal=True, scale=scale,
-                                       force_first=1, force_local=2, shared_per_group=shared)
-        return F._fused_forward(Q, K, V, cfg, scale, a.cmp_stride, G, idx, 1.0, 1.0, 1.0, engine=engine)
+        # the public entry point (selection inside); a rank that shares its KV head goes through the layout's wrapper
+        if group is not None:
+            return parallel.nsa_forward_head_parallel(Q, K, V, cfg, gate_logits=G, group=group)
+        return nsa.nsa_forward(Q, K, V, cfg, gate_logits=G)
     LAUNCHES_PER_STEP = 6   # pool Q means, pool K means, select, pool K, pool V, fused attention
 
     for _ in range(a.warmup):
@@ -261,24 +353,25 @@ def run_ours(a):
         out = step()
     ev[1].record()
     barrier()
-    ms_total = ev[0].elapsed_time(ev[1])
-    if dist is not None:
-        t_ = torch.tensor([ms_total], device="cuda")
-        dist.all_reduce(t_, op=dist.ReduceOp.MAX)
-        ms_total = float(t_.item())
-    ms_step = ms_total / a.steps
-    value = world * T / (ms_step * 1e-3)
+    ms_step = max_over_ranks(ev[0].elapsed_time(ev[1])) / a.steps
+    value = tokens_total / (ms_step * 1e-3)
 
-    # ---- per-kernel timing of the dominant (fused attention) kernel ---------------------------------
-    idx = F._resolve_block_indices(Q, K, block_size_m=64, block_size_n=64, top_k=a.top_k, causal=True, scale=scale,
-                                   force_first=1, force_local=2, shared_per_group=shared)
-    flops = algorithmic_flops(a, idx)
+    # ---- per-kernel timing of the dominant (fused attention) kernel on this rank's share ------------------
+    def indices():
+        if group is not None:
+            return parallel.resolve_block_indices_split(Q, K, cfg, group, scale=scale)
+        return F._resolve_block_indices(Q, K, block_size_m=64, block_size_n=64, top_k=a.top_k, causal=True, scale=scale,
+                                        force_first=1, force_local=2, shared_per_group=shared)
+    import copy
+    mine = copy.copy(a)
+    mine.heads, mine.kv_heads = Q.shape[1], K.shape[1]
+    idx = indices()
+    flops = algorithmic_flops(mine, idx)
     stage_ms = {"pool_select": [], "fused_attention": []}
     for _ in range(a.steps):
         e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
         e[0].record()
-        idx = F._resolve_block_indices(Q, K, block_size_m=64, block_size_n=64, top_k=a.top_k, causal=True, scale=scale,
-                                       force_first=1, force_local=2, shared_per_group=shared)
+        idx = indices()
         Kc = ops.pool_mean(K, a.cmp_block, a.cmp_stride)
         Vc = ops.pool_mean(V, a.cmp_block, a.cmp_stride)
         e[1].record()
@@ -312,23 +405,23 @@ def run_ours(a):
     # the clock sampler ran through the timed region and the per-kernel timing loops (same kernels, same load)
     clocks = sampler.stop() if sampler else None
     fused_ms = statistics.mean(stage_ms["fused_attention"])
-    peaks = {}
-    try:
-        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-    except Exception:
-        pass
-    peak = peaks.get("bf16_tflops_sustained")
-    peak_src = "measured (sustained cuBLAS bf16, MEASURED_PEAKS.json)"
+    peaks = measured_peaks()
+    # the kernel is timed launch by launch (an event pair and a synchronize around each), the conditions of the burst
+    # figure; the sustained figure (seconds of back-to-back GEMMs under the power cap) is kept as a second key
+    peak = peaks.get("bf16_tflops")
+    peak_src = "measured (burst cuBLAS bf16, MEASURED_PEAKS.json)"
     if peak is None:
         peak, peak_src = 1590.0, "fallback"
     achieved = flops["total"] / (fused_ms * 1e-3) / 1e12
     # DRAM bytes per launch of the fused kernel: dram__bytes_read + dram__bytes_write of one ncu capture at
-    # T=16384 with these heads (577.0 MB), scaled by T -- every operand of this shape family grows with T
-    traffic = 576.957696e6 * T / 16384 if (a.heads, a.kv_heads, a.head_dim) == (64, 4, 128) else None
+    # T=16384 with 64 query / 4 KV heads of 128 (577.0 MB), scaled by T and by this rank's share of the heads -- every
+    # operand of this shape family grows with both
+    traffic = 576.957696e6 * T / 16384 * Q.shape[1] / 64 if (a.heads, a.kv_heads, a.head_dim) == (64, 4, 128) else None
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "traffic": traffic, "peak_source": peak_src, "kernel": "fused three-branch attention",
+                "traffic": traffic, "traffic_source": "ncu capture at T=16384, scaled (profiles/)", "peak_source": peak_src,
+                "kernel": "fused three-branch attention (nsa_fwd_tc5_kernel)" + (f", rank 0's {Q.shape[1]} of {H} heads" if world > 1 and a.layout == "heads" else ""),
                 "kernel_ms": fused_ms, "algorithmic_tflop": {k: v / 1e12 for k, v in flops.items()},
-                "frac_of_burst_peak": achieved / peaks["bf16_tflops"] if "bf16_tflops" in peaks else None,
+                "frac_of_sustained_peak": achieved / peaks["bf16_tflops_sustained"] if "bf16_tflops_sustained" in peaks else None,
                 "pool_select_ms": statistics.mean(stage_ms["pool_select"]),
                 "branches_alone": {k: {"ms": branch_ms[k], "tflops": flops[k] / (branch_ms[k] * 1e-3) / 1e12,
                                        "frac": flops[k] / (branch_ms[k] * 1e-3) / 1e12 / peak} for k in branch_ms}}
@@ -337,11 +430,13 @@ def run_ours(a):
     e2e = None
     if not a.no_e2e:
         out_h = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+        idx_fn = (lambda qd, kd: parallel.resolve_block_indices_split(qd, kd, cfg, group, scale=scale)) if group is not None else None
 
         def e2e_step():
             # the public host-tensor entry point: copies in, kernels and copy out pipelined per
-            # (batch, KV head, query chunk)
-            nsa.nsa_forward_host(Qh, Kh, Vh, cfg, gate_logits=Gh, out=out_h, chunk_rows=a.host_chunk or None)
+            # (batch, KV head, query chunk); it returns when the result is in host memory
+            nsa.nsa_forward_host(Qh, Kh, Vh, cfg, gate_logits=Gh, out=out_h, chunk_rows=a.host_chunk or None,
+                                 block_indices_fn=idx_fn)
         for _ in range(2):
             e2e_step()
         barrier()
@@ -352,87 +447,110 @@ def run_ours(a):
             e2e_step()
         e1.record()
         barrier()
-        ms = e0.elapsed_time(e1)
-        if dist is not None:
-            t_ = torch.tensor([ms], device="cuda")
-            dist.all_reduce(t_, op=dist.ReduceOp.MAX)
-            ms = float(t_.item())
+        ms = max_over_ranks(e0.elapsed_time(e1))
         h2d = sum(t.numel() * t.element_size() for t in (Qh, Kh, Vh, Gh))
-        e2e = {"value": world * T / (ms / n_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
-               "d2h_bytes_per_step": out_h.numel() * out_h.element_size(), "ms_per_step": ms / n_e2e}
+        e2e = {"value": tokens_total / (ms / n_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": out_h.numel() * out_h.element_size(), "ms_per_step": ms / n_e2e,
+               "bytes_are": "per rank" if world > 1 else "whole job"}
+        del out_h
 
-    cpu = None
+    cpu = cpu_native = None
     if rank == 0 and world == 1 and not a.no_cpu_baseline:
         v, dt, desc = cpu_sample(a, a.cpu_tiles)
         cpu = {"value": v, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": desc,
                "seconds": dt}
+        cpu_native = native_reference_cpu(a.seed)
+    ops.device_status()
+
+    # ---- context parallel at its own length, same process group (N > 1) ---------------------------------
+    cp_block = None
+    if world > 1 and a.layout == "heads" and a.cp_seq_len > 0 and a.cp_seq_len % (world * 64) == 0:
+        del Q, K, V, G, Qh, Kh, Vh, Gh, out, Kc, Vc, idx
+        torch.cuda.empty_cache()
+        cp_line = run_cp(a, a.cp_seq_len, nsa, cfg, rank, world, dist, barrier, max_over_ranks, max(2, min(a.steps, 3)), 1)
+        cp_block = {k: cp_line[k] for k in ("value", "unit", "ms_per_step", "seq_len", "per_rank_ms", "all_gather_ms",
+                                              "bytes_received_per_rank", "imbalance_last_over_mean", "steps")} if rank == 0 else None
 
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {"workload": workload_name(a), "global_batch": world, "seq_len": T,
-                       "parallelism": f"batch x kv-head partition, {world} rank(s), no collective",
+            "config": {"workload": workload_name(a), "global_batch": 1 if a.layout == "heads" else world, "seq_len": T,
+                       "parallelism": par, "layout": a.layout,
                        "l2": "inputs (Q alone 1 GiB at the default size) exceed the 126 MB L2", "engine": a.engine},
-            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
-            "gpu_launches": LAUNCHES_PER_STEP * a.steps,
+            "roofline": roofline, "cpu_baseline": cpu, "cpu_baseline_reference_native": cpu_native, "e2e": e2e,
+            "clocks": clocks, "gpu_launches": LAUNCHES_PER_STEP * a.steps, "context_parallel": cp_block,
         }
-        ops.device_status()
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
 
 
-def run_cp(a, nsa, cfg, rank, world, dist, barrier):
-    """Context-parallel layout: rank r holds rows [r*Tl, (r+1)*Tl) of Q / gates / out and of K, V."""
+def run_cp(a, T, nsa, cfg, rank, world, dist, barrier, max_over_ranks, steps, warmup):
+    """Context-parallel layout: rank r holds rows [r*Tl, (r+1)*Tl) of Q / gates / out and of K, V -- slices of ONE
+    seeded sequence of length T.  Returns the JSON line (meaningful on rank 0)."""
     import copy
     from nsa_from_scratch_b200 import ops, parallel
-    T = a.seq_len
-    assert T % (world * 64) == 0, "--seq-len must be a multiple of 64 * ranks for the cp layout"
-    loc = copy.copy(a)
-    loc.seq_len = T // world
-    Q, K, V, G = (t.cuda() for t in make_inputs(loc, a.seed + rank))
-    group = None
+    assert T % (world * 64) == 0, "the sequence length must be a multiple of 64 * ranks for the cp layout"
+    tot = copy.copy(a)
+    tot.seq_len = T
+    Tl = T // world
+    Q, K, V, G = (t.cuda() for t in make_inputs(tot, a.seed, rows=(rank * Tl, (rank + 1) * Tl)))
+    stats = {}
 
     def step():
         if world > 1:
-            return parallel.nsa_forward_context_parallel(Q, K, V, cfg, gate_logits=G, group=group)
+            return parallel.nsa_forward_context_parallel(Q, K, V, cfg, gate_logits=G, stats=stats)
         return nsa.nsa_forward(Q, K, V, cfg, gate_logits=G)
-    for _ in range(a.warmup):
+    for _ in range(warmup):
         out = step()
     barrier()
     sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0"))) if rank == 0 else None
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
     barrier()
     ev[0].record()
-    for _ in range(a.steps):
+    for _ in range(steps):
         out = step()
     ev[1].record()
     barrier()
-    ms = ev[0].elapsed_time(ev[1])
+    ms_mine = ev[0].elapsed_time(ev[1]) / steps
     clocks = sampler.stop() if sampler else None
+    ms_step = max_over_ranks(ms_mine * steps) / steps
+    # the collective alone (events around it, every rank in step), and each rank's own time
+    ag_ms, per_rank = None, [ms_mine]
     if dist is not None:
-        t_ = torch.tensor([ms], device="cuda")
-        dist.all_reduce(t_, op=dist.ReduceOp.MAX)
-        ms = float(t_.item())
-    ms_step = ms / a.steps
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            kp = parallel.gather_key_prefix(K)
+            vp = parallel.gather_key_prefix(V)
+        e1.record()
+        barrier()
+        ag_ms = max_over_ranks(e0.elapsed_time(e1)) / steps
+        del kp, vp
+        allms = torch.zeros(world, device="cuda")
+        allms[rank] = ms_mine
+        dist.all_reduce(allms)
+        per_rank = [float(x) for x in allms.tolist()]
     ops.device_status()
-    if rank == 0:
-        kv_bytes = 2 * K.numel() * K.element_size() * (world - 1)
-        line = {
-            "metric": METRIC, "value": T / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": a.steps,
-            "warmup": a.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": workload_name(a) + " [context parallel: total T, contiguous query shards]",
-                       "global_batch": 1, "seq_len": T, "parallelism": f"cp{world}: all-gather of K/V ({kv_bytes} B received per rank per step) + local forward",
-                       "l2": "inputs exceed the 126 MB L2"},
-            "roofline": None, "cpu_baseline": None, "e2e": None, "clocks": clocks,
-            "gpu_launches": 6 * a.steps,
-        }
-        print(json.dumps(line), flush=True)
-    if dist is not None:
-        dist.destroy_process_group()
+    kv_bytes = 2 * K.numel() * K.element_size() * (world - 1)
+    line = {
+        "metric": METRIC, "value": T / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": steps,
+        "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "seq_len": T,
+        "per_rank_ms": per_rank, "all_gather_ms": ag_ms, "bytes_received_per_rank": kv_bytes,
+        "imbalance_last_over_mean": per_rank[-1] / (sum(per_rank) / len(per_rank)),
+        "config": {"workload": workload_name(tot) + " [context parallel: total T, contiguous query shards]",
+                   "global_batch": 1, "seq_len": T, "parallelism": f"cp{world}: all-gather of K/V ({kv_bytes} B received per rank per step) + local forward",
+                   "l2": "inputs exceed the 126 MB L2"},
+        "roofline": None, "cpu_baseline": None, "e2e": None, "clocks": clocks,
+        "gpu_launches": 6 * steps,
+    }
+    del Q, K, V, G, out
+    torch.cuda.empty_cache()
+    return line
 
 
 def run_sweep(a):

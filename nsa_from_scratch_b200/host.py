@@ -48,12 +48,15 @@ def _side_streams(dev):
 
 def nsa_forward_host(Q: Tensor, K: Tensor, V: Tensor, cfg, *, gate_logits: Optional[Tensor] = None,
                      out: Optional[Tensor] = None, device=None, chunk_rows: Optional[int] = 16384,
-                     non_blocking: bool = False):
+                     non_blocking: bool = False, block_indices_fn=None):
     """Q [B,H,Tq,D], K/V [B,Hkv,Tk,D], gate_logits [B,H,Tq,3] on the HOST (ideally pinned); returns the
     output [B,H,Tq,D] on the host (`out` if given, else a new pinned tensor).  Inference only.
     The call returns when the last device -> host copy has landed, so the result can be read on the CPU at once.
     With non_blocking=True it returns (out, event) as soon as everything is queued; the caller must
     event.synchronize() (or synchronize the device) before reading `out`.
+    `block_indices_fn(q_dev, k_dev)`: where the block lists of a unit come from instead of nsa_forward's own
+    selection -- a rank that holds only some query heads of a KV head passes the selection that all-gathers the
+    heads' block means (parallel.resolve_block_indices_split).
     `chunk_rows`: query positions per pipeline unit (None = whole sequences).  Smaller chunks shorten the
     unhidden head and tail of the pipeline but cost a fixed host-side launch sequence each; 16384 was the
     fastest at 64k tokens x 64 heads on a B200 over PCIe (29.9 ms; 8192: 31.7, whole sequences: 32.3)."""
@@ -110,7 +113,8 @@ def nsa_forward_host(Q: Tensor, K: Tensor, V: Tensor, cfg, *, gate_logits: Optio
     with torch.cuda.device(dev):
         for b, hs, c0, c1, qd, kd, vd, gd, k_end, ev in staged:
             cur.wait_event(ev)
-            o = nsa_forward(qd, kd[:, :, :k_end], vd[:, :, :k_end], cfg, gate_logits=gd)
+            idx = block_indices_fn(qd, kd[:, :, :k_end]) if block_indices_fn is not None else None
+            o = nsa_forward(qd, kd[:, :, :k_end], vd[:, :, :k_end], cfg, gate_logits=gd, block_indices=idx)
             ev2 = torch.cuda.Event()
             ev2.record(cur)
             o.record_stream(s_out)
