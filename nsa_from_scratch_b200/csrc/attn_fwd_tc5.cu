@@ -26,6 +26,7 @@
 #include "tc5_ptx.cuh"
 
 #include <cudaTypedefs.h>
+#include <stdlib.h>
 
 namespace nsa {
 
@@ -748,6 +749,632 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
 }
 
+// ---------------------------------------------------------------- persistent variant
+// The same arithmetic, one thread block per SM looping over work items (item = blockIdx.x, += gridDim.x; the items are
+// ordered long rows first, so a round-robin deal gives every block a like mix).  What a one-item block pays per item
+// -- barrier set-up, TMEM allocation, the list of selected blocks, the Q load and the first K tile before the first
+// MMA, and an idle tensor pipe during the last epilogue -- is overlapped with the neighbouring items instead:
+//   * warp 2 builds the NEXT item's block list into the other of two list buffers while the current item runs;
+//   * warp 0 requests the next item's Q tiles as soon as the MMA warp has committed the current item's last Q K^T
+//     (Q's shared memory is then free), and goes straight on to the next item's K/V tiles, ring permitting;
+//   * warp 1 issues the next item's first Q K^T while the softmax warps are still in the current item's last epilogue
+//     (its first P V is ordered behind that epilogue by the P-ready barrier, which the softmax warps reach only after it).
+// All barrier phases come from running counters (tiles, items) instead of per-item ones.  bf16/fp16 storage, unsplit.
+enum { PB_LISTFULL = B_COUNT, PB_LISTEMPTY = B_COUNT + 2, PB_QFREE = B_COUNT + 4, PB_COUNT = B_COUNT + 5 };
+
+template <int D, int FMT>
+__global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_persist_kernel(const __grid_constant__ Tc5Params p, int n_items) {
+  using T = typename std::conditional<FMT == 1, __nv_bfloat16, __half>::type;
+  constexpr int DH = D / 64;
+  constexpr int QTILE = DH * 128 * 128;
+  constexpr int KVTILE = DH * 128 * 128;
+  constexpr int DHSTRIDE = 128 * 128;
+  constexpr bool EARLY = (D == 64);
+  const nsa_fwd_args& a = p.a;
+
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sQ = smem_u32(smem);
+  const uint32_t sK = sQ + 2 * QTILE;
+  const uint32_t sV = sK + 2 * KVTILE;
+  __shared__ __align__(8) uint64_t bars[PB_COUNT];
+  __shared__ int sel_list[2][T5_MAX_ENT];
+  __shared__ unsigned char sel_mask[2][T5_MAX_ENT];
+  __shared__ int sel_n[2];
+  __shared__ int ent_blk[T5_MAX_ENT];              // scratch of the list builder
+  __shared__ unsigned char ent_p[T5_MAX_ENT];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  auto bar = [&](int id) { return smem_u32(&bars[id]); };
+  const int G = a.H / a.Hkv;
+  const int GH = p.GH, NQB = 4 / p.GH;
+  const int per_q = a.B * a.Hkv * p.HG;
+
+  // a work item's coordinates (see nsa_fwd_tc5_kernel) and, once its block list is there, its tile counts
+  struct Item {
+    int b, hk, h_base, qb_base, q_first, i_last, kv_slab;
+    int nchunks[3], sld_c0;
+  };
+  auto bounds = [&](int br, int i, bool ok, int& lo, int& hi) {
+    lo = 0; hi = -1;
+    if (!ok) return;
+    if (br == 0) {
+      if (a.causal) {
+        int num = i + a.cmp_offset - (a.cmp_block - 1);
+        hi = num < 0 ? -1 : num / a.cmp_stride;
+      } else hi = a.Nc - 1;
+      hi = min(hi, a.Nc - 1);
+    } else if (br == 1) {
+      hi = a.causal ? min(i + a.offset, a.sel_key_limit - 1) : a.sel_key_limit - 1;
+    } else {
+      int pos = i + a.offset;
+      if (a.causal) { lo = pos - a.window + 1; hi = pos; }
+      else { lo = pos - a.window; hi = pos + a.window; }
+      lo = max(lo, 0); hi = min(hi, a.Tk - 1);
+    }
+  };
+  auto coords = [&](int item) {
+    Item it;
+    const int qbg = p.NQG - 1 - item / per_q;          // long rows first
+    const int rem = item % per_q;
+    it.b = rem / (a.Hkv * p.HG);
+    it.hk = (rem / p.HG) % a.Hkv;
+    const int hg = rem % p.HG;
+    it.h_base = it.hk * G + hg * GH;
+    it.qb_base = qbg * NQB;
+    it.q_first = it.qb_base * 64;
+    it.i_last = min((min(it.qb_base + NQB, a.nq)) * 64, a.Tq) - 1;
+    it.kv_slab = it.b * a.Hkv + it.hk;
+    it.nchunks[0] = it.nchunks[1] = it.nchunks[2] = 0;
+    it.sld_c0 = 0;
+    return it;
+  };
+  auto counts = [&](Item& it, int n_sel) {               // needs the item's block list (n_sel)
+    int lo_f, hi_f, lo_l, hi_l;
+    if (a.branches & NSA_BRANCH_COMPRESSED) {
+      bounds(0, it.i_last, true, lo_l, hi_l);
+      it.nchunks[0] = hi_l < 0 ? 0 : hi_l / 64 + 1;
+    }
+    if (a.branches & NSA_BRANCH_SELECTED) it.nchunks[1] = n_sel;
+    if (a.branches & NSA_BRANCH_SLIDING) {
+      bounds(2, it.q_first, true, lo_f, hi_f);
+      bounds(2, it.i_last, true, lo_l, hi_l);
+      if (hi_l >= lo_f) { it.sld_c0 = lo_f / 64; it.nchunks[2] = hi_l / 64 - it.sld_c0 + 1; }
+    }
+  };
+  auto ntiles = [&](const Item& it, int br) { return (it.nchunks[br] + 1) >> 1; };
+  auto get_tile = [&](const Item& it, int lp, int br, int t) {
+    Tile tl;
+    tl.nch = min(2, it.nchunks[br] - 2 * t);
+    for (int c = 0; c < 2; ++c) {
+      int ci = min(2 * t + c, it.nchunks[br] - 1);
+      tl.mask[c] = 0xF;
+      if (br == 0) { tl.j0[c] = ci * 64; tl.jlim[c] = a.Nc; }
+      else if (br == 1) { int blk = sel_list[lp][ci]; tl.j0[c] = blk * 64; tl.jlim[c] = min(blk * 64 + 64, a.sel_key_limit); tl.mask[c] = sel_mask[lp][ci]; }
+      else { tl.j0[c] = (it.sld_c0 + ci) * 64; tl.jlim[c] = a.Tk; }
+    }
+    return tl;
+  };
+  auto grp_head = [&](const Item& it, int g) { return it.h_base + g % GH; };
+  auto grp_qb = [&](const Item& it, int g) { return it.qb_base + g / GH; };
+
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int i = 0; i < PB_COUNT; ++i) {
+      int cnt = 1;
+      if (i == B_PFULL || i == B_PFULL + 1 || i == B_SREAD || i == B_SREAD + 1) cnt = 128;
+      if (i == PB_LISTEMPTY || i == PB_LISTEMPTY + 1) cnt = 10;     // producer, MMA issuer and the 8 softmax warps
+      mbar_init(bar(i), cnt);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(&tmem_base_s), 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+
+  int fail_id = 0;
+  int last_k_it = -1, last_v_it = -1, q_loads = 0;   // producer: what has been issued (for the drain after an abort)
+
+  if (warp == 0) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;\n");
+    // =============================== TMA producer ===============================
+    const bool leader = elect_one();
+    if (leader) {
+      tma_prefetch_desc(&p.tmQ); tma_prefetch_desc(&p.tmK); tma_prefetch_desc(&p.tmV);
+      if (a.branches & NSA_BRANCH_COMPRESSED) { tma_prefetch_desc(&p.tmKc); tma_prefetch_desc(&p.tmVc); }
+    }
+    __syncwarp();
+    int it = 0, k = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++k) {
+      const int lp = k & 1;
+      Item im = coords(item);
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(PB_LISTFULL + lp), (k >> 1) & 1, &abort_flag));
+      if (!ok) { fail_id = PB_LISTFULL + lp + 1; break; }
+      counts(im, sel_n[lp]);
+      if (ntiles(im, 0) + ntiles(im, 1) + ntiles(im, 2) > 0) {     // an item without a tile needs no Q (and the MMA warp skips it)
+        // Q's shared memory is free once the previous item's last Q K^T has been read by the tensor pipe
+        if (q_loads > 0) {
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(PB_QFREE), (q_loads - 1) & 1, &abort_flag));
+          if (!ok) { fail_id = PB_QFREE + 1; break; }
+        }
+        if (leader) {
+          mbar_expect_tx(bar(B_QFULL), 2 * QTILE);
+          for (int X = 0; X < 2; ++X)
+            for (int hh = 0; hh < 2; ++hh)
+              for (int dh = 0; dh < DH; ++dh)
+                tma_load_3d(sQ + X * QTILE + dh * DHSTRIDE + hh * 8192, &p.tmQ, bar(B_QFULL), dh * 64, grp_qb(im, 2 * X + hh) * 64,
+                            im.b * a.H + grp_head(im, 2 * X + hh));
+        }
+        ++q_loads;
+      }
+      for (int br = 0; br < 3 && ok; ++br) {
+        const CUtensorMap* mk = br == 0 ? &p.tmKc : &p.tmK;
+        const CUtensorMap* mv = br == 0 ? &p.tmVc : &p.tmV;
+        for (int t = 0; t < ntiles(im, br) && ok; ++t, ++it) {
+          const Tile tl = get_tile(im, lp, br, t);
+          const int s = it & 1, ph = (it >> 1) & 1;
+          const uint32_t bytes = (uint32_t)tl.nch * 64 * D * 2;
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(B_KEMPTY + s), ph ^ 1, &abort_flag));
+          if (!ok) { fail_id = B_KEMPTY + s + 1; break; }
+          if (leader) {
+            mbar_expect_tx(bar(B_KFULL + s), bytes);
+            for (int c = 0; c < tl.nch; ++c)
+              for (int dh = 0; dh < DH; ++dh)
+                tma_load_3d(sK + s * KVTILE + dh * DHSTRIDE + c * 8192, mk, bar(B_KFULL + s), dh * 64, tl.j0[c], im.kv_slab);
+          }
+          last_k_it = it;
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(B_VEMPTY + s), ph ^ 1, &abort_flag));
+          if (!ok) { fail_id = B_VEMPTY + s + 1; break; }
+          if (leader) {
+            mbar_expect_tx(bar(B_VFULL + s), bytes);
+            for (int c = 0; c < tl.nch; ++c)
+              for (int dh = 0; dh < DH; ++dh)
+                tma_load_3d(sV + s * KVTILE + dh * DHSTRIDE + c * 8192, mv, bar(B_VFULL + s), dh * 64, tl.j0[c], im.kv_slab);
+          }
+          last_v_it = it;
+          __syncwarp();
+        }
+      }
+      if (ok && lane == 0) mbar_arrive(bar(PB_LISTEMPTY + lp));
+      __syncwarp();
+    }
+  } else if (warp == 1) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;\n");
+    // =============================== MMA issuer ===============================
+    const bool leader = elect_one();
+    constexpr uint32_t IDESC_PV = idesc_f16(FMT, 128, D, 0, 1);
+    constexpr uint32_t IDESC_QK1 = idesc_f16(FMT, 128, 64, 0, 0);
+    constexpr uint32_t IDESC_QK2 = idesc_f16(FMT, 128, 128, 0, 0);
+    const uint64_t dQ[2] = {smem_desc_sw128(sQ, 16, 1024), smem_desc_sw128(sQ + QTILE, 16, 1024)};
+    const uint64_t dK[2] = {smem_desc_sw128(sK, 16, 1024), smem_desc_sw128(sK + KVTILE, 16, 1024)};
+    const uint64_t dV[2] = {smem_desc_sw128(sV, DHSTRIDE, 1024), smem_desc_sw128(sV + KVTILE, DHSTRIDE, 1024)};
+    const uint32_t tSx[2] = {tmem, tmem + 128}, tOx[2] = {tmem + 256, tmem + 384};
+    const uint32_t tPx[2] = {EARLY ? tmem + 320 : tmem, EARLY ? tmem + 448 : tmem + 128};
+    bool ok = true;
+
+    // The issuer walks two cursors over the flattened (item, branch, tile) sequence: q = the tile whose Q K^T is
+    // issued next, v = the tile whose P V is issued next; q is one tile ahead of v and crosses into the next item
+    // first.  Items without a tile are skipped (nothing is loaded or issued for them).
+    struct Cur { int item, k, br, t, it, live, nch[3]; bool valid; };
+    auto nt = [](const Cur& c, int br) { return (c.nch[br] + 1) >> 1; };
+    auto open_item = [&](Cur& c, int item, int kk) -> bool {      // positions c on the first tile of `item` or of the next item that has one
+      c.item = item; c.k = kk; c.valid = false;
+      while (c.item < n_items) {
+        const int lp = c.k & 1;
+        if (!__all_sync(0xffffffffu, mbar_wait(bar(PB_LISTFULL + lp), (c.k >> 1) & 1, &abort_flag))) { fail_id = PB_LISTFULL + lp + 1; return false; }
+        Item im = coords(c.item);
+        counts(im, sel_n[lp]);
+        c.nch[0] = im.nchunks[0]; c.nch[1] = im.nchunks[1]; c.nch[2] = im.nchunks[2];
+        c.br = 0; c.t = 0;
+        while (c.br < 3 && c.t >= nt(c, c.br)) { ++c.br; c.t = 0; }
+        if (c.br < 3) { c.valid = true; ++c.live; return true; }
+        c.item += gridDim.x; ++c.k;
+      }
+      return true;
+    };
+    auto advance = [&](Cur& c) -> bool {                           // next tile; crosses item boundaries
+      ++c.t; ++c.it;
+      while (c.br < 3 && c.t >= nt(c, c.br)) { ++c.br; c.t = 0; }
+      if (c.br < 3) return true;
+      return open_item(c, c.item + gridDim.x, c.k + 1);
+    };
+    auto release_lists = [&](int k0, int k1) {                     // this warp is done with the block lists of items k0..k1-1
+      for (int kk = k0; kk < k1; ++kk)
+        if (lane == 0) mbar_arrive(bar(PB_LISTEMPTY + (kk & 1)));
+      __syncwarp();
+    };
+    Cur q;
+    q.it = 0; q.live = 0;
+    ok = open_item(q, blockIdx.x, 0);
+    Cur v = q;
+    if (ok) release_lists(0, v.k);                                 // leading items without a tile
+    int q_ready = 0;                  // live items whose Q is known to have landed
+
+    auto issue_qk = [&](int X) -> bool {     // Q K^T of tile q for 128-row tile X
+      const int s = q.it & 1;
+      if (X == 0) {
+        if (q.live > q_ready) {              // first tile of an item: its Q must be in shared memory
+          if (!__all_sync(0xffffffffu, mbar_wait(bar(B_QFULL), (q.live - 1) & 1, &abort_flag))) { fail_id = B_QFULL + 1; return false; }
+          q_ready = q.live;
+        }
+        if (!__all_sync(0xffffffffu, mbar_wait(bar(B_KFULL + s), (q.it >> 1) & 1, &abort_flag))) { fail_id = B_KFULL + s + 1; return false; }
+        tc_fence_after();
+      }
+      const int nch = min(2, q.nch[q.br] - 2 * q.t);
+      const uint32_t idesc = nch == 2 ? IDESC_QK2 : IDESC_QK1;
+      bool last = false;                     // the item's last tile: its Q is free once these MMAs have read it
+      if (X == 1) {
+        int br2 = q.br, t2 = q.t + 1;
+        while (br2 < 3 && t2 >= nt(q, br2)) { ++br2; t2 = 0; }
+        last = br2 >= 3;
+      }
+      if (leader) {
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (uint32_t)(((ks >> 2) * DHSTRIDE + (ks & 3) * 32) >> 4);
+          if (ks == 0) mma_ss(tSx[X], dQ[X] + off, dK[s] + off, idesc, 0u);
+          else mma_ss(tSx[X], dQ[X] + off, dK[s] + off, idesc, 1u);
+        }
+        tc_commit(bar(B_SFULL + X));
+        if (X == 1) tc_commit(bar(B_KEMPTY + s));
+        if (last) tc_commit(bar(PB_QFREE));
+      }
+      __syncwarp();
+      return true;
+    };
+
+    if (ok && q.valid) {
+      ok = issue_qk(0) && issue_qk(1);
+      if (ok) ok = advance(q);
+    }
+    while (ok && v.valid) {
+      const int it = v.it;
+      const int nch = min(2, v.nch[v.br] - 2 * v.t);
+      const bool fresh = v.t == 0;                       // first tile of a branch starts a new O
+      const int s = it & 1;
+      // Q K^T of the next tile is interleaved with this tile's P V -- unless it belongs to the next item: its Q arrives a
+      // TMA round trip after this item's last Q K^T, and waiting for it here would hold up this item's last P V
+      const bool same_item = q.valid && q.k == v.k;
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(B_VFULL + s), (it >> 1) & 1, &abort_flag));
+      if (!ok) { fail_id = B_VFULL + s + 1; break; }
+      if constexpr (EARLY) {
+#pragma unroll
+        for (int X = 0; X < 2; ++X) {
+          if (!ok || !same_item) break;
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(B_SREAD + X), it & 1, &abort_flag));
+          if (!ok) { fail_id = B_SREAD + X + 1; break; }
+          tc_fence_after();
+          ok = issue_qk(X);
+        }
+      }
+#pragma unroll
+      for (int X = 0; X < 2; ++X) {
+        if (!ok) break;
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(B_PFULL + X), it & 1, &abort_flag));
+        if (!ok) { fail_id = B_PFULL + X + 1; break; }
+        tc_fence_after();
+        if (leader) {
+          if (fresh) mma_ts(tOx[X], tPx[X], dV[s], IDESC_PV, 0u);
+          else mma_ts(tOx[X], tPx[X], dV[s], IDESC_PV, 1u);
+#pragma unroll
+          for (int kk = 1; kk < 4; ++kk) mma_ts(tOx[X], tPx[X] + kk * 8, dV[s] + kk * 128, IDESC_PV, 1u);
+          if (nch == 2) {
+#pragma unroll
+            for (int kk = 4; kk < 8; ++kk) mma_ts(tOx[X], tPx[X] + kk * 8, dV[s] + kk * 128, IDESC_PV, 1u);
+          }
+          tc_commit(bar(B_PVDONE + X));
+          if (X == 1) tc_commit(bar(B_VEMPTY + s));
+        }
+        __syncwarp();
+        if (!EARLY && same_item) ok = issue_qk(X);
+      }
+      if (!ok) break;
+      if (q.valid && !same_item) {
+        // first tile of the next item, behind this item's last P V (S aliases P at D=128; at D=64 the S rows of this
+        // item's last tile have been read long before its P was written)
+        ok = issue_qk(0) && issue_qk(1);
+        if (!ok) break;
+      }
+      // v first: leaving an item releases its block list, which the builder may need before it can build the list q is
+      // about to ask for (an item of a single tile puts q two items ahead of the list v still holds)
+      const int k_before = v.k;
+      ok = advance(v);
+      if (ok && v.k != k_before) release_lists(k_before, v.k);
+      if (ok && q.valid) ok = advance(q);
+    }
+  } else if (warp == 2) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;\n");
+    // =============================== block-list builder ===============================
+    int k = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++k) {
+      const int lp = k & 1;
+      const Item im = coords(item);
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(PB_LISTEMPTY + lp), ((k >> 1) & 1) ^ 1, &abort_flag));
+      if (!ok) { fail_id = PB_LISTEMPTY + lp + 1; break; }
+      int n = 0;
+      if (a.branches & NSA_BRANCH_SELECTED) {
+        const bool shared = a.Hi != a.H && GH == 4;
+        const int ngrp = shared ? 1 : 4;
+        const int n_ent = ngrp * a.top_k;
+        for (int i = lane; i < n_ent; i += 32) {
+          const int g = i / a.top_k, sl = i % a.top_k;
+          const int qb = grp_qb(im, g);
+          int blk = -1;
+          if (qb < a.nq) {
+            const int hi_ = (a.Hi == a.H) ? grp_head(im, g) : im.hk;
+            blk = a.idx[(((size_t)im.b * a.Hi + hi_) * a.nq + qb) * a.top_k + sl];
+            const int last_pos = min(qb * 64 + 64, a.Tq) - 1 + a.offset;
+            if (blk < 0 || blk >= a.sel_key_limit / 64 || (a.causal && (long long)blk * 64 > last_pos)) blk = -1;
+          }
+          ent_blk[i] = blk;
+        }
+        __syncwarp();
+        if (!shared) {
+          for (int i = lane; i < n_ent; i += 32) {
+            int pc = 0;
+            const int blk = ent_blk[i], g0 = (i / a.top_k) * a.top_k;
+            for (int j = g0; j < i; ++j) pc += (ent_blk[j] == blk);
+            ent_p[i] = (unsigned char)pc;
+          }
+          __syncwarp();
+        }
+        for (int i0 = 0; i0 < n_ent; i0 += 32) {
+          const int i = i0 + lane;
+          bool lead = false;
+          unsigned msk = 0xFu;
+          if (i < n_ent && ent_blk[i] >= 0) {
+            lead = true;
+            if (!shared) {
+              const int blk = ent_blk[i], pi = ent_p[i], gi = i / a.top_k;
+              msk = 0;
+              for (int j = 0; j < n_ent; ++j) {
+                if (ent_blk[j] == blk && ent_p[j] == pi) {
+                  const int gj = j / a.top_k;
+                  msk |= 1u << gj;
+                  if (gj < gi) lead = false;
+                }
+              }
+            }
+          }
+          const unsigned bal = __ballot_sync(0xffffffffu, lead);
+          if (lead) {
+            const int pos = n + __popc(bal & ((1u << lane) - 1));
+            sel_list[lp][pos] = ent_blk[i];
+            sel_mask[lp][pos] = (unsigned char)msk;
+          }
+          n += __popc(bal);
+        }
+      }
+      if (lane == 0) sel_n[lp] = n;
+      __syncwarp();
+      __threadfence_block();
+      if (lane == 0) mbar_arrive(bar(PB_LISTFULL + lp));
+      __syncwarp();
+    }
+  } else if (warp == 3) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;\n");
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;\n");
+    // =============================== softmax / epilogue ===============================
+    const int X = (warp - 4) >> 2;
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tS = tmem + lane_addr + X * 128;
+    const uint32_t tO = tmem + lane_addr + 256 + X * 128;
+    const uint32_t tP = EARLY ? tmem + lane_addr + 320 + X * 128 : tS;
+    const int rg = 2 * X + (r >> 6);
+    int it = 0, k = 0;
+    bool ok = true;
+#pragma unroll 1
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++k) {
+      const int lp = k & 1;
+      Item im = coords(item);
+      const int head = grp_head(im, rg);
+      const int qi = grp_qb(im, rg) * 64 + (r & 63);
+      const bool row_ok = grp_qb(im, rg) < a.nq && qi < a.Tq;
+      const size_t row_index = ((size_t)im.b * a.H + head) * a.Tq + qi;
+      const size_t row_bthd = ((size_t)im.b * a.Tq + qi) * a.H + head;
+      float gate[3] = {0.5f, 0.5f, 0.5f};
+      if (a.fused) {
+        float x[3] = {0.f, 0.f, 0.f};
+        if (a.gates != nullptr && row_ok) {
+#pragma unroll
+          for (int c = 0; c < 3; ++c) {
+            const size_t gi = ((a.io_layout & NSA_IO_GATES_BTHD) ? row_bthd : row_index) * 3 + c;
+            x[c] = a.gate_dtype == NSA_FP32 ? reinterpret_cast<const float*>(a.gates)[gi]
+                 : a.gate_dtype == NSA_FP16 ? __half2float(reinterpret_cast<const __half*>(a.gates)[gi])
+                                            : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.gates)[gi]);
+          }
+        }
+        if (a.gate_act == NSA_GATE_SOFTMAX) {
+          float mx = fmaxf(x[0], fmaxf(x[1], x[2]));
+          float e0 = __expf(x[0] - mx), e1 = __expf(x[1] - mx), e2 = __expf(x[2] - mx);
+          float inv = 1.f / (e0 + e1 + e2);
+          gate[0] = e0 * inv; gate[1] = e1 * inv; gate[2] = e2 * inv;
+        } else {
+#pragma unroll
+          for (int c = 0; c < 3; ++c) gate[c] = 1.f / (1.f + __expf(-x[c]));
+        }
+      }
+      float lse_out = -INFINITY;
+      bool have_partial = a.accumulate != 0;
+      T* orow = reinterpret_cast<T*>(a.out) + ((a.io_layout & NSA_IO_OUT_BTHD) ? row_bthd : row_index) * D;
+
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(PB_LISTFULL + lp), (k >> 1) & 1, &abort_flag));
+      if (!ok) { fail_id = PB_LISTFULL + lp + 1; break; }
+      counts(im, sel_n[lp]);
+#pragma unroll 1
+      for (int br = 0; br < 3 && ok; ++br) {
+        if (ntiles(im, br) == 0) continue;
+        int lo, hi;
+        bounds(br, qi, row_ok, lo, hi);
+        float m_used = -INFINITY, l = 0.f;
+        const float sl2 = p.scale_log2[br];
+#pragma unroll 1
+        for (int t = 0; t < ntiles(im, br) && ok; ++t, ++it) {
+          const Tile tl = get_tile(im, lp, br, t);
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(B_SFULL + X), it & 1, &abort_flag));
+          if (!ok) { fail_id = B_SFULL + X + 1; break; }
+          tc_fence_after();
+          uint32_t sv[4][32];
+          tmem_ld32(tS, sv[0]);
+          tmem_ld32(tS + 32, sv[1]);
+          if (tl.nch == 2) { tmem_ld32(tS + 64, sv[2]); tmem_ld32(tS + 96, sv[3]); }
+          tc_wait_ld();
+          if constexpr (EARLY) {
+            tc_fence_before();
+            mbar_arrive(bar(B_SREAD + X));
+          }
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int vlo = max(lo - tl.j0[c], 0);
+            const int vhi = (c < tl.nch && ((tl.mask[c] >> rg) & 1)) ? min(hi, tl.jlim[c] - 1) - tl.j0[c] : -1;
+            if (c < tl.nch && (vlo > 0 || vhi < 63)) {
+#pragma unroll
+              for (int g = 0; g < 2; ++g)
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (g * 32 + i < vlo || g * 32 + i > vhi) sv[2 * c + g][i] = 0xff800000u;
+            }
+          }
+          float mxa[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) mxa[i] = -INFINITY;
+#pragma unroll
+          for (int g = 0; g < 2; ++g)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mxa[i & 7] = fmaxf(mxa[i & 7], __uint_as_float(sv[g][i]));
+          if (tl.nch == 2) {
+#pragma unroll
+            for (int g = 2; g < 4; ++g)
+#pragma unroll
+              for (int i = 0; i < 32; ++i) mxa[i & 7] = fmaxf(mxa[i & 7], __uint_as_float(sv[g][i]));
+          }
+          float mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])), fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
+          mx *= p.scale_log2[br];
+          const bool grow = mx > m_used + 8.f;
+          if (__any_sync(0xffffffffu, grow)) {
+            const float m_new = fmaxf(m_used, mx);
+            const float alpha = m_new == -INFINITY ? 1.f : ex2(m_used - m_new);
+            if (t > 0) {
+              ok = __all_sync(0xffffffffu, mbar_wait(bar(B_PVDONE + X), (it - 1) & 1, &abort_flag));
+              if (!ok) { fail_id = B_PVDONE + X + 1; break; }
+              tc_fence_after();
+              for (int g = 0; g < D / 32; ++g) {
+                uint32_t v[32];
+                tmem_ld32(tO + g * 32, v);
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                tmem_st32(tO + g * 32, v);
+              }
+              tc_wait_st();
+            }
+            l *= alpha;
+            m_used = m_new;
+          }
+          const float m_ref = m_used == -INFINITY ? 0.f : m_used;
+          if constexpr (EARLY) {
+            if (it > 0) {
+              ok = __all_sync(0xffffffffu, mbar_wait(bar(B_PVDONE + X), (it - 1) & 1, &abort_flag));
+              if (!ok) { fail_id = B_PVDONE + X + 1; break; }
+              tc_fence_after();
+            }
+          }
+          float psum0 = 0.f, psum1 = 0.f, psum2 = 0.f, psum3 = 0.f;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (g < 2 * tl.nch) {
+              uint32_t pk[16];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const float p0 = ex2(fmaf(__uint_as_float(sv[g][2 * i]), sl2, -m_ref));
+                const float p1 = ex2(fmaf(__uint_as_float(sv[g][2 * i + 1]), sl2, -m_ref));
+                if (i & 1) { psum2 += p0; psum3 += p1; } else { psum0 += p0; psum1 += p1; }
+                pk[i] = Elem<T>::pack(p0, p1);
+              }
+              tmem_st16(tP + g * 16, pk);
+            }
+          }
+          psum0 += psum2;
+          psum1 += psum3;
+          l += psum0 + psum1;
+          tc_wait_st();
+          tc_fence_before();
+          mbar_arrive(bar(B_PFULL + X));
+        }
+        if (!ok) break;
+        // ---- end of the branch ----
+        uint4 prevv[D / 8];
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c)
+          prevv[c] = (have_partial && row_ok) ? reinterpret_cast<const uint4*>(orow)[c] : make_uint4(0u, 0u, 0u, 0u);
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(B_PVDONE + X), (it - 1) & 1, &abort_flag));
+        if (!ok) { fail_id = B_PVDONE + X + 1; break; }
+        tc_fence_after();
+        const bool has = l > 0.f;
+        const float coef = has ? (a.fused ? gate[br] : 1.f) * p.out_scale[br] / l : 0.f;
+        if (a.lse != nullptr) lse_out = has ? m_used * kLn2 + __logf(l) : -INFINITY;
+#pragma unroll
+        for (int g = 0; g < D / 32; ++g) {
+          uint32_t v[32];
+          tmem_ld32(tO + g * 32, v);
+          tc_wait_ld();
+          if (row_ok) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const uint4 prev = prevv[g * 4 + c];
+              const uint32_t pw[4] = {prev.x, prev.y, prev.z, prev.w};
+              uint32_t w[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 acc = Elem<T>::unpack(pw[e]);
+                w[e] = Elem<T>::pack(fmaf(__uint_as_float(v[8 * c + 2 * e]), coef, acc.x),
+                                     fmaf(__uint_as_float(v[8 * c + 2 * e + 1]), coef, acc.y));
+              }
+              reinterpret_cast<uint4*>(orow)[g * 4 + c] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+        }
+        have_partial = true;
+        tc_fence_before();
+      }
+      if (!ok) break;
+      if (row_ok) {
+        if (!have_partial) {
+#pragma unroll
+          for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(orow)[c] = make_uint4(0u, 0u, 0u, 0u);
+        }
+        if (a.lse != nullptr) a.lse[row_index] = lse_out;
+      }
+      if (lane == 0) mbar_arrive(bar(PB_LISTEMPTY + lp));      // this warp is done with the item's block list
+      __syncwarp();
+    }
+  }
+
+  // ---- teardown ----
+  if (fail_id != 0) atomicCAS(&g_tc5_status, 0, fail_id);
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag && warp == 0 && lane == 0) {
+    if (q_loads > 0)
+      for (int i = 0; i < 20000 && !mbar_try_wait(bar(B_QFULL), (q_loads - 1) & 1); ++i) __nanosleep(100);
+    if (last_k_it >= 0)
+      for (int i = 0; i < 20000 && !mbar_try_wait(bar(B_KFULL + (last_k_it & 1)), (last_k_it >> 1) & 1); ++i) __nanosleep(100);
+    if (last_v_it >= 0)
+      for (int i = 0; i < 20000 && !mbar_try_wait(bar(B_VFULL + (last_v_it & 1)), (last_v_it >> 1) & 1); ++i) __nanosleep(100);
+  }
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
 // Merges the partial results of a split launch: per row and branch, the splits' (O_s, m_s, l_s) combine to
 // O = sum_s 2^(m_s - m) O_s / sum_s 2^(m_s - m) l_s with m = max_s m_s; the three branches are then added with
 // the row's gates, in fp32, and the row is rounded once.  One warp per row, D/32 columns per lane.
@@ -901,6 +1528,13 @@ bool attention_fwd_tc5_supports(const nsa_fwd_args& a) {
   return true;
 }
 
+// The persistent variant is the default for unsplit launches on 16-bit storage; NSA_TC5_PERSIST=0 in the environment
+// selects the one-item-per-block kernel (kept for the split and fp8 launches) for comparison.
+static bool tc5_persistent() {
+  static const bool on = [] { const char* e = getenv("NSA_TC5_PERSIST"); return !(e && e[0] == '0'); }();
+  return on;
+}
+
 int attention_fwd_tc5(const nsa_fwd_args& a, cudaStream_t st) {
   Tc5Params p;
   p.a = a;
@@ -980,6 +1614,26 @@ int attention_fwd_tc5(const nsa_fwd_args& a, cudaStream_t st) {
     else NSA_TC5_COMBINE(__half, 64);
 #undef NSA_TC5_COMBINE
     return launch_status("split_combine");
+  }
+  if (!in8 && tc5_persistent()) {
+    // one thread block per SM walking the items (see nsa_fwd_tc5_persist_kernel)
+    int dev = 0, sms = 0;
+    NSA_CUDA_OK(cudaGetDevice(&dev));
+    NSA_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const unsigned grid = (unsigned)(blocks < sms ? blocks : sms);
+    const size_t smem_p = (size_t)(2 + 2 + 2) * (a.D / 64) * 128 * 128 + 1024;
+#define NSA_TC5_PERSIST_LAUNCH(DD, FF)                                                                     \
+  {                                                                                                         \
+    auto fn = nsa_fwd_tc5_persist_kernel<DD, FF>;                                                           \
+    NSA_CUDA_OK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_p));       \
+    fn<<<grid, T5_THREADS, smem_p, st>>>(p, (int)blocks);                                                  \
+  }
+    if (a.D == 128 && fmt == 1) NSA_TC5_PERSIST_LAUNCH(128, 1)
+    else if (a.D == 128) NSA_TC5_PERSIST_LAUNCH(128, 0)
+    else if (fmt == 1) NSA_TC5_PERSIST_LAUNCH(64, 1)
+    else NSA_TC5_PERSIST_LAUNCH(64, 0)
+#undef NSA_TC5_PERSIST_LAUNCH
+    return launch_status("attn_fwd_tc5 (persistent)");
   }
   if (in8 && a.D == 128) NSA_TC5_LAUNCH(128, 1, true, false)
   else if (in8) NSA_TC5_LAUNCH(64, 1, true, false)
