@@ -67,6 +67,14 @@ int nsa_abi_version(void);
 int nsa_pool_mean(const void* x, void* out, int B, int H, int T, int D, int block, int stride,
                   int n_out, int dtype, float dequant_scale, nsa_stream_t stream);
 
+/* Learned pooling: out[b,h,c,:] = sum_s x[b,h,c*stride+s,:] * w[s,:] over the `block` rows of window c (rows past
+ * the end count as zero, which is what the reference's zero padding gives); w [block, D] fp32, 16-byte aligned;
+ * fp32 sum in row order, one rounding to the 16-bit type of x.  n_out as for nsa_pool_mean.
+ * Replaces: torch.einsum("bhnsd,sd->bhnd", K_blocks, pool_proj_k), nsa/reference.py:109-113 (the reference's
+ * kernels refuse pool="learned", nsa/triton/compressed.py:219-220; only its plain-torch path has it). */
+int nsa_pool_learned(const void* x, const float* w, void* out, int B, int H, int T, int D, int block, int stride,
+                     int n_out, int dtype, nsa_stream_t stream);
+
 /* Block scoring + causal legality + top-k in one kernel.
  *   Qb [B,H,nq,D], Kb [B,Hkv,nk,D]: block means (nsa_pool_mean), 16-bit.
  *   idx [B,H,nq,k_out] int32, k_out = min(top_k, nk), ordered by descending score,

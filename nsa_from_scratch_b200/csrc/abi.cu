@@ -18,6 +18,7 @@ int fail(int code, const char* fmt, ...) {
 
 // kernels (other translation units)
 int pool_mean(const void*, void*, int, int, int, int, int, int, int, int, float, cudaStream_t);
+int pool_weighted(const void*, const float*, void*, int, int, int, int, int, int, int, int, cudaStream_t);
 int select_blocks(const void*, const void*, int32_t*, int, int, int, int, int, int, int, int, int, int, int, float, int,
                   int, int, int, const int32_t*, cudaStream_t);
 int topk_from_scores(const float*, int32_t*, int, int, int, int, int, int, int, int, cudaStream_t);
@@ -106,6 +107,12 @@ int nsa_pool_mean(const void* x, void* out, int B, int H, int T, int D, int bloc
                   float dequant_scale, nsa_stream_t stream) {
   NSA_REQUIRE(x && out, NSA_ERR_ARG, "pool: NULL pointer");
   return pool_mean(x, out, B, H, T, D, block, stride, n_out, dtype, dequant_scale, (cudaStream_t)stream);
+}
+
+int nsa_pool_learned(const void* x, const float* w, void* out, int B, int H, int T, int D, int block, int stride, int n_out,
+                     int dtype, nsa_stream_t stream) {
+  NSA_REQUIRE(x && w && out, NSA_ERR_ARG, "pool (learned): NULL pointer");
+  return pool_weighted(x, w, out, B, H, T, D, block, stride, n_out, dtype, (cudaStream_t)stream);
 }
 
 int nsa_select_blocks(const void* Qb, const void* Kb, int32_t* idx, int B, int H, int Hkv, int nq, int nk, int D,

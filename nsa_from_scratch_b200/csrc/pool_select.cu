@@ -47,6 +47,56 @@ __global__ void __launch_bounds__(256) pool_mean_kernel(const void* __restrict__
   *reinterpret_cast<uint4*>(q) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// Learned pooling: out[c, d] = sum_s x[c*stride + s, d] * w[s, d] over the `block` rows of the window (rows past the
+// end of the sequence count as zero), fp32 sum in row order, one rounding to the 16-bit type.
+template <typename T>
+__global__ void __launch_bounds__(256) pool_weighted_kernel(const T* __restrict__ x, const float* __restrict__ wgt, T* __restrict__ out,
+                                                            int Tlen, int D, int block, int stride, int n_out) {
+  const int CH = D / 8;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_out * CH) return;
+  const int c = i / CH, ch = i % CH;
+  const size_t slab = (size_t)blockIdx.y * Tlen * D;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  const int r0 = c * stride;
+  const int r1 = min(r0 + block, Tlen);
+  for (int r = r0; r < r1; ++r) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(x + slab + (size_t)r * D + ch * 8);
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
+    const float4 g0 = *reinterpret_cast<const float4*>(wgt + (size_t)(r - r0) * D + ch * 8);
+    const float4 g1 = *reinterpret_cast<const float4*>(wgt + (size_t)(r - r0) * D + ch * 8 + 4);
+    const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = Elem<T>::unpack(w[e]);
+      acc[2 * e] = fmaf(f.x, g[2 * e], acc[2 * e]);
+      acc[2 * e + 1] = fmaf(f.y, g[2 * e + 1], acc[2 * e + 1]);
+    }
+  }
+  uint32_t w[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) w[e] = Elem<T>::pack(acc[2 * e], acc[2 * e + 1]);
+  *reinterpret_cast<uint4*>(out + ((size_t)blockIdx.y * n_out + c) * D + ch * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+int pool_weighted(const void* x, const float* w, void* out, int B, int H, int T, int D, int block, int stride, int n_out, int dtype,
+                  cudaStream_t st) {
+  NSA_REQUIRE(D % 8 == 0 && D > 0, NSA_ERR_ARG, "pool: D %d must be a positive multiple of 8", D);
+  NSA_REQUIRE(block > 0 && stride > 0 && stride <= block, NSA_ERR_ARG, "pool: need 0 < stride <= block (%d, %d)", stride, block);
+  const int expect = stride == block ? (T + block - 1) / block : (T >= block ? (T - block) / stride + 1 : 0);
+  NSA_REQUIRE(n_out == expect, NSA_ERR_ARG, "pool: n_out %d, expected %d", n_out, expect);
+  NSA_REQUIRE((reinterpret_cast<uintptr_t>(w) & 15) == 0, NSA_ERR_ARG, "pool: weights must be 16-byte aligned");
+  if (n_out == 0 || B * H == 0) return NSA_OK;
+  NSA_REQUIRE((long long)B * H <= 65535, NSA_ERR_ARG, "pool: B*H %lld too large", (long long)B * H);
+  dim3 grid((unsigned)(((long long)n_out * (D / 8) + 255) / 256), (unsigned)(B * H));
+  switch (dtype) {
+    case NSA_BF16: pool_weighted_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, w, (__nv_bfloat16*)out, T, D, block, stride, n_out); break;
+    case NSA_FP16: pool_weighted_kernel<__half><<<grid, 256, 0, st>>>((const __half*)x, w, (__half*)out, T, D, block, stride, n_out); break;
+    default: return fail(NSA_ERR_UNSUPPORTED, "pool (learned): dtype %d", dtype);
+  }
+  return launch_status("pool_weighted");
+}
+
 int pool_mean(const void* x, void* out, int B, int H, int T, int D, int block, int stride, int n_out, int dtype,
               float dq, cudaStream_t st) {
   NSA_REQUIRE(D % 8 == 0 && D > 0, NSA_ERR_ARG, "pool: D %d must be a positive multiple of 8", D);

@@ -144,7 +144,8 @@ def _cfg(cfg, name, default):
 
 
 def nsa_forward(Q: Tensor, K: Tensor, V: Tensor, cfg, *, gate_logits: Optional[Tensor] = None,
-                block_indices: Optional[Tensor] = None) -> Tensor:
+                block_indices: Optional[Tensor] = None, pool_proj_k: Optional[Tensor] = None,
+                pool_proj_v: Optional[Tensor] = None) -> Tensor:
     """NSA combined forward.  Q [B,H,Tq,D], K/V [B,H|Hkv,Tk,D] fp16/bf16; `cfg` is any object with
     the reference's NSAConfig fields (optional extras: stride_c, force_first, force_local);
     gate_logits [B,H,Tq,3] (None = zero logits); block_indices [B,H|Hkv,nq,k] int32 (None =
@@ -155,8 +156,11 @@ def nsa_forward(Q: Tensor, K: Tensor, V: Tensor, cfg, *, gate_logits: Optional[T
     assert Q.dtype in (torch.float16, torch.bfloat16), "Q must be fp16 or bf16"
     D = Q.shape[-1]
     scale = cfg.scale if cfg.scale is not None else 1.0 / (D ** 0.5)
-    if cfg.pool != "mean":
-        raise NotImplementedError("nsa_forward: only pool='mean' supported")
+    learned = cfg.pool == "learned"
+    if cfg.pool not in ("mean", "learned"):
+        raise ValueError(f"unknown pool: {cfg.pool}")
+    if learned and (pool_proj_k is None or pool_proj_v is None):
+        raise ValueError("nsa_forward: pool='learned' needs pool_proj_k and pool_proj_v ([block_size_c, D], nsa/reference.py:295-296)")
     stride_c = getattr(cfg, "stride_c", None)
     ff, fl = _cfg(cfg, "force_first", 0), _cfg(cfg, "force_local", 0)
     if block_indices is None and _cfg(cfg, "scorer", "mean") == "compressed":
@@ -173,6 +177,8 @@ def nsa_forward(Q: Tensor, K: Tensor, V: Tensor, cfg, *, gate_logits: Optional[T
                                                shared_per_group=bool(_cfg(cfg, "select_per_group", False)))
     needs_grad = torch.is_grad_enabled() and any(
         t is not None and t.requires_grad for t in (Q, K, V, gate_logits))
+    if needs_grad and learned:
+        raise NotImplementedError("nsa_forward: pool='learned' is forward-only here (no gradient kernels for the pooling weights)")
     if needs_grad:
         out_c = _CompressedFn.apply(Q, K, V, cfg.block_size_c, cfg.pool, cfg.causal, cfg.scale, stride_c)
         out_s = _SelectedFn.apply(Q, K, V, cfg.block_size_n, cfg.block_size_m, cfg.top_k, block_indices,
@@ -183,15 +189,20 @@ def nsa_forward(Q: Tensor, K: Tensor, V: Tensor, cfg, *, gate_logits: Optional[T
             gate_logits = Q.new_full((B, H, Tq, 3), 0.0)
         out = _CombineFn.apply(out_c, out_s, out_w, gate_logits, cfg.gate_activation)
         return out if out.dtype == Q.dtype else out.to(Q.dtype)     # fp32 gate logits: same dtype as the fused route
-    return _fused_forward(Q, K, V, cfg, float(scale), stride_c, gate_logits, block_indices, 1.0, 1.0, 1.0)
+    return _fused_forward(Q, K, V, cfg, float(scale), stride_c, gate_logits, block_indices, 1.0, 1.0, 1.0,
+                          pool_proj=(pool_proj_k, pool_proj_v) if learned else None)
 
 
 def _fused_forward(Q, K, V, cfg, scale, stride_c, gate_logits, block_indices, sq, sk, sv, engine=None,
-                   token_major=False):
+                   token_major=False, pool_proj=None):
     bc = cfg.block_size_c
     stride = bc if stride_c is None else int(stride_c)
-    Kc = ops.pool_mean(K, bc, stride, dequant_scale=sk)
-    Vc = ops.pool_mean(V, bc, stride, dequant_scale=sv)
+    if pool_proj is not None:
+        Kc = ops.pool_learned(K, pool_proj[0], bc, stride)
+        Vc = ops.pool_learned(V, pool_proj[1], bc, stride)
+    else:
+        Kc = ops.pool_mean(K, bc, stride, dequant_scale=sk)
+        Vc = ops.pool_mean(V, bc, stride, dequant_scale=sv)
     Tq, Tk = Q.shape[2], K.shape[2]
     Tk_pad = Kc.shape[2] * bc if stride == bc else Tk
     if cfg.gate_activation not in ("sigmoid", "softmax"):

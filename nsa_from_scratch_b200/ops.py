@@ -105,6 +105,23 @@ def pool_mean(x: Tensor, block: int, stride: Optional[int] = None, dequant_scale
     return out
 
 
+def pool_learned(x: Tensor, w: Tensor, block: int, stride: Optional[int] = None) -> Tensor:
+    """[B,H,T,D] 16-bit, w [block, D] -> [B,H,n,D]: window c is sum_s x[c*stride+s] * w[s] (fp32 sum, one rounding)."""
+    _need_cuda(x, w)
+    B, H, T, D = x.shape
+    stride = block if stride is None else stride
+    if w.shape != (block, D):
+        raise ValueError(f"pool_learned: weights must be [{block}, {D}], got {tuple(w.shape)}")
+    n = n_pooled(T, block, stride)
+    x = _dense(x, "x")
+    w = w.detach().to(torch.float32).contiguous()
+    out = torch.empty((B, H, n, D), device=x.device, dtype=x.dtype)
+    with torch.cuda.device(x.device):
+        L.check(L.load().nsa_pool_learned(x.data_ptr(), w.data_ptr(), out.data_ptr(), B, H, T, D, block, stride, n,
+                                          L.dtype_code(x.dtype), L.stream_ptr()), "nsa_pool_learned")
+    return out
+
+
 def select_blocks_from_means(Qb: Tensor, Kb: Tensor, *, top_k: int, bm: int, bn: int, offset: int, causal: bool,
                              scale: float, force_first: int = 0, force_local: int = 0,
                              shared_per_group: bool = False) -> Tensor:

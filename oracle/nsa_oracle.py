@@ -119,6 +119,21 @@ def pool_mean(x: Tensor, block: int, stride: Optional[int] = None) -> Tensor:
     return (acc / float(block)).to(x.dtype)
 
 
+def pool_learned(x: Tensor, proj: Tensor, block: int, stride: Optional[int] = None) -> Tensor:
+    """fp32 [B,H,n,D]: window c = sum_s x[c*stride+s] * proj[s] (reference.py:109-113: zero padding to a multiple of
+    the block, then einsum("bhnsd,sd->bhnd") over the block's rows); stride < block: whole windows only."""
+    stride = block if stride is None else stride
+    B, H, T, D = x.shape
+    xf = x.float()
+    if stride == block:
+        n = (T + block - 1) // block
+        xf = torch.nn.functional.pad(xf, (0, 0, 0, n * block - T))
+        win = xf.view(B, H, n, block, D)
+    else:
+        win = xf.unfold(2, block, stride).permute(0, 1, 2, 4, 3) if T >= block else xf.new_zeros((B, H, 0, block, D))
+    return torch.einsum("bhnsd,sd->bhnd", win, proj.float())
+
+
 def n_pooled(T: int, block: int, stride: Optional[int] = None) -> int:
     stride = block if stride is None else stride
     if stride == block:
@@ -134,8 +149,10 @@ def compressed_attention(
     Q: Tensor, K: Tensor, V: Tensor, *, block_size_c: int = 64,
     stride_c: Optional[int] = None, causal: bool = True,
     scale: Optional[float] = None, rows: Optional[Tuple[int, int]] = None,
+    pool_proj_k: Optional[Tensor] = None, pool_proj_v: Optional[Tensor] = None,
 ) -> Tuple[Tensor, Tensor]:
-    """Attention of Q over mean-pooled K/V (reference.py:71-134).
+    """Attention of Q over mean-pooled K/V (reference.py:71-134); with pool_proj_k / pool_proj_v
+    [block_size_c, D] over learned-pooled K/V, sum_s K[c*stride+s] * proj[s] (reference.py:109-113).
 
     Causal rule (reference.py:122-126 with stride == block): pooled token c is
     visible to query row i iff its window ends at or before the query's key
@@ -149,8 +166,12 @@ def compressed_attention(
     Hkv, Tk = K.shape[1], K.shape[2]
     G = _group(H, Hkv)
     stride = block_size_c if stride_c is None else stride_c
-    Kc = pool_mean(K, block_size_c, stride).float()
-    Vc = pool_mean(V, block_size_c, stride).float()
+    if pool_proj_k is not None:
+        Kc = pool_learned(K, pool_proj_k, block_size_c, stride)
+        Vc = pool_learned(V, pool_proj_v, block_size_c, stride)
+    else:
+        Kc = pool_mean(K, block_size_c, stride).float()
+        Vc = pool_mean(V, block_size_c, stride).float()
     Nc = Kc.shape[2]
     Tk_pad = Nc * block_size_c if stride == block_size_c else Tk
     s = _softmax_scale(D, scale)
