@@ -75,6 +75,18 @@ int nsa_pool_mean(const void* x, void* out, int B, int H, int T, int D, int bloc
 int nsa_pool_learned(const void* x, const float* w, void* out, int B, int H, int T, int D, int block, int stride,
                      int n_out, int dtype, nsa_stream_t stream);
 
+/* MoBA routing as a producer of block lists: every query TOKEN takes its top_k_per_query (<= 64) key blocks by
+ * q . Kb[block] * scale (Kb [B,Hkv,nk,D]: key block means from nsa_pool_mean; block n legal for row i iff
+ * !causal or n*bn <= i + offset, offset from the lengths padded to the block sizes); query block qb lists the union
+ * of its bm rows' picks (rows past Tq count as zero rows, as in the padded tensor) in ascending order, padded with
+ * the out-of-range id nk up to `cap` slots; a union larger than cap keeps the cap blocks with the best block-level
+ * score (max over the rows), best first.  Ties resolve to the lowest block id; a row with fewer legal blocks than
+ * picks contributes its legal ones only.  idx [B,H,nq,cap] int32, fed to the selected branch as block_indices.
+ * Replaces: _per_query_top_k_indices, nsa/triton/moba.py:18-92. */
+int nsa_moba_block_indices(const void* Q, const void* Kb, int32_t* idx, int B, int H, int Hkv, int Tq, int nq, int nk,
+                           int D, int top_k_per_query, int cap, int bm, int bn, int offset, int causal, float scale,
+                           int dtype, nsa_stream_t stream);
+
 /* Block scoring + causal legality + top-k in one kernel.
  *   Qb [B,H,nq,D], Kb [B,Hkv,nk,D]: block means (nsa_pool_mean), 16-bit.
  *   idx [B,H,nq,k_out] int32, k_out = min(top_k, nk), ordered by descending score,

@@ -18,10 +18,12 @@ from .layer import NSAAttention, nsa_attention_token_major, rope_cache
 from .graph import GraphedForward
 from .decode import KVCache, nsa_decode, GraphedDecoder
 from .scoring import compressed_block_scores, select_blocks_compressed
+from .moba import moba_attention
 
 __all__ = [
     "NSAConfig", "compressed_attention", "selected_attention", "sliding_attention", "combine", "nsa_forward",
     "nsa_forward_fp8", "nsa_forward_host", "selected_backward", "quantize_to_fp8", "selected_attention_fp8",
     "selected_attention_cuda", "selected_backward_cuda", "NSAAttention", "nsa_attention_token_major", "rope_cache",
     "GraphedForward", "KVCache", "nsa_decode", "GraphedDecoder", "compressed_block_scores", "select_blocks_compressed",
+    "moba_attention",
 ]

@@ -79,6 +79,7 @@ PROTOTYPES = {
     "nsa_abi_version": (_i, []),
     "nsa_pool_mean": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "nsa_pool_learned": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "nsa_moba_block_indices": (_i, [_vp, _vp, _vp] + [_i] * 13 + [_f, _i, _vp]),
     "nsa_select_blocks": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp]),
     "nsa_cmp_block_scores": (_i, [_vp, _vp, _vp, _vp] + [_i] * 13 + [_f, _i, _i, _i, _i, _vp]),
     "nsa_cmp_block_scores_tc": (_i, [_vp, _vp, _vp, _vp, _vp] + [_i] * 13 + [_f, _i, _i, _i, _i, _vp]),

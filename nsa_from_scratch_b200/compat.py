@@ -1,5 +1,5 @@
 """Drop-in shim: after `install()`, the module names the reference's callers import
-(`nsa.triton.compressed|selected|sliding|gating|forward|backward|fp8`, `nsa.cuda`) resolve to
+(`nsa.triton.compressed|selected|sliding|gating|forward|backward|fp8|moba`, `nsa.cuda`) resolve to
 this package, so the reference's model, benchmarks and tests run on these kernels unchanged.
 `nsa.reference` (and everything else under `nsa`) still comes from the reference checkout
 when it is importable; otherwise a minimal `nsa.reference` with NSAConfig is provided."""
@@ -12,7 +12,7 @@ import types
 _MAP = {
     "nsa.triton.compressed": "compressed", "nsa.triton.selected": "selected", "nsa.triton.sliding": "sliding",
     "nsa.triton.gating": "gating", "nsa.triton.forward": "forward", "nsa.triton.backward": "backward",
-    "nsa.triton.fp8": "fp8", "nsa.cuda": "native",
+    "nsa.triton.fp8": "fp8", "nsa.triton.moba": "moba", "nsa.cuda": "native",
 }
 
 

@@ -18,6 +18,7 @@ int fail(int code, const char* fmt, ...) {
 
 // kernels (other translation units)
 int pool_mean(const void*, void*, int, int, int, int, int, int, int, int, float, cudaStream_t);
+int moba_route(const void*, const void*, int32_t*, int, int, int, int, int, int, int, int, int, int, int, int, int, float, int, cudaStream_t);
 int pool_weighted(const void*, const float*, void*, int, int, int, int, int, int, int, int, cudaStream_t);
 int select_blocks(const void*, const void*, int32_t*, int, int, int, int, int, int, int, int, int, int, int, float, int,
                   int, int, int, const int32_t*, cudaStream_t);
@@ -113,6 +114,14 @@ int nsa_pool_learned(const void* x, const float* w, void* out, int B, int H, int
                      int dtype, nsa_stream_t stream) {
   NSA_REQUIRE(x && w && out, NSA_ERR_ARG, "pool (learned): NULL pointer");
   return pool_weighted(x, w, out, B, H, T, D, block, stride, n_out, dtype, (cudaStream_t)stream);
+}
+
+int nsa_moba_block_indices(const void* Q, const void* Kb, int32_t* idx, int B, int H, int Hkv, int Tq, int nq, int nk, int D,
+                           int top_k_per_query, int cap, int bm, int bn, int offset, int causal, float scale, int dtype,
+                           nsa_stream_t stream) {
+  NSA_REQUIRE(Q && Kb && idx, NSA_ERR_ARG, "moba routing: NULL pointer");
+  return moba_route(Q, Kb, idx, B, H, Hkv, Tq, nq, nk, D, top_k_per_query, cap, bm, bn, offset, causal, scale, dtype,
+                    (cudaStream_t)stream);
 }
 
 int nsa_select_blocks(const void* Qb, const void* Kb, int32_t* idx, int B, int H, int Hkv, int nq, int nk, int D,

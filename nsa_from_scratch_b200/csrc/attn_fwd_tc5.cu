@@ -750,8 +750,8 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
 }
 
 // ---------------------------------------------------------------- persistent variant
-// The same arithmetic, one thread block per SM looping over work items (item = blockIdx.x, += gridDim.x; the items are
-// ordered long rows first, so a round-robin deal gives every block a like mix).  What a one-item block pays per item
+// The same arithmetic, one thread block per SM looping over work items (the items are ordered long rows first and dealt
+// out in alternating directions, so every block gets a like mix).  What a one-item block pays per item
 // -- barrier set-up, TMEM allocation, the list of selected blocks, the Q load and the first K tile before the first
 // MMA, and an idle tensor pipe during the last epilogue -- is overlapped with the neighbouring items instead:
 //   * warp 2 builds the NEXT item's block list into the other of two list buffers while the current item runs;
@@ -760,6 +760,11 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
 //   * warp 1 issues the next item's first Q K^T while the softmax warps are still in the current item's last epilogue
 //     (its first P V is ordered behind that epilogue by the P-ready barrier, which the softmax warps reach only after it).
 // All barrier phases come from running counters (tiles, items) instead of per-item ones.  bf16/fp16 storage, unsplit.
+// Registers after setmaxnreg: 8 softmax warps x 216, the other four warps 72 each -- every warp runs the common teardown
+// code, which is compiled once for all roles, so no role may shrink below what that code uses (a version that cut the
+// idle warp to 24 registers hung a GPU run: the only unbounded wait in this kernel is a block-wide barrier that a
+// misbehaving warp never reaches).  The .inc calls take 8*48 = 384 registers per lane and the .dec calls release
+// 4*96 = 384: what the .inc calls take must have been released by the same block, or they block forever.
 enum { PB_LISTFULL = B_COUNT, PB_LISTEMPTY = B_COUNT + 2, PB_QFREE = B_COUNT + 4, PB_COUNT = B_COUNT + 5 };
 
 template <int D, int FMT>
@@ -791,6 +796,9 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_persist_kernel(const __gri
   const int G = a.H / a.Hkv;
   const int GH = p.GH, NQB = 4 / p.GH;
   const int per_q = a.B * a.Hkv * p.HG;
+  // The k-th item of this block.  Items are ordered long rows first; dealing them out in alternating directions (block
+  // j takes the j-th of an even round and the j-th from the end of an odd one) keeps the blocks' totals level.
+  auto item_of = [&](int k) { return k * (int)gridDim.x + ((k & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x); };
 
   // a work item's coordinates (see nsa_fwd_tc5_kernel) and, once its block list is there, its tile counts
   struct Item {
@@ -890,7 +898,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_persist_kernel(const __gri
     __syncwarp();
     int it = 0, k = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++k) {
+    for (int item = item_of(0); item < n_items && ok; item = item_of(++k)) {
       const int lp = k & 1;
       Item im = coords(item);
       ok = __all_sync(0xffffffffu, mbar_wait(bar(PB_LISTFULL + lp), (k >> 1) & 1, &abort_flag));
@@ -960,8 +968,9 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_persist_kernel(const __gri
     // The issuer walks two cursors over the flattened (item, branch, tile) sequence: q = the tile whose Q K^T is
     // issued next, v = the tile whose P V is issued next; q is one tile ahead of v and crosses into the next item
     // first.  Items without a tile are skipped (nothing is loaded or issued for them).
-    struct Cur { int item, k, br, t, it, live, nch[3]; bool valid; };
-    auto nt = [](const Cur& c, int br) { return (c.nch[br] + 1) >> 1; };
+    // (scalars only: the cursors are read between every two MMA issues, and an array indexed by the branch would put them
+    // in local memory)
+    struct Cur { int item, k, f, ntot, it, live, c0, c1, c2, n0, n01; bool valid; };
     auto open_item = [&](Cur& c, int item, int kk) -> bool {      // positions c on the first tile of `item` or of the next item that has one
       c.item = item; c.k = kk; c.valid = false;
       while (c.item < n_items) {
@@ -969,19 +978,29 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_persist_kernel(const __gri
         if (!__all_sync(0xffffffffu, mbar_wait(bar(PB_LISTFULL + lp), (c.k >> 1) & 1, &abort_flag))) { fail_id = PB_LISTFULL + lp + 1; return false; }
         Item im = coords(c.item);
         counts(im, sel_n[lp]);
-        c.nch[0] = im.nchunks[0]; c.nch[1] = im.nchunks[1]; c.nch[2] = im.nchunks[2];
-        c.br = 0; c.t = 0;
-        while (c.br < 3 && c.t >= nt(c, c.br)) { ++c.br; c.t = 0; }
-        if (c.br < 3) { c.valid = true; ++c.live; return true; }
-        c.item += gridDim.x; ++c.k;
+        c.c0 = im.nchunks[0]; c.c1 = im.nchunks[1]; c.c2 = im.nchunks[2];
+        c.n0 = (c.c0 + 1) >> 1;
+        c.n01 = c.n0 + ((c.c1 + 1) >> 1);
+        c.ntot = c.n01 + ((c.c2 + 1) >> 1);
+        c.f = 0;
+        if (c.ntot > 0) { c.valid = true; ++c.live; return true; }
+        ++c.k; c.item = item_of(c.k);
       }
       return true;
     };
     auto advance = [&](Cur& c) -> bool {                           // next tile; crosses item boundaries
-      ++c.t; ++c.it;
-      while (c.br < 3 && c.t >= nt(c, c.br)) { ++c.br; c.t = 0; }
-      if (c.br < 3) return true;
-      return open_item(c, c.item + gridDim.x, c.k + 1);
+      ++c.f; ++c.it;
+      if (c.f < c.ntot) return true;
+      return open_item(c, item_of(c.k + 1), c.k + 1);
+    };
+    // chunks (1 or 2) of the cursor's tile, and whether it opens a branch
+    auto tile_of = [](const Cur& c, int& nch, bool& fresh) {
+      int t, cb;
+      if (c.f < c.n0) { t = c.f; cb = c.c0; }
+      else if (c.f < c.n01) { t = c.f - c.n0; cb = c.c1; }
+      else { t = c.f - c.n01; cb = c.c2; }
+      nch = min(2, cb - 2 * t);
+      fresh = t == 0;
     };
     auto release_lists = [&](int k0, int k1) {                     // this warp is done with the block lists of items k0..k1-1
       for (int kk = k0; kk < k1; ++kk)
@@ -990,7 +1009,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_persist_kernel(const __gri
     };
     Cur q;
     q.it = 0; q.live = 0;
-    ok = open_item(q, blockIdx.x, 0);
+    ok = open_item(q, item_of(0), 0);
     Cur v = q;
     if (ok) release_lists(0, v.k);                                 // leading items without a tile
     int q_ready = 0;                  // live items whose Q is known to have landed
@@ -1005,14 +1024,10 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_persist_kernel(const __gri
         if (!__all_sync(0xffffffffu, mbar_wait(bar(B_KFULL + s), (q.it >> 1) & 1, &abort_flag))) { fail_id = B_KFULL + s + 1; return false; }
         tc_fence_after();
       }
-      const int nch = min(2, q.nch[q.br] - 2 * q.t);
+      int nch; bool fr;
+      tile_of(q, nch, fr);
       const uint32_t idesc = nch == 2 ? IDESC_QK2 : IDESC_QK1;
-      bool last = false;                     // the item's last tile: its Q is free once these MMAs have read it
-      if (X == 1) {
-        int br2 = q.br, t2 = q.t + 1;
-        while (br2 < 3 && t2 >= nt(q, br2)) { ++br2; t2 = 0; }
-        last = br2 >= 3;
-      }
+      const bool last = X == 1 && q.f == q.ntot - 1;   // the item's last tile: its Q is free once these MMAs have read it
       if (leader) {
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
@@ -1034,8 +1049,8 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_persist_kernel(const __gri
     }
     while (ok && v.valid) {
       const int it = v.it;
-      const int nch = min(2, v.nch[v.br] - 2 * v.t);
-      const bool fresh = v.t == 0;                       // first tile of a branch starts a new O
+      int nch; bool fresh;                               // fresh: first tile of a branch starts a new O
+      tile_of(v, nch, fresh);
       const int s = it & 1;
       // Q K^T of the next tile is interleaved with this tile's P V -- unless it belongs to the next item: its Q arrives a
       // TMA round trip after this item's last Q K^T, and waiting for it here would hold up this item's last P V
@@ -1092,7 +1107,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_persist_kernel(const __gri
     // =============================== block-list builder ===============================
     int k = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++k) {
+    for (int item = item_of(0); item < n_items && ok; item = item_of(++k)) {
       const int lp = k & 1;
       const Item im = coords(item);
       ok = __all_sync(0xffffffffu, mbar_wait(bar(PB_LISTEMPTY + lp), ((k >> 1) & 1) ^ 1, &abort_flag));
@@ -1173,7 +1188,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_persist_kernel(const __gri
     int it = 0, k = 0;
     bool ok = true;
 #pragma unroll 1
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++k) {
+    for (int item = item_of(0); item < n_items && ok; item = item_of(++k)) {
       const int lp = k & 1;
       Item im = coords(item);
       const int head = grp_head(im, rg);
@@ -1181,28 +1196,26 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_persist_kernel(const __gri
       const bool row_ok = grp_qb(im, rg) < a.nq && qi < a.Tq;
       const size_t row_index = ((size_t)im.b * a.H + head) * a.Tq + qi;
       const size_t row_bthd = ((size_t)im.b * a.Tq + qi) * a.H + head;
-      float gate[3] = {0.5f, 0.5f, 0.5f};
-      if (a.fused) {
-        float x[3] = {0.f, 0.f, 0.f};
-        if (a.gates != nullptr && row_ok) {
+      // gate logits: the loads are issued here and first touched at a branch end, long after they have arrived
+      float gx[3] = {0.f, 0.f, 0.f};
+      if (a.fused && a.gates != nullptr && row_ok) {
 #pragma unroll
-          for (int c = 0; c < 3; ++c) {
-            const size_t gi = ((a.io_layout & NSA_IO_GATES_BTHD) ? row_bthd : row_index) * 3 + c;
-            x[c] = a.gate_dtype == NSA_FP32 ? reinterpret_cast<const float*>(a.gates)[gi]
-                 : a.gate_dtype == NSA_FP16 ? __half2float(reinterpret_cast<const __half*>(a.gates)[gi])
-                                            : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.gates)[gi]);
-          }
-        }
-        if (a.gate_act == NSA_GATE_SOFTMAX) {
-          float mx = fmaxf(x[0], fmaxf(x[1], x[2]));
-          float e0 = __expf(x[0] - mx), e1 = __expf(x[1] - mx), e2 = __expf(x[2] - mx);
-          float inv = 1.f / (e0 + e1 + e2);
-          gate[0] = e0 * inv; gate[1] = e1 * inv; gate[2] = e2 * inv;
-        } else {
-#pragma unroll
-          for (int c = 0; c < 3; ++c) gate[c] = 1.f / (1.f + __expf(-x[c]));
+        for (int c = 0; c < 3; ++c) {
+          const size_t gi = ((a.io_layout & NSA_IO_GATES_BTHD) ? row_bthd : row_index) * 3 + c;
+          gx[c] = a.gate_dtype == NSA_FP32 ? reinterpret_cast<const float*>(a.gates)[gi]
+                : a.gate_dtype == NSA_FP16 ? __half2float(reinterpret_cast<const __half*>(a.gates)[gi])
+                                           : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.gates)[gi]);
         }
       }
+      auto gate_of = [&](int br) {
+        if (a.gate_act == NSA_GATE_SOFTMAX) {
+          const float mx = fmaxf(gx[0], fmaxf(gx[1], gx[2]));
+          const float e0 = __expf(gx[0] - mx), e1 = __expf(gx[1] - mx), e2 = __expf(gx[2] - mx);
+          return (br == 0 ? e0 : br == 1 ? e1 : e2) / (e0 + e1 + e2);
+        }
+        const float x = br == 0 ? gx[0] : br == 1 ? gx[1] : gx[2];
+        return 1.f / (1.f + __expf(-x));
+      };
       float lse_out = -INFINITY;
       bool have_partial = a.accumulate != 0;
       T* orow = reinterpret_cast<T*>(a.out) + ((a.io_layout & NSA_IO_OUT_BTHD) ? row_bthd : row_index) * D;
@@ -1320,7 +1333,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_persist_kernel(const __gri
         if (!ok) { fail_id = B_PVDONE + X + 1; break; }
         tc_fence_after();
         const bool has = l > 0.f;
-        const float coef = has ? (a.fused ? gate[br] : 1.f) * p.out_scale[br] / l : 0.f;
+        const float coef = has ? (a.fused ? gate_of(br) : 1.f) * p.out_scale[br] / l : 0.f;
         if (a.lse != nullptr) lse_out = has ? m_used * kLn2 + __logf(l) : -INFINITY;
 #pragma unroll
         for (int g = 0; g < D / 32; ++g) {
@@ -1528,11 +1541,14 @@ bool attention_fwd_tc5_supports(const nsa_fwd_args& a) {
   return true;
 }
 
-// The persistent variant is the default for unsplit launches on 16-bit storage; NSA_TC5_PERSIST=0 in the environment
-// selects the one-item-per-block kernel (kept for the split and fp8 launches) for comparison.
-static bool tc5_persistent() {
-  static const bool on = [] { const char* e = getenv("NSA_TC5_PERSIST"); return !(e && e[0] == '0'); }();
-  return on;
+// The persistent variant runs the unsplit launches of ONE branch on 16-bit storage (the forward of the autograd route:
+// measured 2-7 % faster there, T=65536, Hq=64, Hkv=4, D=128: compressed 4.53 against 4.61 ms, selected 2.63 against
+// 2.72, sliding 1.93 against 2.02); launches of several branches are 1-4 % slower on it than on the one-item kernel
+// (all three: 8.91-9.25 against 8.54-8.89 ms on the same box) and stay there, as do the split and fp8 launches.
+// NSA_TC5_PERSIST=0 / =1 in the environment forces the one-item / the persistent kernel for every unsplit 16-bit launch.
+static int tc5_persistent_mode() {
+  static const int mode = [] { const char* e = getenv("NSA_TC5_PERSIST"); return !e ? -1 : (e[0] == '0' ? 0 : 1); }();
+  return mode;
 }
 
 int attention_fwd_tc5(const nsa_fwd_args& a, cudaStream_t st) {
@@ -1615,7 +1631,8 @@ int attention_fwd_tc5(const nsa_fwd_args& a, cudaStream_t st) {
 #undef NSA_TC5_COMBINE
     return launch_status("split_combine");
   }
-  if (!in8 && tc5_persistent()) {
+  const int n_br = ((a.branches >> 0) & 1) + ((a.branches >> 1) & 1) + ((a.branches >> 2) & 1);
+  if (!in8 && (tc5_persistent_mode() == 1 || (tc5_persistent_mode() == -1 && n_br == 1))) {
     // one thread block per SM walking the items (see nsa_fwd_tc5_persist_kernel)
     int dev = 0, sms = 0;
     NSA_CUDA_OK(cudaGetDevice(&dev));

@@ -296,6 +296,125 @@ __device__ void warp_topk_row(float* s, int n_scan, int nk, int k_out, int32_t* 
 // score of the group is the dot of that sum with the K block mean -- GS times less work than summing
 // per-head dots, and the definition the CPU oracle restates).
 // Kb tiles of 64 block-means are staged in shared memory once per chunk and shared by the rows.
+// ------------------------------------------------------------------ MoBA routing
+// A second producer of block lists: every query TOKEN picks its top_kq key blocks by q . mean(K block) * scale;
+// a query block lists the union of its rows' picks.  One thread block per (query block, batch*head), one warp per
+// row at a time: lane = key block, fp32 fma over D in index order against the block means (L1/L2 resident), the row's
+// scores in shared memory, picks by the same warp arg-max rounds as the other selections (ties -> lowest id).  The
+// union is a bit set; the best score any row gave a block (for the overflow rule) an order-preserving integer max.
+template <typename T>
+__global__ void __launch_bounds__(256) moba_route_kernel(const T* __restrict__ Q, const T* __restrict__ Kb, int32_t* __restrict__ idx,
+                                                         int H, int Hkv, int Tq, int nq, int nk, int D, int kq, int cap, int bm, int bn,
+                                                         int offset, int causal, float scale) {
+  extern __shared__ unsigned char moba_smem[];
+  const int nkp = (nk + 31) & ~31;
+  float* sc = reinterpret_cast<float*>(moba_smem);                  // [8][nkp] one score row per warp
+  uint32_t* level = reinterpret_cast<uint32_t*>(sc + 8 * nkp);       // [nkp] order keys of the block-level maxima
+  uint32_t* bits = level + nkp;                                      // [nkp/32] union of the picks
+  int32_t* picks = reinterpret_cast<int32_t*>(bits + nkp / 32);      // [8][64]
+  float* qrow = reinterpret_cast<float*>(picks + 8 * 64);            // [8][D]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qb = blockIdx.x, bh = blockIdx.y;
+  const int b = bh / H, h = bh % H;
+  const int hk = h / (H / Hkv);
+  const T* Kh = Kb + ((size_t)b * Hkv + hk) * nk * D;
+  for (int i = threadIdx.x; i < nkp; i += 256) level[i] = 0u;
+  for (int i = threadIdx.x; i < nkp / 32; i += 256) bits[i] = 0u;
+  __syncthreads();
+  float* my = sc + warp * nkp;
+  float* myq = qrow + warp * D;
+  for (int r = warp; r < bm; r += 8) {
+    const int row = qb * bm + r;
+    // the query row as fp32 (rows past the end are the zero rows of the padded tensor)
+    for (int d = lane; d < D; d += 32) myq[d] = row < Tq ? Elem<T>::to_f(Q[((size_t)bh * Tq + row) * D + d]) : 0.f;
+    __syncwarp();
+    int n_legal = nk;
+    if (causal) {
+      const long long lim = (long long)row + offset;
+      n_legal = lim < 0 ? 0 : (int)min((long long)nk, lim / bn + 1);
+    }
+    for (int n = lane; n < n_legal; n += 32) {
+      const T* kr = Kh + (size_t)n * D;
+      float acc = 0.f;
+      for (int d8 = 0; d8 < D; d8 += 8) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(kr + d8);
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = Elem<T>::unpack(w[e]);
+          acc = fmaf(myq[d8 + 2 * e], f.x, acc);
+          acc = fmaf(myq[d8 + 2 * e + 1], f.y, acc);
+        }
+      }
+      const float v = acc * scale;
+      my[n] = v;
+      atomicMax(&level[n], order_key(v));
+    }
+    __syncwarp();
+    const int n_pick = min(kq, n_legal);
+    if (n_pick > 0) {
+      warp_topk_row(my, n_legal, nk, n_pick, picks + warp * 64, lane);
+      __syncwarp();
+      for (int i = lane; i < n_pick; i += 32) {
+        const int c = picks[warp * 64 + i];
+        if (c >= 0 && c < n_legal) atomicOr(&bits[c >> 5], 1u << (c & 31));
+      }
+    }
+    __syncwarp();
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  int32_t* out = idx + ((size_t)bh * nq + qb) * cap;
+  int total = 0;
+  for (int w0 = lane; w0 < nkp / 32; w0 += 32) total += __popc(bits[w0]);
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) total += __shfl_xor_sync(0xffffffffu, total, d);
+  if (total <= cap) {
+    // ascending ids, then the out-of-range id nk
+    int pos = 0;
+    for (int w0 = 0; w0 < nkp / 32; ++w0) {
+      const uint32_t word = bits[w0];
+      if ((word >> lane) & 1u) out[pos + __popc(word & ((1u << lane) - 1))] = w0 * 32 + lane;
+      pos += __popc(word);
+    }
+    for (int i = pos + lane; i < cap; i += 32) out[i] = nk;
+  } else {
+    // more distinct blocks than slots: keep the cap with the best block-level score, best first
+    float* lv = sc;
+    for (int n = lane; n < nk; n += 32) {
+      const uint32_t k = level[n];
+      const uint32_t u = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;         // inverse of order_key
+      lv[n] = ((bits[n >> 5] >> (n & 31)) & 1u) ? __uint_as_float(u) : -INFINITY;
+    }
+    __syncwarp();
+    warp_topk_row(lv, nk, nk, cap, out, lane);
+  }
+}
+
+int moba_route(const void* Q, const void* Kb, int32_t* idx, int B, int H, int Hkv, int Tq, int nq, int nk, int D, int kq, int cap,
+               int bm, int bn, int offset, int causal, float scale, int dtype, cudaStream_t st) {
+  NSA_REQUIRE(B > 0 && H > 0 && Hkv > 0 && H % Hkv == 0 && Tq > 0 && nq == (Tq + bm - 1) / bm && nk > 0, NSA_ERR_ARG, "moba routing: sizes");
+  NSA_REQUIRE(D % 8 == 0 && D > 0 && bm > 0 && bn > 0, NSA_ERR_ARG, "moba routing: D %d must be a positive multiple of 8", D);
+  NSA_REQUIRE(kq >= 1 && kq <= 64, NSA_ERR_UNSUPPORTED, "moba routing: top_k_per_query %d not in [1, 64]", kq);
+  NSA_REQUIRE(cap >= 1 && cap <= nk, NSA_ERR_ARG, "moba routing: cap %d must be in [1, nk = %d]", cap, nk);
+  NSA_REQUIRE((long long)B * H <= 65535, NSA_ERR_ARG, "moba routing: B*H too large");
+  const int nkp = (nk + 31) & ~31;
+  const size_t smem = (size_t)8 * nkp * 4 + (size_t)nkp * 4 + nkp / 8 + 8 * 64 * 4 + (size_t)8 * D * 4;
+  NSA_REQUIRE(smem <= 200 * 1024, NSA_ERR_UNSUPPORTED, "moba routing: %d key blocks do not fit shared memory", nk);
+  dim3 grid((unsigned)nq, (unsigned)(B * H));
+#define NSA_MOBA(TT)                                                                                                   \
+  {                                                                                                                     \
+    auto fn = moba_route_kernel<TT>;                                                                                    \
+    NSA_CUDA_OK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                     \
+    fn<<<grid, 256, smem, st>>>((const TT*)Q, (const TT*)Kb, idx, H, Hkv, Tq, nq, nk, D, kq, cap, bm, bn, offset, causal, scale); \
+  }
+  if (dtype == NSA_BF16) NSA_MOBA(__nv_bfloat16)
+  else if (dtype == NSA_FP16) NSA_MOBA(__half)
+  else return fail(NSA_ERR_UNSUPPORTED, "moba routing: dtype %d", dtype);
+#undef NSA_MOBA
+  return launch_status("moba_route");
+}
+
 template <typename T, int D>
 __global__ void __launch_bounds__(256) select_blocks_kernel(const T* __restrict__ Qb, const T* __restrict__ Kb,
                                                             int32_t* __restrict__ idx, int H, int Hkv, int Hi, int nq, int nk,

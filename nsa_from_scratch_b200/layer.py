@@ -33,9 +33,11 @@ def rope_cache(seq_len: int, head_dim: int, base: float, device, dtype=torch.flo
 
 
 def nsa_attention_token_major(q: Tensor, k: Tensor, v: Tensor, cos: Optional[Tensor], sin: Optional[Tensor], cfg, *,
-                              gate_logits: Optional[Tensor] = None, dtype: torch.dtype = torch.bfloat16) -> Tensor:
+                              gate_logits: Optional[Tensor] = None, dtype: torch.dtype = torch.bfloat16,
+                              pool_proj_k: Optional[Tensor] = None, pool_proj_v: Optional[Tensor] = None) -> Tensor:
     """q [B,T,H,D], k/v [B,T,Hkv,D] as the projections leave them (fp32, bf16 or fp16), cos/sin [T,D]
-    (None: no rotary embedding), gate_logits [B,T,H,3] -> [B,T,H*D] in `dtype`.  Inference path (no autograd)."""
+    (None: no rotary embedding), gate_logits [B,T,H,3] -> [B,T,H*D] in `dtype`.  Inference path (no autograd).
+    pool_proj_k / pool_proj_v [block_size_c, D]: learned pooling (cfg.pool == "learned")."""
     B, T, H, D = q.shape
     qh = ops.rope_to_heads(q, cos, sin, dtype)
     kh = ops.rope_to_heads(k, cos, sin, dtype)
@@ -45,8 +47,11 @@ def nsa_attention_token_major(q: Tensor, k: Tensor, v: Tensor, cos: Optional[Ten
                                  causal=cfg.causal, scale=float(scale), force_first=_cfg(cfg, "force_first", 0),
                                  force_local=_cfg(cfg, "force_local", 0),
                                  shared_per_group=bool(_cfg(cfg, "select_per_group", False)))
+    learned = getattr(cfg, "pool", "mean") == "learned"
+    if learned and (pool_proj_k is None or pool_proj_v is None):
+        raise ValueError("pool='learned' needs pool_proj_k and pool_proj_v")
     out = _fused_forward(qh, kh, vh, cfg, float(scale), getattr(cfg, "stride_c", None), gate_logits, idx, 1.0, 1.0, 1.0,
-                         token_major=True)
+                         token_major=True, pool_proj=(pool_proj_k, pool_proj_v) if learned else None)
     return out.view(B, T, H * D)
 
 
@@ -61,8 +66,13 @@ class NSAAttention(nn.Module):
         self.n_heads, self.head_dim = n_heads, head_dim
         self.n_kv_heads = n_heads if n_kv_heads is None else n_kv_heads
         self.nsa_cfg = nsa_cfg
-        if getattr(nsa_cfg, "pool", "mean") != "mean":
-            raise NotImplementedError("NSAAttention: only pool='mean' is supported")
+        # learned compressed-pool projections, as the reference module creates them (nsa/model/llama_nsa.py:59-65);
+        # used by the inference route only -- training with pool="learned" is not provided
+        if getattr(nsa_cfg, "pool", "mean") == "learned":
+            self.pool_proj_k = nn.Parameter(torch.randn(int(nsa_cfg.block_size_c), head_dim) / head_dim ** 0.5)
+            self.pool_proj_v = nn.Parameter(torch.randn(int(nsa_cfg.block_size_c), head_dim) / head_dim ** 0.5)
+        else:
+            self.pool_proj_k = self.pool_proj_v = None
         self.q_proj = nn.Linear(hidden_size, n_heads * head_dim, bias=False)
         self.k_proj = nn.Linear(hidden_size, self.n_kv_heads * head_dim, bias=False)
         self.v_proj = nn.Linear(hidden_size, self.n_kv_heads * head_dim, bias=False)
@@ -77,7 +87,8 @@ class NSAAttention(nn.Module):
         v = self.v_proj(x).view(B, T, Hkv, D)
         gates = self.gate(x).view(B, T, H, 3)
         if not (torch.is_grad_enabled() and (x.requires_grad or any(p.requires_grad for p in self.parameters()))):
-            out = nsa_attention_token_major(q, k, v, cos, sin, self.nsa_cfg, gate_logits=gates).to(x.dtype)
+            out = nsa_attention_token_major(q, k, v, cos, sin, self.nsa_cfg, gate_logits=gates, pool_proj_k=self.pool_proj_k,
+                                            pool_proj_v=self.pool_proj_v).to(x.dtype)
             return self.o_proj(out)
         q, k, v = (t.transpose(1, 2) for t in (q, k, v))
         c, s = cos[None, None], sin[None, None]

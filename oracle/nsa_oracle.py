@@ -277,6 +277,49 @@ def select_blocks(Q: Tensor, K: Tensor, *, block_size_m: int = 64, block_size_n:
     return idx
 
 
+def moba_block_indices(Q: Tensor, K: Tensor, *, block_size_n: int = 64, block_size_m: int = 64,
+                       top_k_per_query: int = 16, top_k_cap: int = 64, causal: bool = True,
+                       scale: Optional[float] = None) -> Tensor:
+    """MoBA routing as a producer of block lists (nsa/triton/moba.py:18-92): every query TOKEN takes its
+    top_k_per_query key blocks by q . mean(K block) * scale (key block legal iff its first token is not after the
+    token, offset from the PADDED lengths); a query block lists the union of its rows' picks in ascending order,
+    padded with the out-of-range id nk up to cap = min(top_k_cap, nk); a union larger than the cap keeps the cap
+    blocks with the best block-level score (max over the rows), best first.  Ties resolve to the lowest block id
+    (torch.topk / argsort leave them unspecified).  A row with fewer legal blocks than picks contributes only its
+    legal ones (the reference's top-k then returns arbitrary illegal ids, which its attention kernel skips).
+    int32 [B,H,nq,cap]."""
+    B, H, Tq, D = Q.shape
+    Hkv, Tk = K.shape[1], K.shape[2]
+    G = _group(H, Hkv)
+    bn, bm = block_size_n, block_size_m
+    nq, nk = (Tq + bm - 1) // bm, (Tk + bn - 1) // bn
+    Kb = pool_mean(K, bn).float()
+    Qp = torch.nn.functional.pad(Q.float(), (0, 0, 0, nq * bm - Tq))
+    s = _softmax_scale(D, scale)
+    offset = nk * bn - nq * bm
+    rows = torch.arange(nq * bm).view(-1, 1)
+    legal = (torch.arange(nk).view(1, -1) * bn <= rows + offset) if causal else torch.ones((nq * bm, nk), dtype=torch.bool)
+    kq = min(top_k_per_query, nk)
+    cap = min(top_k_cap, nk)
+    out = torch.full((B, H, nq, cap), nk, dtype=torch.int32)
+    for b in range(B):
+        for h in range(H):
+            sc = torch.matmul(Qp[b, h], Kb[b, h // G].t()) * s
+            sc = sc.masked_fill(~legal, NEG_INF)
+            order = torch.sort(sc, dim=-1, descending=True, stable=True).indices[:, :kq]      # ties -> lowest id
+            level = sc.view(nq, bm, nk).amax(dim=1)
+            took = torch.gather(sc, 1, order) > NEG_INF              # a row with fewer legal blocks than picks: the rest is dropped
+            picks = torch.where(took, order, torch.full_like(order, nk)).reshape(nq, bm * kq)
+            for qb in range(nq):
+                u = torch.unique(picks[qb])
+                u = u[u < nk]
+                if u.numel() > cap:
+                    keep = torch.sort(level[qb][u], descending=True, stable=True).indices[:cap]
+                    u = u[keep]
+                out[b, h, qb, : u.numel()] = u.to(torch.int32)
+    return out
+
+
 def overlap_weights(n_cmp: int, nk: int, block_size_c: int, stride_c: int, block_size_n: int) -> Tensor:
     """fp32 [n_cmp, nk]: share of compressed token c's window [c*stride, c*stride + block_c) that lies in
     selection block j = [j*bn, (j+1)*bn), i.e. |overlap| / block_c (exact in fp32 for power-of-two sizes)."""
@@ -496,6 +539,7 @@ def nsa_forward(
     gate_activation: str = "sigmoid", block_indices: Optional[Tensor] = None,
     force_first: int = 0, force_local: int = 0, group_shared: bool = False,
     rows: Optional[Tuple[int, int]] = None,
+    pool_proj_k: Optional[Tensor] = None, pool_proj_v: Optional[Tensor] = None,
 ) -> Tensor:
     """fp32 combined forward (forward.py:362-406 / reference.py:288-347): the
     three branches on the same inputs, gates applied in fp32.  With
@@ -508,7 +552,8 @@ def nsa_forward(
                                       group_shared=group_shared)
     q0, q1 = _rows(rows, Tq)
     oc, _ = compressed_attention(Q, K, V, block_size_c=block_size_c, stride_c=stride_c,
-                                 causal=causal, scale=scale, rows=(q0, q1))
+                                 causal=causal, scale=scale, rows=(q0, q1),
+                                 pool_proj_k=pool_proj_k, pool_proj_v=pool_proj_v)
     os_, _ = selected_attention(Q, K, V, block_indices, block_size_n=block_size_n,
                                 block_size_m=block_size_m, causal=causal, scale=scale,
                                 rows=(q0, q1))

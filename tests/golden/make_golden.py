@@ -74,17 +74,64 @@ def layer_cases():
     print("wrote", len(out), "arrays (layer)")
 
 
+def learned_pool_cases():
+    """Learned pooling: the reference's plain-torch compressed branch and combined forward with pool="learned"
+    (nsa/reference.py:109-113, 288-347), its only implementation of that option."""
+    from nsa import reference as R
+    out, meta = {}, []
+    for name, (B, H, Tq, Tk, D, bc, causal) in {"lp_a": (1, 2, 128, 128, 64, 32, True), "lp_b": (1, 2, 96, 200, 64, 64, True)}.items():
+        Q, K, V, g = qkv(81, B, H, Tq, Tk, D, torch.bfloat16)
+        pk = torch.randn(bc, D, generator=g) / D ** 0.5
+        pv = torch.randn(bc, D, generator=g) / D ** 0.5
+        o, l = R.compressed_attention_reference(Q.float(), K.float(), V.float(), block_size_c=bc, pool="learned",
+                                                pool_proj_k=pk, pool_proj_v=pv, causal=causal)
+        out.update({f"{name}.Q": np32(Q), f"{name}.K": np32(K), f"{name}.V": np32(V), f"{name}.pk": np32(pk), f"{name}.pv": np32(pv),
+                    f"{name}.out": np32(o), f"{name}.lse": np32(l)})
+        meta.append((name, dict(B=B, H=H, Tq=Tq, Tk=Tk, D=D, bc=bc, causal=causal)))
+    # combined forward with learned pooling (geometry 32/32/32, top-3, window 48, as the other combined cases)
+    Q, K, V, g = qkv(82, 1, 2, 128, 128, 64, torch.bfloat16)
+    gates = torch.randn(1, 2, 128, 3, generator=g)
+    pk = torch.randn(32, 64, generator=g) / 8.0
+    pv = torch.randn(32, 64, generator=g) / 8.0
+    cfg = R.NSAConfig(block_size_c=32, block_size_n=32, block_size_m=32, top_k=3, window_size=48, pool="learned")
+    o = R.nsa_attention_reference(Q.float(), K.float(), V.float(), cfg, gates=gates, pool_proj_k=pk, pool_proj_v=pv)
+    out.update({"lp_nsa.Q": np32(Q), "lp_nsa.K": np32(K), "lp_nsa.V": np32(V), "lp_nsa.gates": np32(gates), "lp_nsa.pk": np32(pk),
+                "lp_nsa.pv": np32(pv), "lp_nsa.out": np32(o)})
+    np.savez_compressed(os.path.join(HERE, "learned_pool_golden.npz"), **out)
+    print("wrote", len(out), "arrays (learned pooling)")
+
+
+def moba_cases():
+    """MoBA routing: the reference's per-query top-k block lists (nsa/triton/moba.py:18-92, plain torch)."""
+    from nsa.triton.moba import _per_query_top_k_indices
+    out = {}
+    for name, (B, H, Tq, Tk, D, kq, cap, causal) in {"moba_a": (1, 2, 1024, 1024, 64, 4, 8, True),
+                                                     "moba_b": (1, 2, 1024, 1024, 64, 8, 6, True),      # unions overflow the cap
+                                                     "moba_c": (1, 2, 512, 768, 64, 3, 16, False)}.items():
+        Q, K, V, g = qkv(91, B, H, Tq, Tk, D, torch.bfloat16)
+        idx = _per_query_top_k_indices(Q, K, block_size_n=64, block_size_m=64, top_k_per_query=kq, top_k_cap=cap,
+                                       causal=causal, scale=D ** -0.5)
+        out.update({f"{name}.Q": np32(Q), f"{name}.K": np32(K), f"{name}.idx": idx.numpy().astype(np.int32),
+                    f"{name}.par": np.array([kq, cap, int(causal)], dtype=np.int32)})
+    np.savez_compressed(os.path.join(HERE, "moba_golden.npz"), **out)
+    print("wrote", len(out), "arrays (moba routing)")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the reference checkout")
-    ap.add_argument("--part", default="all", choices=["all", "kernels", "layer"],
-                    help="kernels: reference_golden.npz; layer: layer_golden.npz")
+    ap.add_argument("--part", default="all", choices=["all", "kernels", "layer", "learned", "moba"],
+                    help="kernels: reference_golden.npz; layer: layer_golden.npz; learned: learned_pool_golden.npz; moba: moba_golden.npz")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     sys.path.insert(0, os.path.join(HERE, "..", ".."))
     if args.part in ("all", "layer"):
         layer_cases()
-    if args.part == "layer":
+    if args.part in ("all", "learned"):
+        learned_pool_cases()
+    if args.part in ("all", "moba"):
+        moba_cases()
+    if args.part in ("layer", "learned", "moba"):
         return
     from nsa import reference as R
     from nsa.triton import forward as F_

@@ -686,3 +686,57 @@ def test_strided_operands_warn_or_raise(nsa):
             nsa.sliding_attention(Qs, K.cuda(), V.cuda(), window_size=64)
     finally:
         ops.set_strict_layout(False)
+
+
+def test_learned_pooling_forward(nsa):
+    """pool="learned" (forward): compressed branch and combined forward against the reference's golden outputs and,
+    with grouped heads and stride < block (which the reference lacks), against the oracle."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "learned_pool_golden.npz"))
+    T = lambda k, dt=torch.float32: torch.from_numpy(np.asarray(g[k])).to(dt)
+    for name, bc in (("lp_a", 32), ("lp_b", 64)):
+        Q, K, V = (T(f"{name}.{x}", torch.bfloat16).cuda() for x in "QKV")
+        out, lse = nsa.compressed_attention(Q, K, V, block_size_c=bc, pool="learned", pool_proj_k=T(f"{name}.pk").cuda(),
+                                            pool_proj_v=T(f"{name}.pv").cuda())
+        rl = T(f"{name}.lse")
+        rl = torch.where(torch.isfinite(rl), rl, torch.full_like(rl, float("-inf")))
+        check_out_lse(out, lse, torch.nan_to_num(T(f"{name}.out")), rl, TOL16)
+    Q, K, V = (T(f"lp_nsa.{x}", torch.bfloat16).cuda() for x in "QKV")
+    cfg = nsa.NSAConfig(block_size_c=32, block_size_n=32, block_size_m=32, top_k=3, window_size=48, pool="learned")
+    out = nsa.nsa_forward(Q, K, V, cfg, gate_logits=T("lp_nsa.gates").cuda(), pool_proj_k=T("lp_nsa.pk").cuda(),
+                          pool_proj_v=T("lp_nsa.pv").cuda())
+    ref = T("lp_nsa.out")
+    fin = torch.isfinite(ref).all(-1)
+    assert max_abs(out, ref, fin) <= TOL16
+    # grouped KV heads, stride 16 < block 32, D=128: the oracle's restatement is the checker
+    Qh, Kh, Vh, gen = make_qkv(33, 1, 8, 2, 512, 512, 128)
+    pk = torch.randn(32, 128, generator=gen) / 128 ** 0.5
+    pv = torch.randn(32, 128, generator=gen) / 128 ** 0.5
+    out, lse = nsa.compressed_attention(Qh.cuda(), Kh.cuda(), Vh.cuda(), block_size_c=32, stride_c=16, pool="learned",
+                                        pool_proj_k=pk.cuda(), pool_proj_v=pv.cuda())
+    ro, rl = O.compressed_attention(Qh, Kh, Vh, block_size_c=32, stride_c=16, pool_proj_k=pk, pool_proj_v=pv)
+    check_out_lse(out, lse, ro, rl, TOL16)
+    with pytest.raises(ValueError, match="pool_proj"):
+        nsa.nsa_forward(Q, K, V, cfg)
+
+
+def test_moba_routing_and_attention(nsa):
+    """MoBA routing kernel: block lists equal the oracle's exactly (and through it the reference's, see
+    test_oracle_golden.py), grouped heads and ragged lengths included; attention over them within tolerance."""
+    import os
+    from nsa_from_scratch_b200 import moba
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "moba_golden.npz"))
+    for name in ("moba_a", "moba_b", "moba_c"):
+        Q, K = (torch.from_numpy(np.asarray(g[f"{name}.{x}"])).to(torch.bfloat16) for x in "QK")
+        kq, cap, causal = (int(x) for x in g[f"{name}.par"])
+        idx = moba._per_query_top_k_indices(Q.cuda(), K.cuda(), block_size_n=64, block_size_m=64, top_k_per_query=kq,
+                                            top_k_cap=cap, causal=bool(causal), scale=Q.shape[-1] ** -0.5)
+        assert torch.equal(idx.cpu(), O.moba_block_indices(Q, K, top_k_per_query=kq, top_k_cap=cap, causal=bool(causal))), name
+    Q, K, V, _ = make_qkv(34, 1, 8, 2, 456, 712, 128)
+    idx = moba._per_query_top_k_indices(Q.cuda(), K.cuda(), block_size_n=64, block_size_m=64, top_k_per_query=3, top_k_cap=7,
+                                        causal=True, scale=128 ** -0.5)
+    ref_idx = O.moba_block_indices(Q, K, top_k_per_query=3, top_k_cap=7, causal=True)
+    assert torch.equal(idx.cpu(), ref_idx)
+    out, lse = nsa.moba_attention(Q.cuda(), K.cuda(), V.cuda(), top_k_per_query=3, top_k_cap=7)
+    ro, rl = O.selected_attention(Q, K, V, ref_idx, causal=True)
+    check_out_lse(out, lse, ro, rl, TOL16)

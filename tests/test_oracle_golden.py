@@ -222,3 +222,51 @@ def test_compressed_probability_scorer_degenerate_cases():
     sc = O.compressed_block_scores(Q, K, block_size_c=64, stride_c=64)
     probs = O.compressed_attention(Q, K, V, block_size_c=64)[0][..., :4]                  # [1,4,256,4]: p[i, block]
     assert torch.allclose(sc, probs.view(1, 4, 4, 64, 4).sum(3), atol=1e-5)
+
+
+def test_learned_pooling_vs_reference():
+    """pool="learned": the oracle against the reference's plain-torch compressed branch and combined forward
+    (tests/golden/learned_pool_golden.npz, made by make_golden.py --part learned)."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "learned_pool_golden.npz"))
+    T = lambda k: torch.from_numpy(np.asarray(g[k]))
+    for name, bc in (("lp_a", 32), ("lp_b", 64)):
+        o, l = O.compressed_attention(T(f"{name}.Q"), T(f"{name}.K"), T(f"{name}.V"), block_size_c=bc, causal=True,
+                                      pool_proj_k=T(f"{name}.pk"), pool_proj_v=T(f"{name}.pv"))
+        rl = T(f"{name}.lse")
+        fin = torch.isfinite(rl)
+        assert torch.equal(torch.isfinite(l), fin)
+        assert float((o - torch.nan_to_num(T(f"{name}.out")))[fin].abs().max()) <= 1e-5
+        assert float((l - rl)[fin].abs().max()) <= 1e-5
+    ref = T("lp_nsa.out")
+    idx = O.select_blocks(T("lp_nsa.Q"), T("lp_nsa.K"), block_size_m=32, block_size_n=32, top_k=3)
+    out = O.nsa_forward(T("lp_nsa.Q"), T("lp_nsa.K"), T("lp_nsa.V"), block_size_c=32, block_size_n=32, block_size_m=32, top_k=3,
+                        window_size=48, gate_logits=T("lp_nsa.gates"), block_indices=idx, pool_proj_k=T("lp_nsa.pk"),
+                        pool_proj_v=T("lp_nsa.pv"))
+    fin = torch.isfinite(ref).all(-1)
+    assert float((out - ref)[fin].abs().max()) <= 1e-4
+
+
+def test_moba_routing_vs_reference():
+    """The oracle's MoBA routing against the reference's lists (tests/golden/moba_golden.npz): per query block the same
+    SET of legal blocks; the same order too wherever every row has at least top_k_per_query legal blocks (below that
+    the reference's top-k returns arbitrary illegal ids, which change its union's size and so its ordering rule)."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "moba_golden.npz"))
+    for name in ("moba_a", "moba_b", "moba_c"):
+        Q, K = (torch.from_numpy(np.asarray(g[f"{name}.{x}"])).to(torch.bfloat16) for x in "QK")
+        ref = torch.from_numpy(np.asarray(g[f"{name}.idx"]))
+        kq, cap, causal = (int(x) for x in g[f"{name}.par"])
+        mine = O.moba_block_indices(Q, K, top_k_per_query=kq, top_k_cap=cap, causal=bool(causal))
+        assert mine.shape == ref.shape
+        nq, nk = ref.shape[2], (K.shape[2] + 63) // 64
+        off = nk * 64 - nq * 64
+        for h in range(ref.shape[1]):
+            for qb in range(nq):
+                lim = (qb * 64 + 63 + off) // 64 if causal else nk - 1
+                a = [int(x) for x in ref[0, h, qb] if x <= lim and x < nk]
+                b = [int(x) for x in mine[0, h, qb] if x < nk]
+                assert set(a) == set(b), (name, h, qb, a, b)
+                first_row_legal = (qb * 64 + off) // 64 + 1 if causal else nk
+                if first_row_legal >= kq:
+                    assert a == b, (name, h, qb, a, b)
