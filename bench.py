@@ -518,7 +518,7 @@ def run_cp(a, T, nsa, cfg, rank, world, dist, barrier, max_over_ranks, steps, wa
     clocks = sampler.stop() if sampler else None
     ms_step = max_over_ranks(ms_mine * steps) / steps
     # the collective alone (events around it, every rank in step), and each rank's own time
-    ag_ms, per_rank = None, [ms_mine]
+    ag_ms, per_rank, own = None, [ms_mine], [ms_mine]
     if dist is not None:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
@@ -529,19 +529,31 @@ def run_cp(a, T, nsa, cfg, rank, world, dist, barrier, max_over_ranks, steps, wa
         e1.record()
         barrier()
         ag_ms = max_over_ranks(e0.elapsed_time(e1)) / steps
+        # each rank's forward on its gathered prefix with no collective in the loop: inside the step the ranks are
+        # coupled by the all-gather (an early rank waits there for the last one), so the step time hides the imbalance
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n_own = max(1, min(steps, 3))
+        nsa.nsa_forward(Q, kp, vp, cfg, gate_logits=G)
+        f0.record()
+        for _ in range(n_own):
+            nsa.nsa_forward(Q, kp, vp, cfg, gate_logits=G)
+        f1.record()
+        torch.cuda.synchronize()
         del kp, vp
-        allms = torch.zeros(world, device="cuda")
-        allms[rank] = ms_mine
+        allms = torch.zeros(2, world, device="cuda")
+        allms[0, rank] = ms_mine
+        allms[1, rank] = f0.elapsed_time(f1) / n_own
         dist.all_reduce(allms)
-        per_rank = [float(x) for x in allms.tolist()]
+        per_rank = [float(x) for x in allms[0].tolist()]
+        own = [float(x) for x in allms[1].tolist()]
     ops.device_status()
     kv_bytes = 2 * K.numel() * K.element_size() * (world - 1)
     line = {
         "metric": METRIC, "value": T / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": steps,
         "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "seq_len": T,
-        "per_rank_ms": per_rank, "all_gather_ms": ag_ms, "bytes_received_per_rank": kv_bytes,
-        "imbalance_last_over_mean": per_rank[-1] / (sum(per_rank) / len(per_rank)),
+        "per_rank_ms": per_rank, "per_rank_forward_alone_ms": own, "all_gather_ms": ag_ms,
+        "bytes_received_per_rank": kv_bytes, "imbalance_last_over_mean": own[-1] / (sum(own) / len(own)),
         "config": {"workload": workload_name(tot) + " [context parallel: total T, contiguous query shards]",
                    "global_batch": 1, "seq_len": T, "parallelism": f"cp{world}: all-gather of K/V ({kv_bytes} B received per rank per step) + local forward",
                    "l2": "inputs exceed the 126 MB L2"},
