@@ -40,6 +40,7 @@ __device__ int g_tc5_status;   // 0 ok; otherwise (1 + id of the barrier a wait 
 
 struct Tc5Params {
   CUtensorMap tmQ, tmK, tmV, tmKc, tmVc;
+  CUtensorMap tmO;   // persistent kernel: the output, 4-D in the order of its strides, boxes of 32 positions x 32 elements of one head, 64-byte swizzle
   nsa_fwd_args a;
   float scale_log2[3];   // per branch: softmax scale * log2(e) (* the fp8 dequantisation scales of the operands)
   float out_scale[3];    // per branch: factor on P.V (the fp8 scale of V; 1 otherwise)
@@ -50,6 +51,8 @@ struct Tc5Params {
   int nsplit;      // split launches: thread blocks per work item, each with a share of every branch's key tiles
   float* part;     // split launches: partial results [B*H*Tq][nsplit][3][D+4] = unnormalised O, m (log2 units), l
   int kv8;         // fp8 launches: K/V are fp8 too (converted tile by tile); 0 = K/V arrive as bf16, only Q is fp8
+  int tma_out;     // persistent kernel: an item whose result is ONE branch writes it through shared memory and the TMA (rows_through_tma)
+  int poly;        // tiles without masked entries take 3 of every 8 exponentials on the FMA pipe (exp2_poly_pair)
 };
 
 struct Tile {
@@ -58,6 +61,80 @@ struct Tile {
   int jlim[2];
   int mask[2];   // which of the 4 row groups attend the chunk (selected branch; 0xF otherwise)
 };
+
+// Row maximum (raw scores) of the 64 * nch columns a softmax thread holds: four chains of 3-input max.
+__device__ __forceinline__ float row_max_raw(const uint32_t (&sv)[4][32], int nch) {
+  float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+  for (int g = 0; g < 2; ++g)
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) m4[(i >> 1) & 3] = max3(m4[(i >> 1) & 3], __uint_as_float(sv[g][i]), __uint_as_float(sv[g][i + 1]));
+  if (nch == 2) {
+#pragma unroll
+    for (int g = 2; g < 4; ++g)
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) m4[(i >> 1) & 3] = max3(m4[(i >> 1) & 3], __uint_as_float(sv[g][i]), __uint_as_float(sv[g][i + 1]));
+  }
+  return fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+}
+
+// P = exp2(S * sl2 - m_ref) for 32 columns of a row without masked entries, as 16 packed 16-bit pairs; the row sums
+// go to the packed accumulators.  Of every 8 pairs, 3 are evaluated by the polynomial on the FMA pipe and 5 by ex2 on
+// the special-function unit: alone, a warp's sweep of 128 columns is bound by that unit (1024 of 1190 clocks); mixed
+// this way it measured 947 clocks, and 2040 instead of 2410 with two warps sharing a scheduler.
+template <typename T>
+__device__ __forceinline__ void exp_group_mixed(const uint32_t (&s)[32], f32x2 SL, f32x2 NM, f32x2& sa, f32x2& sb, uint32_t (&pk)[16]) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const f32x2 x = fma2(mk2(__uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1])), SL, NM);
+    float p0, p1;
+    if ((i & 7) < 3) {
+      exp2_poly_pair(x, p0, p1);
+    } else {
+      float x0, x1;
+      un2(x, x0, x1);
+      p0 = ex2(x0);
+      p1 = ex2(x1);
+    }
+    const f32x2 pp = mk2(p0, p1);
+    if (i & 1) sb = add2(sb, pp); else sa = add2(sa, pp);
+    pk[i] = Elem<T>::pack(p0, p1);
+  }
+}
+
+// End of a branch that alone makes up an item's result (single-branch launches), for one softmax warp: its 32 rows of
+// O (one thread per row in TMEM, D fp32 columns at tO) times the rows' coefficients, rounded to 16 bits, leave through a
+// 2 KB staging box (32 rows x 32 elements, 64-byte swizzle: 16-byte piece k of row r sits at piece k ^ ((r >> 1) & 3),
+// which also keeps the lanes' writes off each other's banks) and TMA stores.  A thread writing its own row with
+// 16-byte stores touches 32 lines per instruction; this way the load/store unit is not involved and the values are
+// the same.  The TMA takes about 100 clocks per box instruction and SM, so this pays only where nothing has to be
+// read back: with several branches per item every variant tried (16-bit adds in L2, fp32 sums in an L2-resident
+// slot, transposing through shared memory) lost to the per-row code or to the 2e-2 bound.
+// Rows past Tq are clipped by the tensor map.  `issue(smem address, first column)` starts the copy of one box.
+template <typename T, int D, typename Issue>
+__device__ __forceinline__ void rows_through_tma(unsigned char* stage, uint32_t tO, float coef, int lane, Issue issue) {
+  const int sw = (lane >> 1) & 3;
+#pragma unroll
+  for (int c = 0; c < D / 32; ++c) {
+    uint32_t v[32];
+    tmem_ld32(tO + c * 32, v);
+    tc_wait_ld();
+    uint32_t w[16];
+#pragma unroll
+    for (int e = 0; e < 16; ++e) w[e] = Elem<T>::pack(__uint_as_float(v[2 * e]) * coef, __uint_as_float(v[2 * e + 1]) * coef);
+    if (lane == 0) bulk_wait_read<0>();             // the box issued before has been read out of the staging area
+    __syncwarp();
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      *reinterpret_cast<uint4*>(stage + lane * 64 + ((k ^ sw) << 4)) = make_uint4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
+    fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) {
+      issue(smem_u32(stage), c * 32);
+      bulk_commit();
+    }
+  }
+}
 
 // barrier ids
 enum { B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 3, B_VFULL = 5, B_VEMPTY = 7, B_SFULL = 9, B_PFULL = 11, B_PVDONE = 13,
@@ -582,11 +659,13 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
           mbar_arrive(bar(B_SREAD + X));
         }
         // valid column range of each chunk for this row; masked entries become -inf
+        bool masked = false;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           const int vlo = max(lo - tl.j0[c], 0);
           const int vhi = (c < tl.nch && ((tl.mask[c] >> rg) & 1)) ? min(hi, tl.jlim[c] - 1) - tl.j0[c] : -1;
           if (c < tl.nch && (vlo > 0 || vhi < 63)) {
+            masked = true;
 #pragma unroll
             for (int g = 0; g < 2; ++g)
 #pragma unroll
@@ -594,21 +673,8 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
                 if (g * 32 + i < vlo || g * 32 + i > vhi) sv[2 * c + g][i] = 0xff800000u;   // -inf
           }
         }
-        // row maximum: eight independent chains (a single chain of 128 dependent max ops is latency-bound)
-        float mxa[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) mxa[i] = -INFINITY;
-#pragma unroll
-        for (int g = 0; g < 2; ++g)
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mxa[i & 7] = fmaxf(mxa[i & 7], __uint_as_float(sv[g][i]));
-        if (tl.nch == 2) {
-#pragma unroll
-          for (int g = 2; g < 4; ++g)
-#pragma unroll
-            for (int i = 0; i < 32; ++i) mxa[i & 7] = fmaxf(mxa[i & 7], __uint_as_float(sv[g][i]));
-        }
-        float mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])), fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
+        const bool use_poly = p.poly != 0 && !__any_sync(0xffffffffu, masked);
+        float mx = row_max_raw(sv, tl.nch);
         mx *= p.scale_log2[br];                              // scale > 0 keeps the order
         // lazy rescale: only when some row of the warp outgrows its reference maximum by 2^8
         const bool grow = mx > m_used + 8.f;
@@ -641,24 +707,40 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
           }
         }
         // P = exp2(S*scale - m_ref) as 16-bit (-inf -> 0)
-        float psum0 = 0.f, psum1 = 0.f, psum2 = 0.f, psum3 = 0.f;
+        if (use_poly) {
+          const f32x2 SL = mk2(sl2, sl2), NM = mk2(-m_ref, -m_ref);
+          f32x2 sa = mk2(0.f, 0.f), sb = mk2(0.f, 0.f);
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          if (g < 2 * tl.nch) {
-            uint32_t pk[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const float p0 = ex2(fmaf(__uint_as_float(sv[g][2 * i]), sl2, -m_ref));
-              const float p1 = ex2(fmaf(__uint_as_float(sv[g][2 * i + 1]), sl2, -m_ref));
-              if (i & 1) { psum2 += p0; psum3 += p1; } else { psum0 += p0; psum1 += p1; }
-              pk[i] = Elem<T>::pack(p0, p1);
+          for (int g = 0; g < 4; ++g) {
+            if (g < 2 * tl.nch) {
+              uint32_t pk[16];
+              exp_group_mixed<T>(sv[g], SL, NM, sa, sb, pk);
+              tmem_st16(tP + g * 16, pk);
             }
-            tmem_st16(tP + g * 16, pk);
           }
+          float s0, s1;
+          un2(add2(sa, sb), s0, s1);
+          l += s0 + s1;
+        } else {
+          float psum0 = 0.f, psum1 = 0.f, psum2 = 0.f, psum3 = 0.f;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (g < 2 * tl.nch) {
+              uint32_t pk[16];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const float p0 = ex2(fmaf(__uint_as_float(sv[g][2 * i]), sl2, -m_ref));
+                const float p1 = ex2(fmaf(__uint_as_float(sv[g][2 * i + 1]), sl2, -m_ref));
+                if (i & 1) { psum2 += p0; psum3 += p1; } else { psum0 += p0; psum1 += p1; }
+                pk[i] = Elem<T>::pack(p0, p1);
+              }
+              tmem_st16(tP + g * 16, pk);
+            }
+          }
+          psum0 += psum2;
+          psum1 += psum3;
+          l += psum0 + psum1;
         }
-        psum0 += psum2;
-        psum1 += psum3;
-        l += psum0 + psum1;
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar(B_PFULL + X));
@@ -1219,10 +1301,14 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_persist_kernel(const __gri
       float lse_out = -INFINITY;
       bool have_partial = a.accumulate != 0;
       T* orow = reinterpret_cast<T*>(a.out) + ((a.io_layout & NSA_IO_OUT_BTHD) ? row_bthd : row_index) * D;
+      unsigned char* ostage = smem + 2 * QTILE + 4 * KVTILE + (warp - 4) * 2048;
+      const int qi0_box = grp_qb(im, rg) * 64 + (quarter & 1) * 32;        // this warp's rows: 32 consecutive positions of one head
+      const bool box_ok = grp_qb(im, rg) < a.nq && qi0_box < a.Tq;
 
       ok = __all_sync(0xffffffffu, mbar_wait(bar(PB_LISTFULL + lp), (k >> 1) & 1, &abort_flag));
       if (!ok) { fail_id = PB_LISTFULL + lp + 1; break; }
       counts(im, sel_n[lp]);
+      const int n_with_tiles = (ntiles(im, 0) != 0) + (ntiles(im, 1) != 0) + (ntiles(im, 2) != 0);
 #pragma unroll 1
       for (int br = 0; br < 3 && ok; ++br) {
         if (ntiles(im, br) == 0) continue;
@@ -1245,11 +1331,13 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_persist_kernel(const __gri
             tc_fence_before();
             mbar_arrive(bar(B_SREAD + X));
           }
+          bool masked = false;
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
             const int vlo = max(lo - tl.j0[c], 0);
             const int vhi = (c < tl.nch && ((tl.mask[c] >> rg) & 1)) ? min(hi, tl.jlim[c] - 1) - tl.j0[c] : -1;
             if (c < tl.nch && (vlo > 0 || vhi < 63)) {
+              masked = true;
 #pragma unroll
               for (int g = 0; g < 2; ++g)
 #pragma unroll
@@ -1257,20 +1345,8 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_persist_kernel(const __gri
                   if (g * 32 + i < vlo || g * 32 + i > vhi) sv[2 * c + g][i] = 0xff800000u;
             }
           }
-          float mxa[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) mxa[i] = -INFINITY;
-#pragma unroll
-          for (int g = 0; g < 2; ++g)
-#pragma unroll
-            for (int i = 0; i < 32; ++i) mxa[i & 7] = fmaxf(mxa[i & 7], __uint_as_float(sv[g][i]));
-          if (tl.nch == 2) {
-#pragma unroll
-            for (int g = 2; g < 4; ++g)
-#pragma unroll
-              for (int i = 0; i < 32; ++i) mxa[i & 7] = fmaxf(mxa[i & 7], __uint_as_float(sv[g][i]));
-          }
-          float mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])), fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
+          const bool use_poly = p.poly != 0 && !__any_sync(0xffffffffu, masked);
+          float mx = row_max_raw(sv, tl.nch);
           mx *= p.scale_log2[br];
           const bool grow = mx > m_used + 8.f;
           if (__any_sync(0xffffffffu, grow)) {
@@ -1301,30 +1377,61 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_persist_kernel(const __gri
               tc_fence_after();
             }
           }
-          float psum0 = 0.f, psum1 = 0.f, psum2 = 0.f, psum3 = 0.f;
+          if (use_poly) {
+            const f32x2 SL = mk2(sl2, sl2), NM = mk2(-m_ref, -m_ref);
+            f32x2 sa = mk2(0.f, 0.f), sb = mk2(0.f, 0.f);
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            if (g < 2 * tl.nch) {
-              uint32_t pk[16];
-#pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                const float p0 = ex2(fmaf(__uint_as_float(sv[g][2 * i]), sl2, -m_ref));
-                const float p1 = ex2(fmaf(__uint_as_float(sv[g][2 * i + 1]), sl2, -m_ref));
-                if (i & 1) { psum2 += p0; psum3 += p1; } else { psum0 += p0; psum1 += p1; }
-                pk[i] = Elem<T>::pack(p0, p1);
+            for (int g = 0; g < 4; ++g) {
+              if (g < 2 * tl.nch) {
+                uint32_t pk[16];
+                exp_group_mixed<T>(sv[g], SL, NM, sa, sb, pk);
+                tmem_st16(tP + g * 16, pk);
               }
-              tmem_st16(tP + g * 16, pk);
             }
+            float s0, s1;
+            un2(add2(sa, sb), s0, s1);
+            l += s0 + s1;
+          } else {
+            float psum0 = 0.f, psum1 = 0.f, psum2 = 0.f, psum3 = 0.f;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              if (g < 2 * tl.nch) {
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                  const float p0 = ex2(fmaf(__uint_as_float(sv[g][2 * i]), sl2, -m_ref));
+                  const float p1 = ex2(fmaf(__uint_as_float(sv[g][2 * i + 1]), sl2, -m_ref));
+                  if (i & 1) { psum2 += p0; psum3 += p1; } else { psum0 += p0; psum1 += p1; }
+                  pk[i] = Elem<T>::pack(p0, p1);
+                }
+                tmem_st16(tP + g * 16, pk);
+              }
+            }
+            psum0 += psum2;
+            psum1 += psum3;
+            l += psum0 + psum1;
           }
-          psum0 += psum2;
-          psum1 += psum3;
-          l += psum0 + psum1;
           tc_wait_st();
           tc_fence_before();
           mbar_arrive(bar(B_PFULL + X));
         }
         if (!ok) break;
         // ---- end of the branch ----
+        if (p.tma_out != 0 && n_with_tiles == 1 && !have_partial) {      // this branch alone is the item's result
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(B_PVDONE + X), (it - 1) & 1, &abort_flag));
+          if (!ok) { fail_id = B_PVDONE + X + 1; break; }
+          tc_fence_after();
+          const bool has = l > 0.f;
+          const float coef = has ? (a.fused ? gate_of(br) : 1.f) * p.out_scale[br] / l : 0.f;
+          if (a.lse != nullptr) lse_out = has ? m_used * kLn2 + __logf(l) : -INFINITY;
+          const bool bthd = (a.io_layout & NSA_IO_OUT_BTHD) != 0;
+          if (box_ok)
+            rows_through_tma<T, D>(ostage, tO, coef, lane, [&](uint32_t src, int col) {
+              tma_store_4d(&p.tmO, src, col, bthd ? head : qi0_box, bthd ? qi0_box : head, im.b); });
+          have_partial = true;
+          tc_fence_before();
+          continue;
+        }
         uint4 prevv[D / 8];
 #pragma unroll
         for (int c = 0; c < D / 8; ++c)
@@ -1370,6 +1477,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_persist_kernel(const __gri
       if (lane == 0) mbar_arrive(bar(PB_LISTEMPTY + lp));      // this warp is done with the item's block list
       __syncwarp();
     }
+    if (p.tma_out != 0 && lane == 0) bulk_wait_read<0>();      // the staging area has been read before the block's shared memory goes
   }
 
   // ---- teardown ----
@@ -1546,6 +1654,11 @@ bool attention_fwd_tc5_supports(const nsa_fwd_args& a) {
 // 2.72, sliding 1.93 against 2.02); launches of several branches are 1-4 % slower on it than on the one-item kernel
 // (all three: 8.91-9.25 against 8.54-8.89 ms on the same box) and stay there, as do the split and fp8 launches.
 // NSA_TC5_PERSIST=0 / =1 in the environment forces the one-item / the persistent kernel for every unsplit 16-bit launch.
+// NSA_TC5_POLY=0 keeps every exponential on the special-function unit; default: 3 of 8 on the FMA pipe in unmasked tiles.
+static int tc5_poly_mode() {
+  static const int mode = [] { const char* e = getenv("NSA_TC5_POLY"); return !e ? 1 : (e[0] == '0' ? 0 : 1); }();
+  return mode;
+}
 static int tc5_persistent_mode() {
   static const int mode = [] { const char* e = getenv("NSA_TC5_PERSIST"); return !e ? -1 : (e[0] == '0' ? 0 : 1); }();
   return mode;
@@ -1569,6 +1682,8 @@ int attention_fwd_tc5(const nsa_fwd_args& a, cudaStream_t st) {
   }
   int rc;
   p.kv8 = in8 && a.kv_dtype == a.q_dtype;
+  p.poly = tc5_poly_mode();
+  p.tma_out = 0;
   if (in8) rc = make_map8(&p.tmQ, a.Q, (long long)a.B * a.H, a.Tq, a.D);
   else rc = make_map(&p.tmQ, a.Q, (long long)a.B * a.H, a.Tq, a.D, cdt);
   if (rc != NSA_OK) return rc;
@@ -1638,7 +1753,26 @@ int attention_fwd_tc5(const nsa_fwd_args& a, cudaStream_t st) {
     NSA_CUDA_OK(cudaGetDevice(&dev));
     NSA_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     const unsigned grid = (unsigned)(blocks < sms ? blocks : sms);
-    const size_t smem_p = (size_t)(2 + 2 + 2) * (a.D / 64) * 128 * 128 + 1024;
+    // results of single-branch items leave through the TMA (NSA_TC5_TMA_OUT=0 keeps the per-row stores)
+    static const int tma_out_env = [] { const char* e = getenv("NSA_TC5_TMA_OUT"); return !e ? 1 : (e[0] == '0' ? 0 : 1); }();
+    p.tma_out = 0;
+    if (tma_out_env && (reinterpret_cast<uintptr_t>(a.out) & 15) == 0) {
+      auto enc = encode_fn();
+      NSA_REQUIRE(enc != nullptr, NSA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+      // dims in ascending stride order: (D, Tq, H, B) for [B,H,Tq,D], (D, H, Tq, B) for [B,Tq,H,D]; the kernel swaps the two middle coordinates
+      const bool bthd = (a.io_layout & NSA_IO_OUT_BTHD) != 0;
+      const cuuint64_t D2 = (cuuint64_t)a.D * 2;
+      cuuint64_t dims[4] = {(cuuint64_t)a.D, (cuuint64_t)(bthd ? a.H : a.Tq), (cuuint64_t)(bthd ? a.Tq : a.H), (cuuint64_t)a.B};
+      cuuint64_t strides[3] = {D2, D2 * (cuuint64_t)(bthd ? a.H : a.Tq), D2 * a.Tq * a.H};
+      cuuint32_t box[4] = {32, bthd ? 1u : 32u, bthd ? 32u : 1u, 1};
+      cuuint32_t es[4] = {1, 1, 1, 1};
+      CUresult r = enc(&p.tmO, cdt == NSA_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, a.out, dims,
+                       strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                       CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      NSA_REQUIRE(r == CUDA_SUCCESS, NSA_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with %d", (int)r);
+      p.tma_out = 1;
+    }
+    const size_t smem_p = (size_t)(2 + 2 + 2) * (a.D / 64) * 128 * 128 + (p.tma_out ? 8 * 2048 : 0) + 1024;
 #define NSA_TC5_PERSIST_LAUNCH(DD, FF)                                                                     \
   {                                                                                                         \
     auto fn = nsa_fwd_tc5_persist_kernel<DD, FF>;                                                           \

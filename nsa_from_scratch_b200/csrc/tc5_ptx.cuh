@@ -77,6 +77,16 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
 __device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, int c0, int c1, int c2) {
   asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];\n" ::"l"(map), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
+// Shared memory -> global, 4-D tiled box; completion is tracked by the issuing thread's bulk groups.  x (c0) times the
+// element size must be a multiple of 16 bytes and no coordinate may be negative; elements outside the tensor are
+// not written.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];\n"
+               ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;\n" ::: "memory"); }
+// until at most N of this thread's bulk groups are still reading their shared-memory source
+template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;\n" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];\n" ::"l"(map) : "memory");
 }
@@ -149,6 +159,38 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n"
       ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
         "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+
+// ---------------------------------------------------------------- packed fp32 pairs, 3-input max
+// One 64-bit register holds two floats; fma / add / sub act on both halves with one instruction.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 mk2(float lo, float hi) { f32x2 d; asm("mov.b64 %0, {%1, %2};\n" : "=l"(d) : "f"(lo), "f"(hi)); return d; }
+__device__ __forceinline__ void un2(f32x2 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;\n" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) { f32x2 d; asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d; }
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) { f32x2 d; asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(d) : "l"(a), "l"(b)); return d; }
+__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) { f32x2 d; asm("sub.rn.f32x2 %0, %1, %2;\n" : "=l"(d) : "l"(a), "l"(b)); return d; }
+__device__ __forceinline__ float max3(float a, float b, float c) { float d; asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c)); return d; }
+
+// 2^x for a pair of finite x on the FMA pipe instead of the special-function unit (which delivers 16 results per
+// clock and SM and is what bounds a softmax sweep): x is clamped to >= -125, split as n + f with n = round(x)
+// (adding and subtracting 1.5 * 2^23 leaves n in the low mantissa bits of t), 2^f on [-0.5, 0.5] by a cubic whose
+// relative error, 7.5e-5, is a fiftieth of a bf16 ulp and a sixth of an fp16 ulp, and n added to the exponent field
+// with integer arithmetic.  The result is never 0 (>= 2^-126): callers keep masked (-inf) entries on ex2.
+__device__ __forceinline__ void exp2_poly_pair(f32x2 x, float& p0, float& p1) {
+  const f32x2 MG = mk2(12582912.f, 12582912.f);
+  float x0, x1;
+  un2(x, x0, x1);
+  x = mk2(fmaxf(x0, -125.f), fmaxf(x1, -125.f));
+  const f32x2 t = add2(x, MG);
+  const f32x2 f = sub2(x, sub2(t, MG));
+  f32x2 q = fma2(mk2(0.0551716685295105f, 0.0551716685295105f), f, mk2(0.2426111251115799f, 0.2426111251115799f));
+  q = fma2(q, f, mk2(0.6932609677314758f, 0.6932609677314758f));
+  q = fma2(q, f, mk2(0.9999280571937561f, 0.9999280571937561f));
+  float q0, q1, t0, t1;
+  un2(q, q0, q1);
+  un2(t, t0, t1);
+  p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
+  p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
 }
 
 // ---------------------------------------------------------------- descriptors

@@ -142,7 +142,10 @@ def test_cfg4_backward_sampled_query_blocks(nsa):
             assert max_abs(dQ[:, :, q0:q1], rq) <= TOL * max(1.0, float(rq.abs().max()))
             rK[:, :, :q1] += rk
             rV[:, :, :q1] += rv
-        assert float(dQ.abs().sum()) == float(sum(dQ[:, :, qb * 64:(qb + 1) * 64].abs().sum() for qb in blocks))
+        outside = torch.ones(T, dtype=torch.bool)            # rows whose dO is zero get no gradient at all
+        for qb in blocks:
+            outside[qb * 64:(qb + 1) * 64] = False
+        assert not bool(dQ[:, :, outside].any())
         assert max_abs(dK, rK) <= TOL * max(1.0, float(rK.abs().max()))
         assert max_abs(dV, rV) <= TOL * max(1.0, float(rV.abs().max()))
 
