@@ -52,6 +52,7 @@ struct Tc5Params {
   float* part;     // split launches: partial results [B*H*Tq][nsplit][3][D+4] = unnormalised O, m (log2 units), l
   int kv8;         // fp8 launches: K/V are fp8 too (converted tile by tile); 0 = K/V arrive as bf16, only Q is fp8
   int tma_out;     // persistent kernel: an item whose result is ONE branch writes it through shared memory and the TMA (rows_through_tma)
+  int psum;        // one-item kernel, unsplit 16-bit launches: 32 KB of shared memory hold the first 64 columns of the rows' running gated sum
   int poly;        // tiles without masked entries take 3 of every 8 exponentials on the FMA pipe (exp2_poly_pair)
 };
 
@@ -627,6 +628,18 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
     float lse_out = -INFINITY;
     bool have_partial = !SPLIT && a.accumulate != 0;       // the output row already holds a gated partial sum to add to
     T* orow = reinterpret_cast<T*>(a.out) + ((a.io_layout & NSA_IO_OUT_BTHD) ? row_bthd : row_index) * D;
+    // Between branch ends the first 64 columns of the row's gated sum stay in shared memory (128 bytes per row, 16-byte
+    // piece k at k ^ (row & 7): neighbouring rows on different banks) instead of going to the output row and back: a
+    // thread reading or writing its own row in global memory touches 32 lines per instruction, and at D = 128 those
+    // loads and stores were 12 % of the kernel.  Only the item's last branch writes these columns out; the values
+    // are the same, rounded to 16 bits at every branch end.  At D = 64 that is the whole row.
+    const bool keep = !SPLIT && !IN8 && p.psum != 0;
+    unsigned char* prow_s = smem + 2 * QTILE + 4 * KVTILE + (size_t)(X * 128 + r) * 128;
+    bool kept = false;                                   // the shared-memory columns hold a partial sum
+    int last_br = -1;                                    // the item's last branch with key tiles
+#pragma unroll
+    for (int br = 0; br < 3; ++br)
+      if (tend(br) != tbeg(br)) last_br = br;
 
     int it = 0;
     bool ok = true;
@@ -752,8 +765,10 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
       uint4 prevv[D / 8];
       if constexpr (!SPLIT) {
 #pragma unroll
-        for (int c = 0; c < D / 8; ++c)
-          prevv[c] = (have_partial && row_ok) ? reinterpret_cast<const uint4*>(orow)[c] : make_uint4(0u, 0u, 0u, 0u);
+        for (int c = 0; c < D / 8; ++c) {
+          if (c < 8 && kept) prevv[c] = *reinterpret_cast<const uint4*>(prow_s + ((c ^ (r & 7)) << 4));
+          else prevv[c] = (have_partial && row_ok) ? reinterpret_cast<const uint4*>(orow)[c] : make_uint4(0u, 0u, 0u, 0u);
+        }
       }
       ok = __all_sync(0xffffffffu, mbar_wait(bar(B_PVDONE + X), (it - 1) & 1, &abort_flag));
       if (!ok) { fail_id = B_PVDONE + X + 1; break; }
@@ -795,11 +810,15 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
               w[e] = Elem<T>::pack(fmaf(__uint_as_float(v[8 * c + 2 * e]), coef, acc.x),
                                    fmaf(__uint_as_float(v[8 * c + 2 * e + 1]), coef, acc.y));
             }
-            reinterpret_cast<uint4*>(orow)[g * 4 + c] = make_uint4(w[0], w[1], w[2], w[3]);
+            if (keep && br != last_br && g * 4 + c < 8)
+              *reinterpret_cast<uint4*>(prow_s + (((g * 4 + c) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            else
+              reinterpret_cast<uint4*>(orow)[g * 4 + c] = make_uint4(w[0], w[1], w[2], w[3]);
           }
         }
       }
       have_partial = true;
+      kept = keep && br != last_br;
       tc_fence_before();
     }
     if (!SPLIT && ok && row_ok) {
@@ -1683,6 +1702,9 @@ int attention_fwd_tc5(const nsa_fwd_args& a, cudaStream_t st) {
   int rc;
   p.kv8 = in8 && a.kv_dtype == a.q_dtype;
   p.poly = tc5_poly_mode();
+  // NSA_TC5_KEEP_SUM=0: every branch end writes the whole running sum to the output row
+  static const int psum_env = [] { const char* e = getenv("NSA_TC5_KEEP_SUM"); return !e ? 1 : (e[0] == '0' ? 0 : 1); }();
+  p.psum = (psum_env && !in8 && !((a.nsplit > 1 || a.dyn_len != nullptr) && a.fused)) ? 1 : 0;
   p.tma_out = 0;
   if (in8) rc = make_map8(&p.tmQ, a.Q, (long long)a.B * a.H, a.Tq, a.D);
   else rc = make_map(&p.tmQ, a.Q, (long long)a.B * a.H, a.Tq, a.D, cdt);
@@ -1719,7 +1741,7 @@ int attention_fwd_tc5(const nsa_fwd_args& a, cudaStream_t st) {
   }
   const long long blocks = items * p.nsplit;
   NSA_REQUIRE(blocks > 0 && blocks < 2147483647LL, NSA_ERR_ARG, "attention forward: %lld work items do not fit a grid", blocks);
-  const size_t smem = (size_t)(2 + 2 + 2) * (a.D / 64) * 128 * 128 + (in8 ? (size_t)2 * 128 * a.D : 0) + 1024;
+  const size_t smem = (size_t)(2 + 2 + 2) * (a.D / 64) * 128 * 128 + (in8 ? (size_t)2 * 128 * a.D : 0) + (p.psum ? 256 * 128 : 0) + 1024;
 #define NSA_TC5_LAUNCH(DD, FF, I8, SP)                                                                     \
   {                                                                                                         \
     auto fn = nsa_fwd_tc5_kernel<DD, FF, I8, SP>;                                                           \
