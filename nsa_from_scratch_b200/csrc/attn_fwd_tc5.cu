@@ -139,8 +139,10 @@ __device__ __forceinline__ void rows_through_tma(unsigned char* stage, uint32_t 
 
 // barrier ids
 enum { B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 3, B_VFULL = 5, B_VEMPTY = 7, B_SFULL = 9, B_PFULL = 11, B_PVDONE = 13,
-       B_STGFULL = 15, B_STGEMPTY = 17, B_SREAD = 19, B_COUNT = 21 };
-// STG*: fp8 staging buffers (0 = K side, 1 = V side); SREAD: D=64 only, "S row is in registers"
+       B_STGFULL = 15, B_STGEMPTY = 17, B_SREAD = 19, B_PHALF = 21, B_COUNT = 23 };
+// STG*: fp8 staging buffers (0 = K side, 1 = V side); SREAD: D=64 only, "S row is in registers";
+// PHALF: D=128, one-item kernel: "P of the tile's first 64 keys is in TMEM" -- that half of P V is issued while the second
+// half of the exponentials is still being computed, which takes it off the tile's QK -> softmax -> PV chain
 
 // SPLIT: decoding-sized launches (few work items, long key ranges).  nsplit thread blocks share a work item; block s
 // takes tiles [nt*s/nsplit, nt*(s+1)/nsplit) of each branch and leaves (unnormalised O, m, l) per branch and row
@@ -239,7 +241,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
   if (tid == 0) {
     abort_flag = 0;
     for (int i = 0; i < B_COUNT; ++i)
-      mbar_init(bar(i), (i == B_PFULL || i == B_PFULL + 1 || i == B_SREAD || i == B_SREAD + 1) ? 128 : ((IN8 && i == B_QFULL) ? 2 : 1));
+      mbar_init(bar(i), (i == B_PFULL || i == B_PFULL + 1 || i == B_SREAD || i == B_SREAD + 1 || i == B_PHALF || i == B_PHALF + 1) ? 128 : ((IN8 && i == B_QFULL) ? 2 : 1));
     fence_barrier_init();
   }
   if (warp == 1) { tmem_alloc(smem_u32(&tmem_base_s), 512); tmem_relinquish(); }
@@ -504,14 +506,29 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
 #pragma unroll
         for (int X = 0; X < 2; ++X) {
           if (!ok) break;
+          if constexpr (!EARLY) {
+            // first 64 keys of P V as soon as that half of P is written
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(B_PHALF + X), it & 1, &abort_flag));
+            if (!ok) { fail_id = B_PHALF + X + 1; break; }
+            tc_fence_after();
+            if (leader) {
+              if (fresh) mma_ts(tOx[X], tPx[X], dV[s], IDESC_PV, 0u);
+              else mma_ts(tOx[X], tPx[X], dV[s], IDESC_PV, 1u);
+#pragma unroll
+              for (int kk = 1; kk < 4; ++kk) mma_ts(tOx[X], tPx[X] + kk * 8, dV[s] + kk * 128, IDESC_PV, 1u);
+            }
+            __syncwarp();
+          }
           ok = __all_sync(0xffffffffu, mbar_wait(bar(B_PFULL + X), it & 1, &abort_flag));
           if (!ok) { fail_id = B_PFULL + X + 1; break; }
           tc_fence_after();
           if (leader) {
-            if (fresh) mma_ts(tOx[X], tPx[X], dV[s], IDESC_PV, 0u);
-            else mma_ts(tOx[X], tPx[X], dV[s], IDESC_PV, 1u);
+            if constexpr (EARLY) {
+              if (fresh) mma_ts(tOx[X], tPx[X], dV[s], IDESC_PV, 0u);
+              else mma_ts(tOx[X], tPx[X], dV[s], IDESC_PV, 1u);
 #pragma unroll
-            for (int kk = 1; kk < 4; ++kk) mma_ts(tOx[X], tPx[X] + kk * 8, dV[s] + kk * 128, IDESC_PV, 1u);
+              for (int kk = 1; kk < 4; ++kk) mma_ts(tOx[X], tPx[X] + kk * 8, dV[s] + kk * 128, IDESC_PV, 1u);
+            }
             if (nch == 2) {
 #pragma unroll
               for (int kk = 4; kk < 8; ++kk) mma_ts(tOx[X], tPx[X] + kk * 8, dV[s] + kk * 128, IDESC_PV, 1u);
@@ -730,6 +747,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
               exp_group_mixed<T>(sv[g], SL, NM, sa, sb, pk);
               tmem_st16(tP + g * 16, pk);
             }
+            if (!EARLY && g == 1) { tc_wait_st(); tc_fence_before(); mbar_arrive(bar(B_PHALF + X)); }
           }
           float s0, s1;
           un2(add2(sa, sb), s0, s1);
@@ -749,6 +767,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
               }
               tmem_st16(tP + g * 16, pk);
             }
+            if (!EARLY && g == 1) { tc_wait_st(); tc_fence_before(); mbar_arrive(bar(B_PHALF + X)); }
           }
           psum0 += psum2;
           psum1 += psum3;
@@ -973,7 +992,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_persist_kernel(const __gri
     abort_flag = 0;
     for (int i = 0; i < PB_COUNT; ++i) {
       int cnt = 1;
-      if (i == B_PFULL || i == B_PFULL + 1 || i == B_SREAD || i == B_SREAD + 1) cnt = 128;
+      if (i == B_PFULL || i == B_PFULL + 1 || i == B_SREAD || i == B_SREAD + 1 || i == B_PHALF || i == B_PHALF + 1) cnt = 128;
       if (i == PB_LISTEMPTY || i == PB_LISTEMPTY + 1) cnt = 10;     // producer, MMA issuer and the 8 softmax warps
       mbar_init(bar(i), cnt);
     }
