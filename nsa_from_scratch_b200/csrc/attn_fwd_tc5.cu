@@ -508,7 +508,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
           if (!ok) break;
           if constexpr (!EARLY) {
             // first 64 keys of P V as soon as that half of P is written
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(B_PHALF + X), it & 1, &abort_flag));
+            ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(B_PHALF + X), it & 1, &abort_flag));
             if (!ok) { fail_id = B_PHALF + X + 1; break; }
             tc_fence_after();
             if (leader) {
@@ -519,7 +519,7 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
             }
             __syncwarp();
           }
-          ok = __all_sync(0xffffffffu, mbar_wait(bar(B_PFULL + X), it & 1, &abort_flag));
+          ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(B_PFULL + X), it & 1, &abort_flag));
           if (!ok) { fail_id = B_PFULL + X + 1; break; }
           tc_fence_after();
           if (leader) {

@@ -67,6 +67,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return false;
 }
 
+// The same bounded wait, polling without suspending first (test_wait returns at once; try_wait may park the thread and
+// wake it late): for the one thread whose reaction time sits on every tile's critical path.
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (int i = 0; i < 20000; ++i)
+    if (mbar_test_wait(bar, parity)) return true;
+  return mbar_wait(bar, parity, abort_flag);
+}
+
 // ---------------------------------------------------------------- TMA (tiled, 3-D, no multicast)
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
   asm volatile(
