@@ -414,9 +414,9 @@ def run_ours(a):
         peak, peak_src = 1590.0, "fallback"
     achieved = flops["total"] / (fused_ms * 1e-3) / 1e12
     # DRAM bytes per launch of the fused kernel: dram__bytes_read + dram__bytes_write of one ncu capture at
-    # T=16384 with 64 query / 4 KV heads of 128 (571.8 MB), scaled by T and by this rank's share of the heads -- every
+    # T=16384 with 64 query / 4 KV heads of 128 (572.8 MB), scaled by T and by this rank's share of the heads -- every
     # operand of this shape family grows with both
-    traffic = 571.813120e6 * T / 16384 * Q.shape[1] / 64 if (a.heads, a.kv_heads, a.head_dim) == (64, 4, 128) else None
+    traffic = 572.806144e6 * T / 16384 * Q.shape[1] / 64 if (a.heads, a.kv_heads, a.head_dim) == (64, 4, 128) else None
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                 "traffic": traffic, "traffic_source": "ncu capture at T=16384, scaled (profiles/)", "peak_source": peak_src,
                 "kernel": "fused three-branch attention (nsa_fwd_tc5_kernel)" + (f", rank 0's {Q.shape[1]} of {H} heads" if world > 1 and a.layout == "heads" else ""),
