@@ -468,7 +468,7 @@ def run_ours(a):
         del Q, K, V, G, Qh, Kh, Vh, Gh, out, Kc, Vc, idx
         torch.cuda.empty_cache()
         cp_line = run_cp(a, a.cp_seq_len, nsa, cfg, rank, world, dist, barrier, max_over_ranks, max(2, min(a.steps, 3)), 1)
-        cp_block = {k: cp_line[k] for k in ("value", "unit", "ms_per_step", "seq_len", "per_rank_ms", "all_gather_ms",
+        cp_block = {k: cp_line[k] for k in ("value", "unit", "ms_per_step", "seq_len", "per_rank_ms", "per_rank_forward_alone_ms", "all_gather_ms",
                                               "bytes_received_per_rank", "imbalance_last_over_mean", "steps")} if rank == 0 else None
 
     if rank == 0:
