@@ -15,6 +15,7 @@
   block means are then derived locally from the gathered prefix.  The forward is then the ordinary
   one with Tq = Tl and Tk = (r+1)*Tl: queries align with the tail of the keys, which is exactly the
   global causal geometry (offset = r*Tl; nsa/reference.py:57-59,122-126).  The kernels only ever read local HBM.
+  Both gathers are started together; the block lists need the keys only and are resolved while the values arrive.
   A collective that does not complete within `timeout_s` raises ContextParallelTimeout instead of blocking.
 """
 from __future__ import annotations
@@ -143,29 +144,44 @@ class ContextParallelTimeout(RuntimeError):
     """A collective of the context-parallel layout did not complete in time (a rank is late or gone)."""
 
 
+class _PrefixGather:
+    """One all-gather of [B,Hkv,Tl,D] shards along the sequence, started at construction, finished by `wait()`."""
+
+    def __init__(self, x_local: Tensor, group=None, stats: Optional[dict] = None):
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.x = x_local.contiguous()
+        self.work = None
+        if self.world > 1:
+            B, Hkv, Tl, D = self.x.shape
+            self.flat = torch.empty((self.world * B, Hkv, Tl, D), dtype=self.x.dtype, device=self.x.device)
+            self.work = dist.all_gather_into_tensor(self.flat, self.x, group=group, async_op=True)
+            if stats is not None:
+                stats["bytes_received"] = stats.get("bytes_received", 0) + (self.world - 1) * self.x.numel() * self.x.element_size()
+
+    def wait(self, timeout_s: Optional[float] = None) -> Tensor:
+        """The causal prefix this rank needs, [B,Hkv,(rank+1)*Tl,D] contiguous: the collective's buffer laid out
+        head-major by a single strided copy of the (rank+1)/world part that is needed.  With `timeout_s` the
+        collective is waited for on the host and ContextParallelTimeout is raised if it has not completed by then;
+        without, the current stream waits for it and the host goes on."""
+        if self.work is None:
+            return self.x
+        try:
+            ok = self.work.wait(datetime.timedelta(seconds=timeout_s)) if timeout_s is not None else self.work.wait()
+        except RuntimeError as e:
+            raise ContextParallelTimeout(f"all-gather of the key prefix did not complete within {timeout_s} s: {e}") from e
+        if ok is False:
+            raise ContextParallelTimeout(f"all-gather of the key prefix did not complete within {timeout_s} s")
+        B, Hkv, Tl, D = self.x.shape
+        buf = self.flat.view(self.world, B, Hkv, Tl, D)
+        return buf[: self.rank + 1].permute(1, 2, 0, 3, 4).reshape(B, Hkv, (self.rank + 1) * Tl, D)
+
+
 def gather_key_prefix(x_local: Tensor, group=None, *, timeout_s: Optional[float] = None, stats: Optional[dict] = None) -> Tensor:
     """All-gather [B,Hkv,Tl,D] shards along the sequence and return the causal prefix this rank
-    needs, [B,Hkv,(rank+1)*Tl,D] contiguous.  One collective into one preallocated buffer; the prefix is then laid
-    out head-major by a single strided copy of the (rank+1)/world part that is needed.  With `timeout_s` the
-    collective is waited for on the host and ContextParallelTimeout is raised if it has not completed by then."""
-    world = dist.get_world_size(group)
-    rank = dist.get_rank(group)
-    x_local = x_local.contiguous()
-    if world == 1:
-        return x_local
-    B, Hkv, Tl, D = x_local.shape
-    flat = torch.empty((world * B, Hkv, Tl, D), dtype=x_local.dtype, device=x_local.device)
-    buf = flat.view(world, B, Hkv, Tl, D)
-    work = dist.all_gather_into_tensor(flat, x_local, group=group, async_op=True)
-    try:
-        ok = work.wait(datetime.timedelta(seconds=timeout_s)) if timeout_s is not None else work.wait()
-    except RuntimeError as e:
-        raise ContextParallelTimeout(f"all-gather of the key prefix did not complete within {timeout_s} s: {e}") from e
-    if ok is False:
-        raise ContextParallelTimeout(f"all-gather of the key prefix did not complete within {timeout_s} s")
-    if stats is not None:
-        stats["bytes_received"] = stats.get("bytes_received", 0) + (world - 1) * x_local.numel() * x_local.element_size()
-    return buf[: rank + 1].permute(1, 2, 0, 3, 4).reshape(B, Hkv, (rank + 1) * Tl, D)
+    needs, [B,Hkv,(rank+1)*Tl,D] contiguous.  One collective into one preallocated buffer.  `timeout_s`: see
+    _PrefixGather.wait."""
+    return _PrefixGather(x_local, group, stats).wait(timeout_s)
 
 
 def nsa_forward_context_parallel(Q_local: Tensor, K_local: Tensor, V_local: Tensor, cfg, *,
@@ -174,15 +190,28 @@ def nsa_forward_context_parallel(Q_local: Tensor, K_local: Tensor, V_local: Tens
                                  stats: Optional[dict] = None) -> Tensor:
     """Causal NSA forward with the sequence sharded contiguously over the ranks of `group`.
     Inputs are this rank's shards ([B,H,Tl,D], [B,Hkv,Tl,D]); returns this rank's output shard.
-    `forward_fn(Q, K, V, cfg, gate_logits=...)` defaults to `nsa_forward`.  `stats` (a dict) receives the bytes this
-    rank received; `timeout_s`: see gather_key_prefix."""
+    Both all-gathers are started at once.  With the default forward and block-mean selection, the block lists -- which
+    need the keys only -- are resolved while the values are still arriving (the collectives run on the library's own
+    stream; the pooling and selection kernels on the caller's).  `forward_fn(Q, K, V, cfg, gate_logits=...)` replaces
+    the forward (then nothing is overlapped).  `stats` (a dict) receives the bytes this rank received; `timeout_s`:
+    see _PrefixGather.wait."""
     if not cfg.causal:
         raise ValueError("context-parallel layout is defined for causal attention")
-    if forward_fn is None:
-        from .forward import nsa_forward as forward_fn
-    K_pref = gather_key_prefix(K_local, group, timeout_s=timeout_s, stats=stats)
-    V_pref = gather_key_prefix(V_local, group, timeout_s=timeout_s, stats=stats)
-    return forward_fn(Q_local, K_pref, V_pref, cfg, gate_logits=gate_logits)
+    gk = _PrefixGather(K_local, group, stats)
+    gv = _PrefixGather(V_local, group, stats)
+    K_pref = gk.wait(timeout_s)
+    if forward_fn is not None:
+        return forward_fn(Q_local, K_pref, gv.wait(timeout_s), cfg, gate_logits=gate_logits)
+    from .forward import _cfg, _resolve_block_indices, nsa_forward
+    idx = None
+    if _cfg(cfg, "scorer", "mean") == "mean" and Q_local.is_cuda:
+        D = Q_local.shape[-1]
+        scale = cfg.scale if cfg.scale is not None else 1.0 / (D ** 0.5)
+        idx = _resolve_block_indices(Q_local, K_pref, block_size_m=cfg.block_size_m, block_size_n=cfg.block_size_n,
+                                     top_k=cfg.top_k, causal=cfg.causal, scale=float(scale),
+                                     force_first=_cfg(cfg, "force_first", 0), force_local=_cfg(cfg, "force_local", 0),
+                                     shared_per_group=bool(_cfg(cfg, "select_per_group", False)))
+    return nsa_forward(Q_local, K_pref, gv.wait(timeout_s), cfg, gate_logits=gate_logits, block_indices=idx)
 
 
 __all__ = ["unit_range", "HeadPartition", "head_partition", "head_groups", "shard_heads", "shard_kv_heads", "gather_heads",
