@@ -40,6 +40,7 @@ __device__ int g_tc5_status;   // 0 ok; otherwise (1 + id of the barrier a wait 
 
 struct Tc5Params {
   CUtensorMap tmQ, tmK, tmV, tmKc, tmVc;
+  CUtensorMap tmOf;  // one-item kernel: the output in boxes of 32 positions x 64 elements of one head, 128-byte swizzle (an item's last write)
   CUtensorMap tmO;   // persistent kernel: the output, 4-D in the order of its strides, boxes of 32 positions x 32 elements of one head, 64-byte swizzle
   nsa_fwd_args a;
   float scale_log2[3];   // per branch: softmax scale * log2(e) (* the fp8 dequantisation scales of the operands)
@@ -52,6 +53,7 @@ struct Tc5Params {
   float* part;     // split launches: partial results [B*H*Tq][nsplit][3][D+4] = unnormalised O, m (log2 units), l
   int kv8;         // fp8 launches: K/V are fp8 too (converted tile by tile); 0 = K/V arrive as bf16, only Q is fp8
   int tma_out;     // persistent kernel: an item whose result is ONE branch writes it through shared memory and the TMA (rows_through_tma)
+  int fin_tma;     // one-item kernel, D = 128: the item's last branch end writes the output rows through shared memory and two TMA boxes per warp
   int psum;        // one-item kernel, unsplit 16-bit launches: 32 KB of shared memory hold the first 64 columns of the rows' running gated sum
   int poly;        // tiles without masked entries take 3 of every 8 exponentials on the FMA pipe (exp2_poly_pair)
 };
@@ -653,6 +655,15 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
     const bool keep = !SPLIT && !IN8 && p.psum != 0;
     unsigned char* prow_s = smem + 2 * QTILE + 4 * KVTILE + (size_t)(X * 128 + r) * 128;
     bool kept = false;                                   // the shared-memory columns hold a partial sum
+    // The item's LAST branch end (every column goes to the output row) stages its 16-bit values in shared memory -- columns
+    // 0..63 where the partial sums lay, 64..127 in the Q tiles' area, which no MMA reads any more -- as two boxes of 32 rows
+    // x 128 bytes per warp (128-byte swizzle, the partial sums' own layout) and hands them to the TMA: the 16 stores per
+    // thread, 32 lines each, were the longest part of an item's tail.  Rows past Tq are clipped by the tensor map.
+    const bool fin_tma = keep && p.fin_tma != 0 && D == 128;
+    unsigned char* fin_lo = smem + 2 * QTILE + 4 * KVTILE + (size_t)(warp - 4) * 4096;      // = this warp's rows of prow_s
+    unsigned char* fin_hi = smem + (size_t)(warp - 4) * 4096;
+    const int qi0_box = grp_qb(rg) * 64 + (quarter & 1) * 32;
+    const bool box_ok = grp_qb(rg) < a.nq && qi0_box < a.Tq;
     int last_br = -1;                                    // the item's last branch with key tiles
 #pragma unroll
     for (int br = 0; br < 3; ++br)
@@ -831,15 +842,28 @@ __global__ void __launch_bounds__(384, 1) nsa_fwd_tc5_kernel(const __grid_consta
             }
             if (keep && br != last_br && g * 4 + c < 8)
               *reinterpret_cast<uint4*>(prow_s + (((g * 4 + c) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            else if (fin_tma && br == last_br)
+              *reinterpret_cast<uint4*>((g < 2 ? fin_lo : fin_hi) + lane * 128 + ((((g & 1) * 4 + c) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
             else
               reinterpret_cast<uint4*>(orow)[g * 4 + c] = make_uint4(w[0], w[1], w[2], w[3]);
           }
+        }
+      }
+      if (fin_tma && br == last_br) {
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0 && box_ok) {
+          const bool bthd = (a.io_layout & NSA_IO_OUT_BTHD) != 0;
+          tma_store_4d(&p.tmOf, smem_u32(fin_lo), 0, bthd ? head : qi0_box, bthd ? qi0_box : head, b);
+          tma_store_4d(&p.tmOf, smem_u32(fin_hi), 64, bthd ? head : qi0_box, bthd ? qi0_box : head, b);
+          bulk_commit();
         }
       }
       have_partial = true;
       kept = keep && br != last_br;
       tc_fence_before();
     }
+    if (fin_tma && lane == 0) bulk_wait_read<0>();       // the boxes have been read before the block's shared memory goes
     if (!SPLIT && ok && row_ok) {
       if (!have_partial) {                    // no branch had a visible key: the row is zero
 #pragma unroll
@@ -1724,6 +1748,7 @@ int attention_fwd_tc5(const nsa_fwd_args& a, cudaStream_t st) {
   // NSA_TC5_KEEP_SUM=0: every branch end writes the whole running sum to the output row
   static const int psum_env = [] { const char* e = getenv("NSA_TC5_KEEP_SUM"); return !e ? 1 : (e[0] == '0' ? 0 : 1); }();
   p.psum = (psum_env && !in8 && !((a.nsplit > 1 || a.dyn_len != nullptr) && a.fused)) ? 1 : 0;
+  p.fin_tma = 0;
   p.tma_out = 0;
   if (in8) rc = make_map8(&p.tmQ, a.Q, (long long)a.B * a.H, a.Tq, a.D);
   else rc = make_map(&p.tmQ, a.Q, (long long)a.B * a.H, a.Tq, a.D, cdt);
@@ -1741,6 +1766,24 @@ int attention_fwd_tc5(const nsa_fwd_args& a, cudaStream_t st) {
   } else {
     p.tmKc = p.tmK;
     p.tmVc = p.tmV;
+  }
+  // NSA_TC5_FIN_TMA=0: the last branch end stores its rows thread by thread
+  static const int fin_env = [] { const char* e = getenv("NSA_TC5_FIN_TMA"); return !e ? 1 : (e[0] == '0' ? 0 : 1); }();
+  if (fin_env && p.psum && a.D == 128 && (reinterpret_cast<uintptr_t>(a.out) & 15) == 0) {
+    auto enc = encode_fn();
+    NSA_REQUIRE(enc != nullptr, NSA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    // dims in ascending stride order: (D, Tq, H, B) for [B,H,Tq,D], (D, H, Tq, B) for [B,Tq,H,D]; the kernel swaps the two middle coordinates
+    const bool bthd = (a.io_layout & NSA_IO_OUT_BTHD) != 0;
+    const cuuint64_t D2 = (cuuint64_t)a.D * 2;
+    cuuint64_t dims[4] = {(cuuint64_t)a.D, (cuuint64_t)(bthd ? a.H : a.Tq), (cuuint64_t)(bthd ? a.Tq : a.H), (cuuint64_t)a.B};
+    cuuint64_t strides[3] = {D2, D2 * (cuuint64_t)(bthd ? a.H : a.Tq), D2 * a.Tq * a.H};
+    cuuint32_t box[4] = {64, bthd ? 1u : 32u, bthd ? 32u : 1u, 1};
+    cuuint32_t es[4] = {1, 1, 1, 1};
+    CUresult r = enc(&p.tmOf, cdt == NSA_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, a.out, dims,
+                     strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    NSA_REQUIRE(r == CUDA_SUCCESS, NSA_ERR_CUDA, "cuTensorMapEncodeTiled (output, last write) failed with %d", (int)r);
+    p.fin_tma = 1;
   }
   p.NQG = (p.a.nq + 4 / p.GH - 1) / (4 / p.GH);
   const long long items = (long long)p.NQG * a.B * a.Hkv * p.HG;
